@@ -1,0 +1,291 @@
+"""Benchmark of the hot path: sampled dt-steps of a PaiNN/meanflow denoiser (radius graph rebuilt
+every step -> fused message kernels -> channel mixing), reported as edge-messages/s.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One process per GPU (torchrun for N > 1); systems are sharded across ranks, nothing crosses GPUs
+inside a step, one NCCL gather of the final positions at the end of the timed region."""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "learned-dynamics_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # benchmark config 3: periodic dense-system rollout, graph rebuilt every step
+    "periodic_rollout_16x8192": dict(systems=16, nodes=8192, box=20.0, cutoff=4.0, n=128, n_rbf=8, radial="gaussian",
+                                     blks=(1, 3), ntypes=4, sigma0=0.05, kind="periodic"),
+    # benchmark config 4 geometry (open polymers) with the PaiNN denoiser
+    "polymers_1024x256": dict(systems=1024, nodes=256, box=None, cutoff=5.0, n=128, n_rbf=16, radial="gaussian",
+                              blks=(2, 4), ntypes=20, sigma0=0.05, kind="polymer"),
+    # small case for smoke runs and profiler captures
+    "periodic_small_4x2048": dict(systems=4, nodes=2048, box=12.6, cutoff=4.0, n=128, n_rbf=8, radial="gaussian",
+                                  blks=(1, 3), ntypes=4, sigma0=0.05, kind="periodic"),
+}
+DEFAULT_WORKLOAD = "periodic_rollout_16x8192"
+
+
+def make_positions(w, systems, seed):
+    g = torch.Generator().manual_seed(seed)
+    if w["kind"] == "periodic":
+        return torch.rand(systems, w["nodes"], 3, generator=g) * w["box"]
+    return torch.cumsum(torch.randn(systems, w["nodes"], 3, generator=g) / 3 ** 0.5, dim=1)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return d["hbm_gbs"], d["bf16_tflops"], d["bf16_tflops_sustained"], "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled during the timed region."""
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+            "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [nm for k, nm in enumerate(names) if any(len(r) > 2 + k and r[2 + k] == "Active" for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def message_flops_per_edge(n, n_rbf):
+    """distance MLP (n_rbf -> 4n -> 4n -> 4n) per edge"""
+    return 2 * (n_rbf * 4 * n + 2 * (4 * n) ** 2)
+
+
+def build_model(w, device):
+    from ld_b200 import painn
+    torch.manual_seed(1234)
+    dn = painn.SE3ITO(w["cutoff"], w["n"], w["nodes"], w["ntypes"], w["blks"][0], w["blks"][1], n_rbf=w["n_rbf"],
+                      radial=w["radial"]).to(device)
+    return dn
+
+
+def cpu_reference_rate(w, threads, budget_nodes=1024, steps=1):
+    """The reference's PyTorch formulation on the host cores (oracle restatement), on a bounded
+    sample: one system at the workload's density with `budget_nodes` nodes. Returns
+    (edge-messages/s, description)."""
+    from oracle import reference_math as R
+    torch.set_num_threads(threads)
+    nodes = min(budget_nodes, w["nodes"])
+    torch.manual_seed(1234)
+    dn = R.OSE3ITO(w["cutoff"], w["n"], nodes, w["ntypes"], w["blks"][0], w["blks"][1], w["n_rbf"], w["radial"])
+    g = torch.Generator().manual_seed(4321)
+    if w["kind"] == "periodic":
+        box_len = w["box"] * (nodes / w["nodes"]) ** (1.0 / 3.0)
+        box = (box_len,) * 3
+        x = torch.rand(1, nodes, 3, generator=g) * box_len
+        bs = bd = torch.zeros(0, dtype=torch.int64)
+    else:
+        box = None
+        x = torch.cumsum(torch.randn(1, nodes, 3, generator=g) / 3 ** 0.5, dim=1)
+        bs, bd = R.chain_bonds(1, nodes)
+    types = torch.randint(0, w["ntypes"], (nodes,), generator=g)
+    edges, t0 = 0, time.perf_counter()
+    for _ in range(steps):
+        noise = torch.randn(1, nodes, 3, generator=g)
+        x = R.meanflow_generate(dn, x, noise, w["sigma0"], box, types, bs, bd)
+        edges += dn.edges_last
+    dt = time.perf_counter() - t0
+    desc = f"1 system x {nodes} nodes at the workload's density, {steps} step(s), {edges} edge-messages in {dt:.1f} s"
+    return edges / dt, desc
+
+
+def run_reference(args, w, rank, world):
+    if rank != 0:
+        return
+    threads = len(os.sched_getaffinity(0))
+    rates = []
+    desc = ""
+    for i in range(args.warmup + args.steps):
+        r, desc = cpu_reference_rate(w, threads, budget_nodes=args.cpu_nodes)
+        if i >= args.warmup:
+            rates.append(r)
+    value = sum(rates) / len(rates)
+    line = {
+        "impl": "reference", "metric": "edge_messages_per_sec", "value": value, "unit": "edge-messages/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "note": "reference's PyTorch formulation (CPU oracle restatement) on host cores"},
+        "cpu_baseline": {"value": value, "unit": "edge-messages/s", "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "edge-messages/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-nodes", type=int, default=1024)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, w, rank, world)
+        return
+
+    import torch.distributed as dist
+    from ld_b200 import painn, ops
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    assert w["systems"] % world == 0, "systems must divide across ranks"
+    per = w["systems"] // world
+    box = None if w["box"] is None else (w["box"],) * 3
+
+    dn = build_model(w, dev)
+    types = torch.randint(0, w["ntypes"], (w["nodes"],), generator=torch.Generator().manual_seed(99)).to(dev)
+    bond = painn.chain_bond_graph(per, w["nodes"], dev) if w["kind"] == "polymer" else painn.empty_bond_graph(per, w["nodes"], dev)
+    mf = painn.Meanflow(dn, box, w["sigma0"], types, bond)
+    x_all = make_positions(w, w["systems"], seed=1003)
+    x_host = x_all[rank * per:(rank + 1) * per].contiguous().pin_memory()
+    out_host = torch.empty_like(x_host).pin_memory()
+    noise_gen = torch.Generator(device=dev).manual_seed(777 + rank)
+    counter = torch.zeros(1, dtype=torch.int64, device=dev)
+
+    def device_step(x):
+        noise = torch.randn(x.shape, generator=noise_gen, device=dev)
+        return mf.generate(x, noise, counter)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ------------------------------------------------------------------
+    x = x_host.to(dev)
+    for _ in range(args.warmup):
+        x = device_step(x)
+    barrier()
+    counter.zero_()
+    ops.KERNEL_TIMER.reset(enabled=True)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        x = device_step(x)
+    if world > 1:
+        gathered = [torch.empty_like(x) for _ in range(world)] if rank == 0 else None
+        dist.gather(x, gathered, dst=0)
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    edges = counter.clone()
+    ktimes = ops.KERNEL_TIMER.summary()
+    ops.KERNEL_TIMER.reset(enabled=False)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(edges, op=dist.ReduceOp.SUM)
+    total_ms, total_edges = ms.item(), int(edges.item())
+
+    # ---- end to end through the public API with host buffers ---------------------------------------
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    counter.zero_()
+    barrier()
+    t0.record()
+    for _ in range(args.steps):
+        xd = x_host.to(dev, non_blocking=True)
+        xd = device_step(xd)
+        out_host.copy_(xd, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        x_host.copy_(out_host)
+    t1.record()
+    barrier()
+    ms2 = torch.tensor([t0.elapsed_time(t1)], device=dev)
+    edges2 = counter.clone()
+    if world > 1:
+        dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
+        dist.all_reduce(edges2, op=dist.ReduceOp.SUM)
+
+    if rank == 0:
+        hbm, tf_burst, tf_sus, how = peaks()
+        value = total_edges / (total_ms * 1e-3)
+        e2e_value = int(edges2.item()) / (ms2.item() * 1e-3)
+        msg = ktimes.get("painn_message", {"launches": 0, "ms": 0.0, "edges": 0})
+        flops = message_flops_per_edge(w["n"], w["n_rbf"])
+        roof = None
+        if msg["launches"]:
+            per_launch_s = msg["ms"] * 1e-3 / msg["launches"]
+            achieved = flops * (total_edges / max(msg["launches"], 1)) / per_launch_s / 1e12
+            roof = {"bound": "tensor", "kernel": "painn_message_kernel", "achieved": achieved, "peak": tf_sus, "unit": "TFLOP/s",
+                    "frac": achieved / tf_sus, "traffic": None, "peak_source": f"bf16_tflops_sustained, {how}",
+                    "launches": msg["launches"], "avg_launch_ms": per_launch_s * 1e3,
+                    "note": "FP32 SIMT arithmetic measured against the dense bf16 tensor peak"}
+        line = {
+            "metric": "edge_messages_per_sec", "value": value, "unit": "edge-messages/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "systems": w["systems"], "nodes_per_system": w["nodes"], "cutoff": w["cutoff"],
+                       "width": w["n"], "radial_basis": w["n_rbf"], "message_layers_per_step": 2 * sum(w["blks"]),
+                       "graph_rebuilds_per_step": 2, "edges_per_step": total_edges // args.steps,
+                       "l2_policy": "inputs larger than L2 (per-step node features and gathers exceed 126 MB)"},
+            "dt_steps_per_sec": args.steps / (total_ms * 1e-3),
+            "system_steps_per_sec": args.steps * w["systems"] / (total_ms * 1e-3),
+            "e2e": {"value": e2e_value, "unit": "edge-messages/s", "h2d_bytes_per_step": x_host.numel() * 4 * world,
+                    "d2h_bytes_per_step": out_host.numel() * 4 * world, "ms_per_step": ms2.item() / args.steps},
+            "gpu_launches": ops.KERNEL_TIMER.total_launches,
+            "kernel_ms": {k: round(v["ms"], 3) for k, v in ktimes.items()},
+            "clocks": clocks, "roofline": roof,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            threads = len(os.sched_getaffinity(0))
+            rate, desc = cpu_reference_rate(w, threads, budget_nodes=args.cpu_nodes)
+            line["cpu_baseline"] = {"value": rate, "unit": "edge-messages/s", "cores": threads, "kind": "port", "sample": desc}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

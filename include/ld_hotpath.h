@@ -1,0 +1,114 @@
+/* C ABI of libld_hotpath.so: the equivariant message-passing hot path of learned-dynamics as
+ * sm_100a CUDA kernels. Plain pointers and sizes only; every pointer named "device" below is a
+ * device address owned by the caller, every call is asynchronous on `stream` (a cudaStream_t
+ * passed as void*), nothing is allocated or freed inside the library, and the return value is a
+ * status code (0 = LD_OK). Citations name the reference interface each entry point replaces
+ * (paths inside pb1729/learned-dynamics).
+ */
+#ifndef LD_HOTPATH_H
+#define LD_HOTPATH_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  LD_OK = 0,
+  LD_ERR_SHAPE = -1,          /* bad sizes / null where a pointer is required */
+  LD_ERR_CAPACITY = -2,       /* caller-provided output too small */
+  LD_ERR_BOX_TOO_SMALL = -3,  /* periodic box not > 2*cutoff on some axis (reference: TORCH_CHECK ndiv>=3) */
+  LD_ERR_NONFINITE = -4,
+  LD_ERR_TIMEOUT = -5,        /* a bounded device-side wait ran out */
+  LD_ERR_CUDA = -6,           /* CUDA runtime error; text in ld_last_error() */
+  LD_ERR_WORKSPACE = -7,
+  LD_ERR_UNSUPPORTED = -8
+};
+
+/* bits OR-ed by kernels into the caller's device status word */
+enum { LD_FLAG_CAPACITY = 1, LD_FLAG_NONFINITE = 2, LD_FLAG_TIMEOUT = 4 };
+
+/* activation codes for the dense layers */
+enum { LD_ACT_NONE = 0, LD_ACT_SILU = 1, LD_ACT_LEAKY01 = 2 };
+
+const char* ld_last_error(void);           /* thread-local text of the last failure */
+const char* ld_status_string(int status);
+
+/* ---- radius graph ---------------------------------------------------------------------------
+ * Replaces neighbour_grid_cuda.get_neighbours / get_edges
+ * (extensions/neighbour_grid/neighbour_grid.cpp:59-103, 170-195; kernels
+ * extensions/neighbour_grid/neighbour_grid_kern.cu:57-150, 334-352) and the boxwrap of
+ * graph_setup (managan/graph_layers.py:62-66, archs/meanflow_painn8.py:167-172).
+ * pos: device float32 [batch, nodes, 3]. periodic != 0: box = 3 HOST floats; periodic == 0: open
+ * boundary (no counterpart in the reference, which emulates it with a large box).
+ * mode 0: every pair within the cutoff. mode 1: the reference's ceil(box/cutoff) cell grid, which
+ * misses pairs two cells apart when box/cutoff is not an integer (periodic only).
+ * open_cells_cap: cells reserved per system for open boundaries (0 = default).
+ * Two calls: _count fills row_ptr[batch*nodes+1] (CSR offsets over global node id b*nodes+i) and
+ * edge_counts[batch] (cumulative, as the reference's third return value); the caller sizes the
+ * edge arrays (or keeps a fixed capacity) and _fill writes them. src ascending; order within a
+ * node is deterministic. shift/rij may be NULL. */
+int ld_radius_graph_workspace_size(int batch, int nodes, int periodic, float cutoff, const float* box, int mode,
+                                   int open_cells_cap, size_t* bytes);
+int ld_radius_graph_count(const float* pos, int batch, int nodes, int periodic, float cutoff, const float* box, int mode,
+                          int open_cells_cap, void* workspace, size_t workspace_bytes, int* row_ptr, int* edge_counts,
+                          int* status_dev, void* stream);
+int ld_radius_graph_fill(const float* pos, int batch, int nodes, int periodic, float cutoff, const float* box, int mode,
+                         int open_cells_cap, void* workspace, size_t workspace_bytes, const int* row_ptr,
+                         long long capacity, int* src, int* dst, int* shift, float* rij, int* status_dev, void* stream);
+
+/* ---- edge <-> node movement -----------------------------------------------------------------
+ * ld_segment_sum replaces torch_scatter.segment_coo at managan/graph_layers.py:54-59;
+ * ld_gather_rows replaces the index reads of managan/graph_layers.py:37-52;
+ * ld_row_ptr_from_sorted turns a sorted src array (int32 or int64) into CSR offsets. */
+int ld_row_ptr_from_sorted(const void* src, int index_bytes, long long E, int Nt, int* row_ptr, void* stream);
+int ld_segment_sum(const float* x_edge, const int* row_ptr, int Nt, int F, float* out, void* stream);
+int ld_gather_rows(const float* x_node, const void* idx, int index_bytes, long long E, int F, float* out, void* stream);
+
+/* ---- channel mixing -------------------------------------------------------------------------
+ * Replaces tensor_ops_cuda.tensor_linear forward and backward
+ * (extensions/tensor_ops/tensor_ops.cpp:31-170, tensor_ops_kern.cu:6-71).
+ * y[r,o,s] = sum_i W[o,i] x[r,i,s], s < 3^inds. W element strides sw0, sw1 (dx uses W transposed). */
+int ld_tensor_linear(int inds, const float* W, long long sw0, long long sw1, const float* x, float* y, long long rows,
+                     int dim_in, int dim_out, void* stream);
+int ld_tensor_linear_dw_workspace(int inds, long long rows, int dim_in, int dim_out, size_t* bytes);
+int ld_tensor_linear_dw(int inds, const float* dy, const float* x, float* dW, long long rows, int dim_in, int dim_out,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- l<=2 tensor products ---------------------------------------------------------------------
+ * Replace codegen_tensops_cuda.bee_fwd_cuda / bee_bwl_cuda / bee_bwr_cuda
+ * (extensions/codegen_tensops/codegen_tensops.cpp:1519-1769) and cow_o0_* / cow_o1_*
+ * (codegen_tensops.cpp:1771-1979). Operands contiguous [rows, chan, (3,)^l]. out13/grads13 are
+ * HOST arrays of 13 device pointers in the order 000,110,220,011,101,121,211,022,202,112,222,111,212. */
+int ld_bee_fwd(const float* l0, const float* l1, const float* l2, const float* r0, const float* r1, const float* r2,
+               long long rows, int chan, float* const* out13, void* stream);
+int ld_bee_bw(int left, const float* o0, const float* o1, const float* o2, const float* const* grads13, long long rows,
+              int chan, float* d0, float* d1, float* d2, void* stream);
+int ld_cow_o0_fwd(const float* l0, const float* l1, const float* r0, const float* r1, long long rows, int chan,
+                  float* y000, float* y110, void* stream);
+int ld_cow_o0_bw(const float* o0, const float* o1, const float* g000, const float* g110, long long rows, int chan,
+                 float* d0, float* d1, void* stream);
+int ld_cow_o1_fwd(const float* l0, const float* l1, const float* r0, const float* r1, long long rows, int chan,
+                  float* y011, float* y101, float* y111, void* stream);
+int ld_cow_o1_bw(int left, const float* o0, const float* o1, const float* g011, const float* g101, const float* g111,
+                 long long rows, int chan, float* d0, float* d1, void* stream);
+
+/* ---- dense layers and the fused PaiNN message ----------------------------------------------------
+ * ld_mlp3_rows: the three-layer MLPs applied per node (archs/meanflow_painn8.py:38-51;
+ * archs/diffuser_atoms15.py:98-110 with the direct term Wdt). Weights are "packed":
+ * Wkt = nn.Linear.weight.t().contiguous(), [in][out].
+ * ld_painn_message_f32: Message.forward (archs/meanflow_painn8.py:77-100) fused with the edge
+ * gather and edges_reduce_src; FP32 arithmetic throughout. */
+int ld_mlp3_rows(const float* x, long long rows, int k0, const float* W1t, const float* b1, int n1, const float* W2t,
+                 const float* b2, int n2, const float* W3t, const float* b3, int n3, int act, const float* Wdt,
+                 float* out, void* stream);
+int ld_painn_message_f32(const int* row_ptr, const int* dst, const float* rij, int Nt, int n, int n_rbf, int radial_kind,
+                         float rmax, float eps, const float* W1t, const float* b1, const float* W2t, const float* b2,
+                         const float* W3t, const float* b3, const float* actv, const float* x_v, const float* res_a,
+                         const float* res_v, float* out_a, float* out_v, long long* edge_counter, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,201 @@
+// Channel-wise l<=2 Cartesian tensor products and their adjoints (the "Bee" and "Cow" sets).
+// Replaces bee_fwd/bwl/bwr and cow_o0/o1 fwd/bwl/bwr of the reference's generated
+// extensions/codegen_tensops (codegen_tensops_kern.cu:3800-4394, wrappers codegen_tensops.cpp:1519-1979).
+// One thread per (row, channel); a warp covers 32 consecutive channels, so its loads of the
+// rank-1 / rank-2 operands touch 96 / 288 consecutive floats (every fetched sector is used).
+// These ops are HBM bound: 26 floats in, 63 out per (row, channel) for the forward Bee set.
+#include "common.cuh"
+#include "tp_math.h"
+
+namespace {
+
+__device__ __forceinline__ void ld3(const float* p, size_t i, float* v) { v[0] = p[i * 3]; v[1] = p[i * 3 + 1]; v[2] = p[i * 3 + 2]; }
+__device__ __forceinline__ void ld9(const float* p, size_t i, float* v) {
+#pragma unroll
+  for (int k = 0; k < 9; k++) v[k] = p[i * 9 + k];
+}
+__device__ __forceinline__ void st3(float* p, size_t i, const float* v) { p[i * 3] = v[0]; p[i * 3 + 1] = v[1]; p[i * 3 + 2] = v[2]; }
+__device__ __forceinline__ void st9(float* p, size_t i, const float* v) {
+#pragma unroll
+  for (int k = 0; k < 9; k++) p[i * 9 + k] = v[k];
+}
+
+struct BeePtrs { float* y[13]; };
+struct BeeGrads { const float* g[13]; };
+
+__global__ void bee_fwd_kernel(const float* __restrict__ l0, const float* __restrict__ l1, const float* __restrict__ l2,
+                               const float* __restrict__ r0, const float* __restrict__ r1, const float* __restrict__ r2,
+                               BeePtrs out, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float a1[3], a2[9], b1[3], b2[9];
+    ld3(l1, i, a1); ld9(l2, i, a2); ld3(r1, i, b1); ld9(r2, i, b2);
+    BeeOut o;
+    bee_fwd_point(l0[i], a1, a2, r0[i], b1, b2, &o);
+    out.y[0][i] = o.y000; out.y[1][i] = o.y110; out.y[2][i] = o.y220;
+    st3(out.y[3], i, o.y011); st3(out.y[4], i, o.y101); st3(out.y[5], i, o.y121); st3(out.y[6], i, o.y211);
+    st9(out.y[7], i, o.y022); st9(out.y[8], i, o.y202); st9(out.y[9], i, o.y112); st9(out.y[10], i, o.y222);
+    st3(out.y[11], i, o.y111); st9(out.y[12], i, o.y212);
+  }
+}
+
+__device__ __forceinline__ void load_grads(const BeeGrads& G, size_t i, BeeOut* g) {
+  g->y000 = G.g[0][i]; g->y110 = G.g[1][i]; g->y220 = G.g[2][i];
+  ld3(G.g[3], i, g->y011); ld3(G.g[4], i, g->y101); ld3(G.g[5], i, g->y121); ld3(G.g[6], i, g->y211);
+  ld9(G.g[7], i, g->y022); ld9(G.g[8], i, g->y202); ld9(G.g[9], i, g->y112); ld9(G.g[10], i, g->y222);
+  ld3(G.g[11], i, g->y111); ld9(G.g[12], i, g->y212);
+}
+
+// LEFT=true: d/dl given r ; LEFT=false: d/dr given l
+template <bool LEFT>
+__global__ void bee_bw_kernel(const float* __restrict__ o0, const float* __restrict__ o1, const float* __restrict__ o2,
+                              BeeGrads G, float* __restrict__ d0, float* __restrict__ d1, float* __restrict__ d2, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float b1[3], b2[9];
+    ld3(o1, i, b1); ld9(o2, i, b2);
+    BeeOut g;
+    load_grads(G, i, &g);
+    float r0v, r1v[3], r2v[9];
+    if (LEFT) bee_bwl_point(o0[i], b1, b2, &g, &r0v, r1v, r2v);
+    else bee_bwr_point(o0[i], b1, b2, &g, &r0v, r1v, r2v);
+    d0[i] = r0v; st3(d1, i, r1v); st9(d2, i, r2v);
+  }
+}
+
+// ---- Cow sets (l <= 1) ---------------------------------------------------------------------------
+__global__ void cow_o0_fwd_kernel(const float* __restrict__ l0, const float* __restrict__ l1, const float* __restrict__ r0,
+                                  const float* __restrict__ r1, float* __restrict__ y000, float* __restrict__ y110, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float a[3], b[3];
+    ld3(l1, i, a); ld3(r1, i, b);
+    y000[i] = l0[i] * r0[i];
+    y110[i] = a[0] * b[0] + a[1] * b[1] + a[2] * b[2];
+  }
+}
+
+// adjoint of cow_o0 w.r.t. one side given the other side's operands (the set is symmetric)
+__global__ void cow_o0_bw_kernel(const float* __restrict__ o0, const float* __restrict__ o1, const float* __restrict__ g000,
+                                 const float* __restrict__ g110, float* __restrict__ d0, float* __restrict__ d1, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float b[3];
+    ld3(o1, i, b);
+    const float g1 = g110[i];
+    d0[i] = g000[i] * o0[i];
+    float v[3] = {g1 * b[0], g1 * b[1], g1 * b[2]};
+    st3(d1, i, v);
+  }
+}
+
+__global__ void cow_o1_fwd_kernel(const float* __restrict__ l0, const float* __restrict__ l1, const float* __restrict__ r0,
+                                  const float* __restrict__ r1, float* __restrict__ y011, float* __restrict__ y101,
+                                  float* __restrict__ y111, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float a[3], b[3], c[3];
+    ld3(l1, i, a); ld3(r1, i, b);
+    const float a0 = l0[i], b0 = r0[i];
+    float u[3] = {a0 * b[0], a0 * b[1], a0 * b[2]};
+    float v[3] = {a[0] * b0, a[1] * b0, a[2] * b0};
+    ld_cross(a, b, c);
+    st3(y011, i, u); st3(y101, i, v); st3(y111, i, c);
+  }
+}
+
+// LEFT=true: (dl_0, dl_1) from (r_0, r_1); LEFT=false: (dr_0, dr_1) from (l_0, l_1)
+template <bool LEFT>
+__global__ void cow_o1_bw_kernel(const float* __restrict__ o0, const float* __restrict__ o1, const float* __restrict__ g011,
+                                 const float* __restrict__ g101, const float* __restrict__ g111, float* __restrict__ d0,
+                                 float* __restrict__ d1, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float b[3], ga[3], gb[3], gc[3], c[3];
+    ld3(o1, i, b); ld3(g011, i, ga); ld3(g101, i, gb); ld3(g111, i, gc);
+    const float b0 = o0[i];
+    float s, v[3];
+    if (LEFT) {
+      // y011 = l0 r1 ; y101 = l1 r0 ; y111 = l1 x r1
+      s = ga[0] * b[0] + ga[1] * b[1] + ga[2] * b[2];
+      ld_cross(b, gc, c);
+      for (int k = 0; k < 3; k++) v[k] = gb[k] * b0 + c[k];
+    } else {
+      s = gb[0] * b[0] + gb[1] * b[1] + gb[2] * b[2];
+      ld_cross(gc, b, c);
+      for (int k = 0; k < 3; k++) v[k] = ga[k] * b0 + c[k];
+    }
+    d0[i] = s;
+    st3(d1, i, v);
+  }
+}
+
+inline int grid_for(size_t n) {
+  size_t b = (n + 255) / 256;
+  const size_t cap = 148 * 32;
+  return (int)(b < cap ? (b ? b : 1) : cap);
+}
+
+}  // namespace
+
+// rows*chan elements per rank-0 operand; operands are contiguous [rows, chan, (3,)^l] float32.
+extern "C" int ld_bee_fwd(const float* l0, const float* l1, const float* l2, const float* r0, const float* r1,
+                          const float* r2, long long rows, int chan, float* const* out13, void* stream) {
+  if (rows < 0 || chan < 0) return LD_ERR_SHAPE;
+  const size_t n = (size_t)rows * chan;
+  if (n == 0) return LD_OK;
+  BeePtrs P;
+  for (int k = 0; k < 13; k++) P.y[k] = out13[k];
+  bee_fwd_kernel<<<grid_for(n), 256, 0, (cudaStream_t)stream>>>(l0, l1, l2, r0, r1, r2, P, n);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}
+
+// left != 0: gradients of the left operands from (r_0,r_1,r_2); else of the right operands from (l_0,l_1,l_2)
+extern "C" int ld_bee_bw(int left, const float* o0, const float* o1, const float* o2, const float* const* grads13,
+                         long long rows, int chan, float* d0, float* d1, float* d2, void* stream) {
+  if (rows < 0 || chan < 0) return LD_ERR_SHAPE;
+  const size_t n = (size_t)rows * chan;
+  if (n == 0) return LD_OK;
+  BeeGrads G;
+  for (int k = 0; k < 13; k++) G.g[k] = grads13[k];
+  if (left) bee_bw_kernel<true><<<grid_for(n), 256, 0, (cudaStream_t)stream>>>(o0, o1, o2, G, d0, d1, d2, n);
+  else bee_bw_kernel<false><<<grid_for(n), 256, 0, (cudaStream_t)stream>>>(o0, o1, o2, G, d0, d1, d2, n);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}
+
+extern "C" int ld_cow_o0_fwd(const float* l0, const float* l1, const float* r0, const float* r1, long long rows, int chan,
+                             float* y000, float* y110, void* stream) {
+  if (rows < 0 || chan < 0) return LD_ERR_SHAPE;
+  const size_t n = (size_t)rows * chan;
+  if (n == 0) return LD_OK;
+  cow_o0_fwd_kernel<<<grid_for(n), 256, 0, (cudaStream_t)stream>>>(l0, l1, r0, r1, y000, y110, n);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}
+
+extern "C" int ld_cow_o0_bw(const float* o0, const float* o1, const float* g000, const float* g110, long long rows, int chan,
+                            float* d0, float* d1, void* stream) {
+  if (rows < 0 || chan < 0) return LD_ERR_SHAPE;
+  const size_t n = (size_t)rows * chan;
+  if (n == 0) return LD_OK;
+  cow_o0_bw_kernel<<<grid_for(n), 256, 0, (cudaStream_t)stream>>>(o0, o1, g000, g110, d0, d1, n);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}
+
+extern "C" int ld_cow_o1_fwd(const float* l0, const float* l1, const float* r0, const float* r1, long long rows, int chan,
+                             float* y011, float* y101, float* y111, void* stream) {
+  if (rows < 0 || chan < 0) return LD_ERR_SHAPE;
+  const size_t n = (size_t)rows * chan;
+  if (n == 0) return LD_OK;
+  cow_o1_fwd_kernel<<<grid_for(n), 256, 0, (cudaStream_t)stream>>>(l0, l1, r0, r1, y011, y101, y111, n);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}
+
+extern "C" int ld_cow_o1_bw(int left, const float* o0, const float* o1, const float* g011, const float* g101,
+                            const float* g111, long long rows, int chan, float* d0, float* d1, void* stream) {
+  if (rows < 0 || chan < 0) return LD_ERR_SHAPE;
+  const size_t n = (size_t)rows * chan;
+  if (n == 0) return LD_OK;
+  if (left) cow_o1_bw_kernel<true><<<grid_for(n), 256, 0, (cudaStream_t)stream>>>(o0, o1, g011, g101, g111, d0, d1, n);
+  else cow_o1_bw_kernel<false><<<grid_for(n), 256, 0, (cudaStream_t)stream>>>(o0, o1, g011, g101, g111, d0, d1, n);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}

@@ -1,0 +1,216 @@
+"""Channel mixing, l<=2 tensor products, dense MLP rows and the fused PaiNN message, on the C ABI."""
+import ctypes
+
+import torch
+
+from ._lib import lib, check, ptr, stream_ptr, require_cuda_f32, KERNEL_TIMER
+
+ACT_NONE, ACT_SILU, ACT_LEAKY01 = 0, 1, 2
+KERNEL_TIMER = KERNEL_TIMER  # re-exported for bench.py
+RADIAL_PAINN, RADIAL_GAUSSIAN = 0, 1
+
+BEE_SUFFIX = ("", "", "", (3,), (3,), (3,), (3,), (3, 3), (3, 3), (3, 3), (3, 3), (3,), (3, 3))
+
+
+def tensor_linear_fwd(inds, W, x):
+    """y[..., o, s] = sum_i W[o, i] x[..., i, s]; W may be strided, x contiguous float32 CUDA."""
+    if not W.is_cuda:
+        raise RuntimeError("W must be a CUDA tensor")
+    require_cuda_f32(x, "x")
+    if W.dim() != 2:
+        raise RuntimeError("expected W to be a matrix (2 dims)")
+    if inds not in (0, 1, 2):
+        raise RuntimeError("tensor_linear currently only supports a number of indices up to 2.")
+    dim_out, dim_in = W.shape
+    shape = list(x.shape)
+    bd = len(shape) - (1 + inds)
+    if bd < 0:
+        raise RuntimeError("x has too few dims")
+    if shape[bd] != dim_in:
+        raise RuntimeError("channel dim size mismatch for x")
+    for i in range(bd + 1, bd + 1 + inds):
+        if shape[i] != 3:
+            raise RuntimeError("expected tensor index dim to be 3d for input x")
+    rows = 1
+    for d in shape[:bd]:
+        rows *= d
+    shape[bd] = dim_out
+    y = torch.empty(shape, dtype=torch.float32, device=x.device)
+    if rows == 0:
+        return y
+    with KERNEL_TIMER.region("tensor_linear"):
+        check(lib().ld_tensor_linear(inds, ptr(W), W.stride(0), W.stride(1), ptr(x), ptr(y), rows, dim_in, dim_out,
+                                     stream_ptr(x.device)))
+    return y
+
+
+def tensor_linear_dw(inds, dy, x, dim_out, dim_in):
+    rows = x.numel() // max(dim_in * 3 ** inds, 1)
+    dW = torch.empty(dim_out, dim_in, dtype=torch.float32, device=x.device)
+    nbytes = ctypes.c_size_t(0)
+    check(lib().ld_tensor_linear_dw_workspace(inds, rows, dim_in, dim_out, ctypes.byref(nbytes)))
+    ws = torch.empty(max(nbytes.value, 4), dtype=torch.uint8, device=x.device)
+    check(lib().ld_tensor_linear_dw(inds, ptr(dy), ptr(x), ptr(dW), rows, dim_in, dim_out, ptr(ws), nbytes.value,
+                                    stream_ptr(x.device)))
+    return dW
+
+
+class TensorLinearFn(torch.autograd.Function):
+    """Same split as the reference's C++ autograd function (extensions/tensor_ops/tensor_ops.cpp:31-170):
+    dx is the forward kernel on W transposed (swapped strides), dW is its own kernel."""
+
+    @staticmethod
+    def forward(ctx, inds, W, x):
+        ctx.inds = inds
+        ctx.save_for_backward(W, x)
+        return tensor_linear_fwd(inds, W, x)
+
+    @staticmethod
+    def backward(ctx, dy):
+        W, x = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = dW = None
+        if ctx.needs_input_grad[2]:
+            dx = tensor_linear_fwd(ctx.inds, W.t(), dy)
+        if ctx.needs_input_grad[1]:
+            dW = tensor_linear_dw(ctx.inds, dy, x, W.shape[0], W.shape[1])
+        return None, dW, dx
+
+
+def tensor_linear(inds, W, x):
+    return TensorLinearFn.apply(inds, W, x)
+
+
+def _ptr_array(tensors):
+    arr = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+    return arr
+
+
+def _check_operands(names, tensors, ranks):
+    batch, chan = None, None
+    for name, t, r in zip(names, tensors, ranks):
+        require_cuda_f32(t, name)
+        if t.dim() != 2 + r:
+            raise RuntimeError(f"{name} has wrong number of axes")
+        if batch is None:
+            batch, chan = t.shape[0], t.shape[1]
+        if t.shape[0] != batch:
+            raise RuntimeError(f"{name}: expected axis 0 to have size batch")
+        if t.shape[1] != chan:
+            raise RuntimeError(f"{name}: expected axis 1 to have size chan")
+        for a in range(r):
+            if t.shape[2 + a] != 3:
+                raise RuntimeError(f"{name}: expected axis {2 + a} to have size 3")
+    return batch, chan
+
+
+def bee_fwd(l_0, l_1, l_2, r_0, r_1, r_2):
+    batch, chan = _check_operands(("l_0", "l_1", "l_2", "r_0", "r_1", "r_2"), (l_0, l_1, l_2, r_0, r_1, r_2), (0, 1, 2, 0, 1, 2))
+    outs = [torch.empty((batch, chan) + tuple(s), dtype=torch.float32, device=l_0.device) for s in BEE_SUFFIX]
+    if batch > 0:
+        arr = _ptr_array(outs)
+        check(lib().ld_bee_fwd(ptr(l_0), ptr(l_1), ptr(l_2), ptr(r_0), ptr(r_1), ptr(r_2), batch, chan, arr, stream_ptr(l_0.device)))
+    return outs
+
+
+def bee_bw(left, o_0, o_1, o_2, grads):
+    names = ("r_0", "r_1", "r_2") if left else ("l_0", "l_1", "l_2")
+    batch, chan = _check_operands(names, (o_0, o_1, o_2), (0, 1, 2))
+    grads = [g.contiguous() for g in grads]
+    dev = o_0.device
+    d0 = torch.empty(batch, chan, dtype=torch.float32, device=dev)
+    d1 = torch.empty(batch, chan, 3, dtype=torch.float32, device=dev)
+    d2 = torch.empty(batch, chan, 3, 3, dtype=torch.float32, device=dev)
+    if batch > 0:
+        arr = _ptr_array(grads)
+        check(lib().ld_bee_bw(1 if left else 0, ptr(o_0), ptr(o_1), ptr(o_2), arr, batch, chan, ptr(d0), ptr(d1), ptr(d2), stream_ptr(dev)))
+    return [d0, d1, d2]
+
+
+def cow_o0_fwd(l_0, l_1, r_0, r_1):
+    batch, chan = _check_operands(("l_0", "l_1", "r_0", "r_1"), (l_0, l_1, r_0, r_1), (0, 1, 0, 1))
+    dev = l_0.device
+    y000 = torch.empty(batch, chan, dtype=torch.float32, device=dev)
+    y110 = torch.empty(batch, chan, dtype=torch.float32, device=dev)
+    if batch > 0:
+        check(lib().ld_cow_o0_fwd(ptr(l_0), ptr(l_1), ptr(r_0), ptr(r_1), batch, chan, ptr(y000), ptr(y110), stream_ptr(dev)))
+    return [y000, y110]
+
+
+def cow_o0_bw(o_0, o_1, g000, g110):
+    batch, chan = _check_operands(("o_0", "o_1"), (o_0, o_1), (0, 1))
+    dev = o_0.device
+    g000, g110 = g000.contiguous(), g110.contiguous()
+    d0 = torch.empty(batch, chan, dtype=torch.float32, device=dev)
+    d1 = torch.empty(batch, chan, 3, dtype=torch.float32, device=dev)
+    if batch > 0:
+        check(lib().ld_cow_o0_bw(ptr(o_0), ptr(o_1), ptr(g000), ptr(g110), batch, chan, ptr(d0), ptr(d1), stream_ptr(dev)))
+    return [d0, d1]
+
+
+def cow_o1_fwd(l_0, l_1, r_0, r_1):
+    batch, chan = _check_operands(("l_0", "l_1", "r_0", "r_1"), (l_0, l_1, r_0, r_1), (0, 1, 0, 1))
+    dev = l_0.device
+    outs = [torch.empty(batch, chan, 3, dtype=torch.float32, device=dev) for _ in range(3)]
+    if batch > 0:
+        check(lib().ld_cow_o1_fwd(ptr(l_0), ptr(l_1), ptr(r_0), ptr(r_1), batch, chan, ptr(outs[0]), ptr(outs[1]), ptr(outs[2]), stream_ptr(dev)))
+    return outs
+
+
+def cow_o1_bw(left, o_0, o_1, g011, g101, g111):
+    batch, chan = _check_operands(("o_0", "o_1"), (o_0, o_1), (0, 1))
+    dev = o_0.device
+    g011, g101, g111 = g011.contiguous(), g101.contiguous(), g111.contiguous()
+    d0 = torch.empty(batch, chan, dtype=torch.float32, device=dev)
+    d1 = torch.empty(batch, chan, 3, dtype=torch.float32, device=dev)
+    if batch > 0:
+        check(lib().ld_cow_o1_bw(1 if left else 0, ptr(o_0), ptr(o_1), ptr(g011), ptr(g101), ptr(g111), batch, chan, ptr(d0), ptr(d1), stream_ptr(dev)))
+    return [d0, d1]
+
+
+class PackedMLP:
+    """Weights of a 3-layer MLP in the kernels' layout ([in][out] per layer, float32, contiguous)."""
+
+    def __init__(self, linears, direct=None):
+        l1, l2, l3 = linears
+        self.Wt = [l.weight.detach().t().contiguous().float() for l in (l1, l2, l3)]
+        self.b = [None if l.bias is None else l.bias.detach().contiguous().float() for l in (l1, l2, l3)]
+        self.dims = (l1.weight.shape[1], l1.weight.shape[0], l2.weight.shape[0], l3.weight.shape[0])
+        self.Wdt = None if direct is None else direct.weight.detach().t().contiguous().float()
+
+
+def mlp3_rows(x, mlp, act=ACT_SILU):
+    """Three dense layers (activation after the first two) on the rows of x[..., k0]."""
+    x = x.contiguous()
+    require_cuda_f32(x, "x")
+    k0, n1, n2, n3 = mlp.dims
+    if x.shape[-1] != k0:
+        raise RuntimeError("mlp3_rows: input width mismatch")
+    rows = x.numel() // k0
+    out = torch.empty(tuple(x.shape[:-1]) + (n3,), dtype=torch.float32, device=x.device)
+    with KERNEL_TIMER.region("mlp3_rows"):
+        check(lib().ld_mlp3_rows(ptr(x), rows, k0, ptr(mlp.Wt[0]), ptr(mlp.b[0]), n1, ptr(mlp.Wt[1]), ptr(mlp.b[1]), n2,
+                                 ptr(mlp.Wt[2]), ptr(mlp.b[2]), n3, act, ptr(mlp.Wdt), ptr(out), stream_ptr(x.device)))
+    return out
+
+
+def painn_message_f32(row_ptr, dst, rij, mlp_dist, actv, x_v, rmax, eps=0.1, radial_kind=RADIAL_PAINN, res_a=None,
+                      res_v=None, edge_counter=None):
+    """Fused PaiNN message; returns (out_a [Nt,n], out_v [Nt,n,3]). actv = mlp_actv(x_a) as [Nt,4n]."""
+    require_cuda_f32(actv, "actv")
+    require_cuda_f32(x_v, "x_v")
+    require_cuda_f32(rij, "rij")
+    Nt, n = x_v.shape[0], x_v.shape[1]
+    n_rbf, n1, n2, n3 = mlp_dist.dims
+    if not (n1 == n2 == n3 == 4 * n) or actv.shape != (Nt, 4 * n):
+        raise RuntimeError("painn_message: widths must be n_rbf -> 4n -> 4n -> 4n and actv [Nt,4n]")
+    if dst.dtype != torch.int32 or row_ptr.dtype != torch.int32:
+        raise RuntimeError("painn_message: row_ptr and dst must be int32")
+    out_a = torch.empty(Nt, n, dtype=torch.float32, device=x_v.device)
+    out_v = torch.empty(Nt, n, 3, dtype=torch.float32, device=x_v.device)
+    with KERNEL_TIMER.region("painn_message"):
+        check(lib().ld_painn_message_f32(ptr(row_ptr), ptr(dst), ptr(rij), Nt, n, n_rbf, radial_kind, float(rmax), float(eps),
+                                         ptr(mlp_dist.Wt[0]), ptr(mlp_dist.b[0]), ptr(mlp_dist.Wt[1]), ptr(mlp_dist.b[1]),
+                                         ptr(mlp_dist.Wt[2]), ptr(mlp_dist.b[2]), ptr(actv), ptr(x_v), ptr(res_a), ptr(res_v),
+                                         ptr(out_a), ptr(out_v), ptr(edge_counter), stream_ptr(x_v.device)))
+    return out_a, out_v

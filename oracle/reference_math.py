@@ -1,0 +1,389 @@
+"""TEST INFRASTRUCTURE ONLY - the CPU oracle. Never imported by the product package.
+
+PyTorch-CPU restatement of the reference's own formulation of the hot path, used by tests/,
+__graft_entry__.smoke() and bench.py's cpu_baseline / --impl reference legs as the checker and
+the timed CPU baseline. Each function names the reference lines it follows (paths inside
+pb1729/learned-dynamics). Pinning: tests/golden/ holds outputs of the reference's own Python
+classes (imported on CPU with stub extension modules by tests/golden/make_golden.py) and
+tests/test_oracle_golden.py checks this file against them; the radius graph is pinned by the
+hand-computed table in managan/graph_layers.py:80-124.
+
+Substitutions: torch_scatter.segment_coo -> index_add_; tensor_ops_cuda.tensor_linear -> the
+einsum of managan/tensor_products.py:12-24; neighbour_grid_cuda -> brute force over all pairs
+(oracle/radius_graph_oracle.c) with a fixed float32 predicate."""
+import ctypes
+import math
+import os
+
+import numpy as np
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .build_oracle import build as _build_c
+
+_clib = None
+
+
+def _c():
+    global _clib
+    if _clib is None:
+        L = ctypes.CDLL(_build_c())
+        L.oracle_radius_graph.restype = ctypes.c_longlong
+        L.oracle_radius_graph.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_float,
+                                          ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong] + [ctypes.c_void_p] * 5
+        _clib = L
+    return _clib
+
+
+# ---- radius graph -----------------------------------------------------------------------------
+def radius_graph(pos, cutoff, box=None, mode=0):
+    """pos [B,N,3] float32 (CPU). Returns dict(src, dst, shift[E,3], rij[E,3], degree[B*N]) with
+    edges ordered by (system, i, j). Membership: neighbour_grid_kern.cu:39-48, 95-150; edge order
+    neighbour_grid.cpp:180-194; rij is graph_setup's boxwrap (managan/graph_layers.py:62-66)."""
+    pos = np.ascontiguousarray(pos.detach().cpu().numpy(), dtype=np.float32)
+    B, N, _ = pos.shape
+    periodic = 0 if box is None else 1
+    boxarr = np.asarray(box if box is not None else (0, 0, 0), dtype=np.float32)
+    deg = np.zeros(B * N, dtype=np.int32)
+    E = _c().oracle_radius_graph(pos.ctypes.data, B, N, periodic, ctypes.c_float(cutoff), boxarr.ctypes.data, mode, 0,
+                                 None, None, None, None, deg.ctypes.data)
+    src = np.zeros(E, dtype=np.int32); dst = np.zeros(E, dtype=np.int32)
+    shift = np.zeros(E, dtype=np.int32); rij = np.zeros((E, 3), dtype=np.float32)
+    _c().oracle_radius_graph(pos.ctypes.data, B, N, periodic, ctypes.c_float(cutoff), boxarr.ctypes.data, mode, E,
+                             src.ctypes.data, dst.ctypes.data, shift.ctypes.data, rij.ctypes.data, deg.ctypes.data)
+    sh = np.stack([((shift >> (8 * a)) & 0xFF).astype(np.int32) for a in range(3)], axis=1)
+    sh = np.where(sh >= 128, sh - 256, sh)
+    return {"src": torch.from_numpy(src), "dst": torch.from_numpy(dst), "shift": torch.from_numpy(sh),
+            "rij": torch.from_numpy(rij), "degree": torch.from_numpy(deg), "E": int(E)}
+
+
+def boxwrap(box, delta_pos):
+    """managan/graph_layers.py:62-66"""
+    return (delta_pos + 0.5 * box) % box - 0.5 * box
+
+
+def edges_reduce_src(src, x_edge, num_nodes):
+    """managan/graph_layers.py:54-59 with index_add_ in place of segment_coo"""
+    out = torch.zeros((num_nodes,) + tuple(x_edge.shape[1:]), dtype=x_edge.dtype)
+    return out.index_add_(0, src.long(), x_edge)
+
+
+# ---- channel mixing -----------------------------------------------------------------------------
+def tensor_linear(inds, W, x):
+    """managan/tensor_products.py:12-24 (einsum form); extensions/tensor_ops/test.py:8-15"""
+    idx = "ijk"[:inds]
+    return torch.einsum(f"OI, ...I{idx} -> ...O{idx}", W, x)
+
+
+# ---- l<=2 products ------------------------------------------------------------------------------
+def levi_civita():
+    from itertools import permutations
+    e = torch.zeros(3, 3, 3)
+    for i, j, k in permutations(range(3)):
+        e[i, j, k] = ((i - j) / abs(i - j)) * ((j - k) / abs(j - k)) * ((k - i) / abs(k - i))
+    return e
+
+
+def bee(l_0, l_1, l_2, r_0, r_1, r_2):
+    """managan/codegen_tensor_products.py:235-249; output order of Bee.forward (:66-69)"""
+    lc = levi_civita().to(l_0.dtype)
+    y_000 = torch.einsum("bc, bc -> bc", l_0, r_0)
+    y_110 = torch.einsum("bcx, bcx -> bc", l_1, r_1)
+    y_220 = torch.einsum("bcxy, bcxy -> bc", l_2, r_2)
+    y_011 = torch.einsum("bc, bcx -> bcx", l_0, r_1)
+    y_101 = torch.einsum("bcx, bc -> bcx", l_1, r_0)
+    y_121 = torch.einsum("bcx, bcyx -> bcy", l_1, r_2)
+    y_211 = torch.einsum("bcxy, bcy -> bcx", l_2, r_1)
+    y_111 = torch.einsum("bcx, bcy, xyz -> bcz", l_1, r_1, lc)
+    y_022 = torch.einsum("bc, bcxy -> bcxy", l_0, r_2)
+    y_202 = torch.einsum("bcxy, bc -> bcxy", l_2, r_0)
+    y_112 = torch.einsum("bcx, bcy -> bcxy", l_1, r_1)
+    y_222 = torch.einsum("bcxy, bczy -> bcxz", l_2, r_2)
+    y_212 = torch.einsum("bcxy, bcz, yzw -> bcxw", l_2, r_1, lc)
+    return y_000, y_110, y_220, y_011, y_101, y_121, y_211, y_022, y_202, y_112, y_222, y_111, y_212
+
+
+def cow0(l_0, l_1, r_0, r_1):
+    """managan/codegen_tensor_products.py:279-282"""
+    return torch.einsum("bc, bc -> bc", l_0, r_0), torch.einsum("bcx, bcx -> bc", l_1, r_1)
+
+
+def cow1(l_0, l_1, r_0, r_1):
+    """managan/codegen_tensor_products.py:284-288"""
+    lc = levi_civita().to(l_0.dtype)
+    return (torch.einsum("bc, bcx -> bcx", l_0, r_1), torch.einsum("bcx, bc -> bcx", l_1, r_0),
+            torch.einsum("bcx, bcy, xyz -> bcz", l_1, r_1, lc))
+
+
+# ---- radial encodings ---------------------------------------------------------------------------
+def radial_encode_painn(r, n, rmax):
+    """archs/meanflow_painn8.py:25-35"""
+    hn = (n + 1) // 2
+    coeffs = (torch.pi / rmax) * (1 + torch.arange(0, hn) // 2)
+    dist = torch.linalg.vector_norm(r, dim=-1)[..., None]
+    phase = coeffs * dist
+    return torch.cat([torch.cos(phase), torch.sin(phase[..., :(n - hn)])], dim=-1)
+
+
+def radial_encode_gaussian(r, n, rmax):
+    """Gaussian basis with cosine cutoff asked for by the benchmark configs; not in the reference.
+    centres m*rmax/(n-1), width rmax/(n-1), envelope 0.5(cos(pi d/rmax)+1) for d < rmax."""
+    d = torch.linalg.vector_norm(r, dim=-1)[..., None]
+    width = rmax / (n - 1) if n > 1 else rmax
+    mu = torch.arange(n, dtype=r.dtype) * width
+    env = torch.where(d < rmax, 0.5 * (torch.cos(math.pi * d / rmax) + 1.0), torch.zeros_like(d))
+    return torch.exp(-0.5 * ((d - mu) / width) ** 2) * env
+
+
+def jacobi_matrix(dim):
+    """managan/jacobi_radenc.py:8-24: coefficients of shifted Jacobi(1,0) polynomials on [0,1]"""
+    import sympy as sp
+    from sympy import jacobi, Poly
+    x = sp.symbols("x")
+    A = torch.zeros(dim, 1 + dim)
+    for i in range(dim):
+        coeffs = Poly(jacobi(i, 1, 0, (2 * x - 1)), x, domain="R").all_coeffs()[::-1]
+        for j in range(len(coeffs)):
+            A[i, j] = float(coeffs[j])
+    return A
+
+
+_A8 = None
+
+
+def radial_encode_8(r, rmax):
+    """managan/jacobi_radenc.py:27-37"""
+    global _A8
+    if _A8 is None:
+        _A8 = jacobi_matrix(8)
+    z = (torch.linalg.vector_norm(r, dim=-1) / rmax)[..., None]
+    pows = z ** torch.arange(_A8.shape[1])
+    return F.linear(pows, _A8) * torch.relu(1. - z)
+
+
+def tens_sigmoid(inds, x):
+    """managan/tensor_products.py:167-182"""
+    dims = tuple(-(1 + n) for n in range(inds))
+    xx = (x ** 2).sum(dims, keepdim=True)
+    return x / torch.sqrt(1. + xx)
+
+
+# ---- PaiNN layers (parameter names as in the reference so state dicts transfer) --------------------
+class OTensLinear(nn.Module):
+    def __init__(self, inds, dim_in, dim_out):
+        super().__init__()
+        self.W = nn.Parameter(torch.empty(dim_out, dim_in))
+        self.inds = inds
+        nn.init.normal_(self.W, std=dim_in ** -0.5)
+
+    def forward(self, x):
+        return tensor_linear(self.inds, self.W, x)
+
+
+class OMLP(nn.Module):
+    """archs/meanflow_painn8.py:38-51"""
+
+    def __init__(self, dim_in, dim_out):
+        super().__init__()
+        self.layers = nn.Sequential(nn.Linear(dim_in, dim_out), nn.SiLU(), nn.Linear(dim_out, dim_out), nn.SiLU(),
+                                    nn.Linear(dim_out, dim_out))
+
+    def forward(self, x):
+        return self.layers(x)
+
+
+class OScalGroupNorm(nn.Module):
+    """managan/layers_common.py:201-223"""
+
+    def __init__(self, chan, groups, epsilon=1e-5):
+        super().__init__()
+        self.chan, self.groups, self.epsilon = chan, groups, epsilon
+        self.gamma = nn.Parameter(torch.ones(chan))
+        self.beta = nn.Parameter(torch.zeros(chan))
+
+    def forward(self, x):
+        batch, nodes, _ = x.shape
+        x = x.reshape(batch, nodes, self.groups, -1)
+        mean = x.mean([1, 3], keepdim=True)
+        x_shift = x - mean
+        var = (x_shift ** 2).mean([1, 3], keepdim=True)
+        ans = x_shift / torch.sqrt(self.epsilon + var)
+        return self.beta + self.gamma * ans.reshape(batch, nodes, self.chan)
+
+
+class OUpdate(nn.Module):
+    """archs/meanflow_painn8.py:53-75"""
+
+    def __init__(self, n):
+        super().__init__()
+        self.n = n
+        self.lin_l = OTensLinear(1, n, n)
+        self.lin_r = OTensLinear(1, n, n)
+        self.lin_v = OTensLinear(1, n, n)
+        self.mlp = OMLP(2 * n, 3 * n)
+        self.gn = OScalGroupNorm(n, 4, epsilon=1.)
+
+    def forward(self, x_a, x_v):
+        x_v_l = self.lin_l(x_v)
+        x_v_r = self.lin_r(x_v)
+        inner_prod = (x_v_l * x_v_r).sum(-1)
+        y = self.mlp(torch.cat([x_a, torch.linalg.vector_norm(x_v_r, dim=-1)], dim=-1))
+        x_v = self.lin_v(x_v)
+        x_v = x_v * y[..., :self.n, None]
+        inner_prod = self.gn(inner_prod * y[..., self.n:2 * self.n])
+        x_a = inner_prod + y[..., 2 * self.n:]
+        x_v = x_v / torch.sqrt(1. + (x_v ** 2).sum(-1, keepdim=True))
+        return x_a, x_v
+
+
+class OMessage(nn.Module):
+    """archs/meanflow_painn8.py:77-100. radial: 'painn' (reference) or 'gaussian' (benchmark spec)."""
+
+    def __init__(self, r0, n, n_rbf=None, radial="painn"):
+        super().__init__()
+        self.r0, self.n, self.epsilon, self.radial = r0, n, 0.1, radial
+        self.n_rbf = n if n_rbf is None else n_rbf
+        self.mlp_dist = OMLP(self.n_rbf, 4 * n)
+        self.mlp_actv = OMLP(n, 4 * n)
+
+    def forward(self, src, dst, x_a, x_v, r_ij):
+        batch, atoms, n = x_a.shape
+        Nt = batch * atoms
+        enc = radial_encode_painn(r_ij, self.n_rbf, self.r0) if self.radial == "painn" else radial_encode_gaussian(r_ij, self.n_rbf, self.r0)
+        dist_x_a = self.mlp_dist(enc)
+        actv_x_a = self.mlp_actv(x_a.reshape(Nt, n)[dst.long()])
+        prod_x_a = dist_x_a * actv_x_a
+        direction = r_ij / torch.sqrt(self.epsilon + (r_ij ** 2).sum(-1, keepdim=True))
+        x_v = x_v.reshape(Nt, n, 3)[dst.long()]
+        cross = torch.linalg.cross(x_v, direction[:, None].expand_as(x_v))
+        x_v = x_v * prod_x_a[..., :n, None]
+        x_v = x_v + cross * prod_x_a[..., n:2 * n, None]
+        x_v = x_v + direction[:, None] * prod_x_a[..., 2 * n:3 * n, None]
+        x_v = edges_reduce_src(src, x_v, Nt).reshape(batch, atoms, n, 3)
+        x_a = edges_reduce_src(src, prod_x_a[..., 3 * n:], Nt).reshape(batch, atoms, n)
+        return x_a, x_v
+
+
+class OBlock(nn.Module):
+    """archs/meanflow_painn8.py:102-125 (pos_mutable=False)"""
+
+    def __init__(self, r0, n, n_rbf=None, radial="painn"):
+        super().__init__()
+        self.r0 = r0
+        self.message = OMessage(r0, n, n_rbf, radial)
+        self.message_bond = OMessage(r0, n, n_rbf, radial)
+        self.update = OUpdate(n)
+
+    def forward(self, graph, graph_bond, x_a, x_v):
+        """graph, graph_bond: (src, dst, r_ij)"""
+        dx_a, dx_v = self.message_bond(graph_bond[0], graph_bond[1], x_a, x_v, graph_bond[2])
+        x_a, x_v = x_a + dx_a, x_v + dx_v
+        dx_a, dx_v = self.message(graph[0], graph[1], x_a, x_v, graph[2])
+        x_a, x_v = x_a + dx_a, x_v + dx_v
+        dx_a, dx_v = self.update(x_a, x_v)
+        return x_a + dx_a, x_v + dx_v
+
+
+class OCPaiNN(nn.Module):
+    """archs/meanflow_painn8.py:128-143 with a type-embedding table for ResidueAtomEmbed"""
+
+    def __init__(self, r0, n, blks, ntypes, n_rbf=None, radial="painn"):
+        super().__init__()
+        self.r0 = r0
+        self.atom_embed = nn.Embedding(ntypes, n)
+        self.blocks = nn.Sequential(*[OBlock(r0, n, n_rbf, radial) for _ in range(blks)])
+
+    def forward(self, pos, graph_bond, x_a, x_v, box, types):
+        x_a = x_a + self.atom_embed(types)[None]
+        g = radius_graph(pos, self.r0, box)
+        graph = (g["src"], g["dst"], g["rij"])
+        for blk in self.blocks:
+            x_a, x_v = blk(graph, graph_bond, x_a, x_v)
+        return x_a, x_v, g["E"]
+
+
+class OTimeEmbedding(nn.Module):
+    """archs/meanflow_painn8.py:145-165"""
+
+    def __init__(self, freqs, outdim):
+        super().__init__()
+        self.freqs = freqs
+        self.lin1 = nn.Linear(4 * freqs, outdim)
+
+    def forward(self, st):
+        s, t = st
+        ang = torch.exp(-torch.arange(self.freqs) / (self.freqs - 1))
+        phases = torch.cat([t[:, None] * ang[None, :], (t - s)[:, None] * ang[None, :]], dim=1)
+        return self.lin1(torch.cat([torch.sin(phases), torch.cos(phases)], dim=1))
+
+
+class OPosEmbed(nn.Module):
+    """archs/meanflow_painn8.py:174-183"""
+
+    def __init__(self, dim_v):
+        super().__init__()
+        self.lin_v = OTensLinear(1, 1, dim_v)
+
+    def forward(self, pos_0, pos_1):
+        return self.lin_v(0.1 * (pos_1[:, :, None] - pos_0[:, :, None]))
+
+
+class OSE3ITO(nn.Module):
+    """archs/meanflow_painn8.py:185-217; bond graph supplied as (src, dst) of a batch-1 template
+    replicated over the batch as get_bond_graph does (managan/flavour_layers.py:256-272)."""
+
+    def __init__(self, r0, n, natoms, ntypes=1, blks_0=2, blks_1=5, n_rbf=None, radial="painn"):
+        super().__init__()
+        self.r0 = r0
+        self.atom_embeddings = nn.Parameter(torch.randn(natoms, n))
+        self.t_embed = OTimeEmbedding(32, n)
+        self.mlp_embed = OMLP(n, n)
+        self.mlp_denoise = OMLP(n, n)
+        self.pos_emb = OPosEmbed(n)
+        self.cpainn_0 = OCPaiNN(r0, n, blks_0, ntypes, n_rbf, radial)
+        self.cpainn_1 = OCPaiNN(r0, n, blks_1, ntypes, n_rbf, radial)
+        self.v_readin = OTensLinear(1, 1, n)
+        self.readout = OTensLinear(1, n, 1)
+        self.edges_last = 0
+
+    def forward(self, st, x0, x1, box, types, bond_src, bond_dst):
+        s, t = st
+        x1_t = x1
+        r0b = x0.reshape(-1, 3)[bond_dst.long()] - x0.reshape(-1, 3)[bond_src.long()]
+        r1b = x1.reshape(-1, 3)[bond_dst.long()] - x1.reshape(-1, 3)[bond_src.long()]
+        x_a = self.atom_embeddings[None].expand(x0.shape[0], -1, -1)
+        x_v = self.v_readin((x1 - x0)[..., None, :])
+        x_a = self.mlp_embed(x_a)
+        x_a, x_v, e0 = self.cpainn_0(x0, (bond_src, bond_dst, r0b), x_a, x_v, box, types)
+        x_a = self.mlp_denoise(x_a + self.t_embed(st)[:, None])
+        x_v = x_v + self.pos_emb(x0, x1)
+        x_a, x_v, e1 = self.cpainn_1(x1, (bond_src, bond_dst, r1b), x_a, x_v, box, types)
+        nb = bond_src.numel()
+        self.edges_last = (e0 + nb) * len(self.cpainn_0.blocks) + (e1 + nb) * len(self.cpainn_1.blocks)
+        v_pred = self.readout(x_v).squeeze(-2)
+        return (1. - (t - s)[:, None, None]) * v_pred + x1_t - x1
+
+
+def meanflow_generate(dn, x_0, noise, sigma_0, box, types, bond_src, bond_dst):
+    """archs/meanflow_painn8.py:302-310 with the noise passed in"""
+    batch = x_0.shape[0]
+    z_1 = x_0 + sigma_0 * noise
+    st = (torch.zeros(batch), torch.ones(batch))
+    with torch.no_grad():
+        v_pred = dn(st, x_0, z_1, box, types, bond_src, bond_dst)
+    return z_1 - v_pred
+
+
+def chain_bonds(batch, nodes):
+    i = torch.arange(nodes - 1)
+    src = torch.cat([i, i + 1]); dst = torch.cat([i + 1, i])
+    order = torch.argsort(src, stable=True)
+    src, dst = src[order], dst[order]
+    offs = nodes * torch.arange(batch)[:, None]
+    return (src[None] + offs).reshape(-1), (dst[None] + offs).reshape(-1)
+
+
+def avg_relative_diff(a, b):
+    """managan/utils.py:45-52, the reference's comparison metric"""
+    return (torch.abs(a - b) / torch.sqrt(0.0001 + 0.5 * (a ** 2 + b ** 2))).mean().item()

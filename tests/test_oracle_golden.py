@@ -1,0 +1,94 @@
+"""The CPU oracle against vectors produced by the reference's own classes (tests/golden)."""
+import torch
+
+from oracle import reference_math as R
+
+TOL = dict(rtol=1e-5, atol=1e-6)
+
+
+def test_graph_known_answer(golden):
+    k = golden["graph_kat"]
+    g = R.radius_graph(k["positions"], k["r0"], k["box"])
+    assert torch.all(g["src"][1:] >= g["src"][:-1])
+    ones = torch.ones(g["E"])
+    assert torch.allclose(R.edges_reduce_src(g["src"], ones, 5)[None], k["degrees"])
+    x = torch.arange(5.).repeat(4).reshape(5, 4)
+    sumprod = R.edges_reduce_src(g["src"], x[g["src"].long()] * x[g["dst"].long()], 5)[None]
+    assert torch.allclose(sumprod, k["sumprod"])
+    assert torch.all(g["rij"][0] ** 2 < 2.001 ** 2)
+
+
+def test_radial_encodings(golden):
+    r = golden["radial"]
+    assert torch.allclose(R.radial_encode_painn(r["r"], 16, 3.0), r["painn_n16_r3"], **TOL)
+    assert torch.allclose(R.radial_encode_painn(r["r"], 7, 5.0), r["painn_n7_r5"], **TOL)
+    assert torch.allclose(R.radial_encode_8(r["r"], 4.0), r["jacobi8_r4"], rtol=1e-4, atol=1e-5)
+
+
+def test_norms(golden):
+    n = golden["norms"]
+    sgn = R.OScalGroupNorm(16, 4, epsilon=1.)
+    sgn.load_state_dict(n["sgn_state"])
+    assert torch.allclose(sgn(n["x"]), n["sgn_out"], **TOL)
+    assert torch.allclose(R.tens_sigmoid(1, n["xv"]), n["tens_sigmoid1"], **TOL)
+    assert torch.allclose(R.tens_sigmoid(2, n["xd"]), n["tens_sigmoid2"], **TOL)
+
+
+def test_products(golden):
+    b = golden["bee"]
+    for mine, ref in zip(R.bee(*b["operands"]), b["outputs"]):
+        assert torch.allclose(mine, ref, **TOL)
+    c = golden["cow"]
+    for mine, ref in zip(R.cow0(*c["operands"]), c["o0"]):
+        assert torch.allclose(mine, ref, **TOL)
+    for mine, ref in zip(R.cow1(*c["operands"]), c["o1"]):
+        assert torch.allclose(mine, ref, **TOL)
+
+
+def test_painn_layers(golden):
+    p = golden["painn"]
+    n, r0 = p["n"], p["r0"]
+    msg = R.OMessage(r0, n)
+    msg.load_state_dict(p["message_state"])
+    with torch.no_grad():
+        a, v = msg(p["src"], p["dst"], p["x_a"], p["x_v"], p["r_ij"])
+    assert torch.allclose(a, p["message_out"][0], rtol=1e-4, atol=1e-5)
+    assert torch.allclose(v, p["message_out"][1], rtol=1e-4, atol=1e-5)
+    upd = R.OUpdate(n)
+    upd.load_state_dict(p["update_state"])
+    with torch.no_grad():
+        a, v = upd(p["x_a"], p["x_v"])
+    assert torch.allclose(a, p["update_out"][0], rtol=1e-4, atol=1e-5)
+    assert torch.allclose(v, p["update_out"][1], rtol=1e-4, atol=1e-5)
+    blk = R.OBlock(r0, n)
+    blk.load_state_dict(p["block_state"])
+    with torch.no_grad():
+        a, v = blk((p["src"], p["dst"], p["r_ij"]), (p["bond_src"], p["bond_dst"], p["r_ij_bond"]), p["x_a"], p["x_v"])
+    assert torch.allclose(a, p["block_out"][0], rtol=1e-4, atol=1e-5)
+    assert torch.allclose(v, p["block_out"][1], rtol=1e-4, atol=1e-5)
+
+
+def test_oracle_graph_matches_golden_graph(golden):
+    """the golden graph was built in float64 by the generator; same edge set expected here"""
+    p = golden["painn"]
+    g = R.radius_graph(p["pos"], p["r0"], None)
+    assert torch.equal(g["src"].long(), p["src"]) and torch.equal(g["dst"].long(), p["dst"])
+    assert torch.allclose(g["rij"], p["r_ij"], atol=1e-5)  # golden r_ij went through boxwrap with a 100-wide box
+
+
+def test_periodic_graph_properties():
+    gen = torch.Generator().manual_seed(3)
+    box = (7.5, 8.0, 9.25)
+    pos = torch.rand(2, 150, 3, generator=gen) * torch.tensor(box) * 3 - torch.tensor(box)  # also outside the box
+    g = R.radius_graph(pos, 2.5, box)
+    pairs = set(zip(g["src"].tolist(), g["dst"].tolist()))
+    assert all((j, i) in pairs for (i, j) in pairs)
+    # r_ij = x_j - x_i + shift*box, and |r_ij| <= cutoff up to rounding
+    flat = pos.reshape(-1, 3)
+    recon = flat[g["dst"].long()] - flat[g["src"].long()] + g["shift"].float() * torch.tensor(box)
+    assert torch.allclose(recon, g["rij"], atol=2e-5)
+    assert (g["rij"].norm(dim=1) <= 2.5 * (1 + 1e-5)).all()
+    # reference-compatible mode never adds edges
+    g1 = R.radius_graph(pos, 2.5, box, mode=1)
+    pairs1 = set(zip(g1["src"].tolist(), g1["dst"].tolist()))
+    assert pairs1 <= pairs
