@@ -177,12 +177,22 @@ def test_denoiser_step_vs_oracle(periodic):
         assert torch.equal(gb.src.cpu(), bs) and torch.equal(gb.dst.cpu(), bd)
     types = torch.randint(0, 4, (N,), generator=g)
     noise = torch.randn(B, N, 3, generator=g)
+    # the network itself at a generic (s, t): at the sampler's (0, 1) the reference multiplies the
+    # network's velocity head by (1 - (t - s)) = 0, which would hide every error
+    s_, t_ = torch.rand(B, generator=g) * 0.5, 0.5 + torch.rand(B, generator=g) * 0.4
+    x1 = x0 + 0.3 * noise
+    counter = torch.zeros(1, dtype=torch.int64, device="cuda")
+    with torch.no_grad():
+        want_v = ref((s_, t_), x0, x1, box, types, bs, bd)
+        got_v = mine((s_.cuda(), t_.cuda()), x0.cuda(), x1.cuda(), box, types.cuda(), gb, counter)
+    assert want_v.abs().max() > 1e-3
+    close(got_v, want_v, rel=5e-5)
+    assert int(counter.item()) == ref.edges_last
+    # and the sampler step (generate) through the public wrapper
     want = R.meanflow_generate(ref, x0, noise, 0.3, box, types, bs, bd)
     mf = painn.Meanflow(mine, box, 0.3, types.cuda(), gb)
-    counter = torch.zeros(1, dtype=torch.int64, device="cuda")
-    got = mf.generate(x0.cuda(), noise.cuda(), counter)
+    got = mf.generate(x0.cuda(), noise.cuda())
     close(got, want, rel=5e-5)
-    assert int(counter.item()) == ref.edges_last
 
 
 def test_message_rotation_equivariance_full_width():
