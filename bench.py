@@ -158,6 +158,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp32"],
+                    help="bf16: per-edge MLP on tcgen05 (2e-2 parity); fp32: SIMT path (1e-5 parity)")
     ap.add_argument("--cpu-nodes", type=int, default=1024)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -179,7 +181,7 @@ def main():
     per = w["systems"] // world
     box = None if w["box"] is None else (w["box"],) * 3
 
-    dn = build_model(w, dev)
+    dn = painn.set_precision(build_model(w, dev), args.precision)
     types = torch.randint(0, w["ntypes"], (w["nodes"],), generator=torch.Generator().manual_seed(99)).to(dev)
     bond = painn.chain_bond_graph(per, w["nodes"], dev) if w["kind"] == "polymer" else painn.empty_bond_graph(per, w["nodes"], dev)
     mf = painn.Meanflow(dn, box, w["sigma0"], types, bond)
@@ -252,21 +254,23 @@ def main():
         hbm, tf_burst, tf_sus, how = peaks()
         value = total_edges / (total_ms * 1e-3)
         e2e_value = int(edges2.item()) / (ms2.item() * 1e-3)
-        msg = ktimes.get("painn_message", {"launches": 0, "ms": 0.0, "edges": 0})
+        tc_path = args.precision == "bf16"
+        msg = ktimes.get("painn_message_tc" if tc_path else "painn_message", {"launches": 0, "ms": 0.0})
         flops = message_flops_per_edge(w["n"], w["n_rbf"])
         roof = None
         if msg["launches"]:
             per_launch_s = msg["ms"] * 1e-3 / msg["launches"]
             achieved = flops * (total_edges / max(msg["launches"], 1)) / per_launch_s / 1e12
-            roof = {"bound": "tensor", "kernel": "painn_message_kernel", "achieved": achieved, "peak": tf_sus, "unit": "TFLOP/s",
+            roof = {"bound": "tensor", "kernel": "painn_message_tc_kernel" if tc_path else "painn_message_kernel", "achieved": achieved, "peak": tf_sus, "unit": "TFLOP/s",
                     "frac": achieved / tf_sus, "traffic": None, "peak_source": f"bf16_tflops_sustained, {how}",
                     "launches": msg["launches"], "avg_launch_ms": per_launch_s * 1e3,
-                    "note": "FP32 SIMT arithmetic measured against the dense bf16 tensor peak"}
+                    "note": ("tcgen05 BF16 MMAs of the per-edge distance MLP (algorithmic flops: 2*(n_rbf*4n + 2*(4n)^2) per edge)"
+                             if tc_path else "FP32 SIMT arithmetic measured against the dense bf16 tensor peak")}
         line = {
             "metric": "edge_messages_per_sec", "value": value, "unit": "edge-messages/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "systems": w["systems"], "nodes_per_system": w["nodes"], "cutoff": w["cutoff"],
+            "vs_baseline": None, "dtype": "bf16" if tc_path else "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "precision": args.precision, "systems": w["systems"], "nodes_per_system": w["nodes"], "cutoff": w["cutoff"],
                        "width": w["n"], "radial_basis": w["n_rbf"], "message_layers_per_step": 2 * sum(w["blks"]),
                        "graph_rebuilds_per_step": 2, "edges_per_step": total_edges // args.steps,
                        "l2_policy": "inputs larger than L2 (per-step node features and gathers exceed 126 MB)"},

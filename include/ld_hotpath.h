@@ -108,6 +108,25 @@ int ld_painn_message_f32(const int* row_ptr, const int* dst, const float* rij, i
                          const float* W3t, const float* b3, const float* actv, const float* x_v, const float* res_a,
                          const float* res_v, float* out_a, float* out_v, long long* edge_counter, void* stream);
 
+/* ---- tensor-core dense layers (tcgen05, BF16 operands, FP32 accumulation) ------------------------
+ * ld_linear_bf16_tc: y = act(x W^T + b) with the Cartesian index folded into the rows; the
+ * tensor-core counterpart of tensor_ops_cuda.tensor_linear (extensions/tensor_ops/tensor_ops_kern.cu:6-42)
+ * and of nn.Linear inside the reference's MLPs (archs/meanflow_painn8.py:38-51). 2e-2 relative.
+ * Weights are packed once with ld_pack_weights_bf16 (ld_packed_weight_elems BF16 values). */
+long long ld_packed_weight_elems(int N, int K);
+int ld_pack_weights_bf16(const float* W, long long sw0, long long sw1, int N, int K, void* out, void* stream);
+int ld_linear_bf16_tc(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias, int N, int act,
+                      float* y, int* status_dev, void* stream);
+
+/* ld_painn_message_bf16_tc: ld_painn_message_f32 with the per-edge distance MLP on tcgen05
+ * (BF16 operands, FP32 accumulation in tensor memory); same reference lines
+ * (archs/meanflow_painn8.py:77-100). Weights packed by ld_pack_weights_bf16. 2e-2 relative. */
+int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, const float* rij, int Nt, int n, int n_rbf, int radial_kind,
+                             float rmax, float eps, const void* w1p, const float* b1, const void* w2p, const float* b2,
+                             const void* w3p, const float* b3, const float* actv, const float* x_v, const float* res_a,
+                             const float* res_v, float* out_a, float* out_v, long long* edge_counter, int* status_dev,
+                             void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,214 @@
+// Dense layers on the Blackwell tensor cores (tcgen05.mma, BF16 operands, FP32 accumulation in TMEM):
+//   y[(r,s), o] = act( sum_i W[o,i] * x[(r,s), i] + b[o] ),   s in [0, 3^inds)
+// With S = 3^inds this is the channel mixing of rank-0/1/2 Cartesian tensors (the reference's
+// tensor_linear, extensions/tensor_ops/tensor_ops_kern.cu:6-42, and nn.Linear for S = 1): the
+// spatial index s is folded into the GEMM's row dimension by strided loads (x[r,i,s] sits at
+// r*I*S + i*S + s), so no de-interleaving pass over HBM is needed.
+//
+// One block owns a 128-row tile and all N <= 512 output channels. Per 64-wide K chunk: the weight
+// panel (pre-packed BF16, already in the shared-memory operand layout) arrives by one bulk
+// asynchronous copy, the activations are loaded as FP32, rounded to BF16 and stored in the operand
+// layout by the 128 threads, and one thread issues the MMAs. Two stages: loads of chunk c+1 overlap
+// the MMAs of chunk c. Accumulators: 128 lanes x N columns of TMEM, read back with tcgen05.ld for
+// the bias / activation epilogue. Tolerance of this path: 2e-2 relative (BF16 operands).
+#include "common.cuh"
+#include "tc05.cuh"
+#include "tp_math.h"
+
+namespace {
+
+constexpr int GT_ROWS = 128;
+constexpr int GT_KC = 64;                  // K per chunk
+constexpr int GT_PANELS = GT_KC / 8;       // 8-column panels per chunk
+constexpr int GT_A_STAGE = GT_ROWS * GT_KC * 2;  // bytes
+
+struct GemmParams {
+  const float* x; float* y;
+  const __nv_bfloat16* wp;   // packed weights [nchunks][8 panels][N][8]
+  const float* bias;
+  long long rows;            // logical rows = rows_outer * S
+  int K, N, S, act;
+  int* status;
+};
+
+__device__ __forceinline__ float act_apply(float v, int act) {
+  if (act == 1) return silu_f(v);
+  if (act == 2) return v > 0.f ? v : 0.1f * v;
+  return v;
+}
+
+__global__ void __launch_bounds__(GT_ROWS, 1)
+gemm_tc_kernel(GemmParams P) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t bar_full[2], bar_empty[2], bar_accum;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int N = P.N, K = P.K, S = P.S;
+  const uint32_t b_stage = (uint32_t)N * GT_KC * 2;
+  unsigned char* a_smem[2] = {smem, smem + GT_A_STAGE};
+  unsigned char* b_smem[2] = {smem + 2 * GT_A_STAGE, smem + 2 * GT_A_STAGE + b_stage};
+  const int nchunks = (K + GT_KC - 1) / GT_KC;
+  uint32_t ncols = 32;
+  while (ncols < (uint32_t)N) ncols <<= 1;
+
+  if (tid == 0) {
+    tc::mbar_init(&bar_full[0], 1); tc::mbar_init(&bar_full[1], 1);
+    tc::mbar_init(&bar_empty[0], 1); tc::mbar_init(&bar_empty[1], 1);
+    tc::mbar_init(&bar_accum, 1);
+    tc::mbar_init_fence();
+    s_abort = 0;
+  }
+  if (warp == 0) { tc::tmem_alloc(&tmem_slot, ncols); tc::tmem_relinquish(); }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+
+  const long long ntiles = (P.rows + GT_ROWS - 1) / GT_ROWS;
+  uint32_t g = 0;        // chunks issued so far by this block (stage = g & 1)
+  uint32_t tile_it = 0;
+  bool ok = true;
+  for (long long tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, tile_it++) {
+    const long long row = tile * GT_ROWS + tid;
+    const bool row_ok = row < P.rows;
+    const long long ro = row_ok ? row / S : 0;
+    const int rs = row_ok ? (int)(row - ro * S) : 0;
+    const float* xrow = P.x + (ro * K) * S + rs;
+    for (int c = 0; c < nchunks; c++, g++) {
+      const int st = g & 1;
+      const uint32_t use = g >> 1;
+      bool w = true;
+      if (use >= 1) w = tc::mbar_wait(&bar_empty[st], (use - 1) & 1);  // MMAs that read this stage are done
+      ok = __syncthreads_and(w && !s_abort);
+      if (!ok) break;
+      if (tid == 0) {
+        tc::mbar_expect_tx(&bar_full[st], b_stage);
+        tc::bulk_g2s(b_smem[st], P.wp + (size_t)c * N * GT_KC, b_stage, &bar_full[st]);
+      }
+      // activations: this thread's row, 8 panels of 8 columns
+      const int k0 = c * GT_KC;
+#pragma unroll
+      for (int p = 0; p < GT_PANELS; p++) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const int k = k0 + p * 8 + j;
+          v[j] = (row_ok && k < K) ? __ldg(xrow + (size_t)k * S) : 0.f;
+        }
+        uint4 q;
+        q.x = tc::pack_bf16x2(v[0], v[1]); q.y = tc::pack_bf16x2(v[2], v[3]);
+        q.z = tc::pack_bf16x2(v[4], v[5]); q.w = tc::pack_bf16x2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(a_smem[st] + p * (GT_ROWS * 16) + tid * 16) = q;
+      }
+      tc::fence_async_smem();
+      __syncthreads();
+      if (tid == 0) {
+        if (tc::mbar_wait(&bar_full[st], use & 1)) {
+          tc::fence_after_sync();
+          const int kc = min(GT_KC, K - k0);
+          const int ksteps = (kc + 15) / 16;
+          const uint32_t a_base = tc::smem_u32(a_smem[st]), b_base = tc::smem_u32(b_smem[st]);
+          for (int ks = 0; ks < ksteps; ks++) {
+            const uint64_t ad = tc::smem_desc(a_base + ks * 2 * (GT_ROWS * 16), GT_ROWS * 16, 128);
+            for (int n0 = 0; n0 < N; n0 += 256) {
+              const int n1 = min(256, N - n0);
+              const uint64_t bd = tc::smem_desc(b_base + ks * 2 * (N * 16) + n0 * 16, N * 16, 128);
+              tc::mma_bf16(tmem_base + n0, ad, bd, tc::idesc_bf16(GT_ROWS, n1), (c > 0 || ks > 0) ? 1u : 0u);
+            }
+          }
+          tc::mma_commit(&bar_empty[st]);
+          if (c == nchunks - 1) tc::mma_commit(&bar_accum);
+        } else {
+          s_abort = 1;
+        }
+      }
+    }
+    if (!ok) break;
+    bool w = tc::mbar_wait(&bar_accum, tile_it & 1);
+    ok = __syncthreads_and(w && !s_abort);
+    if (!ok) break;
+    tc::fence_after_sync();
+    float* yrow = P.y + (ro * N) * S + rs;
+    for (int cb = 0; cb < N; cb += 32) {
+      float v[32];
+      tc::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + cb, v);
+      if (row_ok) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+          float t = v[j] + (P.bias != nullptr ? __ldg(P.bias + cb + j) : 0.f);
+          yrow[(size_t)(cb + j) * S] = act_apply(t, P.act);
+        }
+      }
+    }
+    tc::fence_before_sync();
+    __syncthreads();  // accumulators are free for the next tile
+  }
+  if (!ok && tid == 0 && P.status != nullptr) atomicOr(P.status, LD_FLAG_TIMEOUT);
+  // every MMA and copy this block issued has been waited for on the success path; on the failure
+  // path give outstanding work a bounded chance to land before releasing TMEM
+  if (!ok && tid == 0) {
+    for (int s = 0; s < 2; s++) tc::mbar_wait(&bar_full[s], ((g >> 1) & 1));
+  }
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem_base, ncols);
+}
+
+// W[N][K] FP32 (element strides sw0, sw1) -> BF16 panels [nchunks][8][N][8], zero padded in K
+__global__ void pack_weights_kernel(const float* __restrict__ W, long long sw0, long long sw1, int N, int K,
+                                    __nv_bfloat16* __restrict__ out, size_t total) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int j = (int)(i & 7);
+    size_t t = i >> 3;
+    const int n = (int)(t % N); t /= N;
+    const int p = (int)(t % GT_PANELS);
+    const int c = (int)(t / GT_PANELS);
+    const int k = c * GT_KC + p * 8 + j;
+    out[i] = __float2bfloat16(k < K ? W[(long long)n * sw0 + (long long)k * sw1] : 0.f);
+  }
+}
+
+int gt_sm_count() {
+  int dev = 0, n = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n > 0 ? n : 148;
+}
+
+}  // namespace
+
+// number of BF16 elements of the packed form of a [N][K] weight matrix
+extern "C" long long ld_packed_weight_elems(int N, int K) {
+  if (N <= 0 || K <= 0) return 0;
+  return (long long)((K + GT_KC - 1) / GT_KC) * GT_KC * N;
+}
+
+// W: FP32 [N][K] with element strides (sw0, sw1) -> out: ld_packed_weight_elems(N,K) BF16 values
+extern "C" int ld_pack_weights_bf16(const float* W, long long sw0, long long sw1, int N, int K, void* out, void* stream) {
+  if (N <= 0 || K <= 0) return LD_ERR_SHAPE;
+  const size_t total = (size_t)ld_packed_weight_elems(N, K);
+  pack_weights_kernel<<<ld_cdiv((long long)total, 256), 256, 0, (cudaStream_t)stream>>>(W, sw0, sw1, N, K, (__nv_bfloat16*)out, total);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}
+
+// y = act(x W^T + b) on the tensor cores. x: FP32 [rows_outer, K, S] contiguous, y: [rows_outer, N, S].
+// S in {1,3,9}; N a multiple of 32, N <= 512. wp from ld_pack_weights_bf16. status_dev: optional
+// device int32 that receives LD_FLAG_TIMEOUT if a bounded wait ran out.
+extern "C" int ld_linear_bf16_tc(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias,
+                                 int N, int act, float* y, int* status_dev, void* stream) {
+  if (rows_outer < 0 || K <= 0 || N <= 0 || (S != 1 && S != 3 && S != 9)) return LD_ERR_SHAPE;
+  if (N % 32 != 0 || N > 512) { ld_set_last_message("tensor-core linear: N must be a multiple of 32, at most 512"); return LD_ERR_UNSUPPORTED; }
+  if (((uintptr_t)wp) % 16 != 0) { ld_set_last_message("tensor-core linear: packed weights must be 16-byte aligned"); return LD_ERR_SHAPE; }
+  if (rows_outer == 0) return LD_OK;
+  GemmParams P;
+  P.x = x; P.y = y; P.wp = (const __nv_bfloat16*)wp; P.bias = bias; P.rows = rows_outer * S; P.K = K; P.N = N; P.S = S;
+  P.act = act; P.status = status_dev;
+  const size_t smem = 2 * GT_A_STAGE + 2 * (size_t)N * GT_KC * 2 + 1024;
+  LD_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const long long ntiles = (P.rows + GT_ROWS - 1) / GT_ROWS;
+  const int grid = (int)(ntiles < gt_sm_count() ? ntiles : gt_sm_count());
+  gemm_tc_kernel<<<grid, GT_ROWS, smem, (cudaStream_t)stream>>>(P);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}

@@ -118,6 +118,17 @@ __device__ __forceinline__ int lower_bound_row(const int* __restrict__ row_ptr, 
   return lo;
 }
 
+
+// first node v in [0, Nt] with row_ptr[v] + v >= target (work = edges + nodes before v)
+__device__ __forceinline__ int work_lower_bound(const int* __restrict__ row_ptr, int Nt, long long target) {
+  int lo = 0, hi = Nt;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if ((long long)row_ptr[mid] + mid < target) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
 template <int NCOL>
 __global__ void __launch_bounds__(MT_THREADS, 1)
 painn_message_kernel(MessageParams P, MlpWeights m) {
@@ -134,12 +145,12 @@ painn_message_kernel(MessageParams P, MlpWeights m) {
   const int tid = threadIdx.x;
   const int n = P.n;
   const long long E = P.row_ptr[P.Nt];
-  // node-aligned share of the edge list for this block
-  long long per = (E + gridDim.x - 1) / gridDim.x;
-  per = (per + MT_ROWS - 1) / MT_ROWS * MT_ROWS;
+  // node-aligned share for this block, balanced over edges + nodes (nodes without edges still
+  // have to be written)
+  long long per = (E + P.Nt + gridDim.x - 1) / gridDim.x;
   if (per < MT_ROWS) per = MT_ROWS;
-  const int n_begin = blockIdx.x == 0 ? 0 : lower_bound_row(P.row_ptr, 0, P.Nt, per * blockIdx.x);
-  const int n_end = blockIdx.x == gridDim.x - 1 ? P.Nt : lower_bound_row(P.row_ptr, 0, P.Nt, per * (blockIdx.x + 1));
+  const int n_begin = blockIdx.x == 0 ? 0 : work_lower_bound(P.row_ptr, P.Nt, per * blockIdx.x);
+  const int n_end = blockIdx.x == gridDim.x - 1 ? P.Nt : work_lower_bound(P.row_ptr, P.Nt, per * (blockIdx.x + 1));
   if (n_begin >= n_end) return;
   const long long e_begin = P.row_ptr[n_begin], e_end = P.row_ptr[n_end];
 

@@ -32,6 +32,9 @@ SIGNATURES = {
     "ld_cow_o1_fwd": [P, P, P, P, LL, I, P, P, P, P],
     "ld_cow_o1_bw": [I, P, P, P, P, P, LL, I, P, P, P],
     "ld_mlp3_rows": [P, LL, I, P, P, I, P, P, I, P, P, I, I, P, P, P],
+    "ld_pack_weights_bf16": [P, LL, LL, I, I, P, P],
+    "ld_linear_bf16_tc": [P, LL, I, I, P, P, I, I, P, P, P],
+    "ld_painn_message_bf16_tc": [P, P, P, I, I, I, I, F, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P],
     "ld_painn_message_f32": [P, P, P, I, I, I, I, F, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P],
 }
 
@@ -56,6 +59,8 @@ def lib():
             fn = getattr(L, name)
             fn.argtypes = argtypes
             fn.restype = c_int
+        L.ld_packed_weight_elems.restype = c_ll
+        L.ld_packed_weight_elems.argtypes = [c_int, c_int]
         L.ld_last_error.restype = ctypes.c_char_p
         L.ld_status_string.restype = ctypes.c_char_p
         L.ld_status_string.argtypes = [c_int]

@@ -169,14 +169,23 @@ def cow_o1_bw(left, o_0, o_1, g011, g101, g111):
 
 
 class PackedMLP:
-    """Weights of a 3-layer MLP in the kernels' layout ([in][out] per layer, float32, contiguous)."""
+    """Weights of a 3-layer MLP in the kernels' layouts: FP32 [in][out] per layer for the SIMT
+    kernels and (built on first use) BF16 operand panels for the tensor-core kernels."""
 
     def __init__(self, linears, direct=None):
         l1, l2, l3 = linears
+        self._linears = (l1, l2, l3)
+        self._bf16 = None
         self.Wt = [l.weight.detach().t().contiguous().float() for l in (l1, l2, l3)]
         self.b = [None if l.bias is None else l.bias.detach().contiguous().float() for l in (l1, l2, l3)]
         self.dims = (l1.weight.shape[1], l1.weight.shape[0], l2.weight.shape[0], l3.weight.shape[0])
         self.Wdt = None if direct is None else direct.weight.detach().t().contiguous().float()
+
+
+def _packed_bf16(mlp):
+    if mlp._bf16 is None:
+        mlp._bf16 = [pack_weights_bf16(l.weight.detach().float()) for l in mlp._linears]
+    return mlp._bf16
 
 
 def mlp3_rows(x, mlp, act=ACT_SILU):
@@ -213,4 +222,67 @@ def painn_message_f32(row_ptr, dst, rij, mlp_dist, actv, x_v, rmax, eps=0.1, rad
                                          ptr(mlp_dist.Wt[0]), ptr(mlp_dist.b[0]), ptr(mlp_dist.Wt[1]), ptr(mlp_dist.b[1]),
                                          ptr(mlp_dist.Wt[2]), ptr(mlp_dist.b[2]), ptr(actv), ptr(x_v), ptr(res_a), ptr(res_v),
                                          ptr(out_a), ptr(out_v), ptr(edge_counter), stream_ptr(x_v.device)))
+    return out_a, out_v
+
+
+_TC_STATUS = {}
+
+
+def tc_status(device):
+    """Device status word shared by the tensor-core kernels of one device (LD_FLAG_* bits)."""
+    key = torch.device(device).index or 0
+    if key not in _TC_STATUS:
+        _TC_STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _TC_STATUS[key]
+
+
+def pack_weights_bf16(W):
+    """[N, K] float32 (any strides) -> BF16 operand panels for the tensor-core kernels."""
+    N, K = W.shape
+    n = lib().ld_packed_weight_elems(N, K)
+    out = torch.empty(n, dtype=torch.bfloat16, device=W.device)
+    check(lib().ld_pack_weights_bf16(ptr(W), W.stride(0), W.stride(1), N, K, ptr(out), stream_ptr(W.device)))
+    return out
+
+
+def linear_bf16_tc(x, W_packed, N, bias=None, act=ACT_NONE, inds=0):
+    """y[..., o, s] = act(sum_i W[o,i] x[..., i, s] + b[o]) on tcgen05 (BF16 operands, FP32 accumulate)."""
+    x = x.contiguous()
+    require_cuda_f32(x, "x")
+    S = 3 ** inds
+    shape = list(x.shape)
+    bd = len(shape) - (1 + inds)
+    K = shape[bd]
+    rows = 1
+    for d in shape[:bd]:
+        rows *= d
+    shape[bd] = N
+    y = torch.empty(shape, dtype=torch.float32, device=x.device)
+    with KERNEL_TIMER.region("linear_bf16_tc"):
+        check(lib().ld_linear_bf16_tc(ptr(x), rows, K, S, ptr(W_packed), ptr(bias), N, act, ptr(y), ptr(tc_status(x.device)),
+                                      stream_ptr(x.device)))
+    return y
+
+
+def painn_message_bf16_tc(row_ptr, dst, rij, mlp_dist, actv, x_v, rmax, eps=0.1, radial_kind=RADIAL_PAINN, res_a=None,
+                          res_v=None, edge_counter=None):
+    """Tensor-core variant of painn_message_f32 (BF16 operands in the per-edge MLP, 2e-2 relative)."""
+    require_cuda_f32(actv, "actv")
+    require_cuda_f32(x_v, "x_v")
+    require_cuda_f32(rij, "rij")
+    Nt, n = x_v.shape[0], x_v.shape[1]
+    n_rbf, n1, n2, n3 = mlp_dist.dims
+    if not (n1 == n2 == n3 == 4 * n) or actv.shape != (Nt, 4 * n):
+        raise RuntimeError("painn_message: widths must be n_rbf -> 4n -> 4n -> 4n and actv [Nt,4n]")
+    if dst.dtype != torch.int32 or row_ptr.dtype != torch.int32:
+        raise RuntimeError("painn_message: row_ptr and dst must be int32")
+    w = _packed_bf16(mlp_dist)
+    out_a = torch.empty(Nt, n, dtype=torch.float32, device=x_v.device)
+    out_v = torch.empty(Nt, n, 3, dtype=torch.float32, device=x_v.device)
+    with KERNEL_TIMER.region("painn_message_tc"):
+        check(lib().ld_painn_message_bf16_tc(ptr(row_ptr), ptr(dst), ptr(rij), Nt, n, n_rbf, radial_kind, float(rmax),
+                                             float(eps), ptr(w[0]), ptr(mlp_dist.b[0]), ptr(w[1]), ptr(mlp_dist.b[1]),
+                                             ptr(w[2]), ptr(mlp_dist.b[2]), ptr(actv), ptr(x_v), ptr(res_a), ptr(res_v),
+                                             ptr(out_a), ptr(out_v), ptr(edge_counter), ptr(tc_status(x_v.device)),
+                                             stream_ptr(x_v.device)))
     return out_a, out_v

@@ -115,6 +115,7 @@ class Message(nn.Module):
         self.n = n
         self.epsilon = 0.1
         self.radial = radial
+        self.precision = "fp32"  # "bf16": per-edge MLP on the tensor cores (2e-2 relative)
         self.n_rbf = n if n_rbf is None else n_rbf
         self.mlp_dist = MLP(self.n_rbf, 4 * n)
         self.mlp_actv = MLP(n, 4 * n)
@@ -129,7 +130,8 @@ class Message(nn.Module):
         xa = x_a.reshape(Nt, n).contiguous()
         xv = x_v.reshape(Nt, n, 3).contiguous()
         actv = ops.mlp3_rows(xa, self.mlp_actv.packed(), ops.ACT_SILU)
-        out_a, out_v = ops.painn_message_f32(
+        fused = ops.painn_message_bf16_tc if self.precision == "bf16" else ops.painn_message_f32
+        out_a, out_v = fused(
             graph.row_ptr, graph.dst32, r_ij.contiguous(), self.mlp_dist.packed(), actv, xv, rmax=self.r0,
             eps=self.epsilon, radial_kind=ops.RADIAL_PAINN if self.radial == "painn" else ops.RADIAL_GAUSSIAN, res_a=xa if residual else None,
             res_v=xv if residual else None, edge_counter=edge_counter)
@@ -175,7 +177,8 @@ class Block(nn.Module):
         counter = tup[8] if len(tup) > 8 else None
         if graph is None:
             graph, r_ij = graph_setup(self.r0, box, pos)
-        x_a, x_v = self.message_bond(graph_bond, x_a, x_v, r_ij_bond, residual=True, edge_counter=counter)
+        if graph_bond.src.numel() > 0:  # a bond graph without edges contributes exactly zero
+            x_a, x_v = self.message_bond(graph_bond, x_a, x_v, r_ij_bond, residual=True, edge_counter=counter)
         x_a, x_v = self.message(graph, x_a, x_v, r_ij, residual=True, edge_counter=counter)
         dx_a, dx_v = self.update(x_a, x_v)
         x_a, x_v = x_a + dx_a, x_v + dx_v
@@ -271,6 +274,15 @@ class SE3ITO(nn.Module):
         x_v = x_v + self.pos_emb(x0, x1)
         x1, x_a, x_v = self.cpainn_1(x1, graph_bond, r_ij_bond_1, x_a, x_v, box, types, counter)
         return self.get_v_pred(st, self.readout(x_v).squeeze(-2), x1, x1_t)
+
+
+def set_precision(module, precision):
+    """"fp32" (default, 1e-5 parity) or "bf16" (tensor-core per-edge MLP, 2e-2) for every Message below `module`."""
+    assert precision in ("fp32", "bf16")
+    for m in module.modules():
+        if isinstance(m, Message):
+            m.precision = precision
+    return module
 
 
 class Meanflow:

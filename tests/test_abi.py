@@ -21,7 +21,7 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(L, n), f"{n} declared in include/ld_hotpath.h but not exported"
     # the Python binding covers the same set
-    bound = set(_lib.SIGNATURES) | {"ld_last_error", "ld_status_string"}
+    bound = set(_lib.SIGNATURES) | {"ld_last_error", "ld_status_string", "ld_packed_weight_elems"}
     assert set(names) == bound, set(names) ^ bound
 
 
