@@ -127,6 +127,10 @@ int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, const float* ri
                              const float* res_v, float* out_a, float* out_v, long long* edge_counter, int* status_dev,
                              void* stream);
 
+/* Diagnostics (no counterpart in the reference): per-phase cycle counters of the fused tensor-core
+ * kernel, added into 16 device int64 by later launches; NULL switches them off. */
+int ld_debug_set_phase_counters(long long* device_buffer16);
+
 #ifdef __cplusplus
 }
 #endif

@@ -3,16 +3,22 @@
 // edges_reduce_src), with the three layers of the per-edge distance MLP running as tcgen05 MMAs:
 // BF16 operands, FP32 accumulation in tensor memory. Tolerance of this path: 2e-2 relative.
 //
-// A block owns a node-aligned, contiguous slice of the CSR and walks it 128 edges at a time:
-//   1. radial features of the 128 edges -> BF16 operand tile A in shared memory
-//   2. three layers: weights stream from L2 as pre-packed BF16 panels (bulk asynchronous copies,
-//      4 stages of K=16), one thread issues [128 x 4n x 16] MMAs into 128 lanes x 4n columns of TMEM;
-//      between layers all threads read the accumulators (tcgen05.ld), add bias, apply SiLU and
-//      write the next operand tile back over A
-//   3. last layer: accumulator x gathered neighbour activation -> vector/scalar messages, staged
-//      in shared memory, then summed per source node in edge order; sums for the node that spans
-//      tiles stay in registers, every node is written once (no atomics, fixed summation order)
-// Edge-sized data never reaches HBM. Every mbarrier wait is bounded (LD_FLAG_TIMEOUT).
+// A block owns a node-aligned, contiguous slice of the CSR and walks it 128 edges at a time.
+// Three roles (warp specialised):
+//   * 8 working warps: edge geometry, radial features -> BF16 operand tile A in shared memory;
+//     between layers they read the accumulators (tcgen05.ld), add bias, apply SiLU and write the
+//     next operand tile over A; after the last layer: accumulator x gathered neighbour activation
+//     -> vector/scalar messages, staged in shared memory and summed per source node in edge order.
+//     Sums of a node that spans tiles stay in registers; every node is written once (no atomics,
+//     fixed summation order).
+//   * 1 MMA warp (lane 0): per layer, waits for the operand tile and for each K=16 weight slab,
+//     issues the [128 x 4n x 16] MMAs into 128 lanes x 4n columns of TMEM, commits stage release
+//     and layer completion to mbarriers.
+//   * 1 producer warp (lane 0): streams the pre-packed BF16 weight slabs from L2 with bulk
+//     asynchronous copies through a ring of stages; weights do not depend on the data, so it runs
+//     ahead across layers and tiles as far as the ring allows.
+// Edge-sized data never reaches HBM. Every mbarrier wait is bounded (LD_FLAG_TIMEOUT): a failed
+// wait is OR-ed into the next block barrier so that all threads leave together.
 #include "common.cuh"
 #include "tc05.cuh"
 #include "tp_math.h"
@@ -20,16 +26,28 @@
 namespace {
 
 constexpr int MT_EDGES = 128;          // edges per tile = MMA M
-constexpr int MT_WORK_WARPS = 8;       // working warps: TMEM lane quarter = warp % 4, column half = warp / 4
-constexpr int MT_THREADS_TC = (MT_WORK_WARPS + 1) * 32;  // + one warp whose lane 0 streams weights and issues MMAs
-constexpr int MT_STAGES = 4;           // weight stages of K = 16
+constexpr int MT_WORK_WARPS = 8;       // TMEM lane quarter = warp % 4, column half = warp / 4
+constexpr int MT_WORK_THREADS = MT_WORK_WARPS * 32;
+constexpr int MT_MMA_WARP = MT_WORK_WARPS;
+constexpr int MT_PROD_WARP = MT_WORK_WARPS + 1;
+constexpr int MT_THREADS_TC = (MT_WORK_WARPS + 2) * 32;
+constexpr int MT_SYNC_THREADS = (MT_WORK_WARPS + 1) * 32;  // working warps + MMA warp meet at barrier 1
+constexpr int MT_MAX_STAGES = 4;       // weight ring: slabs of K = 32 (as many as fit, at least 2)
+constexpr int MT_SLAB_KSTEPS = 2;      // MMA K-steps (K = 16) per slab: larger copies stream faster from L2
 constexpr int MT_CG = 64;              // channels per reduction pass
 constexpr int MT_MAX_PASS = 2;         // n <= 128
+constexpr size_t MT_STAGING_BYTES = (size_t)MT_EDGES * MT_CG * 4 * 4;  // 128 KB
+
+// diagnostics slots (cycles, summed over blocks): 0 geometry, 1 radial features, 2/4/6 waiting for
+// layer 1/2/3 accumulators, 3/5 inter-layer epilogues, 7 per-node sums, 8 message staging,
+// 9 MMA lane waiting for weights, 10 producer waiting for a free stage
+constexpr int MT_PROF_SLOTS = 12;
 
 struct TcMessageParams {
   const int* row_ptr; const int* dst; const float* rij;
   int Nt, n, n_rbf, k0p, radial_kind;
-  unsigned bias_off;   // byte offset of the bias copy in dynamic shared memory
+  unsigned stage_off, bias_off;   // byte offsets of the weight ring and the bias copy in dynamic shared memory
+  int nstages;                    // slabs in the weight ring
   float rmax, pi_over_rmax, eps;
   const __nv_bfloat16* w1; const __nv_bfloat16* w2; const __nv_bfloat16* w3;  // packed panels [K/8][4n][8]
   const float* b1; const float* b2; const float* b3;
@@ -37,6 +55,7 @@ struct TcMessageParams {
   float* out_a; float* out_v;
   long long* edge_counter;
   int* status;
+  long long* prof;   // optional [16] cycle counters (diagnostics)
 };
 
 __device__ __forceinline__ int lb_row(const int* __restrict__ row_ptr, int lo, int hi, long long target) {
@@ -46,7 +65,6 @@ __device__ __forceinline__ int lb_row(const int* __restrict__ row_ptr, int lo, i
   }
   return lo;
 }
-
 
 // first node v in [0, Nt] with row_ptr[v] + v >= target (work = edges + nodes before v)
 __device__ __forceinline__ int work_lower_bound(const int* __restrict__ row_ptr, int Nt, long long target) {
@@ -58,90 +76,52 @@ __device__ __forceinline__ int work_lower_bound(const int* __restrict__ row_ptr,
   return lo;
 }
 
-struct Pipe {
-  uint32_t loads;   // weight slabs requested so far (block lifetime)
-  uint32_t mmas;    // weight slabs consumed so far
-  int requested;    // slabs of the current layer requested so far
-};
-
-struct IssueCtx {
-  unsigned char* b_smem; uint64_t* bar_full; uint64_t* bar_empty; uint64_t* bar_accum;
-  uint32_t a_base, tmem_base; int N;
-};
-
-// request the K=16 weight slab `ks` of a layer into the next free stage (one thread)
-__device__ __forceinline__ bool request_slab(const IssueCtx& c, Pipe& pipe, const __nv_bfloat16* __restrict__ wp, int ks) {
-  const uint32_t slab = (uint32_t)c.N * 32;  // 2 panels x N rows x 16 B
-  const uint32_t st = pipe.loads % MT_STAGES, use = pipe.loads / MT_STAGES;
-  if (use >= 1 && !tc::mbar_wait(&c.bar_empty[st], (use - 1) & 1)) return false;  // MMAs that read the stage are done
-  tc::mbar_expect_tx(&c.bar_full[st], slab);
-  tc::bulk_g2s(c.b_smem + (size_t)st * slab, wp + (size_t)ks * c.N * 16, slab, &c.bar_full[st]);
-  pipe.loads++;
-  return true;
+// barrier 1: working warps + MMA warp; returns the OR of `flag` over its participants
+__device__ __forceinline__ int sync_or(int flag) {
+  int out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "barrier.cta.red.or.pred p, 1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(flag), "n"(MT_SYNC_THREADS)
+      : "memory");
+  return out;
 }
+// barrier 2: working warps only
+__device__ __forceinline__ void sync_workers() { asm volatile("barrier.cta.sync 2, %0;" ::"n"(MT_WORK_THREADS) : "memory"); }
 
-__device__ __forceinline__ bool prefetch_layer(const IssueCtx& c, Pipe& pipe, const __nv_bfloat16* __restrict__ wp, int ksteps) {
-  for (pipe.requested = 0; pipe.requested < ksteps && pipe.requested < MT_STAGES - 1; pipe.requested++)
-    if (!request_slab(c, pipe, wp, pipe.requested)) return false;
-  return true;
-}
-
-// issue the MMAs of one layer (operand tile A is ready), keep the weight pipeline full, signal bar_accum
-__device__ __forceinline__ bool run_layer(const IssueCtx& c, Pipe& pipe, const __nv_bfloat16* __restrict__ wp, int ksteps) {
-  const uint32_t slab = (uint32_t)c.N * 32;
-  for (int ks = 0; ks < ksteps; ks++) {
-    const uint32_t st = pipe.mmas % MT_STAGES, use = pipe.mmas / MT_STAGES;
-    if (!tc::mbar_wait(&c.bar_full[st], use & 1)) return false;
-    tc::fence_after_sync();
-    const uint64_t ad = tc::smem_desc(c.a_base + ks * 2 * (MT_EDGES * 16), MT_EDGES * 16, 128);
-    const uint32_t b_base = tc::smem_u32(c.b_smem + (size_t)st * slab);
-    for (int n0 = 0; n0 < c.N; n0 += 256) {
-      const int n1 = min(256, c.N - n0);
-      const uint64_t bd = tc::smem_desc(b_base + n0 * 16, c.N * 16, 128);
-      tc::mma_bf16(c.tmem_base + n0, ad, bd, tc::idesc_bf16(MT_EDGES, n1), ks > 0 ? 1u : 0u);
-    }
-    tc::mma_commit(&c.bar_empty[st]);
-    pipe.mmas++;
-    if (pipe.requested < ksteps) {
-      if (!request_slab(c, pipe, wp, pipe.requested)) return false;
-      pipe.requested++;
-    }
-  }
-  tc::mma_commit(c.bar_accum);
-  return true;
-}
-
-// Warps 0..7: geometry, operand tiles, epilogues, reduction (thread = one edge row / one output
-// column). Warp 8: lane 0 streams weights and issues MMAs; it never spins in the same warp as
-// working threads. All 288 threads meet at the same sequence of block barriers; a failed bounded
-// wait is OR-ed in at the next barrier so that everybody leaves together.
 __global__ void __launch_bounds__(MT_THREADS_TC, 1)
 painn_message_tc_kernel(TcMessageParams P) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t bar_full[MT_STAGES], bar_empty[MT_STAGES], bar_accum;
+  __shared__ __align__(8) uint64_t bar_full[MT_MAX_STAGES], bar_empty[MT_MAX_STAGES], bar_accum;
   __shared__ uint32_t tmem_slot;
   __shared__ float s_dir[MT_EDGES][3];
   __shared__ float s_dist[MT_EDGES];
   __shared__ int s_dst[MT_EDGES];
   __shared__ int s_src[MT_EDGES];
+  __shared__ int s_rowwin[MT_EDGES + 1];  // row_ptr[node_lo .. node_lo+128] of the coming tile
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool issuer_warp = warp == MT_WORK_WARPS;
-  const bool issuer = issuer_warp && lane == 0;
+  const bool mma_lane = warp == MT_MMA_WARP && lane == 0;
+  const bool prod_lane = warp == MT_PROD_WARP && lane == 0;
   const int quarter = warp & 3, half = (warp >> 2) & 1;
   const int row = quarter * 32 + lane;  // edge slot / TMEM lane owned in the epilogues
   const int n = P.n, N = 4 * n;
-  // shared-memory carve-up: A operand tile | weight stages ; reduction staging overlays both ; biases after
+  // dynamic shared memory: [ A operand tile, overlaid by the reduction staging | weight ring | biases ]
   unsigned char* a_smem = smem;                                   // 128 x N BF16
-  unsigned char* b_smem = a_smem + (size_t)MT_EDGES * N * 2;      // MT_STAGES x N*32
+  unsigned char* b_smem = smem + P.stage_off;                     // nstages x slab
   float* s_bias = reinterpret_cast<float*>(smem + P.bias_off);    // 3 x N
   float* stage_f = reinterpret_cast<float*>(smem);                // [128][MT_CG*4]
+  const uint32_t slab = (uint32_t)N * 32 * MT_SLAB_KSTEPS;        // bytes of a full weight slab
+  const uint32_t nst = (uint32_t)P.nstages;
 
   for (int i = tid; i < N; i += MT_THREADS_TC) {
     s_bias[i] = P.b1[i]; s_bias[N + i] = P.b2[i]; s_bias[2 * N + i] = P.b3[i];
   }
   if (tid == 0) {
-    for (int s = 0; s < MT_STAGES; s++) { tc::mbar_init(&bar_full[s], 1); tc::mbar_init(&bar_empty[s], 1); }
+    for (int s = 0; s < MT_MAX_STAGES; s++) { tc::mbar_init(&bar_full[s], 1); tc::mbar_init(&bar_empty[s], 1); }
     tc::mbar_init(&bar_accum, 1);
     tc::mbar_init_fence();
   }
@@ -153,7 +133,6 @@ painn_message_tc_kernel(TcMessageParams P) {
   tc::fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
   const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
-  IssueCtx ctx{b_smem, bar_full, bar_empty, &bar_accum, tc::smem_u32(a_smem), tmem_base, N};
 
   // node-aligned share, balanced over edges + nodes: nodes without edges still have to be written
   const long long E = P.row_ptr[P.Nt];
@@ -163,99 +142,195 @@ painn_message_tc_kernel(TcMessageParams P) {
   const int n_end = blockIdx.x == gridDim.x - 1 ? P.Nt : work_lower_bound(P.row_ptr, P.Nt, per * (blockIdx.x + 1));
   const long long e_begin = n_begin < n_end ? P.row_ptr[n_begin] : 0;
   const long long e_end = n_begin < n_end ? P.row_ptr[n_end] : 0;
-
-  // reduction role: column `tid` of the staging tile = (channel tid/4 of the pass, component tid%4)
-  const int red_c = (tid >> 2) & (MT_CG - 1), red_k = tid & 3;
-  const int npass = (n + MT_CG - 1) / MT_CG;
+  const long long ntiles = (e_end - e_begin + MT_EDGES - 1) / MT_EDGES;
   const int k0steps = P.k0p / 16, ksteps = N / 16;
-  float acc[MT_MAX_PASS] = {0.f, 0.f};
-  int cur = n_begin;
-  Pipe pipe{0, 0, 0};
-  uint32_t accum_phase = 0;
+  const int npass = (n + MT_CG - 1) / MT_CG;
+  long long pc[MT_PROF_SLOTS];
+#pragma unroll
+  for (int i = 0; i < MT_PROF_SLOTS; i++) pc[i] = 0;
   int fail = 0;
 
-  auto flush_until = [&](int pass, int from, int next, float value) {
-    // write node `from` (value), zero-fill (from, next) for this pass's channel
-    const int c = pass * MT_CG + red_c;
-    if (c >= n) return;
-    for (int v = from; v < next; v++) {
-      float val = (v == from) ? value : 0.f;
-      if (red_k < 3) {
-        const size_t off = ((size_t)v * n + c) * 3 + red_k;
-        if (P.res_v != nullptr) val += P.res_v[off];
-        P.out_v[off] = val;
-      } else {
-        const size_t off = (size_t)v * n + c;
-        if (P.res_a != nullptr) val += P.res_a[off];
-        P.out_a[off] = val;
-      }
-    }
-  };
-
-  for (long long e0 = e_begin; e0 < e_end; e0 += MT_EDGES) {
-    const int cnt = (int)((e_end - e0) < MT_EDGES ? (e_end - e0) : MT_EDGES);
-    // ---- 1. edge geometry ------------------------------------------------------------------------
-    if (tid < MT_EDGES) {
-      float dx = 0.f, dy = 0.f, dz = 0.f;
-      int j = 0, s = -1;
-      if (tid < cnt) {
-        const long long e = e0 + tid;
-        dx = P.rij[e * 3]; dy = P.rij[e * 3 + 1]; dz = P.rij[e * 3 + 2];
-        j = P.dst[e];
-        s = lb_row(P.row_ptr, n_begin, n_end, e + 1) - 1;
-      }
-      const float r2 = dx * dx + dy * dy + dz * dz;
-      const float inv = 1.0f / sqrtf(P.eps + r2);
-      s_dir[tid][0] = dx * inv; s_dir[tid][1] = dy * inv; s_dir[tid][2] = dz * inv;
-      s_dist[tid] = sqrtf(r2);
-      s_dst[tid] = j;
-      s_src[tid] = s;
-    }
-    if (__syncthreads_or(fail)) { fail = 1; break; }                                   // [S1]
-    // ---- 2. radial features -> operand tile ; issuer prefetches the first layer's weights --------------
-    if (issuer) {
-      if (!prefetch_layer(ctx, pipe, P.w1, k0steps)) fail = 1;
-    } else if (!issuer_warp) {
-      const int e = tid & (MT_EDGES - 1);
-      const float d = s_dist[e];
-      for (int p = tid >> 7; p < P.k0p / 8; p += MT_WORK_WARPS * 32 / MT_EDGES) {
-        float v[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-          const int k = p * 8 + j;
-          v[j] = (e < cnt && k < P.n_rbf) ? radial_feature(P.radial_kind, k, P.n_rbf, d, P.rmax, P.pi_over_rmax) : 0.f;
+  if (warp == MT_PROD_WARP) {
+    // ===== producer: weight slabs through the ring, independent of the data ==============================
+    if (prod_lane) {
+      uint32_t loads = 0;
+      for (long long t = 0; t < ntiles && !fail; t++) {
+        for (int layer = 0; layer < 3 && !fail; layer++) {
+          const __nv_bfloat16* wp = layer == 0 ? P.w1 : (layer == 1 ? P.w2 : P.w3);
+          const int steps = layer == 0 ? k0steps : ksteps;
+          for (int ks = 0; ks < steps; ks += MT_SLAB_KSTEPS, loads++) {
+            const uint32_t st = loads % nst, use = loads / nst;
+            const uint32_t bytes = (uint32_t)min(MT_SLAB_KSTEPS, steps - ks) * N * 32;
+            const long long t0 = clock64();
+            if (use >= 1 && !tc::mbar_wait(&bar_empty[st], (use - 1) & 1)) { fail = 1; break; }  // MMAs that read it are done
+            pc[10] += clock64() - t0;
+            tc::mbar_expect_tx(&bar_full[st], bytes);
+            tc::bulk_g2s(b_smem + (size_t)st * slab, wp + (size_t)ks * N * 16, bytes, &bar_full[st]);
+          }
         }
-        uint4 q;
-        q.x = tc::pack_bf16x2(v[0], v[1]); q.y = tc::pack_bf16x2(v[2], v[3]);
-        q.z = tc::pack_bf16x2(v[4], v[5]); q.w = tc::pack_bf16x2(v[6], v[7]);
-        *reinterpret_cast<uint4*>(a_smem + (size_t)p * (MT_EDGES * 16) + e * 16) = q;
       }
-      tc::fence_async_smem();
+      if (fail) {
+        // copies already requested still land in this block's shared memory: give them a bounded chance
+        for (uint32_t i = loads > nst ? loads - nst : 0; i < loads; i++)
+          tc::mbar_wait(&bar_full[i % nst], (i / nst) & 1);
+      }
     }
-    tc::fence_before_sync();
-    if (__syncthreads_or(fail)) { fail = 1; break; }                                   // [S2]
+  } else if (warp == MT_MMA_WARP) {
+    // ===== MMA issue ========================================================================================
+    uint32_t mmas = 0;
+    const uint32_t a_base = tc::smem_u32(a_smem);
+    for (long long t = 0; t < ntiles; t++) {
+      if (sync_or(fail)) { fail = 1; break; }      // [B1] geometry staged
+      if (sync_or(fail)) { fail = 1; break; }      // [B2] first operand tile ready
+      for (int layer = 0; layer < 3; layer++) {
+        if (mma_lane && !fail) {
+          tc::fence_after_sync();
+          const int steps = layer == 0 ? k0steps : ksteps;
+          for (int ks0 = 0; ks0 < steps; ks0 += MT_SLAB_KSTEPS, mmas++) {
+            const uint32_t st = mmas % nst, use = mmas / nst;
+            const long long t0 = clock64();
+            if (!tc::mbar_wait(&bar_full[st], use & 1)) { fail = 1; break; }
+            pc[9] += clock64() - t0;
+            tc::fence_after_sync();
+            const uint32_t b_base = tc::smem_u32(b_smem + (size_t)st * slab);
+            for (int kk = 0; kk < MT_SLAB_KSTEPS && ks0 + kk < steps; kk++) {
+              const int ks = ks0 + kk;
+              const uint64_t ad = tc::smem_desc(a_base + ks * 2 * (MT_EDGES * 16), MT_EDGES * 16, 128);
+              for (int n0 = 0; n0 < N; n0 += 256) {
+                const int n1 = min(256, N - n0);
+                const uint64_t bd = tc::smem_desc(b_base + kk * 2 * (N * 16) + n0 * 16, N * 16, 128);
+                tc::mma_bf16(tmem_base + n0, ad, bd, tc::idesc_bf16(MT_EDGES, n1), ks > 0 ? 1u : 0u);
+              }
+            }
+            tc::mma_commit(&bar_empty[st]);
+          }
+          if (!fail) tc::mma_commit(&bar_accum);
+        }
+        fail = __shfl_sync(0xffffffffu, fail, 0);
+        if (sync_or(fail)) { fail = 1; break; }    // [B3..B5] accumulators consumed / next operand tile ready
+      }
+      if (fail) break;
+      if (sync_or(fail)) { fail = 1; break; }      // [B6] tile finished: TMEM and A free again
+    }
+  } else {
+    // ===== working warps =========================================================================================
+    // reduction role: column `tid` of the staging tile = (channel tid/4 of the pass, component tid%4)
+    const int red_c = (tid >> 2) & (MT_CG - 1), red_k = tid & 3;
+    float acc[MT_MAX_PASS] = {0.f, 0.f};
+    int cur = n_begin;
+    int node_lo = n_begin;  // source node of the next tile's first edge (or an earlier node)
+    if (tid <= MT_EDGES) s_rowwin[tid] = P.row_ptr[min(node_lo + tid, n_end > n_begin ? n_end : n_begin)];
+    sync_workers();
+    long long tprev = clock64();
+    auto lap = [&](int i) { const long long t = clock64(); pc[i] += t - tprev; tprev = t; };
+    uint32_t accum_phase = 0;
 
-    // ---- 3. three layers ---------------------------------------------------------------------------------
-    for (int layer = 0; layer < 3; layer++) {
-      if (issuer) {
+    auto flush_until = [&](int pass, int from, int next, float value) {
+      // write node `from` (value), zero-fill (from, next) for this pass's channel
+      const int c = pass * MT_CG + red_c;
+      if (c >= n) return;
+      for (int v = from; v < next; v++) {
+        float val = (v == from) ? value : 0.f;
+        if (red_k < 3) {
+          const size_t off = ((size_t)v * n + c) * 3 + red_k;
+          if (P.res_v != nullptr) val += P.res_v[off];
+          P.out_v[off] = val;
+        } else {
+          const size_t off = (size_t)v * n + c;
+          if (P.res_a != nullptr) val += P.res_a[off];
+          P.out_a[off] = val;
+        }
+      }
+    };
+
+    for (long long e0 = e_begin; e0 < e_end; e0 += MT_EDGES) {
+      const int cnt = (int)((e_end - e0) < MT_EDGES ? (e_end - e0) : MT_EDGES);
+      // ---- 1. edge geometry ------------------------------------------------------------------------
+      if (tid < MT_EDGES) {
+        float dx = 0.f, dy = 0.f, dz = 0.f;
+        int j = 0, s = -1;
+        if (tid < cnt) {
+          const long long e = e0 + tid;
+          dx = P.rij[e * 3]; dy = P.rij[e * 3 + 1]; dz = P.rij[e * 3 + 2];
+          j = P.dst[e];
+          // source node: largest v with row_ptr[v] <= e, searched in the staged window first
+          if ((long long)s_rowwin[MT_EDGES] > e) {
+            int lo = 0, hi = MT_EDGES;  // win[lo] <= e < win[hi]
+            while (hi - lo > 1) {
+              const int mid = (lo + hi) >> 1;
+              if ((long long)s_rowwin[mid] > e) hi = mid; else lo = mid;
+            }
+            s = node_lo + lo;
+          } else {
+            s = lb_row(P.row_ptr, node_lo + MT_EDGES, n_end, e + 1) - 1;
+          }
+        }
+        const float r2 = dx * dx + dy * dy + dz * dz;
+        const float inv = rsqrtf(P.eps + r2);
+        s_dir[tid][0] = dx * inv; s_dir[tid][1] = dy * inv; s_dir[tid][2] = dz * inv;
+        s_dist[tid] = sqrtf(r2);
+        s_dst[tid] = j;
+        s_src[tid] = s;
+      }
+      if (sync_or(fail)) { fail = 1; break; }                                            // [B1]
+      lap(0);
+      // ---- 2. radial features -> operand tile ---------------------------------------------------------------
+      {
+        const int e = tid & (MT_EDGES - 1);
+        const float d = s_dist[e];
+        // Gaussian basis: envelope once per edge, fast exponentials (the features are rounded to BF16)
+        const float width = P.n_rbf > 1 ? P.rmax / (float)(P.n_rbf - 1) : P.rmax;
+        const float inv_w = 1.0f / width;
+        const float env = d < P.rmax ? 0.5f * (__cosf(P.pi_over_rmax * d) + 1.0f) : 0.f;
+        for (int p = tid >> 7; p < P.k0p / 8; p += MT_WORK_THREADS / MT_EDGES) {
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const int k = p * 8 + j;
+            float f = 0.f;
+            if (e < cnt && k < P.n_rbf) {
+              if (P.radial_kind == 1) {
+                const float u = (d - (float)k * width) * inv_w;
+                f = __expf(-0.5f * u * u) * env;
+              } else {
+                f = radial_feature(P.radial_kind, k, P.n_rbf, d, P.rmax, P.pi_over_rmax);
+              }
+            }
+            v[j] = f;
+          }
+          uint4 q;
+          q.x = tc::pack_bf16x2(v[0], v[1]); q.y = tc::pack_bf16x2(v[2], v[3]);
+          q.z = tc::pack_bf16x2(v[4], v[5]); q.w = tc::pack_bf16x2(v[6], v[7]);
+          *reinterpret_cast<uint4*>(a_smem + (size_t)p * (MT_EDGES * 16) + e * 16) = q;
+        }
+        tc::fence_async_smem();
+      }
+      tc::fence_before_sync();
+      if (sync_or(fail)) { fail = 1; break; }                                            // [B2]
+      lap(1);
+
+      // ---- 3. three layers -------------------------------------------------------------------------------------
+      for (int layer = 0; layer < 3; layer++) {
+        {  // one lane per warp polls, the others wait for it
+          int done = 1;
+          if (lane == 0) done = tc::mbar_wait(&bar_accum, accum_phase & 1) ? 1 : 0;
+          done = __shfl_sync(0xffffffffu, done, 0);
+          if (!done) fail = 1;
+        }
+        accum_phase++;
         tc::fence_after_sync();
-        const __nv_bfloat16* wp = layer == 0 ? P.w1 : (layer == 1 ? P.w2 : P.w3);
-        if (!run_layer(ctx, pipe, wp, layer == 0 ? k0steps : ksteps)) fail = 1;
-        if (!fail && layer < 2 && !prefetch_layer(ctx, pipe, layer == 0 ? P.w2 : P.w3, ksteps)) fail = 1;
-      } else if (!issuer_warp) {
-        if (!tc::mbar_wait(&bar_accum, accum_phase & 1)) fail = 1;
-        tc::fence_after_sync();
+        lap(2 + 2 * layer);
         if (!fail && layer < 2) {
           // bias + SiLU -> next operand tile (this thread: row `row`, columns of its half)
           const float* bias = s_bias + layer * N;
-          for (int cb = half * (N / 2); cb < (half + 1) * (N / 2); cb += 32) {
-            float v[32];
-            tc::tmem_ld32(tmem_row + cb, v);
+          for (int cb = half * (N / 2); cb < (half + 1) * (N / 2); cb += 64) {
+            float v[64];
+            tc::tmem_ld64(tmem_row + cb, v);
 #pragma unroll
-            for (int g8 = 0; g8 < 4; g8++) {
+            for (int g8 = 0; g8 < 8; g8++) {
               float t[8];
 #pragma unroll
-              for (int j = 0; j < 8; j++) t[j] = silu_f(v[g8 * 8 + j] + bias[cb + g8 * 8 + j]);
+              for (int j = 0; j < 8; j++) t[j] = tc::silu_fast(v[g8 * 8 + j] + bias[cb + g8 * 8 + j]);
               uint4 q;
               q.x = tc::pack_bf16x2(t[0], t[1]); q.y = tc::pack_bf16x2(t[2], t[3]);
               q.z = tc::pack_bf16x2(t[4], t[5]); q.w = tc::pack_bf16x2(t[6], t[7]);
@@ -263,43 +338,37 @@ painn_message_tc_kernel(TcMessageParams P) {
             }
           }
           tc::fence_async_smem();
+          tc::fence_before_sync();
         }
+        if (sync_or(fail)) { fail = 1; break; }                                          // [B3], [B4], [B5]
+        if (layer < 2) lap(3 + 2 * layer);
       }
-      accum_phase++;
-      tc::fence_before_sync();
-      if (__syncthreads_or(fail)) { fail = 1; break; }                                 // [S3], [S4], [S5]
-    }
-    if (fail) break;  // uniform: the flag was OR-ed across the block at the barrier above
+      if (fail) break;
 
-    // ---- 4. messages and per-node sums (working warps; the issuer warp only keeps the barriers) ------------
-    const float* b3 = s_bias + 2 * N;
-    const int j_node = issuer_warp ? 0 : s_dst[row];
-    const float* Aj = P.actv + (size_t)j_node * N;
-    const float* Xj = P.x_v + (size_t)j_node * n * 3;
-    const float dir0 = s_dir[row][0], dir1 = s_dir[row][1], dir2 = s_dir[row][2];
-    const int tile_cur = cur;
-    for (int pass = 0; pass < npass; pass++) {
-      if (!issuer_warp) {
+      // ---- 4. messages and per-node sums -----------------------------------------------------------------------
+      const float* b3 = s_bias + 2 * N;
+      const int j_node = s_dst[row];
+      const float* Aj = P.actv + (size_t)j_node * N;
+      const float* Xj = P.x_v + (size_t)j_node * n * 3;
+      const float dir0 = s_dir[row][0], dir1 = s_dir[row][1], dir2 = s_dir[row][2];
+      const int tile_cur = cur;
+      node_lo = s_src[cnt - 1];
+      // stage the row_ptr window of the next tile (read after the barrier that ends this tile)
+      if (tid <= MT_EDGES) s_rowwin[tid] = P.row_ptr[min(node_lo + tid, n_end)];
+      for (int pass = 0; pass < npass; pass++) {
         // this thread: edge `row`, channels [pass*CG + half*CG/2, +CG/2) in groups of 8
         for (int g8 = 0; g8 < MT_CG / 16; g8++) {
           const int c0 = pass * MT_CG + half * (MT_CG / 2) + g8 * 8;
           if (c0 < n) {  // n is a multiple of 8: a group is entirely valid or entirely not
-            float d[32];
-            tc::tmem_ld8x4(tmem_row + c0, (uint32_t)n, d);  // D[.., c0 + k*n + j] at d[k*8 + j]
+            // 32-byte loads: every fetched sector is requested exactly once
             float a[32];
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-              const float4 u0 = __ldg(reinterpret_cast<const float4*>(Aj + k * n + c0));
-              const float4 u1 = __ldg(reinterpret_cast<const float4*>(Aj + k * n + c0 + 4));
-              a[k * 8 + 0] = u0.x; a[k * 8 + 1] = u0.y; a[k * 8 + 2] = u0.z; a[k * 8 + 3] = u0.w;
-              a[k * 8 + 4] = u1.x; a[k * 8 + 5] = u1.y; a[k * 8 + 6] = u1.z; a[k * 8 + 7] = u1.w;
-            }
+            for (int k = 0; k < 4; k++) tc::ldg_v8(Aj + k * n + c0, a + 8 * k);
             float xv[24];
 #pragma unroll
-            for (int q4 = 0; q4 < 6; q4++) {
-              const float4 u = __ldg(reinterpret_cast<const float4*>(Xj + (size_t)c0 * 3) + q4);
-              xv[q4 * 4 + 0] = u.x; xv[q4 * 4 + 1] = u.y; xv[q4 * 4 + 2] = u.z; xv[q4 * 4 + 3] = u.w;
-            }
+            for (int q8 = 0; q8 < 3; q8++) tc::ldg_v8(Xj + (size_t)c0 * 3 + 8 * q8, xv + 8 * q8);
+            float d[32];
+            tc::tmem_ld8x4(tmem_row + c0, (uint32_t)n, d);  // D[.., c0 + k*n + j] at d[k*8 + j]
 #pragma unroll
             for (int j = 0; j < 8; j++) {
               const int c = c0 + j;
@@ -321,44 +390,70 @@ painn_message_tc_kernel(TcMessageParams P) {
             }
           }
         }
-      }
-      __syncthreads();
-      // sum per source node, in edge order; thread = one (channel, component) column
-      if (!issuer_warp) {
-        int c_node = tile_cur;
-        float a_sum = acc[pass];
-        const int slot = red_c;
-        for (int e = 0; e < cnt; e++) {
-          const int s = s_src[e];
-          if (s != c_node) {
-            flush_until(pass, c_node, s, a_sum);
-            a_sum = 0.f;
-            c_node = s;
+        sync_workers();
+        lap(8);
+        // sum per source node, in edge order; thread = one (channel, component) column
+        {
+          int c_node = tile_cur;
+          float a_sum = acc[pass];
+          const int slot = red_c;
+          for (int eb = 0; eb < cnt; eb += 8) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {  // rows beyond cnt hold zeros
+              const int e = eb + i;
+              const int sw = (slot & ~7) | ((slot ^ e) & 7);
+              v[i] = stage_f[(size_t)e * (MT_CG * 4) + sw * 4 + red_k];
+            }
+            const int last = min(eb + 7, cnt - 1);
+            if (s_src[eb] == c_node && s_src[last] == c_node) {
+              // whole group belongs to the current node (src is sorted): fixed-shape tree sum
+              a_sum += ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; i++) {
+                if (eb + i < cnt) {
+                  const int s = s_src[eb + i];
+                  if (s != c_node) {
+                    flush_until(pass, c_node, s, a_sum);
+                    a_sum = 0.f;
+                    c_node = s;
+                  }
+                  a_sum += v[i];
+                }
+              }
+            }
           }
-          const int sw = (slot & ~7) | ((slot ^ e) & 7);
-          a_sum += stage_f[(size_t)e * (MT_CG * 4) + sw * 4 + red_k];
+          acc[pass] = a_sum;
+          if (pass == npass - 1) cur = c_node;
         }
-        acc[pass] = a_sum;
-        if (pass == npass - 1) cur = c_node;
+        if (pass + 1 < npass) sync_workers();  // staging is rewritten by the next pass
+        lap(7);
       }
       tc::fence_before_sync();
-      __syncthreads();  // staging (and TMEM after the last pass) is rewritten by the next pass / tile
+      if (sync_or(fail)) { fail = 1; break; }                                            // [B6]
+    }
+    if (!fail && n_begin < n_end) {
+      for (int pass = 0; pass < npass; pass++) flush_until(pass, cur, n_end, acc[pass]);
+      if (P.edge_counter != nullptr && tid == 0) atomicAdd((unsigned long long*)P.edge_counter, (unsigned long long)(e_end - e_begin));
     }
   }
-  if (!fail && !issuer_warp && n_begin < n_end) {
-    for (int pass = 0; pass < npass; pass++) flush_until(pass, cur, n_end, acc[pass]);
-    if (P.edge_counter != nullptr && tid == 0) atomicAdd((unsigned long long*)P.edge_counter, (unsigned long long)(e_end - e_begin));
+  if (P.prof != nullptr && (tid == 0 || mma_lane || prod_lane)) {
+    for (int i = 0; i < MT_PROF_SLOTS; i++)
+      if (pc[i]) atomicAdd((unsigned long long*)&P.prof[i], (unsigned long long)pc[i]);
   }
-  if (fail && tid == 0 && P.status != nullptr) atomicOr(P.status, LD_FLAG_TIMEOUT);
-  if (fail && issuer) {
-    // give copies still in flight a bounded chance to land before the block's shared memory is released
-    for (uint32_t i = pipe.mmas; i < pipe.loads; i++) tc::mbar_wait(&bar_full[i % MT_STAGES], (i / MT_STAGES) & 1);
-  }
+  if (fail && lane == 0 && P.status != nullptr) atomicOr(P.status, LD_FLAG_TIMEOUT);
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem_base, ncols);
 }
 
+long long* g_prof_buffer = nullptr;
+
 }  // namespace
+
+// Diagnostics: device buffer of 16 int64 that later ld_painn_message_bf16_tc launches add per-phase
+// cycle counts to (summed over blocks); NULL switches it off. Not thread safe.
+extern "C" int ld_debug_set_phase_counters(long long* device_buffer16) { g_prof_buffer = device_buffer16; return LD_OK; }
 
 // Tensor-core variant of ld_painn_message_f32 (same graph / feature arguments). w1p/w2p/w3p are the
 // distance-MLP weights packed by ld_pack_weights_bf16 ([4n][n_rbf], [4n][4n], [4n][4n]); biases FP32.
@@ -371,8 +466,8 @@ extern "C" int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, cons
   if (Nt < 0 || n <= 0 || n_rbf <= 0) return LD_ERR_SHAPE;
   if (n % 8 != 0 || n > 128) { ld_set_last_message("painn message (tensor-core path): n must be a multiple of 8, at most 128"); return LD_ERR_UNSUPPORTED; }
   if (b1 == nullptr || b2 == nullptr || b3 == nullptr) { ld_set_last_message("painn message: biases are required"); return LD_ERR_SHAPE; }
-  if ((((uintptr_t)w1p | (uintptr_t)w2p | (uintptr_t)w3p | (uintptr_t)actv | (uintptr_t)x_v) % 16) != 0) {
-    ld_set_last_message("painn message (tensor-core path): weights and node features must be 16-byte aligned");
+  if ((((uintptr_t)w1p | (uintptr_t)w2p | (uintptr_t)w3p) % 16) != 0 || (((uintptr_t)actv | (uintptr_t)x_v) % 32) != 0) {
+    ld_set_last_message("painn message (tensor-core path): packed weights must be 16-byte, node features 32-byte aligned");
     return LD_ERR_SHAPE;
   }
   if (Nt == 0) return LD_OK;
@@ -381,15 +476,22 @@ extern "C" int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, cons
   P.radial_kind = radial_kind; P.rmax = rmax; P.pi_over_rmax = (float)(3.14159265358979323846 / (double)rmax); P.eps = eps;
   P.w1 = (const __nv_bfloat16*)w1p; P.w2 = (const __nv_bfloat16*)w2p; P.w3 = (const __nv_bfloat16*)w3p;
   P.b1 = b1; P.b2 = b2; P.b3 = b3; P.actv = actv; P.x_v = x_v; P.res_a = res_a; P.res_v = res_v;
-  P.out_a = out_a; P.out_v = out_v; P.edge_counter = edge_counter; P.status = status_dev;
+  P.out_a = out_a; P.out_v = out_v; P.edge_counter = edge_counter; P.status = status_dev; P.prof = g_prof_buffer;
   const int N = 4 * n;
   if (P.k0p > N) { ld_set_last_message("painn message (tensor-core path): n_rbf above 4n is not supported"); return LD_ERR_UNSUPPORTED; }
-  size_t a_bytes = (size_t)MT_EDGES * N * 2, b_bytes = (size_t)MT_STAGES * N * 32;
-  size_t staging = (size_t)MT_EDGES * MT_CG * 4 * 4;  // 128 KB, overlays A and the weight stages
-  size_t front = a_bytes + b_bytes > staging ? a_bytes + b_bytes : staging;
-  P.bias_off = (unsigned)front;
-  const size_t smem = front + (size_t)3 * N * 4 + 1024;
-  if (smem > 227 * 1024) return LD_ERR_UNSUPPORTED;
+  // the staging tile overlays only the operand tile, never the weight ring (the producer runs ahead)
+  const size_t a_bytes = (size_t)MT_EDGES * N * 2;
+  const size_t front = a_bytes > MT_STAGING_BYTES ? a_bytes : MT_STAGING_BYTES;
+  const size_t slab = (size_t)N * 32 * MT_SLAB_KSTEPS;
+  const size_t fixed = front + (size_t)3 * N * 4 + 1024 + 6 * 1024;  // + static shared memory of the kernel
+  int nstages = (int)((227 * 1024 - fixed) / slab);
+  if (nstages > MT_MAX_STAGES) nstages = MT_MAX_STAGES;
+  if (nstages < 2) return LD_ERR_UNSUPPORTED;
+  const size_t ring = (size_t)nstages * slab;
+  P.nstages = nstages;
+  P.stage_off = (unsigned)front;
+  P.bias_off = (unsigned)(front + ring);
+  const size_t smem = front + ring + (size_t)3 * N * 4 + 1024;
   LD_CUDA_TRY(cudaFuncSetAttribute(painn_message_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

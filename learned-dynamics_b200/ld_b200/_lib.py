@@ -35,6 +35,7 @@ SIGNATURES = {
     "ld_pack_weights_bf16": [P, LL, LL, I, I, P, P],
     "ld_linear_bf16_tc": [P, LL, I, I, P, P, I, I, P, P, P],
     "ld_painn_message_bf16_tc": [P, P, P, I, I, I, I, F, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P],
+    "ld_debug_set_phase_counters": [P],
     "ld_painn_message_f32": [P, P, P, I, I, I, I, F, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P],
 }
 
