@@ -177,8 +177,9 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    assert w["systems"] % world == 0, "systems must divide across ranks"
-    per = w["systems"] // world
+    from ld_b200 import sharding
+    sys_begin, sys_end = sharding.shard_range(w["systems"], rank, world)
+    per = sys_end - sys_begin
     box = None if w["box"] is None else (w["box"],) * 3
 
     dn = painn.set_precision(build_model(w, dev), args.precision)
@@ -186,7 +187,7 @@ def main():
     bond = painn.chain_bond_graph(per, w["nodes"], dev) if w["kind"] == "polymer" else painn.empty_bond_graph(per, w["nodes"], dev)
     mf = painn.Meanflow(dn, box, w["sigma0"], types, bond)
     x_all = make_positions(w, w["systems"], seed=1003)
-    x_host = x_all[rank * per:(rank + 1) * per].contiguous().pin_memory()
+    x_host = x_all[sys_begin:sys_end].contiguous().pin_memory()
     out_host = torch.empty_like(x_host).pin_memory()
     noise_gen = torch.Generator(device=dev).manual_seed(777 + rank)
     counter = torch.zeros(1, dtype=torch.int64, device=dev)
@@ -215,14 +216,13 @@ def main():
     e0.record()
     for _ in range(args.steps):
         x = device_step(x)
-    if world > 1:
-        gathered = [torch.empty_like(x) for _ in range(world)] if rank == 0 else None
-        dist.gather(x, gathered, dst=0)
+    final = sharding.gather_positions(x, w["systems"])  # the one collective of a rollout (NCCL over NVLink)
     e1.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
     edges = counter.clone()
+    local_edges = int(counter.item())
     ktimes = ops.KERNEL_TIMER.summary()
     ops.KERNEL_TIMER.reset(enabled=False)
     if world > 1:
@@ -260,7 +260,7 @@ def main():
         roof = None
         if msg["launches"]:
             per_launch_s = msg["ms"] * 1e-3 / msg["launches"]
-            achieved = flops * (total_edges / max(msg["launches"], 1)) / per_launch_s / 1e12
+            achieved = flops * (local_edges / max(msg["launches"], 1)) / per_launch_s / 1e12  # rank 0's own launches
             roof = {"bound": "tensor", "kernel": "painn_message_tc_kernel" if tc_path else "painn_message_kernel", "achieved": achieved, "peak": tf_sus, "unit": "TFLOP/s",
                     "frac": achieved / tf_sus, "traffic": None, "peak_source": f"bf16_tflops_sustained, {how}",
                     "launches": msg["launches"], "avg_launch_ms": per_launch_s * 1e3,
