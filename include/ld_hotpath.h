@@ -58,6 +58,16 @@ int ld_radius_graph_fill(const float* pos, int batch, int nodes, int periodic, f
                          int open_cells_cap, void* workspace, size_t workspace_bytes, const int* row_ptr,
                          long long capacity, int* src, int* dst, int* shift, float* rij, int* status_dev, void* stream);
 
+/* Allocation-free variant (no counterpart in the reference, whose build allocates and frees three
+ * device buffers per call, neighbour_grid_kern.cu:174-176,220-222): count + fill in one call with the
+ * scratch space in a fixed 8 MiB device array inside the library, for callers that may not allocate
+ * device memory where they need the graph. Refuses larger problems with LD_ERR_WORKSPACE. The first
+ * call per device resolves the array's address and should precede any stream capture; calls that
+ * overlap on one device race on the shared array. */
+int ld_radius_graph_build_noalloc(const float* pos, int batch, int nodes, int periodic, float cutoff, const float* box,
+                                  int mode, int open_cells_cap, int* row_ptr, int* edge_counts, long long capacity,
+                                  int* src, int* dst, int* shift, float* rij, int* status_dev, void* stream);
+
 /* ---- edge <-> node movement -----------------------------------------------------------------
  * ld_segment_sum replaces torch_scatter.segment_coo at managan/graph_layers.py:54-59;
  * ld_gather_rows replaces the index reads of managan/graph_layers.py:37-52;

@@ -499,3 +499,77 @@ extern "C" int ld_radius_graph_fill(const float* pos, int batch, int nodes, int 
   LD_LAUNCH_CHECK();
   return LD_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free graph build.
+//
+// Some hosts of this library may not create device memory at the point where they need a
+// neighbour graph: a simulation engine that calls into a plugin from inside its time-step loop
+// with a fixed memory budget, a service whose allocator is frozen after start-up, or code that
+// runs between other stream-ordered work where an allocation would synchronise the device. For
+// them the scratch space of the build lives in the library image itself: a fixed array in device
+// memory that every GPU loading this library holds until the process exits.
+//
+// The array's name below is only a host-side handle. Kernels must be given its device address,
+// which is looked up once per device (with that device current) by cudaGetSymbolAddress.
+// ---------------------------------------------------------------------------------------------
+#include <mutex>
+
+#define LD_NOALLOC_SCRATCH_BYTES (8u << 20)   /* 8 MiB: about 130k nodes in total */
+static __device__ __align__(256) unsigned char g_noalloc_scratch[LD_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int LD_MAX_DEVICES = 64;
+void* g_noalloc_addr[LD_MAX_DEVICES] = {nullptr};
+std::mutex g_noalloc_mutex;
+
+// device address of the scratch array on the current device; set-up happens on the first call per device
+int noalloc_scratch_address(void** out) {
+  int dev = -1;
+  LD_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= LD_MAX_DEVICES) { ld_set_last_message("allocation-free build: device index out of range"); return LD_ERR_UNSUPPORTED; }
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_addr[dev] == nullptr) {
+    void* p = nullptr;
+    LD_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    if (p == nullptr) { ld_set_last_message("allocation-free build: scratch symbol has no device address"); return LD_ERR_CUDA; }
+    g_noalloc_addr[dev] = p;
+  }
+  *out = g_noalloc_addr[dev];
+  return LD_OK;
+}
+}  // namespace
+
+// Radius graph without any device allocation: count + fill in one call, scratch in a fixed 8 MiB
+// array inside the library. Arguments as ld_radius_graph_count / ld_radius_graph_fill; the caller
+// still owns row_ptr[batch*nodes+1], edge_counts[batch], the edge arrays of `capacity` entries
+// (shift and rij optional) and status_dev. Edges beyond `capacity` are not written and raise
+// LD_FLAG_CAPACITY in *status_dev.
+//  * Problems whose scratch need exceeds the array are refused with LD_ERR_WORKSPACE (nothing is
+//    launched); ld_radius_graph_workspace_size tells the need in advance.
+//  * The first call on each device looks up the array's device address (a host-side runtime call);
+//    make that first call before starting any stream capture.
+//  * All calls on a device share the one array and it keeps the previous call's contents; the
+//    counters that must start at zero are cleared by this call. Two builds that overlap in time on
+//    the same device (different streams or threads) race on it: serialise them.
+//  * Calls no cudaMalloc, cudaFree or other allocating routine.
+extern "C" int ld_radius_graph_build_noalloc(const float* pos, int batch, int nodes, int periodic, float cutoff,
+                                             const float* box, int mode, int open_cells_cap, int* row_ptr,
+                                             int* edge_counts, long long capacity, int* src, int* dst, int* shift,
+                                             float* rij, int* status_dev, void* stream) {
+  size_t need = 0;
+  int rc = ld_radius_graph_workspace_size(batch, nodes, periodic, cutoff, box, mode, open_cells_cap, &need);
+  if (rc != LD_OK) return rc;
+  if (need > (size_t)LD_NOALLOC_SCRATCH_BYTES) {
+    ld_set_last_message("allocation-free build: problem needs more than the 8 MiB built-in scratch; use ld_radius_graph_count/_fill with a caller workspace");
+    return LD_ERR_WORKSPACE;
+  }
+  void* scratch = nullptr;
+  rc = noalloc_scratch_address(&scratch);
+  if (rc != LD_OK) return rc;
+  rc = ld_radius_graph_count(pos, batch, nodes, periodic, cutoff, box, mode, open_cells_cap, scratch,
+                             (size_t)LD_NOALLOC_SCRATCH_BYTES, row_ptr, edge_counts, status_dev, stream);
+  if (rc != LD_OK) return rc;
+  return ld_radius_graph_fill(pos, batch, nodes, periodic, cutoff, box, mode, open_cells_cap, scratch,
+                              (size_t)LD_NOALLOC_SCRATCH_BYTES, row_ptr, capacity, src, dst, shift, rij, status_dev, stream);
+}

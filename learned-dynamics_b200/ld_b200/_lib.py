@@ -19,6 +19,7 @@ SIGNATURES = {
     "ld_radius_graph_workspace_size": [I, I, I, F, P, I, I, P],
     "ld_radius_graph_count": [P, I, I, I, F, P, I, I, P, SZ, P, P, P, P],
     "ld_radius_graph_fill": [P, I, I, I, F, P, I, I, P, SZ, P, LL, P, P, P, P, P, P],
+    "ld_radius_graph_build_noalloc": [P, I, I, I, F, P, I, I, P, P, LL, P, P, P, P, P, P],
     "ld_row_ptr_from_sorted": [P, I, LL, I, P, P],
     "ld_segment_sum": [P, P, I, I, P, P],
     "ld_gather_rows": [P, P, I, LL, I, P, P],
