@@ -48,6 +48,7 @@ struct TcMessageParams {
   int Nt, n, n_rbf, k0p, radial_kind;
   unsigned stage_off, bias_off;   // byte offsets of the weight ring and the bias copy in dynamic shared memory
   int nstages;                    // slabs in the weight ring
+  int seg_nodes;                  // nodes per scheduling segment (all blocks work on one segment at a time: L2 reuse)
   float rmax, pi_over_rmax, eps;
   const __nv_bfloat16* w1; const __nv_bfloat16* w2; const __nv_bfloat16* w3;  // packed panels [K/8][4n][8]
   const float* b1; const float* b2; const float* b3;
@@ -66,14 +67,31 @@ __device__ __forceinline__ int lb_row(const int* __restrict__ row_ptr, int lo, i
   return lo;
 }
 
-// first node v in [0, Nt] with row_ptr[v] + v >= target (work = edges + nodes before v)
-__device__ __forceinline__ int work_lower_bound(const int* __restrict__ row_ptr, int Nt, long long target) {
-  int lo = 0, hi = Nt;
+// first node v in [lo, hi] whose preceding work inside the segment, (edges + nodes) in [lo, v), reaches target
+__device__ __forceinline__ int work_lower_bound(const int* __restrict__ row_ptr, int lo, int hi, long long target) {
+  const long long base = (long long)row_ptr[lo] + lo;
   while (lo < hi) {
     int mid = (lo + hi) >> 1;
-    if ((long long)row_ptr[mid] + mid < target) lo = mid + 1; else hi = mid;
+    if ((long long)row_ptr[mid] + mid - base < target) lo = mid + 1; else hi = mid;
   }
   return lo;
+}
+
+struct BlockRange { int n_begin, n_end; long long e_begin, e_end, ntiles; };
+
+// node-aligned share of segment [seg_lo, seg_hi) for this block, balanced over edges + nodes
+// (nodes without edges still have to be written)
+__device__ __forceinline__ BlockRange block_range(const int* __restrict__ row_ptr, int seg_lo, int seg_hi, int tile) {
+  BlockRange r;
+  const long long work = ((long long)row_ptr[seg_hi] - row_ptr[seg_lo]) + (seg_hi - seg_lo);
+  long long per = (work + gridDim.x - 1) / gridDim.x;
+  if (per < tile) per = tile;
+  r.n_begin = blockIdx.x == 0 ? seg_lo : work_lower_bound(row_ptr, seg_lo, seg_hi, per * blockIdx.x);
+  r.n_end = blockIdx.x == gridDim.x - 1 ? seg_hi : work_lower_bound(row_ptr, seg_lo, seg_hi, per * (blockIdx.x + 1));
+  r.e_begin = r.n_begin < r.n_end ? row_ptr[r.n_begin] : 0;
+  r.e_end = r.n_begin < r.n_end ? row_ptr[r.n_end] : 0;
+  r.ntiles = (r.e_end - r.e_begin + tile - 1) / tile;
+  return r;
 }
 
 // barrier 1: working warps + MMA warp; returns the OR of `flag` over its participants
@@ -134,15 +152,7 @@ painn_message_tc_kernel(TcMessageParams P) {
   const uint32_t tmem_base = tmem_slot;
   const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
 
-  // node-aligned share, balanced over edges + nodes: nodes without edges still have to be written
-  const long long E = P.row_ptr[P.Nt];
-  long long per = (E + P.Nt + gridDim.x - 1) / gridDim.x;
-  if (per < MT_EDGES) per = MT_EDGES;
-  const int n_begin = blockIdx.x == 0 ? 0 : work_lower_bound(P.row_ptr, P.Nt, per * blockIdx.x);
-  const int n_end = blockIdx.x == gridDim.x - 1 ? P.Nt : work_lower_bound(P.row_ptr, P.Nt, per * (blockIdx.x + 1));
-  const long long e_begin = n_begin < n_end ? P.row_ptr[n_begin] : 0;
-  const long long e_end = n_begin < n_end ? P.row_ptr[n_end] : 0;
-  const long long ntiles = (e_end - e_begin + MT_EDGES - 1) / MT_EDGES;
+  const int seg_nodes = P.seg_nodes > 0 ? P.seg_nodes : P.Nt;
   const int k0steps = P.k0p / 16, ksteps = N / 16;
   const int npass = (n + MT_CG - 1) / MT_CG;
   long long pc[MT_PROF_SLOTS];
@@ -154,6 +164,8 @@ painn_message_tc_kernel(TcMessageParams P) {
     // ===== producer: weight slabs through the ring, independent of the data ==============================
     if (prod_lane) {
       uint32_t loads = 0;
+      for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
+      const long long ntiles = block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt), MT_EDGES).ntiles;
       for (long long t = 0; t < ntiles && !fail; t++) {
         for (int layer = 0; layer < 3 && !fail; layer++) {
           const __nv_bfloat16* wp = layer == 0 ? P.w1 : (layer == 1 ? P.w2 : P.w3);
@@ -169,6 +181,7 @@ painn_message_tc_kernel(TcMessageParams P) {
           }
         }
       }
+      }
       if (fail) {
         // copies already requested still land in this block's shared memory: give them a bounded chance
         for (uint32_t i = loads > nst ? loads - nst : 0; i < loads; i++)
@@ -179,6 +192,8 @@ painn_message_tc_kernel(TcMessageParams P) {
     // ===== MMA issue ========================================================================================
     uint32_t mmas = 0;
     const uint32_t a_base = tc::smem_u32(a_smem);
+    for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
+    const long long ntiles = block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt), MT_EDGES).ntiles;
     for (long long t = 0; t < ntiles; t++) {
       if (sync_or(fail)) { fail = 1; break; }      // [B1] geometry staged
       if (sync_or(fail)) { fail = 1; break; }      // [B2] first operand tile ready
@@ -212,15 +227,11 @@ painn_message_tc_kernel(TcMessageParams P) {
       if (fail) break;
       if (sync_or(fail)) { fail = 1; break; }      // [B6] tile finished: TMEM and A free again
     }
+    }
   } else {
     // ===== working warps =========================================================================================
     // reduction role: column `tid` of the staging tile = (channel tid/4 of the pass, component tid%4)
     const int red_c = (tid >> 2) & (MT_CG - 1), red_k = tid & 3;
-    float acc[MT_MAX_PASS] = {0.f, 0.f};
-    int cur = n_begin;
-    int node_lo = n_begin;  // source node of the next tile's first edge (or an earlier node)
-    if (tid <= MT_EDGES) s_rowwin[tid] = P.row_ptr[min(node_lo + tid, n_end > n_begin ? n_end : n_begin)];
-    sync_workers();
     long long tprev = clock64();
     auto lap = [&](int i) { const long long t = clock64(); pc[i] += t - tprev; tprev = t; };
     uint32_t accum_phase = 0;
@@ -243,6 +254,17 @@ painn_message_tc_kernel(TcMessageParams P) {
       }
     };
 
+    long long edges_done = 0;
+    for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
+    const BlockRange br = block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt), MT_EDGES);
+    const int n_begin = br.n_begin, n_end = br.n_end;
+    const long long e_begin = br.e_begin, e_end = br.e_end;
+    float acc[MT_MAX_PASS] = {0.f, 0.f};
+    int cur = n_begin;
+    int node_lo = n_begin;  // source node of the next tile's first edge (or an earlier node)
+    sync_workers();         // the previous segment's last readers of s_rowwin are done
+    if (tid <= MT_EDGES) s_rowwin[tid] = P.row_ptr[min(node_lo + tid, n_end > n_begin ? n_end : n_begin)];
+    sync_workers();
     for (long long e0 = e_begin; e0 < e_end; e0 += MT_EDGES) {
       const int cnt = (int)((e_end - e0) < MT_EDGES ? (e_end - e0) : MT_EDGES);
       // ---- 1. edge geometry ------------------------------------------------------------------------
@@ -435,8 +457,11 @@ painn_message_tc_kernel(TcMessageParams P) {
     }
     if (!fail && n_begin < n_end) {
       for (int pass = 0; pass < npass; pass++) flush_until(pass, cur, n_end, acc[pass]);
-      if (P.edge_counter != nullptr && tid == 0) atomicAdd((unsigned long long*)P.edge_counter, (unsigned long long)(e_end - e_begin));
+      edges_done += e_end - e_begin;
     }
+    }
+    if (!fail && P.edge_counter != nullptr && tid == 0 && edges_done > 0)
+      atomicAdd((unsigned long long*)P.edge_counter, (unsigned long long)edges_done);
   }
   if (P.prof != nullptr && (tid == 0 || mma_lane || prod_lane)) {
     for (int i = 0; i < MT_PROF_SLOTS; i++)
@@ -489,6 +514,12 @@ extern "C" int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, cons
   if (nstages < 2) return LD_ERR_UNSUPPORTED;
   const size_t ring = (size_t)nstages * slab;
   P.nstages = nstages;
+  // all blocks walk the node range segment by segment so that the gathered rows of a segment
+  // (28n bytes per node) stay resident in L2 while its edges are processed
+  {
+    const long long seg = (40LL << 20) / (28LL * n);
+    P.seg_nodes = (int)(seg < 1024 ? 1024 : seg);
+  }
   P.stage_off = (unsigned)front;
   P.bias_off = (unsigned)(front + ring);
   const size_t smem = front + ring + (size_t)3 * N * 4 + 1024;

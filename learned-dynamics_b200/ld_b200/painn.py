@@ -36,6 +36,7 @@ class MLP(nn.Module):
             nn.Linear(dim_in, dim_out), nn.SiLU(), nn.Linear(dim_out, dim_out), nn.SiLU(), nn.Linear(dim_out, dim_out))
         self._packed = None
         self._packed_key = None
+        self.precision = "fp32"  # "bf16": the three layers run as tcgen05 GEMMs (2e-2 relative)
 
     def packed(self):
         lin = (self.layers[0], self.layers[2], self.layers[4])
@@ -48,7 +49,13 @@ class MLP(nn.Module):
     def forward(self, x_a):
         if torch.is_grad_enabled() or not x_a.is_cuda:
             return self.layers(x_a)
-        return ops.mlp3_rows(x_a, self.packed(), ops.ACT_SILU)
+        mlp = self.packed()
+        if self.precision == "bf16" and all(d % 32 == 0 for d in mlp.dims[1:]):
+            w = ops._packed_bf16(mlp)
+            h = ops.linear_bf16_tc(x_a, w[0], mlp.dims[1], mlp.b[0], ops.ACT_SILU)
+            h = ops.linear_bf16_tc(h, w[1], mlp.dims[2], mlp.b[1], ops.ACT_SILU)
+            return ops.linear_bf16_tc(h, w[2], mlp.dims[3], mlp.b[2], ops.ACT_NONE)
+        return ops.mlp3_rows(x_a, mlp, ops.ACT_SILU)
 
 
 class ScalGroupNorm(nn.Module):
@@ -129,7 +136,7 @@ class Message(nn.Module):
         Nt = batch * atoms
         xa = x_a.reshape(Nt, n).contiguous()
         xv = x_v.reshape(Nt, n, 3).contiguous()
-        actv = ops.mlp3_rows(xa, self.mlp_actv.packed(), ops.ACT_SILU)
+        actv = self.mlp_actv(xa)
         fused = ops.painn_message_bf16_tc if self.precision == "bf16" else ops.painn_message_f32
         out_a, out_v = fused(
             graph.row_ptr, graph.dst32, r_ij.contiguous(), self.mlp_dist.packed(), actv, xv, rmax=self.r0,
@@ -280,7 +287,7 @@ def set_precision(module, precision):
     """"fp32" (default, 1e-5 parity) or "bf16" (tensor-core per-edge MLP, 2e-2) for every Message below `module`."""
     assert precision in ("fp32", "bf16")
     for m in module.modules():
-        if isinstance(m, Message):
+        if isinstance(m, (Message, MLP)):
             m.precision = precision
     return module
 

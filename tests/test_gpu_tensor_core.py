@@ -149,3 +149,27 @@ def test_message_tc_deterministic():
         a1, v1 = mine(graph, x_a, x_v, graph.rij)
         a2, v2 = mine(graph, x_a, x_v, graph.rij)
     assert torch.equal(a1, a2) and torch.equal(v1, v2)
+
+
+def test_denoiser_bf16_vs_oracle():
+    """whole denoiser with every Message and MLP on the tensor-core path, against the FP32 CPU oracle"""
+    from ld_b200 import painn
+    from oracle import reference_math as R
+    n, B, N, r0 = 128, 2, 60, 2.5
+    torch.manual_seed(5)
+    ref = R.OSE3ITO(r0, n, N, 4, 1, 2, 8, "gaussian")
+    mine = painn.SE3ITO(r0, n, N, 4, 1, 2, n_rbf=8, radial="gaussian")
+    mine.load_state_dict(ref.state_dict())
+    painn.set_precision(mine.cuda(), "bf16")
+    g = torch.Generator().manual_seed(78)
+    box = (8.0, 8.0, 9.0)
+    x0 = torch.rand(B, N, 3, generator=g) * torch.tensor(box)
+    x1 = x0 + 0.3 * torch.randn(B, N, 3, generator=g)
+    types = torch.randint(0, 4, (N,), generator=g)
+    s_, t_ = torch.full((B,), 0.2), torch.full((B,), 0.7)
+    empty = torch.zeros(0, dtype=torch.int64)
+    with torch.no_grad():
+        want = ref((s_, t_), x0, x1, box, types, empty, empty)
+        got = mine((s_.cuda(), t_.cuda()), x0.cuda(), x1.cuda(), box, types.cuda(), painn.empty_bond_graph(B, N, "cuda"))
+    _status_ok()
+    close(got, want, 2e-2)
