@@ -31,6 +31,8 @@ WORKLOADS = {
     "periodic_small_4x2048": dict(systems=4, nodes=2048, box=12.6, cutoff=4.0, n=128, n_rbf=8, radial="gaussian",
                                   blks=(1, 3), ntypes=4, sigma0=0.05, kind="periodic"),
 }
+# benchmark config 1: neighbour graph only (handled by run_graph_bench)
+WORKLOADS["graph_32x4096"] = dict(systems=32, nodes=4096, box=16.0, cutoff=2.5, kind="periodic", graph_only=True)
 DEFAULT_WORKLOAD = "periodic_rollout_16x8192"
 
 
@@ -151,6 +153,77 @@ def run_reference(args, w, rank, world):
     print(json.dumps(line))
 
 
+def run_graph_bench(args, w):
+    """Radius graph only (benchmark config 1): count + fill per step at a fixed capacity, no host sync."""
+    from ld_b200 import graph as G
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    box = (w["box"],) * 3
+    pos = make_positions(w, w["systems"], seed=1001).to(dev)
+    builder = G.RadiusGraphBuilder(w["systems"], w["nodes"], w["cutoff"], box, device=dev)
+    g = builder.build(pos, want_shift=True, want_rij=False)
+    E, Nt = g["E"], w["systems"] * w["nodes"]
+    src, dst, shift = torch.empty_like(g["src"]), torch.empty_like(g["dst"]), torch.empty_like(g["shift"])
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than L2
+
+    def step():
+        builder.build_fixed(pos, E, src, dst, shift, None)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    total_ms = 0.0
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step()
+        e1.record()
+        torch.cuda.synchronize()
+        total_ms += e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    assert int(builder.status.item()) == 0 and torch.equal(dst, g["dst"])
+    # end to end: host positions in, edge list out
+    pos_host = pos.cpu().pin_memory()
+    out_host = torch.empty(3 * E, dtype=torch.int32).pin_memory()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        p = pos_host.to(dev, non_blocking=True)
+        builder.build_fixed(p, E, src, dst, shift, None)
+        out_host[:E].copy_(src, non_blocking=True); out_host[E:2 * E].copy_(dst, non_blocking=True)
+        out_host[2 * E:].copy_(shift, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    t1.record()
+    torch.cuda.synchronize()
+    e2e_ms = t0.elapsed_time(t1)
+    hbm, _, _, how = peaks()
+    ms = total_ms / args.steps
+    alg_bytes = 12 * Nt + 4 * (Nt + 1) + 12 * E   # positions in, CSR offsets, (src, dst, packed shift) out
+    achieved = alg_bytes / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "graph_edges_per_sec", "value": E / (ms * 1e-3), "unit": "edges/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32/int32", "data": "synthetic",
+        "config": {"workload": args.workload, "systems": w["systems"], "nodes_per_system": w["nodes"], "box": w["box"],
+                   "cutoff": w["cutoff"], "edges": E, "l2_policy": "256 MB flush buffer written between timed iterations"},
+        "e2e": {"value": E * args.steps / (e2e_ms * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": Nt * 12, "d2h_bytes_per_step": 12 * E},
+        "gpu_launches": 14 * args.steps, "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "radius graph build (13 kernels; neighbour_kernel<0/1> dominate)", "achieved": achieved,
+                     "peak": hbm, "unit": "GB/s", "frac": achieved / hbm, "traffic": None, "peak_source": f"hbm_gbs, {how}"},
+    }
+    if not args.no_cpu_baseline:
+        from oracle import reference_math as R
+        t = time.perf_counter()
+        o = R.radius_graph(pos[:1].cpu(), w["cutoff"], box)
+        dt = time.perf_counter() - t
+        line["cpu_baseline"] = {"value": o["E"] / dt, "unit": "edges/s", "cores": 1, "kind": "port",
+                                "sample": f"1 system x {w['nodes']} particles, brute force over all pairs, {o['E']} edges in {dt:.1f} s"}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -167,6 +240,10 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if w.get("graph_only"):
+        if rank == 0:
+            run_graph_bench(args, w)
+        return
     if args.impl == "reference":
         run_reference(args, w, rank, world)
         return

@@ -213,7 +213,33 @@ __device__ __forceinline__ float torch_mod_wrap(float d, float box) {
 
 constexpr int NB_WARPS = 8;
 
+// minimum image of a difference of two wrapped coordinates, d in [-box, box]. Bit-identical to
+// remainderf(d, box) there: the quotient is -1, 0 or +1 (ties at +-box/2 go to the even quotient 0)
+// and d -+ box is exact (Sterbenz), so two compares replace the library routine.
+__device__ __forceinline__ float min_image(float d, float box, float half) {
+  if (d > half) return __fsub_rn(d, box);
+  if (d < -half) return __fadd_rn(d, box);
+  return d;
+}
+
+// ((d + 0.5*box) % box) - 0.5*box with torch's floor-mod; fast exact paths for |d + box/2| < 2*box
+__device__ __forceinline__ float torch_mod_wrap_fast(float d, float box, float half) {
+  const float t = __fadd_rn(d, half);
+  float m;
+  if (t >= 0.f && t < box) m = t;                                   // fmod(t, box) = t
+  else if (t >= box && t < __fadd_rn(box, box)) m = __fsub_rn(t, box);   // exact
+  else if (t < 0.f && t > -box) m = __fadd_rn(t, box);              // fmod = t (negative) then + box, as torch does
+  else {
+    m = fmodf(t, box);
+    if (m != 0.f && m < 0.f) m = __fadd_rn(m, box);
+  }
+  return __fsub_rn(m, half);
+}
+
 // One warp per particle (in cell order). FILL=false: degree per node. FILL=true: write the edges.
+// Candidates: the 3x3 neighbouring cell columns in (x, y); along z the cells cz-1, cz, cz+1 are
+// consecutive in the cell-sorted particle array, so each column is one contiguous run (two when it
+// wraps around the box): at most 18 runs, walked 32 candidates at a time.
 template <bool FILL>
 __global__ void __launch_bounds__(NB_WARPS * 32)
 neighbour_kernel(const float* __restrict__ pos, GraphParams P, const GridDesc* __restrict__ desc,
@@ -221,8 +247,6 @@ neighbour_kernel(const float* __restrict__ pos, GraphParams P, const GridDesc* _
                  const int* __restrict__ sorted_cell, int* __restrict__ degree, const int* __restrict__ row_ptr,
                  long long capacity, int* __restrict__ src, int* __restrict__ dst, int* __restrict__ shift,
                  float* __restrict__ rij, int* __restrict__ status) {
-  __shared__ int s_excl[NB_WARPS][32];
-  __shared__ int s_start[NB_WARPS][32];
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int s = blockIdx.x * NB_WARPS + w;
   const int total = P.batch * P.nodes;
@@ -236,38 +260,41 @@ neighbour_kernel(const float* __restrict__ pos, GraphParams P, const GridDesc* _
   const int cz = lc % g.nz;
   const int cy = (lc / g.nz) % g.ny;
   const int cx = lc / (g.nz * g.ny);
+  const float hx = __fmul_rn(0.5f, P.bx), hy = __fmul_rn(0.5f, P.by), hz = __fmul_rn(0.5f, P.bz);
 
-  // lanes 0..26 each own one neighbouring cell
-  int len = 0, start = 0;
-  if (lane < 27) {
-    const int dx = lane / 9 - 1, dy = (lane / 3) % 3 - 1, dz = lane % 3 - 1;
-    int ncx = cx + dx, ncy = cy + dy, ncz = cz + dz;
-    bool ok = true;
-    if (P.periodic) {
-      // with fewer than 3 cells on an axis the offsets {-1,0,1} would visit a cell twice
-      if (g.nx < 3) ok = ok && (dx >= 0) && (dx < g.nx);
-      if (g.ny < 3) ok = ok && (dy >= 0) && (dy < g.ny);
-      if (g.nz < 3) ok = ok && (dz >= 0) && (dz < g.nz);
-      ncx = (ncx + g.nx) % g.nx; ncy = (ncy + g.ny) % g.ny; ncz = (ncz + g.nz) % g.nz;
-    } else {
-      ok = ncx >= 0 && ncx < g.nx && ncy >= 0 && ncy < g.ny && ncz >= 0 && ncz < g.nz;
-    }
-    if (ok) {
-      const int nc = b * P.cells_cap + (ncx * g.ny + ncy) * g.nz + ncz;
-      start = cell_start[nc];
-      len = cell_start[nc + 1] - start;
+  // lanes 0..8: (dx, dy) column, first run; lanes 16..24: same column, second run (z wrap-around)
+  int run_start = 0, run_len = 0;
+  {
+    const int col = lane & 15;
+    const bool second = lane >= 16;
+    if (col < 9) {
+      const int dx = col / 3 - 1, dy = col % 3 - 1;
+      int ncx = cx + dx, ncy = cy + dy;
+      bool ok = true;
+      int z_lo, z_hi;  // inclusive range of cz offsets handled by this run, in unwrapped cell units
+      if (P.periodic) {
+        // with fewer than 3 cells on an axis the offsets {-1,0,1} would visit a cell twice
+        if (g.nx < 3) ok = ok && (dx >= 0) && (dx < g.nx);
+        if (g.ny < 3) ok = ok && (dy >= 0) && (dy < g.ny);
+        ncx = (ncx + g.nx) % g.nx; ncy = (ncy + g.ny) % g.ny;
+        if (g.nz < 3) { z_lo = 0; z_hi = g.nz - 1; ok = ok && !second; }   // the whole column, once
+        else {
+          const int lo = cz - 1, hi = cz + 1;
+          if (lo >= 0 && hi < g.nz) { z_lo = lo; z_hi = hi; ok = ok && !second; }
+          else if (lo < 0) { if (!second) { z_lo = 0; z_hi = hi; } else { z_lo = g.nz - 1; z_hi = g.nz - 1; } }
+          else { if (!second) { z_lo = lo; z_hi = g.nz - 1; } else { z_lo = 0; z_hi = 0; } }
+        }
+      } else {
+        ok = ncx >= 0 && ncx < g.nx && ncy >= 0 && ncy < g.ny && !second;
+        z_lo = max(cz - 1, 0); z_hi = min(cz + 1, g.nz - 1);
+      }
+      if (ok) {
+        const int base_cell = b * P.cells_cap + (ncx * g.ny + ncy) * g.nz;
+        run_start = cell_start[base_cell + z_lo];
+        run_len = cell_start[base_cell + z_hi + 1] - run_start;
+      }
     }
   }
-  int incl = len;
-#pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    int t = __shfl_up_sync(0xffffffffu, incl, d);
-    if (lane >= d) incl += t;
-  }
-  const int T = __shfl_sync(0xffffffffu, incl, 31);
-  s_excl[w][lane] = incl - len;
-  s_start[w][lane] = start;
-  __syncwarp();
 
   const int node = b * P.nodes + idx;
   long long base = 0;
@@ -278,57 +305,57 @@ neighbour_kernel(const float* __restrict__ pos, GraphParams P, const GridDesc* _
     xi = p[0]; yi = p[1]; zi = p[2];
   }
   int found = 0;
-  for (int k0 = 0; k0 < T; k0 += 32) {
-    const int k = k0 + lane;
-    bool hit = false;
-    int jdx = 0;
-    if (k < T) {
-      // largest r with excl[r] <= k
-      int r = 0;
-#pragma unroll
-      for (int step = 16; step > 0; step >>= 1) {
-        if (s_excl[w][r + step] <= k) r += step;
+  unsigned live = __ballot_sync(0xffffffffu, run_len > 0);
+  while (live) {
+    const int r = __ffs(live) - 1;
+    live &= live - 1;
+    const int rs = __shfl_sync(0xffffffffu, run_start, r);
+    const int rl = __shfl_sync(0xffffffffu, run_len, r);
+    for (int k0 = 0; k0 < rl; k0 += 32) {
+      const int k = k0 + lane;
+      bool hit = false;
+      int jdx = 0;
+      if (k < rl) {
+        const float4 q = __ldg(&sorted[rs + k]);
+        jdx = __float_as_int(q.w);
+        float dx = __fsub_rn(me.x, q.x), dy = __fsub_rn(me.y, q.y), dz = __fsub_rn(me.z, q.z);
+        if (P.periodic) { dx = min_image(dx, P.bx, hx); dy = min_image(dy, P.by, hy); dz = min_image(dz, P.bz, hz); }
+        const float d2 = __fmaf_rn(dz, dz, __fmaf_rn(dy, dy, __fmul_rn(dx, dx)));
+        hit = (jdx != idx) && (d2 <= P.rc2);
       }
-      const float4 q = sorted[s_start[w][r] + (k - s_excl[w][r])];
-      jdx = __float_as_int(q.w);
-      float dx = __fsub_rn(me.x, q.x), dy = __fsub_rn(me.y, q.y), dz = __fsub_rn(me.z, q.z);
-      if (P.periodic) {
-        dx = remainderf(dx, P.bx); dy = remainderf(dy, P.by); dz = remainderf(dz, P.bz);
-      }
-      const float d2 = __fmaf_rn(dz, dz, __fmaf_rn(dy, dy, __fmul_rn(dx, dx)));
-      hit = (jdx != idx) && (d2 <= P.rc2);
-    }
-    const unsigned bal = __ballot_sync(0xffffffffu, hit);
-    if (FILL) {
-      if (hit) {
-        const long long e = base + found + __popc(bal & ((1u << lane) - 1));
-        if (e < capacity) {
-          const int nj = b * P.nodes + jdx;
-          src[e] = node;
-          dst[e] = nj;
-          if (rij != nullptr || shift != nullptr) {
-            const float* pj = pos + (size_t)nj * 3;
-            float ddx = __fsub_rn(pj[0], xi), ddy = __fsub_rn(pj[1], yi), ddz = __fsub_rn(pj[2], zi);
-            if (shift != nullptr) {
-              int sx = 0, sy = 0, sz = 0;
-              if (P.periodic) {
-                sx = -(int)floorf(__fdiv_rn(__fadd_rn(ddx, __fmul_rn(0.5f, P.bx)), P.bx));
-                sy = -(int)floorf(__fdiv_rn(__fadd_rn(ddy, __fmul_rn(0.5f, P.by)), P.by));
-                sz = -(int)floorf(__fdiv_rn(__fadd_rn(ddz, __fmul_rn(0.5f, P.bz)), P.bz));
+      const unsigned bal = __ballot_sync(0xffffffffu, hit);
+      if (FILL) {
+        if (hit) {
+          const long long e = base + found + __popc(bal & ((1u << lane) - 1));
+          if (e < capacity) {
+            const int nj = b * P.nodes + jdx;
+            src[e] = node;
+            dst[e] = nj;
+            if (rij != nullptr || shift != nullptr) {
+              const float* pj = pos + (size_t)nj * 3;
+              float ddx = __fsub_rn(__ldg(pj), xi), ddy = __fsub_rn(__ldg(pj + 1), yi), ddz = __fsub_rn(__ldg(pj + 2), zi);
+              if (shift != nullptr) {
+                int sx = 0, sy = 0, sz = 0;
+                if (P.periodic) {
+                  sx = -(int)floorf(__fdiv_rn(__fadd_rn(ddx, hx), P.bx));
+                  sy = -(int)floorf(__fdiv_rn(__fadd_rn(ddy, hy), P.by));
+                  sz = -(int)floorf(__fdiv_rn(__fadd_rn(ddz, hz), P.bz));
+                }
+                shift[e] = (sx & 0xff) | ((sy & 0xff) << 8) | ((sz & 0xff) << 16);
               }
-              shift[e] = (sx & 0xff) | ((sy & 0xff) << 8) | ((sz & 0xff) << 16);
-            }
-            if (rij != nullptr) {
-              if (P.periodic) {
-                ddx = torch_mod_wrap(ddx, P.bx); ddy = torch_mod_wrap(ddy, P.by); ddz = torch_mod_wrap(ddz, P.bz);
+              if (rij != nullptr) {
+                if (P.periodic) {
+                  ddx = torch_mod_wrap_fast(ddx, P.bx, hx); ddy = torch_mod_wrap_fast(ddy, P.by, hy);
+                  ddz = torch_mod_wrap_fast(ddz, P.bz, hz);
+                }
+                rij[e * 3 + 0] = ddx; rij[e * 3 + 1] = ddy; rij[e * 3 + 2] = ddz;
               }
-              rij[e * 3 + 0] = ddx; rij[e * 3 + 1] = ddy; rij[e * 3 + 2] = ddz;
             }
           }
         }
       }
+      found += __popc(bal);
     }
-    found += __popc(bal);
   }
   if (!FILL) {
     if (lane == 0) degree[node] = found;

@@ -39,7 +39,8 @@ def _noalloc_build(pos, cutoff, box, capacity):
                                          shift.data_ptr(), rij.data_ptr(), status.data_ptr(),
                                          torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated() == before
+    # no growth; the caching allocator may release blocks of earlier tests meanwhile, so not '=='
+    assert torch.cuda.memory_allocated() <= before
     return rc, row_ptr, counts, src, dst, shift, rij, status
 
 
