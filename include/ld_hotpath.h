@@ -137,6 +137,22 @@ int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, const float* ri
                              const float* res_v, float* out_a, float* out_v, long long* edge_counter, int* status_dev,
                              void* stream);
 
+/* ---- fused l<=2 message layer ------------------------------------------------------------------------
+ * Messages.forward (archs/diffuser_atoms15.py:227-253) without edge-sized tensors: the radial
+ * read-in (managan/jacobi_radenc.py:27-33), the Bee products (managan/codegen_tensor_products.py:64-75)
+ * and edges_reduce_src (managan/graph_layers.py:54-59) in one pass over the CSR.
+ * _vd: per-node sums of the five rank-1 and five rank-2 products (the Y maps are linear, so the
+ * caller applies them per node with ld_tensor_linear over 5*chan inputs). _scalar: per-edge Y maps
+ * and mlp_a, summed per node. `jacobi` = 8x9 coefficients of the shifted Jacobi(1,0) polynomials. */
+int ld_bee_messages_vd_f32(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, float r0, const float* L0,
+                           const float* L1, const float* L2, const float* enc_w, const float* enc_b, const float* jacobi,
+                           float scale, float* S_v, float* S_d, void* stream);
+int ld_bee_messages_scalar_f32(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, int dim_a, float r0,
+                               const float* L0, const float* L1, const float* L2, const float* enc_w, const float* enc_b,
+                               const float* jacobi, const float* Yt, const float* W1t, const float* b1, const float* W2t,
+                               const float* b2, const float* W3t, const float* b3, const float* Wdt, float scale,
+                               float* out_a, void* stream);
+
 /* Diagnostics (no counterpart in the reference): per-phase cycle counters of the fused tensor-core
  * kernel, added into 16 device int64 by later launches; NULL switches them off. */
 int ld_debug_set_phase_counters(long long* device_buffer16);

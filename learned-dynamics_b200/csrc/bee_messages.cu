@@ -1,0 +1,335 @@
+// l<=2 ("Bee") message layer, fused: Messages.forward of the reference
+// (archs/diffuser_atoms15.py:227-253) without edge-sized tensors in HBM.
+//
+//   phi_a = lin_enc(radial_encode_8(r_ij))                      (managan/jacobi_radenc.py:27-33)
+//   rhat  = tens_sigmoid(1, r_ij * 7/r0)                        (managan/tensor_products.py:167-182)
+//   phi_v = phi_a (x) rhat,  phi_d = phi_a (x) rhat (x) rhat
+//   y_k   = Bee(L0(x_a)[dst], L1(x_v)[dst], L2(x_d)[dst]; phi_a, phi_v, phi_d)   13 products / channel
+//   psi_a = Y_000 y_000 + Y_110 y_110 + Y_220 y_220 ; psi_a += mlp_a(psi_a)      per edge
+//   psi_v = sum of five Y_k y_k (rank 1), psi_d = sum of five Y_k y_k (rank 2)   per edge
+//   B_*   = 0.1 * sum over the edges of each source node
+//
+// The rank-1 and rank-2 outputs are linear in the products, and the edge sum is linear, so the
+// ten products are summed per node first (ld_bee_messages_vd_f32: one thread per channel, sixty
+// accumulators in registers, one write per node) and the Y maps then run once per NODE as an
+// ordinary channel mixing over 5*chan inputs. Only the scalar output has a per-edge non-linearity
+// (mlp_a); ld_bee_messages_scalar_f32 keeps that per edge, in 32-edge tiles in shared memory.
+// Both kernels walk node-aligned slices of the CSR; no atomics, fixed summation order.
+#include "common.cuh"
+#include "mlp_tile.cuh"
+#include "tp_math.h"
+
+namespace {
+
+constexpr int BM_TILE = 32;  // edges staged per step
+
+struct BeeEdgeParams {
+  const int* row_ptr; const int* dst; const float* rij;
+  int Nt, chan;
+  float r0;
+  const float* L0; const float* L1; const float* L2;   // [Nt,chan], [Nt,chan,3], [Nt,chan,9]
+  const float* enc_w; const float* enc_b;               // lin_enc: [chan,8], [chan]
+  const float* jacobi;                                  // [8][9] polynomial coefficients
+};
+
+// first node v in [lo, hi] whose preceding work (edges + nodes) reaches target
+__device__ __forceinline__ int bm_work_lower_bound(const int* __restrict__ row_ptr, int lo, int hi, long long target) {
+  const long long base = (long long)row_ptr[lo] + lo;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if ((long long)row_ptr[mid] + mid - base < target) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ void bm_block_range(const int* __restrict__ row_ptr, int Nt, int* n_begin, int* n_end) {
+  const long long work = (long long)row_ptr[Nt] + Nt;
+  long long per = (work + gridDim.x - 1) / gridDim.x;
+  if (per < 1) per = 1;
+  *n_begin = blockIdx.x == 0 ? 0 : bm_work_lower_bound(row_ptr, 0, Nt, per * blockIdx.x);
+  *n_end = blockIdx.x == gridDim.x - 1 ? Nt : bm_work_lower_bound(row_ptr, 0, Nt, per * (blockIdx.x + 1));
+}
+
+// per-edge geometry shared by all channels: rhat[3] and the eight radial features
+struct EdgeGeom { float rhat[3]; float enc[8]; };
+
+__device__ __forceinline__ void edge_geometry(const float* __restrict__ rij, long long e, float r0,
+                                              const float* __restrict__ jac, EdgeGeom* g) {
+  const float x = rij[e * 3], y = rij[e * 3 + 1], z = rij[e * 3 + 2];
+  const float d = sqrtf(x * x + y * y + z * z);
+  const float zz = d / r0;
+  float pw[9];
+  pw[0] = 1.f;
+#pragma unroll
+  for (int p = 1; p < 9; p++) pw[p] = pw[p - 1] * zz;
+  const float env = fmaxf(1.f - zz, 0.f);
+#pragma unroll
+  for (int m = 0; m < 8; m++) {
+    float a = 0.f;
+#pragma unroll
+    for (int p = 0; p < 9; p++) a = fmaf(pw[p], jac[m * 9 + p], a);
+    g->enc[m] = a * env;
+  }
+  const float s = 7.f / r0;
+  const float ux = x * s, uy = y * s, uz = z * s;
+  const float inv = 1.0f / sqrtf(1.f + ux * ux + uy * uy + uz * uz);
+  g->rhat[0] = ux * inv; g->rhat[1] = uy * inv; g->rhat[2] = uz * inv;
+}
+
+// the right-hand operands of one channel: phi_a scalar, phi_v = phi_a rhat, phi_d = phi_a rhat rhat^T
+__device__ __forceinline__ void edge_phi(const EdgeGeom& g, const float* w8, float bias, float* pa, float* pv, float* pd) {
+  float a = bias;
+#pragma unroll
+  for (int m = 0; m < 8; m++) a = fmaf(g.enc[m], w8[m], a);
+  *pa = a;
+#pragma unroll
+  for (int k = 0; k < 3; k++) pv[k] = a * g.rhat[k];
+#pragma unroll
+  for (int x = 0; x < 3; x++)
+#pragma unroll
+    for (int y = 0; y < 3; y++) pd[x * 3 + y] = a * g.rhat[x] * g.rhat[y];
+}
+
+
+// ---- rank-1 / rank-2 products summed per node --------------------------------------------------
+// S_v[node][k][c][3], k over (011,101,121,211,111); S_d[node][k][c][9], k over (022,202,112,222,212):
+// the layouts a channel mixing with 5*chan inputs expects. Thread = channel; a block walks its nodes
+// and stages the geometry of up to 32 edges at a time in shared memory.
+__global__ void __launch_bounds__(128)
+bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d, float scale) {
+  __shared__ EdgeGeom s_geom[BM_TILE];
+  __shared__ int s_dst[BM_TILE];
+  __shared__ float s_jac[72];
+  for (int i = threadIdx.x; i < 72; i += blockDim.x) s_jac[i] = P.jacobi[i];
+  __syncthreads();
+  int n_begin, n_end;
+  bm_block_range(P.row_ptr, P.Nt, &n_begin, &n_end);
+  const int C = P.chan;
+  for (int c0 = 0; c0 < C; c0 += blockDim.x) {   // channel groups (one pass when chan <= 128)
+    const int c = c0 + threadIdx.x;
+    const bool cok = c < C;
+    float w8[8], wb = 0.f;
+#pragma unroll
+    for (int m = 0; m < 8; m++) w8[m] = cok ? P.enc_w[c * 8 + m] : 0.f;
+    if (cok) wb = P.enc_b[c];
+    for (int v = n_begin; v < n_end; v++) {
+      float av[15], ad[45];
+#pragma unroll
+      for (int i = 0; i < 15; i++) av[i] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 45; i++) ad[i] = 0.f;
+      const int e_lo = P.row_ptr[v], e_hi = P.row_ptr[v + 1];
+      for (int eb = e_lo; eb < e_hi; eb += BM_TILE) {
+        const int cnt = min(BM_TILE, e_hi - eb);
+        __syncthreads();  // previous tile's readers are done
+        if (threadIdx.x < cnt) {
+          edge_geometry(P.rij, (long long)eb + threadIdx.x, P.r0, s_jac, &s_geom[threadIdx.x]);
+          s_dst[threadIdx.x] = P.dst[eb + threadIdx.x];
+        }
+        __syncthreads();
+        if (cok) {
+          for (int t = 0; t < cnt; t++) {
+            const size_t j = (size_t)s_dst[t] * C + c;
+            float l1[3], l2[9], pa, pv[3], pd[9];
+            const float l0 = __ldg(P.L0 + j);
+#pragma unroll
+            for (int k = 0; k < 3; k++) l1[k] = __ldg(P.L1 + j * 3 + k);
+#pragma unroll
+            for (int k = 0; k < 9; k++) l2[k] = __ldg(P.L2 + j * 9 + k);
+            edge_phi(s_geom[t], w8, wb, &pa, pv, pd);
+            BeeOut o;
+            bee_fwd_point(l0, l1, l2, pa, pv, pd, &o);
+#pragma unroll
+            for (int k = 0; k < 3; k++) {
+              av[k] += o.y011[k]; av[3 + k] += o.y101[k]; av[6 + k] += o.y121[k]; av[9 + k] += o.y211[k]; av[12 + k] += o.y111[k];
+            }
+#pragma unroll
+            for (int k = 0; k < 9; k++) {
+              ad[k] += o.y022[k]; ad[9 + k] += o.y202[k]; ad[18 + k] += o.y112[k]; ad[27 + k] += o.y222[k]; ad[36 + k] += o.y212[k];
+            }
+          }
+        }
+      }
+      if (cok) {
+        float* sv = S_v + (size_t)v * 5 * C * 3;
+        float* sd = S_d + (size_t)v * 5 * C * 9;
+#pragma unroll
+        for (int k = 0; k < 5; k++) {
+#pragma unroll
+          for (int x = 0; x < 3; x++) sv[((size_t)k * C + c) * 3 + x] = av[k * 3 + x] * scale;
+#pragma unroll
+          for (int x = 0; x < 9; x++) sd[((size_t)k * C + c) * 9 + x] = ad[k * 9 + x] * scale;
+        }
+      }
+    }
+  }
+}
+
+
+// ---- scalar output: per-edge Y maps and mlp_a, then per-node sum -------------------------------------
+struct BeeScalarParams {
+  BeeEdgeParams g;
+  int dim_a;
+  const float* Yt;                       // [3*chan][dim_a]: (Y_000 | Y_110 | Y_220) transposed
+  const float* W1t; const float* b1;     // mlp_a layers, transposed [in][out]
+  const float* W2t; const float* b2;
+  const float* W3t; const float* b3;
+  const float* Wdt;                      // lin_direct, transposed [dim_a][dim_a]
+  float scale;
+  float* out_a;                          // [Nt, dim_a]
+};
+
+constexpr int BM_LDH = 36;  // row stride of the product tile: 16-byte aligned rows, 4-way instead of 32-way store conflicts
+
+template <int NCOL>
+__global__ void __launch_bounds__(MT_THREADS, 1)
+bee_scalar_kernel(BeeScalarParams P) {
+  extern __shared__ __align__(16) float smem[];
+  __shared__ EdgeGeom s_geom[BM_TILE];
+  __shared__ int s_dst[BM_TILE];
+  __shared__ int s_src[BM_TILE];
+  __shared__ float s_jac[72];
+  const int C = P.g.chan, A = P.dim_a, tid = threadIdx.x;
+  float* hin = smem;                                   // [3C][36]
+  float* psi = hin + (size_t)3 * C * BM_LDH;           // [A][32]
+  float* bufA = psi + (size_t)A * MT_ROWS;             // [2A][32], later row-major [32][A+1]
+  float* bufB = bufA + (size_t)2 * A * MT_ROWS;        // [2A][32]
+  float* wstage = bufB + (size_t)2 * A * MT_ROWS;      // 2 x 16 x 2A
+  const int ldo = A + 1;
+  for (int i = tid; i < 72; i += MT_THREADS) s_jac[i] = P.g.jacobi[i];
+  int n_begin, n_end;
+  bm_block_range(P.g.row_ptr, P.g.Nt, &n_begin, &n_end);
+  if (n_begin >= n_end) return;
+  const long long e_begin = P.g.row_ptr[n_begin], e_end = P.g.row_ptr[n_end];
+  __syncthreads();
+
+  // per-node sum: thread o < A owns output channel o
+  float acc = 0.f;
+  int cur = n_begin;
+  auto flush_until = [&](int next) {
+    if (tid < A)
+      for (int v = cur; v < next; v++) P.out_a[(size_t)v * A + tid] = (v == cur ? acc : 0.f) * P.scale;
+    acc = 0.f;
+    cur = next;
+  };
+
+  for (long long e0 = e_begin; e0 < e_end; e0 += BM_TILE) {
+    const int cnt = (int)((e_end - e0) < BM_TILE ? (e_end - e0) : BM_TILE);
+    if (tid < BM_TILE) {
+      int j = 0, sN = -1;
+      if (tid < cnt) {
+        const long long e = e0 + tid;
+        edge_geometry(P.g.rij, e, P.g.r0, s_jac, &s_geom[tid]);
+        j = P.g.dst[e];
+        int lo = n_begin, hi = n_end;   // largest v with row_ptr[v] <= e
+        while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if ((long long)P.g.row_ptr[mid] <= e) lo = mid; else hi = mid; }
+        sN = lo;
+      }
+      s_dst[tid] = j;
+      s_src[tid] = sN;
+    }
+    __syncthreads();
+    // scalar products of every (channel, edge): all lanes of a warp read the same neighbour row
+    for (int it = tid; it < 2 * C; it += MT_THREADS) {
+      const int c = it % C, h = it / C;
+      const float wb = P.g.enc_b[c];
+      float w8[8];
+#pragma unroll
+      for (int m = 0; m < 8; m++) w8[m] = P.g.enc_w[c * 8 + m];
+      for (int t = h; t < BM_TILE; t += 2) {
+        float y0 = 0.f, y1 = 0.f, y2 = 0.f;
+        if (t < cnt) {
+          const size_t j = (size_t)s_dst[t] * C + c;
+          float pa, pv[3], pd[9];
+          edge_phi(s_geom[t], w8, wb, &pa, pv, pd);
+          y0 = __ldg(P.g.L0 + j) * pa;
+#pragma unroll
+          for (int k = 0; k < 3; k++) y1 = fmaf(__ldg(P.g.L1 + j * 3 + k), pv[k], y1);
+#pragma unroll
+          for (int k = 0; k < 9; k++) y2 = fmaf(__ldg(P.g.L2 + j * 9 + k), pd[k], y2);
+        }
+        hin[(size_t)c * BM_LDH + t] = y0;
+        hin[(size_t)(C + c) * BM_LDH + t] = y1;
+        hin[(size_t)(2 * C + c) * BM_LDH + t] = y2;
+      }
+    }
+    __syncthreads();
+    mt_tile_linear<NCOL, false>(hin, 3 * C, P.Yt, nullptr, A, LD_ACT_NONE, psi, 0, wstage, BM_LDH);
+    mt_tile_linear<NCOL, false>(psi, A, P.W1t, P.b1, 2 * A, LD_ACT_LEAKY01, bufA, 0, wstage);
+    mt_tile_linear<NCOL, false>(bufA, 2 * A, P.W2t, P.b2, 2 * A, LD_ACT_LEAKY01, bufB, 0, wstage);
+    mt_tile_linear<NCOL, true>(bufB, 2 * A, P.W3t, P.b3, A, LD_ACT_NONE, bufA, ldo, wstage);
+    // psi + lin_direct(psi) + layers(psi)
+    for (int idx = tid; idx < MT_ROWS * A; idx += MT_THREADS) {
+      const int r = idx / A, c = idx - r * A;
+      float a = psi[(size_t)c * MT_ROWS + r];
+      for (int k = 0; k < A; k++) a = fmaf(psi[(size_t)k * MT_ROWS + r], __ldg(P.Wdt + (size_t)k * A + c), a);
+      bufA[(size_t)r * ldo + c] += a;
+    }
+    __syncthreads();
+    if (tid < A) {
+      for (int t = 0; t < cnt; t++) {
+        const int sN = s_src[t];
+        if (sN != cur) flush_until(sN);
+        acc += bufA[(size_t)t * ldo + tid];
+      }
+    } else {
+      // keep `cur` in step for threads that own no output (uniform control flow is not required, but cheap)
+      if (cnt > 0) cur = s_src[cnt - 1];
+    }
+    __syncthreads();
+  }
+  flush_until(n_end);
+}
+
+}  // namespace
+
+// Per-node sums of the ten rank-1 / rank-2 Bee products of a Messages layer, times `scale`.
+// S_v: [Nt, 5*chan, 3] (product order 011,101,121,211,111), S_d: [Nt, 5*chan, 3, 3] (022,202,112,222,212).
+// L0/L1/L2 are the node-level left operands, enc_w [chan,8] / enc_b [chan] the radial read-in,
+// jacobi the 8x9 coefficient matrix of the radial basis. Graph in CSR form sorted by source.
+extern "C" int ld_bee_messages_vd_f32(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, float r0,
+                                      const float* L0, const float* L1, const float* L2, const float* enc_w,
+                                      const float* enc_b, const float* jacobi, float scale, float* S_v, float* S_d,
+                                      void* stream) {
+  if (Nt < 0 || chan <= 0 || !(r0 > 0.f)) return LD_ERR_SHAPE;
+  if (Nt == 0) return LD_OK;
+  BeeEdgeParams P{row_ptr, dst, rij, Nt, chan, r0, L0, L1, L2, enc_w, enc_b, jacobi};
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  bee_vd_kernel<<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}
+
+// Scalar output of a Messages layer: out_a[node] = scale * sum_e (psi_e + mlp_a(psi_e)),
+// psi_e = [y_000 | y_110 | y_220] Y^T. Yt: [3*chan][dim_a]; mlp_a = lin_direct + (a -> 2a -> 2a -> a,
+// LeakyReLU(0.1)), weights transposed [in][out]. dim_a a multiple of 8, at most 256.
+extern "C" int ld_bee_messages_scalar_f32(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, int dim_a,
+                                          float r0, const float* L0, const float* L1, const float* L2, const float* enc_w,
+                                          const float* enc_b, const float* jacobi, const float* Yt, const float* W1t,
+                                          const float* b1, const float* W2t, const float* b2, const float* W3t,
+                                          const float* b3, const float* Wdt, float scale, float* out_a, void* stream) {
+  if (Nt < 0 || chan <= 0 || dim_a <= 0 || !(r0 > 0.f)) return LD_ERR_SHAPE;
+  if (dim_a % 8 != 0 || dim_a > 256) { ld_set_last_message("bee messages: dim_a must be a multiple of 8, at most 256"); return LD_ERR_UNSUPPORTED; }
+  if ((((uintptr_t)Yt | (uintptr_t)W1t | (uintptr_t)W2t | (uintptr_t)W3t) % 16) != 0) return LD_ERR_SHAPE;
+  if (Nt == 0) return LD_OK;
+  BeeScalarParams P;
+  P.g = BeeEdgeParams{row_ptr, dst, rij, Nt, chan, r0, L0, L1, L2, enc_w, enc_b, jacobi};
+  P.dim_a = dim_a; P.Yt = Yt; P.W1t = W1t; P.b1 = b1; P.W2t = W2t; P.b2 = b2; P.W3t = W3t; P.b3 = b3; P.Wdt = Wdt;
+  P.scale = scale; P.out_a = out_a;
+  const size_t floats = (size_t)3 * chan * BM_LDH + (size_t)dim_a * MT_ROWS + (size_t)4 * dim_a * MT_ROWS +
+                        (size_t)2 * MT_KC * 2 * dim_a;
+  const size_t smem = floats * 4 + 256;
+  if (smem > 220 * 1024) { ld_set_last_message("bee messages: shared-memory plan exceeds the limit (chan or dim_a too large)"); return LD_ERR_UNSUPPORTED; }
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (2 * dim_a <= 256) {
+    LD_CUDA_TRY(cudaFuncSetAttribute(bee_scalar_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    bee_scalar_kernel<1><<<sms, MT_THREADS, smem, (cudaStream_t)stream>>>(P);
+  } else {
+    LD_CUDA_TRY(cudaFuncSetAttribute(bee_scalar_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    bee_scalar_kernel<2><<<sms, MT_THREADS, smem, (cudaStream_t)stream>>>(P);
+  }
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}

@@ -41,13 +41,13 @@ __device__ __forceinline__ void mt_stage_weights(float* dst, const float* __rest
 }
 
 // hout = act(hin * Wt + bias) for one 32-row tile.
-//   hin  : shared, k-major [K][32]
+//   hin  : shared, k-major [K][ldh] (ldh >= 32, multiple of 4; default 32)
 //   hout : shared; ROW_MAJOR_OUT ? [32][ldo] : k-major [N][32]
 //   wstage : shared, 2 * MT_KC * N floats
 // Requires N % 8 == 0 and N <= 256 * NCOL. Ends with __syncthreads().
 template <int NCOL, bool ROW_MAJOR_OUT>
 __device__ void mt_tile_linear(const float* hin, int K, const float* __restrict__ Wt, const float* __restrict__ bias, int N,
-                               int act, float* hout, int ldo, float* wstage) {
+                               int act, float* hout, int ldo, float* wstage, int ldh = MT_ROWS) {
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cpw = N >> 3;  // columns per warp
   int col[NCOL];
@@ -80,7 +80,7 @@ __device__ void mt_tile_linear(const float* hin, int K, const float* __restrict_
     __syncthreads();
     for (int kk = 0; kk < kc; kk++) {
       float a[MT_ROWS];
-      const float4* ap = reinterpret_cast<const float4*>(hin + (size_t)(k0 + kk) * MT_ROWS);
+      const float4* ap = reinterpret_cast<const float4*>(hin + (size_t)(k0 + kk) * ldh);
 #pragma unroll
       for (int q = 0; q < MT_ROWS / 4; q++) {
         const float4 v = ap[q];

@@ -1,0 +1,146 @@
+"""l<=2 ("Bee"-path) message layer on the fused kernels.
+
+Mirrors Messages of archs/diffuser_atoms15.py:227-253 (and its helpers MLP :98-110,
+add_tens_prod_submodules :29-42, apply_tens_prod_submodules :52-57, radial_encode_8 of
+managan/jacobi_radenc.py:8-37) with the reference's parameter names. Without autograd the layer
+runs as: three node-level channel mixings (L0, L1, L2), one pass over the edges for the rank-1/2
+products summed per node, one pass for the scalar channel (per-edge Y maps + mlp_a), and two
+node-level channel mixings for the hoisted Y maps. With autograd it runs the reference's op
+sequence on this library's Bee / TensLinear / gather / segment-sum functions."""
+from math import comb
+
+import torch
+import torch.nn as nn
+
+from . import ops
+from ._lib import lib, check, ptr, stream_ptr, KERNEL_TIMER
+from .codegen_tensor_products import Bee
+from .graph_layers import edges_read_dst, edges_reduce_src
+from .tensor_products import TensLinear, tens_sigmoid
+
+V_ORDER = ("011", "101", "121", "211", "111")
+D_ORDER = ("022", "202", "112", "222", "212")
+
+
+def jacobi_matrix(dim=8):
+    """Coefficients (ascending powers of x) of the shifted Jacobi(1,0) polynomials on [0,1]:
+    P_n(x) = sum_s C(n+1, n-s) C(n, s) (x-1)^s x^(n-s); exact integers, as the reference's sympy expansion."""
+    A = torch.zeros(dim, dim + 1)
+    for n in range(dim):
+        coeffs = [0] * (n + 1)
+        for s in range(n + 1):
+            w = comb(n + 1, n - s) * comb(n, s)
+            for t in range(s + 1):
+                coeffs[n - s + t] += w * comb(s, t) * (-1) ** (s - t)
+        for j, c in enumerate(coeffs):
+            A[n, j] = float(c)
+    return A
+
+
+def radial_encode_8(r, rmax):
+    """r: (..., 3) -> (..., 8)"""
+    A = jacobi_matrix(8).to(r.device)
+    z = (torch.linalg.vector_norm(r, dim=-1) / rmax)[..., None]
+    pows = z ** torch.arange(A.shape[1], device=r.device)
+    return torch.nn.functional.linear(pows, A) * torch.relu(1. - z)
+
+
+class MLP(nn.Module):
+    def __init__(self, dim_a):
+        super().__init__()
+        self.lin_direct = nn.Linear(dim_a, dim_a, bias=False)
+        self.layers = nn.Sequential(
+            nn.Linear(dim_a, 2 * dim_a), nn.LeakyReLU(0.1), nn.Linear(2 * dim_a, 2 * dim_a), nn.LeakyReLU(0.1),
+            nn.Linear(2 * dim_a, dim_a))
+
+    def forward(self, x):
+        return self.lin_direct(x) + self.layers(x)
+
+
+class Messages(nn.Module):
+    def __init__(self, r0, dim_a, dim_v, dim_d, chan):
+        super().__init__()
+        self.r0, self.dim_a, self.dim_v, self.dim_d, self.chan = r0, dim_a, dim_v, dim_d, chan
+        self.L0 = TensLinear(0, dim_a, chan)
+        self.L1 = TensLinear(1, dim_v, chan)
+        self.L2 = TensLinear(2, dim_d, chan)
+        for name in ("000", "110", "220"):
+            setattr(self, "Y_" + name, TensLinear(0, chan, dim_a))
+        for name in V_ORDER:
+            setattr(self, "Y_" + name, TensLinear(1, chan, dim_v))
+        for name in D_ORDER:
+            setattr(self, "Y_" + name, TensLinear(2, chan, dim_d))
+        self.lin_enc = nn.Linear(8, chan)
+        self.mlp_a = MLP(dim_a)
+        self._packed = None
+        self._packed_key = None
+
+    def load_state_dict(self, state, *a, **k):
+        # the reference wraps mlp_a in torch.compile, which prefixes its keys
+        state = {key.replace("mlp_a._orig_mod.", "mlp_a."): v for key, v in state.items()}
+        return super().load_state_dict(state, *a, **k)
+
+    def _pack(self):
+        key = tuple((p.data_ptr(), p._version) for p in self.parameters())
+        if self._packed_key != key:
+            dev = self.lin_enc.weight.device
+            f = lambda t: t.detach().float().contiguous()
+            lay = self.mlp_a.layers
+            self._packed = {
+                "jac": jacobi_matrix(8).to(dev).contiguous(),
+                "enc_w": f(self.lin_enc.weight), "enc_b": f(self.lin_enc.bias),
+                "Yt": f(torch.cat([self.Y_000.W, self.Y_110.W, self.Y_220.W], dim=1).t()),
+                "Yv": f(torch.cat([getattr(self, "Y_" + n).W for n in V_ORDER], dim=1)),
+                "Yd": f(torch.cat([getattr(self, "Y_" + n).W for n in D_ORDER], dim=1)),
+                "W1t": f(lay[0].weight.t()), "b1": f(lay[0].bias), "W2t": f(lay[2].weight.t()), "b2": f(lay[2].bias),
+                "W3t": f(lay[4].weight.t()), "b3": f(lay[4].bias), "Wdt": f(self.mlp_a.lin_direct.weight.t()),
+            }
+            self._packed_key = key
+        return self._packed
+
+    def forward(self, graph, r_ij, x_a, x_v, x_d):
+        if torch.is_grad_enabled() or not x_a.is_cuda:
+            return self._forward_unfused(graph, r_ij, x_a, x_v, x_d)
+        batch, nodes = x_a.shape[0], x_a.shape[1]
+        Nt, C, dev = batch * nodes, self.chan, x_a.device
+        w = self._pack()
+        l0 = self.L0(x_a.reshape(Nt, -1))
+        l1 = self.L1(x_v.reshape(Nt, -1, 3))
+        l2 = self.L2(x_d.reshape(Nt, -1, 3, 3))
+        rij = r_ij.contiguous()
+        S_v = torch.empty(Nt, 5 * C, 3, dtype=torch.float32, device=dev)
+        S_d = torch.empty(Nt, 5 * C, 3, 3, dtype=torch.float32, device=dev)
+        B_a = torch.empty(Nt, self.dim_a, dtype=torch.float32, device=dev)
+        st = stream_ptr(dev)
+        with KERNEL_TIMER.region("bee_messages_vd"):
+            check(lib().ld_bee_messages_vd_f32(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, float(self.r0), ptr(l0),
+                                               ptr(l1), ptr(l2), ptr(w["enc_w"]), ptr(w["enc_b"]), ptr(w["jac"]), 0.1,
+                                               ptr(S_v), ptr(S_d), st))
+        with KERNEL_TIMER.region("bee_messages_scalar"):
+            check(lib().ld_bee_messages_scalar_f32(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, self.dim_a,
+                                                   float(self.r0), ptr(l0), ptr(l1), ptr(l2), ptr(w["enc_w"]), ptr(w["enc_b"]),
+                                                   ptr(w["jac"]), ptr(w["Yt"]), ptr(w["W1t"]), ptr(w["b1"]), ptr(w["W2t"]),
+                                                   ptr(w["b2"]), ptr(w["W3t"]), ptr(w["b3"]), ptr(w["Wdt"]), 0.1, ptr(B_a), st))
+        B_v = ops.tensor_linear(1, w["Yv"], S_v)
+        B_d = ops.tensor_linear(2, w["Yd"], S_d)
+        return (B_a.reshape(batch, nodes, -1), B_v.reshape(batch, nodes, -1, 3), B_d.reshape(batch, nodes, -1, 3, 3))
+
+    def _forward_unfused(self, graph, r_ij, x_a, x_v, x_d):
+        rad_enc_ij = self.lin_enc(radial_encode_8(r_ij, self.r0))
+        r = tens_sigmoid(1, r_ij * (7. / self.r0))
+        phi_a = rad_enc_ij
+        phi_v = rad_enc_ij[..., None] * r[..., None, :]
+        phi_d = rad_enc_ij[..., None, None] * r[..., None, None, :] * r[..., None, :, None]
+        x_a_j = edges_read_dst(graph, self.L0(x_a))
+        x_v_j = edges_read_dst(graph, self.L1(x_v))
+        x_d_j = edges_read_dst(graph, self.L2(x_d))
+        (y_000, y_110, y_220, y_011, y_101, y_121, y_211, y_022, y_202, y_112, y_222, y_111, y_212) = Bee.apply(
+            x_a_j, x_v_j, x_d_j, phi_a.contiguous(), phi_v.contiguous(), phi_d.contiguous())
+        psi_a = self.Y_000(y_000) + self.Y_110(y_110) + self.Y_220(y_220)
+        psi_v = self.Y_011(y_011) + self.Y_101(y_101) + self.Y_121(y_121) + self.Y_211(y_211) + self.Y_111(y_111)
+        psi_d = self.Y_022(y_022) + self.Y_202(y_202) + self.Y_112(y_112) + self.Y_222(y_222) + self.Y_212(y_212)
+        psi_a = psi_a + self.mlp_a(psi_a)
+        B_a = edges_reduce_src(graph, psi_a)
+        B_v = edges_reduce_src(graph, psi_v)
+        B_d = edges_reduce_src(graph, psi_d)
+        return 0.1 * B_a, 0.1 * B_v, 0.1 * B_d

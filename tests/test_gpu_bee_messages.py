@@ -1,0 +1,55 @@
+"""Fused l<=2 message layer against the reference's own Messages output (tests/golden) and against
+the unfused op sequence on the same GPU. FP32; the radial basis is a degree-7 polynomial with
+cancelling coefficients of order 1e3, so the bar is 1e-4 relative (max-norm) here."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def close(a, b, rel):
+    a, b = a.detach().cpu().double(), b.detach().cpu().double()
+    assert a.shape == b.shape
+    err = (a - b).abs().max().item()
+    scale = max(b.abs().max().item(), 1e-30)
+    assert err <= rel * scale, f"max abs err {err:.3e} vs scale {scale:.3e} (rel {err / scale:.2e})"
+
+
+def test_messages_against_reference_golden(golden):
+    from ld_b200 import bee, graph_layers as GL
+    p, m = golden["painn"], golden["bee_messages"]
+    da, dv, dd, chan = m["dims"]
+    mes = bee.Messages(p["r0"], da, dv, dd, chan)
+    mes.load_state_dict(m["state"])
+    mes.cuda()
+    B, N = m["x_a"].shape[:2]
+    graph = GL.Graph(p["src"].cuda(), p["dst"].cuda(), None, B, N)
+    args = (graph, p["r_ij"].cuda(), m["x_a"].cuda(), m["x_v"].cuda(), m["x_d"].cuda())
+    with torch.no_grad():
+        fused = mes(*args)
+    unfused = mes._forward_unfused(*args)
+    for got, ref, want in zip(fused, unfused, m["out"]):
+        close(ref, want, 1e-4)
+        close(got, want, 1e-4)
+
+
+@pytest.mark.parametrize("dims,B,N,r0,box", [((128, 64, 32, 128), 2, 200, 3.0, (9.0, 9.0, 9.5)), ((64, 32, 16, 96), 3, 50, 5.0, None),
+                                             ((32, 8, 8, 32), 1, 6, 1.0, None)])
+def test_messages_fused_vs_unfused(dims, B, N, r0, box):
+    """benchmark config 2 widths (128, 64, 32, chan 128) in the first row"""
+    from ld_b200 import bee, graph_layers as GL
+    torch.manual_seed(sum(dims))
+    mes = bee.Messages(r0, *dims).cuda()
+    g = torch.Generator().manual_seed(7)
+    if box is None:
+        pos = torch.cumsum(torch.randn(B, N, 3, generator=g) / 3 ** 0.5, dim=1)
+    else:
+        pos = torch.rand(B, N, 3, generator=g) * torch.tensor(box)
+    da, dv, dd, _ = dims
+    x_a, x_v, x_d = torch.randn(B, N, da, generator=g), torch.randn(B, N, dv, 3, generator=g), torch.randn(B, N, dd, 3, 3, generator=g)
+    with torch.no_grad():
+        graph = GL.Graph.radius_graph(r0, box, pos.cuda())
+        fused = mes(graph, graph.rij, x_a.cuda(), x_v.cuda(), x_d.cuda())
+    unfused = mes._forward_unfused(graph, graph.rij, x_a.cuda(), x_v.cuda(), x_d.cuda())
+    for got, ref in zip(fused, unfused):
+        close(got, ref, 1e-4)
