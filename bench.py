@@ -31,6 +31,12 @@ WORKLOADS = {
     "periodic_small_4x2048": dict(systems=4, nodes=2048, box=12.6, cutoff=4.0, n=128, n_rbf=8, radial="gaussian",
                                   blks=(1, 3), ntypes=4, sigma0=0.05, kind="periodic"),
 }
+# benchmark configs 4 and 2 with the l<=2 (scalar / vector / rank-2) denoiser: 6 layers, (128, 64, 32) channels,
+# 128 product channels, cutoff 5.0, 20 bead types; radial read-in = the reference's 8 Jacobi functions
+WORKLOADS["polymers_l2_1024x256"] = dict(systems=1024, nodes=256, box=None, cutoff=5.0, model="bee", dims=(128, 64, 32, 128),
+                                         depth=6, ntypes=20, sigma0=0.05, kind="polymer")
+WORKLOADS["polymers_l2_64x512"] = dict(systems=64, nodes=512, box=None, cutoff=5.0, model="bee", dims=(128, 64, 32, 128),
+                                       depth=6, ntypes=20, sigma0=0.05, kind="polymer")
 # benchmark config 1: neighbour graph only (handled by run_graph_bench)
 WORKLOADS["graph_32x4096"] = dict(systems=32, nodes=4096, box=16.0, cutoff=2.5, kind="periodic", graph_only=True)
 DEFAULT_WORKLOAD = "periodic_rollout_16x8192"
@@ -96,6 +102,12 @@ def message_flops_per_edge(n, n_rbf):
 def build_model(w, device):
     from ld_b200 import painn
     torch.manual_seed(1234)
+    if w.get("model") == "bee":
+        from ld_b200 import bee
+        dn = bee.BeeDenoiser(w["cutoff"], *w["dims"], ntypes=w["ntypes"], depth=w["depth"]).to(device)
+        with torch.no_grad():
+            dn.readout.W.mul_(1e-3)  # small velocity read-out: a random-init rollout stays in the input distribution
+        return dn
     dn = painn.SE3ITO(w["cutoff"], w["n"], w["nodes"], w["ntypes"], w["blks"][0], w["blks"][1], n_rbf=w["n_rbf"],
                       radial=w["radial"]).to(device)
     return dn
@@ -109,6 +121,20 @@ def cpu_reference_rate(w, threads, budget_nodes=1024, steps=1):
     torch.set_num_threads(threads)
     nodes = min(budget_nodes, w["nodes"])
     torch.manual_seed(1234)
+    if w.get("model") == "bee":
+        systems = max(1, budget_nodes // w["nodes"])
+        dn = R.OBeeDenoiser(w["cutoff"], *w["dims"], ntypes=w["ntypes"], depth=w["depth"])
+        with torch.no_grad():
+            dn.readout.W.mul_(1e-3)
+        g = torch.Generator().manual_seed(4321)
+        x = torch.cumsum(torch.randn(systems, w["nodes"], 3, generator=g) / 3 ** 0.5, dim=1)
+        types = torch.randint(0, w["ntypes"], (w["nodes"],), generator=g)
+        edges, t0 = 0, time.perf_counter()
+        for _ in range(steps):
+            x = dn.generate(x, torch.randn(x.shape, generator=g), w["sigma0"], None, types)
+            edges += dn.edges_last
+        dt = time.perf_counter() - t0
+        return edges / dt, f"{systems} system(s) x {w['nodes']} nodes, {steps} step(s), {edges} edge-messages in {dt:.1f} s"
     dn = R.OSE3ITO(w["cutoff"], w["n"], nodes, w["ntypes"], w["blks"][0], w["blks"][1], w["n_rbf"], w["radial"])
     g = torch.Generator().manual_seed(4321)
     if w["kind"] == "periodic":
@@ -259,10 +285,14 @@ def main():
     per = sys_end - sys_begin
     box = None if w["box"] is None else (w["box"],) * 3
 
-    dn = painn.set_precision(build_model(w, dev), args.precision)
+    is_bee = w.get("model") == "bee"
+    if is_bee:
+        args.precision = "fp32"  # the l<=2 layers run on the FP32 kernels so far
+    dn = build_model(w, dev) if is_bee else painn.set_precision(build_model(w, dev), args.precision)
     types = torch.randint(0, w["ntypes"], (w["nodes"],), generator=torch.Generator().manual_seed(99)).to(dev)
-    bond = painn.chain_bond_graph(per, w["nodes"], dev) if w["kind"] == "polymer" else painn.empty_bond_graph(per, w["nodes"], dev)
-    mf = painn.Meanflow(dn, box, w["sigma0"], types, bond)
+    if not is_bee:
+        bond = painn.chain_bond_graph(per, w["nodes"], dev) if w["kind"] == "polymer" else painn.empty_bond_graph(per, w["nodes"], dev)
+        mf = painn.Meanflow(dn, box, w["sigma0"], types, bond)
     x_all = make_positions(w, w["systems"], seed=1003)
     x_host = x_all[sys_begin:sys_end].contiguous().pin_memory()
     out_host = torch.empty_like(x_host).pin_memory()
@@ -271,6 +301,8 @@ def main():
 
     def device_step(x):
         noise = torch.randn(x.shape, generator=noise_gen, device=dev)
+        if is_bee:
+            return dn.generate(x, noise, w["sigma0"], box, types, counter)
         return mf.generate(x, noise, counter)
 
     def barrier():
@@ -332,13 +364,18 @@ def main():
         value = total_edges / (total_ms * 1e-3)
         e2e_value = int(edges2.item()) / (ms2.item() * 1e-3)
         tc_path = args.precision == "bf16"
-        msg = ktimes.get("painn_message_tc" if tc_path else "painn_message", {"launches": 0, "ms": 0.0})
-        flops = message_flops_per_edge(w["n"], w["n_rbf"])
+        if is_bee:
+            da, _, _, ch = w["dims"]
+            msg = ktimes.get("bee_messages_scalar", {"launches": 0, "ms": 0.0})
+            flops = 2 * (3 * ch * da + 9 * da * da)  # per-edge Y maps + mlp_a of the scalar channel
+        else:
+            msg = ktimes.get("painn_message_tc" if tc_path else "painn_message", {"launches": 0, "ms": 0.0})
+            flops = message_flops_per_edge(w["n"], w["n_rbf"])
         roof = None
         if msg["launches"]:
             per_launch_s = msg["ms"] * 1e-3 / msg["launches"]
             achieved = flops * (local_edges / max(msg["launches"], 1)) / per_launch_s / 1e12  # rank 0's own launches
-            roof = {"bound": "tensor", "kernel": "painn_message_tc_kernel" if tc_path else "painn_message_kernel", "achieved": achieved, "peak": tf_sus, "unit": "TFLOP/s",
+            roof = {"bound": "tensor", "kernel": "bee_scalar_kernel" if is_bee else ("painn_message_tc_kernel" if tc_path else "painn_message_kernel"), "achieved": achieved, "peak": tf_sus, "unit": "TFLOP/s",
                     "frac": achieved / tf_sus, "traffic": None, "peak_source": f"bf16_tflops_sustained, {how}",
                     "launches": msg["launches"], "avg_launch_ms": per_launch_s * 1e3,
                     "note": ("tcgen05 BF16 MMAs of the per-edge distance MLP (algorithmic flops: 2*(n_rbf*4n + 2*(4n)^2) per edge)"
@@ -348,8 +385,9 @@ def main():
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16" if tc_path else "f32", "data": "synthetic",
             "config": {"workload": args.workload, "precision": args.precision, "systems": w["systems"], "nodes_per_system": w["nodes"], "cutoff": w["cutoff"],
-                       "width": w["n"], "radial_basis": w["n_rbf"], "message_layers_per_step": 2 * sum(w["blks"]),
-                       "graph_rebuilds_per_step": 2, "edges_per_step": total_edges // args.steps,
+                       "width": w["dims"] if is_bee else w["n"], "radial_basis": 8 if is_bee else w["n_rbf"],
+                       "message_layers_per_step": w["depth"] if is_bee else 2 * sum(w["blks"]),
+                       "graph_rebuilds_per_step": 1 if is_bee else 2, "edges_per_step": total_edges // args.steps,
                        "l2_policy": "inputs larger than L2 (per-step node features and gathers exceed 126 MB)"},
             "dt_steps_per_sec": args.steps / (total_ms * 1e-3),
             "system_steps_per_sec": args.steps * w["systems"] / (total_ms * 1e-3),

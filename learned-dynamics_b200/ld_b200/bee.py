@@ -144,3 +144,85 @@ class Messages(nn.Module):
         B_v = edges_reduce_src(graph, psi_v)
         B_d = edges_reduce_src(graph, psi_d)
         return 0.1 * B_a, 0.1 * B_v, 0.1 * B_d
+
+
+class SelfTensProds(nn.Module):
+    """Node-local tensor products (archs/diffuser_atoms15.py:59-95): left/right channel mixings,
+    the 13 Bee products, the Y maps and a group norm per rank."""
+
+    def __init__(self, dim_a, dim_v, dim_d, chan, groups=8):
+        super().__init__()
+        from .tensor_products import TensGroupNorm
+        self.L0, self.R0 = TensLinear(0, dim_a, chan), TensLinear(0, dim_a, chan)
+        self.L1, self.R1 = TensLinear(1, dim_v, chan), TensLinear(1, dim_v, chan)
+        self.L2, self.R2 = TensLinear(2, dim_d, chan), TensLinear(2, dim_d, chan)
+        for name in ("000", "110", "220"):
+            setattr(self, "Y_" + name, TensLinear(0, chan, dim_a))
+        for name in V_ORDER:
+            setattr(self, "Y_" + name, TensLinear(1, chan, dim_v))
+        for name in D_ORDER:
+            setattr(self, "Y_" + name, TensLinear(2, chan, dim_d))
+        self.gn_a = TensGroupNorm(0, dim_a, groups)
+        self.gn_v = TensGroupNorm(1, dim_v, groups)
+        self.gn_d = TensGroupNorm(2, dim_d, groups)
+
+    def forward(self, x_a, x_v, x_d):
+        rest = x_a.shape[:-1]
+        n = 1
+        for d in rest:
+            n *= d
+        xa, xv, xd = x_a.reshape(n, -1), x_v.reshape(n, -1, 3), x_d.reshape(n, -1, 3, 3)
+        y = Bee.apply(self.L0(xa), self.L1(xv), self.L2(xd), self.R0(xa), self.R1(xv), self.R2(xd))
+        (y_000, y_110, y_220, y_011, y_101, y_121, y_211, y_022, y_202, y_112, y_222, y_111, y_212) = y
+        y_a = self.Y_000(y_000) + self.Y_110(y_110) + self.Y_220(y_220)
+        y_v = self.Y_011(y_011) + self.Y_101(y_101) + self.Y_121(y_121) + self.Y_211(y_211) + self.Y_111(y_111)
+        y_d = self.Y_022(y_022) + self.Y_202(y_202) + self.Y_112(y_112) + self.Y_222(y_222) + self.Y_212(y_212)
+        return (self.gn_a(y_a.reshape(*rest, -1)), self.gn_v(y_v.reshape(*rest, -1, 3)), self.gn_d(y_d.reshape(*rest, -1, 3, 3)))
+
+
+class BeeBlock(nn.Module):
+    """One l<=2 layer: neighbour messages then node-local products, both residual."""
+
+    def __init__(self, r0, dim_a, dim_v, dim_d, chan):
+        super().__init__()
+        self.messages = Messages(r0, dim_a, dim_v, dim_d, chan)
+        self.prods = SelfTensProds(dim_a, dim_v, dim_d, chan)
+
+    def forward(self, graph, r_ij, x_a, x_v, x_d):
+        d_a, d_v, d_d = self.messages(graph, r_ij, x_a, x_v, x_d)
+        x_a, x_v, x_d = x_a + d_a, x_v + d_v, x_d + d_d
+        d_a, d_v, d_d = self.prods(x_a, x_v, x_d)
+        return x_a + d_a, x_v + d_v, x_d + d_d
+
+
+class BeeDenoiser(nn.Module):
+    """Meanflow-style denoiser with scalar, vector and rank-2 channels: the model the benchmark
+    configs 2 and 4 describe (type embedding -> `depth` l<=2 layers on the radius graph of the
+    noised positions -> vector read-out), built from the reference's Messages / SelfTensProds
+    layers (archs/diffuser_atoms15.py) and the read-in / read-out of archs/meanflow_painn8.py:185-217."""
+
+    def __init__(self, r0, dim_a, dim_v, dim_d, chan, ntypes, depth):
+        super().__init__()
+        self.r0, self.dim_d = r0, dim_d
+        self.type_embed = nn.Embedding(ntypes, dim_a)
+        self.v_readin = TensLinear(1, 1, dim_v)
+        self.blocks = nn.ModuleList([BeeBlock(r0, dim_a, dim_v, dim_d, chan) for _ in range(depth)])
+        self.readout = TensLinear(1, dim_v, 1)
+
+    def forward(self, x0, x1, box, types, counter=None):
+        from .graph_layers import Graph
+        batch, nodes, _ = x0.shape
+        graph = Graph.radius_graph(self.r0, box, x1.contiguous())
+        x_a = self.type_embed(types)[None].expand(batch, -1, -1).contiguous()
+        x_v = self.v_readin((x1 - x0)[..., None, :].contiguous())
+        x_d = torch.zeros(batch, nodes, self.dim_d, 3, 3, device=x0.device)
+        for blk in self.blocks:
+            x_a, x_v, x_d = blk(graph, graph.rij, x_a, x_v, x_d)
+        if counter is not None:
+            counter += graph.src.numel() * len(self.blocks)
+        return self.readout(x_v).squeeze(-2)
+
+    @torch.no_grad()
+    def generate(self, x_0, noise, sigma_0, box, types, counter=None):
+        z_1 = x_0 + sigma_0 * noise
+        return z_1 - self.forward(x_0, z_1, box, types, counter)

@@ -387,3 +387,151 @@ def chain_bonds(batch, nodes):
 def avg_relative_diff(a, b):
     """managan/utils.py:45-52, the reference's comparison metric"""
     return (torch.abs(a - b) / torch.sqrt(0.0001 + 0.5 * (a ** 2 + b ** 2))).mean().item()
+
+
+# ---- l<=2 ("Bee"-path) layers -------------------------------------------------------------------
+V_ORDER = ("011", "101", "121", "211", "111")
+D_ORDER = ("022", "202", "112", "222", "212")
+
+
+def _add_y_maps(mod, dim_a, dim_v, dim_d, chan):
+    """archs/diffuser_atoms15.py:29-42"""
+    for name in ("000", "110", "220"):
+        setattr(mod, "Y_" + name, OTensLinear(0, chan, dim_a))
+    for name in V_ORDER:
+        setattr(mod, "Y_" + name, OTensLinear(1, chan, dim_v))
+    for name in D_ORDER:
+        setattr(mod, "Y_" + name, OTensLinear(2, chan, dim_d))
+
+
+def _apply_y_maps(mod, prods):
+    """archs/diffuser_atoms15.py:52-57"""
+    y_000, y_110, y_220, y_011, y_101, y_121, y_211, y_022, y_202, y_112, y_222, y_111, y_212 = prods
+    y_0 = mod.Y_000(y_000) + mod.Y_110(y_110) + mod.Y_220(y_220)
+    y_1 = mod.Y_011(y_011) + mod.Y_101(y_101) + mod.Y_121(y_121) + mod.Y_211(y_211) + mod.Y_111(y_111)
+    y_2 = mod.Y_022(y_022) + mod.Y_202(y_202) + mod.Y_112(y_112) + mod.Y_222(y_222) + mod.Y_212(y_212)
+    return y_0, y_1, y_2
+
+
+class OBeeMLP(nn.Module):
+    """archs/diffuser_atoms15.py:98-110"""
+
+    def __init__(self, dim_a):
+        super().__init__()
+        self.lin_direct = nn.Linear(dim_a, dim_a, bias=False)
+        self.layers = nn.Sequential(nn.Linear(dim_a, 2 * dim_a), nn.LeakyReLU(0.1), nn.Linear(2 * dim_a, 2 * dim_a),
+                                    nn.LeakyReLU(0.1), nn.Linear(2 * dim_a, dim_a))
+
+    def forward(self, x):
+        return self.lin_direct(x) + self.layers(x)
+
+
+class OTensGroupNorm(nn.Module):
+    """managan/tensor_products.py:215-232"""
+
+    def __init__(self, inds, chan, groups, epsilon=1e-5):
+        super().__init__()
+        self.inds, self.chan, self.groups, self.epsilon = inds, chan, groups, epsilon
+        self.gamma = nn.Parameter(torch.ones(chan, *[1] * inds))
+
+    def forward(self, x):
+        batch, nodes = x.shape[0], x.shape[1]
+        xg = x.reshape(batch, nodes, self.groups, -1, 3 ** self.inds)
+        moment2 = (xg ** 2).sum(-1, keepdim=True).mean([1, 3], keepdim=True)
+        ans = xg / torch.sqrt(self.epsilon + moment2)
+        return self.gamma * ans.reshape(batch, nodes, self.chan, *[3] * self.inds)
+
+
+class OMessages(nn.Module):
+    """archs/diffuser_atoms15.py:227-253"""
+
+    def __init__(self, r0, dim_a, dim_v, dim_d, chan):
+        super().__init__()
+        self.r0 = r0
+        self.L0, self.L1, self.L2 = OTensLinear(0, dim_a, chan), OTensLinear(1, dim_v, chan), OTensLinear(2, dim_d, chan)
+        _add_y_maps(self, dim_a, dim_v, dim_d, chan)
+        self.lin_enc = nn.Linear(8, chan)
+        self.mlp_a = OBeeMLP(dim_a)
+
+    def forward(self, src, dst, r_ij, x_a, x_v, x_d):
+        batch, nodes = x_a.shape[:2]
+        Nt = batch * nodes
+        rad = self.lin_enc(radial_encode_8(r_ij, self.r0))
+        r = tens_sigmoid(1, r_ij * (7. / self.r0))
+        phi_a = rad
+        phi_v = rad[..., None] * r[..., None, :]
+        phi_d = rad[..., None, None] * r[..., None, None, :] * r[..., None, :, None]
+        j = dst.long()
+        x_a_j = self.L0(x_a).reshape(Nt, -1)[j]
+        x_v_j = self.L1(x_v).reshape(Nt, -1, 3)[j]
+        x_d_j = self.L2(x_d).reshape(Nt, -1, 3, 3)[j]
+        psi_a, psi_v, psi_d = _apply_y_maps(self, bee(x_a_j, x_v_j, x_d_j, phi_a, phi_v, phi_d))
+        psi_a = psi_a + self.mlp_a(psi_a)
+        B_a = edges_reduce_src(src, psi_a, Nt).reshape(batch, nodes, -1)
+        B_v = edges_reduce_src(src, psi_v, Nt).reshape(batch, nodes, -1, 3)
+        B_d = edges_reduce_src(src, psi_d, Nt).reshape(batch, nodes, -1, 3, 3)
+        return 0.1 * B_a, 0.1 * B_v, 0.1 * B_d
+
+
+class OSelfTensProds(nn.Module):
+    """archs/diffuser_atoms15.py:59-95"""
+
+    def __init__(self, dim_a, dim_v, dim_d, chan, groups=8):
+        super().__init__()
+        self.L0, self.R0 = OTensLinear(0, dim_a, chan), OTensLinear(0, dim_a, chan)
+        self.L1, self.R1 = OTensLinear(1, dim_v, chan), OTensLinear(1, dim_v, chan)
+        self.L2, self.R2 = OTensLinear(2, dim_d, chan), OTensLinear(2, dim_d, chan)
+        _add_y_maps(self, dim_a, dim_v, dim_d, chan)
+        self.gn_a, self.gn_v, self.gn_d = OTensGroupNorm(0, dim_a, groups), OTensGroupNorm(1, dim_v, groups), OTensGroupNorm(2, dim_d, groups)
+
+    def forward(self, x_a, x_v, x_d):
+        rest = x_a.shape[:-1]
+        n = math.prod(rest)
+        xa, xv, xd = x_a.reshape(n, -1), x_v.reshape(n, -1, 3), x_d.reshape(n, -1, 3, 3)
+        prods = bee(self.L0(xa), self.L1(xv), self.L2(xd), self.R0(xa), self.R1(xv), self.R2(xd))
+        y_a, y_v, y_d = _apply_y_maps(self, prods)
+        return (self.gn_a(y_a.reshape(*rest, -1)), self.gn_v(y_v.reshape(*rest, -1, 3)), self.gn_d(y_d.reshape(*rest, -1, 3, 3)))
+
+
+class OBeeBlock(nn.Module):
+    def __init__(self, r0, dim_a, dim_v, dim_d, chan):
+        super().__init__()
+        self.messages = OMessages(r0, dim_a, dim_v, dim_d, chan)
+        self.prods = OSelfTensProds(dim_a, dim_v, dim_d, chan)
+
+    def forward(self, src, dst, r_ij, x_a, x_v, x_d):
+        d = self.messages(src, dst, r_ij, x_a, x_v, x_d)
+        x_a, x_v, x_d = x_a + d[0], x_v + d[1], x_d + d[2]
+        d = self.prods(x_a, x_v, x_d)
+        return x_a + d[0], x_v + d[1], x_d + d[2]
+
+
+class OBeeDenoiser(nn.Module):
+    """The l<=2 denoiser of benchmark configs 2 and 4 (see ld_b200.bee.BeeDenoiser): reference layers
+    (archs/diffuser_atoms15.py Messages / SelfTensProds) between the read-in and read-out of
+    archs/meanflow_painn8.py:185-217."""
+
+    def __init__(self, r0, dim_a, dim_v, dim_d, chan, ntypes, depth):
+        super().__init__()
+        self.r0, self.dim_d = r0, dim_d
+        self.type_embed = nn.Embedding(ntypes, dim_a)
+        self.v_readin = OTensLinear(1, 1, dim_v)
+        self.blocks = nn.ModuleList([OBeeBlock(r0, dim_a, dim_v, dim_d, chan) for _ in range(depth)])
+        self.readout = OTensLinear(1, dim_v, 1)
+        self.edges_last = 0
+
+    def forward(self, x0, x1, box, types):
+        batch, nodes, _ = x0.shape
+        g = radius_graph(x1, self.r0, box)
+        x_a = self.type_embed(types)[None].expand(batch, -1, -1)
+        x_v = self.v_readin((x1 - x0)[..., None, :])
+        x_d = torch.zeros(batch, nodes, self.dim_d, 3, 3)
+        for blk in self.blocks:
+            x_a, x_v, x_d = blk(g["src"], g["dst"], g["rij"], x_a, x_v, x_d)
+        self.edges_last = g["E"] * len(self.blocks)
+        return self.readout(x_v).squeeze(-2)
+
+    def generate(self, x_0, noise, sigma_0, box, types):
+        z_1 = x_0 + sigma_0 * noise
+        with torch.no_grad():
+            return z_1 - self.forward(x_0, z_1, box, types)

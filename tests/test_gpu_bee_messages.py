@@ -53,3 +53,28 @@ def test_messages_fused_vs_unfused(dims, B, N, r0, box):
     unfused = mes._forward_unfused(graph, graph.rij, x_a.cuda(), x_v.cuda(), x_d.cuda())
     for got, ref in zip(fused, unfused):
         close(got, ref, 1e-4)
+
+
+def test_bee_denoiser_vs_oracle():
+    from ld_b200 import bee
+    from oracle import reference_math as R
+    torch.manual_seed(3)
+    dims = (32, 16, 8, 32)
+    ref = R.OBeeDenoiser(3.0, *dims, ntypes=5, depth=2)
+    mine = bee.BeeDenoiser(3.0, *dims, ntypes=5, depth=2)
+    mine.load_state_dict(ref.state_dict())
+    mine.cuda()
+    g = torch.Generator().manual_seed(9)
+    B, N = 3, 48
+    x0 = torch.cumsum(torch.randn(B, N, 3, generator=g) / 3 ** 0.5, dim=1)
+    noise = torch.randn(B, N, 3, generator=g)
+    types = torch.randint(0, 5, (N,), generator=g)
+    x1 = x0 + 0.3 * noise
+    counter = torch.zeros(1, dtype=torch.int64, device="cuda")
+    with torch.no_grad():
+        want_v = ref(x0, x1, None, types)
+        got_v = mine(x0.cuda(), x1.cuda(), None, types.cuda(), counter)
+    assert want_v.abs().max() > 1e-3
+    close(got_v, want_v, 2e-4)
+    assert int(counter.item()) == ref.edges_last
+    close(mine.generate(x0.cuda(), noise.cuda(), 0.3, None, types.cuda()), ref.generate(x0, noise, 0.3, None, types), 2e-4)

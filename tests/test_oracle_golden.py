@@ -92,3 +92,17 @@ def test_periodic_graph_properties():
     g1 = R.radius_graph(pos, 2.5, box, mode=1)
     pairs1 = set(zip(g1["src"].tolist(), g1["dst"].tolist()))
     assert pairs1 <= pairs
+
+
+def test_bee_messages_layer(golden):
+    p, m = golden["painn"], golden["bee_messages"]
+    mes = R.OMessages(p["r0"], *m["dims"])
+    mes.load_state_dict(m["state"])
+    with torch.no_grad():
+        out = mes(p["src"], p["dst"], p["r_ij"], m["x_a"], m["x_v"], m["x_d"])
+    for mine, ref in zip(out, m["out"]):
+        assert torch.allclose(mine, ref, rtol=1e-4, atol=1e-5)
+    n = golden["norms"]
+    for inds, key, x in ((1, "tgn1_out", n["xv"]), (2, "tgn2_out", n["xd"])):
+        gn = R.OTensGroupNorm(inds, 8, 4 if inds == 1 else 2)
+        assert torch.allclose(gn(x), n[key], rtol=1e-5, atol=1e-6)
