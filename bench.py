@@ -287,8 +287,10 @@ def main():
 
     is_bee = w.get("model") == "bee"
     if is_bee:
-        args.precision = "fp32"  # the l<=2 layers run on the FP32 kernels so far
-    dn = build_model(w, dev) if is_bee else painn.set_precision(build_model(w, dev), args.precision)
+        from ld_b200 import bee
+        dn = bee.set_precision(build_model(w, dev), args.precision)
+    else:
+        dn = painn.set_precision(build_model(w, dev), args.precision)
     types = torch.randint(0, w["ntypes"], (w["nodes"],), generator=torch.Generator().manual_seed(99)).to(dev)
     if not is_bee:
         bond = painn.chain_bond_graph(per, w["nodes"], dev) if w["kind"] == "polymer" else painn.empty_bond_graph(per, w["nodes"], dev)
@@ -366,7 +368,7 @@ def main():
         tc_path = args.precision == "bf16"
         if is_bee:
             da, _, _, ch = w["dims"]
-            msg = ktimes.get("bee_messages_scalar", {"launches": 0, "ms": 0.0})
+            msg = ktimes.get("bee_messages_scalar_tc" if tc_path else "bee_messages_scalar", {"launches": 0, "ms": 0.0})
             flops = 2 * (3 * ch * da + 9 * da * da)  # per-edge Y maps + mlp_a of the scalar channel
         else:
             msg = ktimes.get("painn_message_tc" if tc_path else "painn_message", {"launches": 0, "ms": 0.0})
@@ -375,7 +377,7 @@ def main():
         if msg["launches"]:
             per_launch_s = msg["ms"] * 1e-3 / msg["launches"]
             achieved = flops * (local_edges / max(msg["launches"], 1)) / per_launch_s / 1e12  # rank 0's own launches
-            roof = {"bound": "tensor", "kernel": "bee_scalar_kernel" if is_bee else ("painn_message_tc_kernel" if tc_path else "painn_message_kernel"), "achieved": achieved, "peak": tf_sus, "unit": "TFLOP/s",
+            roof = {"bound": "tensor", "kernel": ("bee_scalar_tc_kernel" if tc_path else "bee_scalar_kernel") if is_bee else ("painn_message_tc_kernel" if tc_path else "painn_message_kernel"), "achieved": achieved, "peak": tf_sus, "unit": "TFLOP/s",
                     "frac": achieved / tf_sus, "traffic": None, "peak_source": f"bf16_tflops_sustained, {how}",
                     "launches": msg["launches"], "avg_launch_ms": per_launch_s * 1e3,
                     "note": ("tcgen05 BF16 MMAs of the per-edge distance MLP (algorithmic flops: 2*(n_rbf*4n + 2*(4n)^2) per edge)"

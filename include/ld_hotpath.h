@@ -153,6 +153,14 @@ int ld_bee_messages_scalar_f32(const int* row_ptr, const int* dst, const float* 
                                const float* b2, const float* W3t, const float* b3, const float* Wdt, float scale,
                                float* out_a, void* stream);
 
+/* Tensor-core variant of ld_bee_messages_scalar_f32 (tcgen05, BF16 operands, 2e-2 relative); weights
+ * packed by ld_pack_weights_bf16: Yp [a][3*chan], W1p [2a][a], W2p [2a][2a], W3p [a][3a] = (W3 | W_direct + I). */
+int ld_bee_messages_scalar_bf16_tc(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, int dim_a, float r0,
+                                   const float* L0, const float* L1, const float* L2, const float* enc_w, const float* enc_b,
+                                   const float* jacobi, const void* Yp, const void* W1p, const float* b1, const void* W2p,
+                                   const float* b2, const void* W3p, const float* b3, float scale, float* out_a,
+                                   int* status_dev, void* stream);
+
 /* Diagnostics (no counterpart in the reference): per-phase cycle counters of the fused tensor-core
  * kernel, added into 16 device int64 by later launches; NULL switches them off. */
 int ld_debug_set_phase_counters(long long* device_buffer16);

@@ -1,0 +1,453 @@
+// Scalar channel of the l<=2 ("Bee") message layer on the Blackwell tensor cores: the per-edge
+// work of Messages.forward (archs/diffuser_atoms15.py:227-253) that cannot be hoisted to nodes,
+//   psi_e = [y_000 | y_110 | y_220] Y^T ;  out_e = psi_e + lin_direct(psi_e) + layers(psi_e)
+//   B_a[i] = scale * sum_{e: src_e = i} out_e
+// as four tcgen05 GEMMs per 128-edge tile (BF16 operands, FP32 accumulation in tensor memory;
+// 2e-2 relative). Same block structure as the fused PaiNN kernel (painn_message_tc.cu): 8 working
+// warps build the operand tile and run the epilogues, one warp issues MMAs, one warp streams
+// weight slabs from L2 with bulk copies; node-aligned CSR slices, one write per node, no atomics.
+//
+// Operand tile A (K-major panels, 128 rows): columns [0, 3*chan) hold the products for the Y
+// map; afterwards columns [0, 2a) hold the hidden activations and [2a, 3a) keep psi, so that the
+// last layer is ONE GEMM over K = 3a with weights [W3 | W_direct + I]: the residual and the direct
+// term ride on the tensor cores.
+#include "common.cuh"
+#include "tc05.cuh"
+#include "tp_math.h"
+
+namespace {
+
+constexpr int BT_EDGES = 128;
+constexpr int BT_WORK_WARPS = 8;
+constexpr int BT_WORK_THREADS = BT_WORK_WARPS * 32;
+constexpr int BT_MMA_WARP = BT_WORK_WARPS;
+constexpr int BT_PROD_WARP = BT_WORK_WARPS + 1;
+constexpr int BT_THREADS = (BT_WORK_WARPS + 2) * 32;
+constexpr int BT_SYNC_THREADS = (BT_WORK_WARPS + 1) * 32;
+constexpr int BT_STAGES = 4;        // weight ring: slabs of K = 32
+constexpr int BT_SLAB_KSTEPS = 2;
+constexpr int BT_LAYERS = 4;
+
+struct BtLayer {
+  const __nv_bfloat16* w;   // packed panels [K/8][N][8]
+  const float* bias;        // may be null
+  int a_panel;              // first 8-column panel of A this layer reads
+  int ksteps;               // K / 16
+  int N;                    // output width (multiple of 64, <= 256)
+  int act;                  // 0 none, 2 LeakyReLU(0.1)
+  int out_col;              // A column where the epilogue writes its BF16 result (-1: last layer)
+};
+
+struct BtParams {
+  const int* row_ptr; const int* dst; const float* rij;
+  int Nt, chan, dim_a;
+  float r0, scale;
+  const float* L0; const float* L1; const float* L2;
+  const float* enc_w; const float* enc_b; const float* jacobi;
+  BtLayer layer[BT_LAYERS];
+  unsigned stage_off, bias_off, slab_bytes;
+  int seg_nodes;
+  float* out_a;
+  int* status;
+};
+
+struct BtGeom { float rhat[3]; float enc[8]; };
+
+__device__ __forceinline__ int bt_lb_row(const int* __restrict__ row_ptr, int lo, int hi, long long target) {
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if ((long long)row_ptr[mid] < target) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ int bt_work_lb(const int* __restrict__ row_ptr, int lo, int hi, long long target) {
+  const long long base = (long long)row_ptr[lo] + lo;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if ((long long)row_ptr[mid] + mid - base < target) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+struct BtRange { int n_begin, n_end; long long e_begin, e_end, ntiles; };
+
+__device__ __forceinline__ BtRange bt_block_range(const int* __restrict__ row_ptr, int seg_lo, int seg_hi) {
+  BtRange r;
+  const long long work = ((long long)row_ptr[seg_hi] - row_ptr[seg_lo]) + (seg_hi - seg_lo);
+  long long per = (work + gridDim.x - 1) / gridDim.x;
+  if (per < BT_EDGES) per = BT_EDGES;
+  r.n_begin = blockIdx.x == 0 ? seg_lo : bt_work_lb(row_ptr, seg_lo, seg_hi, per * blockIdx.x);
+  r.n_end = blockIdx.x == gridDim.x - 1 ? seg_hi : bt_work_lb(row_ptr, seg_lo, seg_hi, per * (blockIdx.x + 1));
+  r.e_begin = r.n_begin < r.n_end ? row_ptr[r.n_begin] : 0;
+  r.e_end = r.n_begin < r.n_end ? row_ptr[r.n_end] : 0;
+  r.ntiles = (r.e_end - r.e_begin + BT_EDGES - 1) / BT_EDGES;
+  return r;
+}
+
+__device__ __forceinline__ int bt_sync_or(int flag) {
+  int out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "barrier.cta.red.or.pred p, 1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(flag), "n"(BT_SYNC_THREADS)
+      : "memory");
+  return out;
+}
+__device__ __forceinline__ void bt_sync_workers() { asm volatile("barrier.cta.sync 2, %0;" ::"n"(BT_WORK_THREADS) : "memory"); }
+
+__device__ __forceinline__ void bt_geometry(const float* __restrict__ rij, long long e, float r0, const float* jac, BtGeom* g) {
+  const float x = rij[e * 3], y = rij[e * 3 + 1], z = rij[e * 3 + 2];
+  const float d = sqrtf(x * x + y * y + z * z);
+  const float zz = d / r0;
+  float pw[9];
+  pw[0] = 1.f;
+#pragma unroll
+  for (int p = 1; p < 9; p++) pw[p] = pw[p - 1] * zz;
+  const float env = fmaxf(1.f - zz, 0.f);
+#pragma unroll
+  for (int m = 0; m < 8; m++) {
+    float a = 0.f;
+#pragma unroll
+    for (int p = 0; p < 9; p++) a = fmaf(pw[p], jac[m * 9 + p], a);
+    g->enc[m] = a * env;
+  }
+  const float s = 7.f / r0;
+  const float ux = x * s, uy = y * s, uz = z * s;
+  const float inv = rsqrtf(1.f + ux * ux + uy * uy + uz * uz);
+  g->rhat[0] = ux * inv; g->rhat[1] = uy * inv; g->rhat[2] = uz * inv;
+}
+
+__device__ __forceinline__ unsigned short bt_bf16(float v) {
+  __nv_bfloat16 h = __float2bfloat16_rn(v);
+  return *reinterpret_cast<unsigned short*>(&h);
+}
+
+__global__ void __launch_bounds__(BT_THREADS, 1)
+bee_scalar_tc_kernel(BtParams P) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t bar_full[BT_STAGES], bar_empty[BT_STAGES], bar_accum;
+  __shared__ uint32_t tmem_slot;
+  __shared__ BtGeom s_geom[BT_EDGES];
+  __shared__ int s_dst[BT_EDGES];
+  __shared__ int s_src[BT_EDGES];
+  __shared__ int s_rowwin[BT_EDGES + 1];
+  __shared__ float s_jac[72];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool mma_lane = warp == BT_MMA_WARP && lane == 0;
+  const bool prod_lane = warp == BT_PROD_WARP && lane == 0;
+  const int quarter = warp & 3, half = (warp >> 2) & 1;
+  const int row = quarter * 32 + lane;
+  const int C = P.chan, A = P.dim_a;
+  unsigned char* a_smem = smem;                                   // 128 x max(3C, 3A) BF16, overlaid by the staging tile
+  unsigned char* b_smem = smem + P.stage_off;                     // BT_STAGES x slab
+  float* s_bias = reinterpret_cast<float*>(smem + P.bias_off);    // biases of layers 1..3: [2A | 2A | A]
+  float* stage_f = reinterpret_cast<float*>(smem);                // [128][A] FP32
+  const uint32_t slab = P.slab_bytes;
+
+  for (int i = tid; i < 72; i += BT_THREADS) s_jac[i] = P.jacobi[i];
+  for (int i = tid; i < 2 * A; i += BT_THREADS) { s_bias[i] = P.layer[1].bias[i]; s_bias[2 * A + i] = P.layer[2].bias[i]; }
+  for (int i = tid; i < A; i += BT_THREADS) s_bias[4 * A + i] = P.layer[3].bias[i];
+  if (tid == 0) {
+    for (int s = 0; s < BT_STAGES; s++) { tc::mbar_init(&bar_full[s], 1); tc::mbar_init(&bar_empty[s], 1); }
+    tc::mbar_init(&bar_accum, 1);
+    tc::mbar_init_fence();
+  }
+  uint32_t ncols = 32;
+  while (ncols < (uint32_t)(2 * A)) ncols <<= 1;
+  if (warp == 0) { tc::tmem_alloc(&tmem_slot, ncols); tc::tmem_relinquish(); }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+  const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
+  const int seg_nodes = P.seg_nodes > 0 ? P.seg_nodes : P.Nt;
+  int fail = 0;
+
+  if (warp == BT_PROD_WARP) {
+    // ===== producer: weight slabs through the ring =========================================================
+    if (prod_lane) {
+      uint32_t loads = 0;
+      for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
+        const long long ntiles = bt_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt)).ntiles;
+        for (long long t = 0; t < ntiles && !fail; t++) {
+          for (int l = 0; l < BT_LAYERS && !fail; l++) {
+            const BtLayer& L = P.layer[l];
+            for (int ks = 0; ks < L.ksteps; ks += BT_SLAB_KSTEPS, loads++) {
+              const uint32_t st = loads % BT_STAGES, use = loads / BT_STAGES;
+              const uint32_t bytes = (uint32_t)min(BT_SLAB_KSTEPS, L.ksteps - ks) * L.N * 32;
+              if (use >= 1 && !tc::mbar_wait(&bar_empty[st], (use - 1) & 1)) { fail = 1; break; }
+              tc::mbar_expect_tx(&bar_full[st], bytes);
+              tc::bulk_g2s(b_smem + (size_t)st * slab, L.w + (size_t)ks * L.N * 16, bytes, &bar_full[st]);
+            }
+          }
+        }
+      }
+      if (fail) {
+        for (uint32_t i = loads > BT_STAGES ? loads - BT_STAGES : 0; i < loads; i++)
+          tc::mbar_wait(&bar_full[i % BT_STAGES], (i / BT_STAGES) & 1);
+      }
+    }
+  } else if (warp == BT_MMA_WARP) {
+    // ===== MMA issue =========================================================================================
+    uint32_t mmas = 0;
+    const uint32_t a_base = tc::smem_u32(a_smem);
+    for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
+      const long long ntiles = bt_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt)).ntiles;
+      for (long long t = 0; t < ntiles; t++) {
+        if (bt_sync_or(fail)) { fail = 1; break; }      // [B1] geometry staged
+        if (bt_sync_or(fail)) { fail = 1; break; }      // [B2] product tile ready
+        for (int l = 0; l < BT_LAYERS; l++) {
+          if (mma_lane && !fail) {
+            tc::fence_after_sync();
+            const BtLayer& L = P.layer[l];
+            for (int ks0 = 0; ks0 < L.ksteps; ks0 += BT_SLAB_KSTEPS, mmas++) {
+              const uint32_t st = mmas % BT_STAGES, use = mmas / BT_STAGES;
+              if (!tc::mbar_wait(&bar_full[st], use & 1)) { fail = 1; break; }
+              tc::fence_after_sync();
+              const uint32_t b_base = tc::smem_u32(b_smem + (size_t)st * slab);
+              for (int kk = 0; kk < BT_SLAB_KSTEPS && ks0 + kk < L.ksteps; kk++) {
+                const int ks = ks0 + kk;
+                const uint64_t ad = tc::smem_desc(a_base + (L.a_panel + ks * 2) * (BT_EDGES * 16), BT_EDGES * 16, 128);
+                const uint64_t bd = tc::smem_desc(b_base + kk * 2 * (L.N * 16), L.N * 16, 128);
+                tc::mma_bf16(tmem_base, ad, bd, tc::idesc_bf16(BT_EDGES, L.N), ks > 0 ? 1u : 0u);
+              }
+              tc::mma_commit(&bar_empty[st]);
+            }
+            if (!fail) tc::mma_commit(&bar_accum);
+          }
+          fail = __shfl_sync(0xffffffffu, fail, 0);
+          if (bt_sync_or(fail)) { fail = 1; break; }    // [B3..B6] accumulators consumed / next operand ready
+        }
+        if (fail) break;
+        if (bt_sync_or(fail)) { fail = 1; break; }      // [B7] tile finished
+      }
+    }
+  } else {
+    // ===== working warps =========================================================================================
+    uint32_t accum_phase = 0;
+    auto flush_until = [&](int from, int next, float value) {
+      if (tid < A)
+        for (int v = from; v < next; v++) P.out_a[(size_t)v * A + tid] = (v == from ? value : 0.f) * P.scale;
+    };
+    // product role: channel c, every second edge (both halves of a warp-uniform edge stay coalesced)
+    const int pc_c = tid % C, pc_h = tid / C, pc_stride = BT_WORK_THREADS / C;
+    float w8[8], wb = 0.f;
+    if (pc_h < pc_stride) {
+#pragma unroll
+      for (int m = 0; m < 8; m++) w8[m] = P.enc_w[pc_c * 8 + m];
+      wb = P.enc_b[pc_c];
+    }
+    for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
+      const BtRange br = bt_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt));
+      const int n_begin = br.n_begin, n_end = br.n_end;
+      float acc = 0.f;
+      int cur = n_begin, node_lo = n_begin;
+      bt_sync_workers();
+      if (tid <= BT_EDGES) s_rowwin[tid] = P.row_ptr[min(node_lo + tid, n_end > n_begin ? n_end : n_begin)];
+      bt_sync_workers();
+      for (long long e0 = br.e_begin; e0 < br.e_end; e0 += BT_EDGES) {
+        const int cnt = (int)((br.e_end - e0) < BT_EDGES ? (br.e_end - e0) : BT_EDGES);
+        // ---- 1. edge geometry ----------------------------------------------------------------------------
+        if (tid < BT_EDGES) {
+          int j = 0, s = -1;
+          if (tid < cnt) {
+            const long long e = e0 + tid;
+            bt_geometry(P.rij, e, P.r0, s_jac, &s_geom[tid]);
+            j = P.dst[e];
+            if ((long long)s_rowwin[BT_EDGES] > e) {
+              int lo = 0, hi = BT_EDGES;
+              while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if ((long long)s_rowwin[mid] > e) hi = mid; else lo = mid; }
+              s = node_lo + lo;
+            } else {
+              s = bt_lb_row(P.row_ptr, node_lo + BT_EDGES, n_end, e + 1) - 1;
+            }
+          }
+          s_dst[tid] = j;
+          s_src[tid] = s;
+        }
+        if (bt_sync_or(fail)) { fail = 1; break; }                                        // [B1]
+        // ---- 2. scalar products -> operand tile (columns c, C+c, 2C+c of row t) ------------------------------
+        if (pc_h < pc_stride) {
+          for (int t = pc_h; t < BT_EDGES; t += pc_stride) {
+            float y0 = 0.f, y1 = 0.f, y2 = 0.f;
+            if (t < cnt) {
+              const BtGeom& g = s_geom[t];
+              float pa = wb;
+#pragma unroll
+              for (int m = 0; m < 8; m++) pa = fmaf(g.enc[m], w8[m], pa);
+              const size_t j = (size_t)s_dst[t] * C + pc_c;
+              y0 = __ldg(P.L0 + j) * pa;
+              float dv = 0.f;
+#pragma unroll
+              for (int k = 0; k < 3; k++) dv = fmaf(__ldg(P.L1 + j * 3 + k), g.rhat[k], dv);
+              y1 = dv * pa;
+              float dd = 0.f;
+#pragma unroll
+              for (int x = 0; x < 3; x++)
+#pragma unroll
+                for (int y = 0; y < 3; y++) dd = fmaf(__ldg(P.L2 + j * 9 + x * 3 + y), g.rhat[x] * g.rhat[y], dd);
+              y2 = dd * pa;
+            }
+            unsigned short* arow = reinterpret_cast<unsigned short*>(a_smem + (size_t)t * 16);
+            const int k0 = pc_c, k1 = C + pc_c, k2 = 2 * C + pc_c;
+            arow[(size_t)(k0 >> 3) * (BT_EDGES * 8) + (k0 & 7)] = bt_bf16(y0);
+            arow[(size_t)(k1 >> 3) * (BT_EDGES * 8) + (k1 & 7)] = bt_bf16(y1);
+            arow[(size_t)(k2 >> 3) * (BT_EDGES * 8) + (k2 & 7)] = bt_bf16(y2);
+          }
+        }
+        tc::fence_async_smem();
+        tc::fence_before_sync();
+        if (bt_sync_or(fail)) { fail = 1; break; }                                        // [B2]
+        // ---- 3. four layers ------------------------------------------------------------------------------------
+        for (int l = 0; l < BT_LAYERS; l++) {
+          {
+            int done = 1;
+            if (lane == 0) done = tc::mbar_wait(&bar_accum, accum_phase & 1) ? 1 : 0;
+            done = __shfl_sync(0xffffffffu, done, 0);
+            if (!done) fail = 1;
+          }
+          accum_phase++;
+          tc::fence_after_sync();
+          const int N = P.layer[l].N;
+          if (!fail && l < BT_LAYERS - 1) {
+            // bias, activation -> BF16 into the operand tile at out_col (this thread: row `row`, its half of the columns)
+            const float* bias = l == 0 ? nullptr : s_bias + (l - 1) * 2 * A;
+            const int act = P.layer[l].act, oc = P.layer[l].out_col;
+            for (int cb = half * (N / 2); cb < (half + 1) * (N / 2); cb += 32) {
+              float v[32];
+              tc::tmem_ld32(tmem_row + cb, v);
+#pragma unroll
+              for (int g8 = 0; g8 < 4; g8++) {
+                float t8[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                  float u = v[g8 * 8 + j] + (bias != nullptr ? bias[cb + g8 * 8 + j] : 0.f);
+                  t8[j] = (act == 2) ? (u > 0.f ? u : 0.1f * u) : u;
+                }
+                uint4 q;
+                q.x = tc::pack_bf16x2(t8[0], t8[1]); q.y = tc::pack_bf16x2(t8[2], t8[3]);
+                q.z = tc::pack_bf16x2(t8[4], t8[5]); q.w = tc::pack_bf16x2(t8[6], t8[7]);
+                *reinterpret_cast<uint4*>(a_smem + (size_t)(((oc + cb) >> 3) + g8) * (BT_EDGES * 16) + row * 16) = q;
+              }
+            }
+            tc::fence_async_smem();
+            tc::fence_before_sync();
+          }
+          if (bt_sync_or(fail)) { fail = 1; break; }                                      // [B3..B6]
+        }
+        if (fail) break;
+        // ---- 4. last layer's accumulators -> staging -> per-node sums -----------------------------------------
+        const int tile_cur = cur;
+        node_lo = s_src[cnt - 1];
+        if (tid <= BT_EDGES) s_rowwin[tid] = P.row_ptr[min(node_lo + tid, n_end)];
+        {
+          const float* bias = s_bias + 4 * A;
+          for (int cb = half * (A / 2); cb < (half + 1) * (A / 2); cb += 32) {
+            float v[32];
+            tc::tmem_ld32(tmem_row + cb, v);
+#pragma unroll
+            for (int g4 = 0; g4 < 8; g4++) {
+              float4 m = make_float4(v[g4 * 4] + bias[cb + g4 * 4], v[g4 * 4 + 1] + bias[cb + g4 * 4 + 1],
+                                     v[g4 * 4 + 2] + bias[cb + g4 * 4 + 2], v[g4 * 4 + 3] + bias[cb + g4 * 4 + 3]);
+              if (row >= cnt) m = make_float4(0.f, 0.f, 0.f, 0.f);
+              // 16-byte slot = 4 consecutive channels, xor-swizzled by row within groups of 8 slots
+              const int slot = (cb >> 2) + g4;
+              const int sw = (slot & ~7) | ((slot ^ row) & 7);
+              *reinterpret_cast<float4*>(stage_f + (size_t)row * A + sw * 4) = m;
+            }
+          }
+        }
+        tc::fence_before_sync();
+        bt_sync_workers();
+        if (tid < A) {
+          int c_node = tile_cur;
+          float a_sum = acc;
+          const int slot = tid >> 2, sub = tid & 3;
+          for (int eb = 0; eb < cnt; eb += 8) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+              const int e = eb + i;
+              const int sw = (slot & ~7) | ((slot ^ e) & 7);
+              v[i] = stage_f[(size_t)e * A + sw * 4 + sub];
+            }
+            const int last = min(eb + 7, cnt - 1);
+            if (s_src[eb] == c_node && s_src[last] == c_node) {
+              a_sum += ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; i++) {
+                if (eb + i < cnt) {
+                  const int s = s_src[eb + i];
+                  if (s != c_node) { flush_until(c_node, s, a_sum); a_sum = 0.f; c_node = s; }
+                  a_sum += v[i];
+                }
+              }
+            }
+          }
+          acc = a_sum;
+          cur = c_node;
+        }
+        if (bt_sync_or(fail)) { fail = 1; break; }                                        // [B7]
+      }
+      if (!fail && n_begin < n_end) flush_until(cur, n_end, acc);
+    }
+  }
+  if (fail && lane == 0 && P.status != nullptr) atomicOr(P.status, LD_FLAG_TIMEOUT);
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem_base, ncols);
+}
+
+}  // namespace
+
+// Tensor-core variant of ld_bee_messages_scalar_f32. Packed BF16 weights (ld_pack_weights_bf16):
+// Yp = [dim_a][3*chan] (Y_000 | Y_110 | Y_220), W1p = [2a][a], W2p = [2a][2a],
+// W3p = [a][3a] = (W3 | W_direct + identity). Biases FP32. chan a multiple of 32 (<= 256), dim_a 64 or 128.
+extern "C" int ld_bee_messages_scalar_bf16_tc(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan,
+                                              int dim_a, float r0, const float* L0, const float* L1, const float* L2,
+                                              const float* enc_w, const float* enc_b, const float* jacobi, const void* Yp,
+                                              const void* W1p, const float* b1, const void* W2p, const float* b2,
+                                              const void* W3p, const float* b3, float scale, float* out_a, int* status_dev,
+                                              void* stream) {
+  if (Nt < 0 || chan <= 0 || dim_a <= 0 || !(r0 > 0.f)) return LD_ERR_SHAPE;
+  if (chan % 32 != 0 || chan > 256 || (dim_a != 64 && dim_a != 128)) {
+    ld_set_last_message("bee messages (tensor-core path): chan must be a multiple of 32 up to 256, dim_a 64 or 128");
+    return LD_ERR_UNSUPPORTED;
+  }
+  if (b1 == nullptr || b2 == nullptr || b3 == nullptr) return LD_ERR_SHAPE;
+  if ((((uintptr_t)Yp | (uintptr_t)W1p | (uintptr_t)W2p | (uintptr_t)W3p) % 16) != 0) return LD_ERR_SHAPE;
+  if (Nt == 0) return LD_OK;
+  const int A = dim_a, C = chan;
+  BtParams P;
+  P.row_ptr = row_ptr; P.dst = dst; P.rij = rij; P.Nt = Nt; P.chan = C; P.dim_a = A; P.r0 = r0; P.scale = scale;
+  P.L0 = L0; P.L1 = L1; P.L2 = L2; P.enc_w = enc_w; P.enc_b = enc_b; P.jacobi = jacobi;
+  P.layer[0] = BtLayer{(const __nv_bfloat16*)Yp, nullptr, 0, 3 * C / 16, A, 0, 2 * A};
+  P.layer[1] = BtLayer{(const __nv_bfloat16*)W1p, b1, 2 * A / 8, A / 16, 2 * A, 2, 0};
+  P.layer[2] = BtLayer{(const __nv_bfloat16*)W2p, b2, 0, 2 * A / 16, 2 * A, 2, 0};
+  P.layer[3] = BtLayer{(const __nv_bfloat16*)W3p, b3, 0, 3 * A / 16, A, 0, -1};
+  const int cols = 3 * (C > A ? C : A);
+  const size_t a_bytes = (size_t)BT_EDGES * cols * 2;
+  const size_t staging = (size_t)BT_EDGES * A * 4;
+  const size_t front = a_bytes > staging ? a_bytes : staging;
+  P.slab_bytes = (unsigned)(BT_SLAB_KSTEPS * 2 * A * 32);
+  P.stage_off = (unsigned)front;
+  P.bias_off = (unsigned)(front + (size_t)BT_STAGES * P.slab_bytes);
+  const size_t smem = P.bias_off + (size_t)5 * A * 4 + 256;
+  if (smem > 215 * 1024) { ld_set_last_message("bee messages (tensor-core path): shared-memory plan exceeds the limit"); return LD_ERR_UNSUPPORTED; }
+  {
+    const long long seg = (40LL << 20) / (52LL * C);  // 13*chan floats gathered per neighbour
+    P.seg_nodes = (int)(seg < 1024 ? 1024 : seg);
+  }
+  P.out_a = out_a; P.status = status_dev;
+  LD_CUDA_TRY(cudaFuncSetAttribute(bee_scalar_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  bee_scalar_tc_kernel<<<sms, BT_THREADS, smem, (cudaStream_t)stream>>>(P);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}

@@ -37,6 +37,7 @@ SIGNATURES = {
     "ld_linear_bf16_tc": [P, LL, I, I, P, P, I, I, P, P, P],
     "ld_painn_message_bf16_tc": [P, P, P, I, I, I, I, F, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P],
     "ld_debug_set_phase_counters": [P],
+    "ld_bee_messages_scalar_bf16_tc": [P, P, P, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P, P, P, F, P, P, P],
     "ld_bee_messages_vd_f32": [P, P, P, I, I, F, P, P, P, P, P, P, F, P, P, P],
     "ld_bee_messages_scalar_f32": [P, P, P, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P, F, P, P],
     "ld_painn_message_f32": [P, P, P, I, I, I, I, F, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P],

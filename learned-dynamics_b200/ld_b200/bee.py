@@ -74,6 +74,7 @@ class Messages(nn.Module):
         self.mlp_a = MLP(dim_a)
         self._packed = None
         self._packed_key = None
+        self.precision = "fp32"  # "bf16": scalar channel on the tensor cores (2e-2 relative)
 
     def load_state_dict(self, state, *a, **k):
         # the reference wraps mlp_a in torch.compile, which prefixes its keys
@@ -81,7 +82,7 @@ class Messages(nn.Module):
         return super().load_state_dict(state, *a, **k)
 
     def _pack(self):
-        key = tuple((p.data_ptr(), p._version) for p in self.parameters())
+        key = (self.precision,) + tuple((p.data_ptr(), p._version) for p in self.parameters())
         if self._packed_key != key:
             dev = self.lin_enc.weight.device
             f = lambda t: t.detach().float().contiguous()
@@ -95,6 +96,13 @@ class Messages(nn.Module):
                 "W1t": f(lay[0].weight.t()), "b1": f(lay[0].bias), "W2t": f(lay[2].weight.t()), "b2": f(lay[2].bias),
                 "W3t": f(lay[4].weight.t()), "b3": f(lay[4].bias), "Wdt": f(self.mlp_a.lin_direct.weight.t()),
             }
+            if self.precision == "bf16":
+                eye = torch.eye(self.dim_a, device=dev)
+                p = self._packed
+                p["Yp"] = ops.pack_weights_bf16(p["Yt"].t().contiguous())
+                p["W1p"] = ops.pack_weights_bf16(f(lay[0].weight))
+                p["W2p"] = ops.pack_weights_bf16(f(lay[2].weight))
+                p["W3p"] = ops.pack_weights_bf16(torch.cat([f(lay[4].weight), f(self.mlp_a.lin_direct.weight) + eye], dim=1).contiguous())
             self._packed_key = key
         return self._packed
 
@@ -116,11 +124,20 @@ class Messages(nn.Module):
             check(lib().ld_bee_messages_vd_f32(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, float(self.r0), ptr(l0),
                                                ptr(l1), ptr(l2), ptr(w["enc_w"]), ptr(w["enc_b"]), ptr(w["jac"]), 0.1,
                                                ptr(S_v), ptr(S_d), st))
-        with KERNEL_TIMER.region("bee_messages_scalar"):
-            check(lib().ld_bee_messages_scalar_f32(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, self.dim_a,
-                                                   float(self.r0), ptr(l0), ptr(l1), ptr(l2), ptr(w["enc_w"]), ptr(w["enc_b"]),
-                                                   ptr(w["jac"]), ptr(w["Yt"]), ptr(w["W1t"]), ptr(w["b1"]), ptr(w["W2t"]),
-                                                   ptr(w["b2"]), ptr(w["W3t"]), ptr(w["b3"]), ptr(w["Wdt"]), 0.1, ptr(B_a), st))
+        if self.precision == "bf16":
+            with KERNEL_TIMER.region("bee_messages_scalar_tc"):
+                check(lib().ld_bee_messages_scalar_bf16_tc(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, self.dim_a,
+                                                           float(self.r0), ptr(l0), ptr(l1), ptr(l2), ptr(w["enc_w"]),
+                                                           ptr(w["enc_b"]), ptr(w["jac"]), ptr(w["Yp"]), ptr(w["W1p"]), ptr(w["b1"]),
+                                                           ptr(w["W2p"]), ptr(w["b2"]), ptr(w["W3p"]), ptr(w["b3"]), 0.1, ptr(B_a),
+                                                           ptr(ops.tc_status(dev)), st))
+        else:
+            with KERNEL_TIMER.region("bee_messages_scalar"):
+                check(lib().ld_bee_messages_scalar_f32(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, self.dim_a,
+                                                       float(self.r0), ptr(l0), ptr(l1), ptr(l2), ptr(w["enc_w"]),
+                                                       ptr(w["enc_b"]), ptr(w["jac"]), ptr(w["Yt"]), ptr(w["W1t"]), ptr(w["b1"]),
+                                                       ptr(w["W2t"]), ptr(w["b2"]), ptr(w["W3t"]), ptr(w["b3"]), ptr(w["Wdt"]),
+                                                       0.1, ptr(B_a), st))
         B_v = ops.tensor_linear(1, w["Yv"], S_v)
         B_d = ops.tensor_linear(2, w["Yd"], S_d)
         return (B_a.reshape(batch, nodes, -1), B_v.reshape(batch, nodes, -1, 3), B_d.reshape(batch, nodes, -1, 3, 3))
@@ -144,6 +161,15 @@ class Messages(nn.Module):
         B_v = edges_reduce_src(graph, psi_v)
         B_d = edges_reduce_src(graph, psi_d)
         return 0.1 * B_a, 0.1 * B_v, 0.1 * B_d
+
+
+def set_precision(module, precision):
+    """"fp32" or "bf16" (scalar channel of every Messages layer on the tensor cores, 2e-2 relative)."""
+    assert precision in ("fp32", "bf16")
+    for m in module.modules():
+        if isinstance(m, Messages):
+            m.precision = precision
+    return module
 
 
 class SelfTensProds(nn.Module):

@@ -78,3 +78,30 @@ def test_bee_denoiser_vs_oracle():
     close(got_v, want_v, 2e-4)
     assert int(counter.item()) == ref.edges_last
     close(mine.generate(x0.cuda(), noise.cuda(), 0.3, None, types.cuda()), ref.generate(x0, noise, 0.3, None, types), 2e-4)
+
+
+@pytest.mark.parametrize("dims,B,N,r0,box", [((128, 64, 32, 128), 2, 300, 3.0, (9.0, 9.0, 9.5)), ((64, 32, 16, 96), 3, 50, 5.0, None),
+                                             ((128, 8, 8, 32), 1, 6, 1.0, None)])
+def test_messages_tensor_core_vs_fp32(dims, B, N, r0, box):
+    """scalar channel on tcgen05 (BF16 operands) against the FP32 fused kernels: 2e-2 relative"""
+    from ld_b200 import bee, graph_layers as GL, ops
+    torch.manual_seed(sum(dims) + 1)
+    mes = bee.Messages(r0, *dims).cuda()
+    g = torch.Generator().manual_seed(8)
+    if box is None:
+        pos = torch.cumsum(torch.randn(B, N, 3, generator=g) / 3 ** 0.5, dim=1)
+    else:
+        pos = torch.rand(B, N, 3, generator=g) * torch.tensor(box)
+    da, dv, dd, _ = dims
+    x_a, x_v, x_d = torch.randn(B, N, da, generator=g), torch.randn(B, N, dv, 3, generator=g), torch.randn(B, N, dd, 3, 3, generator=g)
+    with torch.no_grad():
+        graph = GL.Graph.radius_graph(r0, box, pos.cuda())
+        ref = mes(graph, graph.rij, x_a.cuda(), x_v.cuda(), x_d.cuda())
+        mes.precision = "bf16"
+        got = mes(graph, graph.rij, x_a.cuda(), x_v.cuda(), x_d.cuda())
+        got2 = mes(graph, graph.rij, x_a.cuda(), x_v.cuda(), x_d.cuda())
+    torch.cuda.synchronize()
+    assert int(ops.tc_status("cuda").item()) == 0
+    for a, b in zip(got, ref):
+        close(a, b, 2e-2)
+    assert torch.equal(got[0], got2[0])
