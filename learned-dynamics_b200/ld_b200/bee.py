@@ -103,6 +103,7 @@ class Messages(nn.Module):
                 p["W1p"] = ops.pack_weights_bf16(f(lay[0].weight))
                 p["W2p"] = ops.pack_weights_bf16(f(lay[2].weight))
                 p["W3p"] = ops.pack_weights_bf16(torch.cat([f(lay[4].weight), f(self.mlp_a.lin_direct.weight) + eye], dim=1).contiguous())
+                p["Yvp"], p["Ydp"] = ops.pack_weights_bf16(p["Yv"]), ops.pack_weights_bf16(p["Yd"])
             self._packed_key = key
         return self._packed
 
@@ -138,8 +139,12 @@ class Messages(nn.Module):
                                                        ptr(w["enc_b"]), ptr(w["jac"]), ptr(w["Yt"]), ptr(w["W1t"]), ptr(w["b1"]),
                                                        ptr(w["W2t"]), ptr(w["b2"]), ptr(w["W3t"]), ptr(w["b3"]), ptr(w["Wdt"]),
                                                        0.1, ptr(B_a), st))
-        B_v = ops.tensor_linear(1, w["Yv"], S_v)
-        B_d = ops.tensor_linear(2, w["Yd"], S_d)
+        if self.precision == "bf16" and self.dim_v % 32 == 0 and self.dim_d % 32 == 0:
+            B_v = ops.linear_bf16_tc(S_v, w["Yvp"], self.dim_v, None, ops.ACT_NONE, inds=1)
+            B_d = ops.linear_bf16_tc(S_d, w["Ydp"], self.dim_d, None, ops.ACT_NONE, inds=2)
+        else:
+            B_v = ops.tensor_linear(1, w["Yv"], S_v)
+            B_d = ops.tensor_linear(2, w["Yd"], S_d)
         return (B_a.reshape(batch, nodes, -1), B_v.reshape(batch, nodes, -1, 3), B_d.reshape(batch, nodes, -1, 3, 3))
 
     def _forward_unfused(self, graph, r_ij, x_a, x_v, x_d):
@@ -169,6 +174,12 @@ def set_precision(module, precision):
     for m in module.modules():
         if isinstance(m, Messages):
             m.precision = precision
+    # the node-level channel mixings inside the l<=2 layers follow (read-in / read-out stay FP32)
+    for m in module.modules():
+        if isinstance(m, (Messages, SelfTensProds)):
+            for sub in m.modules():
+                if isinstance(sub, TensLinear):
+                    sub.precision = precision
     return module
 
 

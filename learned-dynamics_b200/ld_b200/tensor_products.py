@@ -4,6 +4,7 @@ reference (W is [dim_out, dim_in]) so its state dicts load unchanged."""
 import torch
 import torch.nn as nn
 
+from . import ops
 from .ops import tensor_linear
 
 
@@ -14,6 +15,8 @@ class TensLinear(nn.Module):
         super().__init__()
         self.W = nn.Parameter(torch.empty(dim_out, dim_in))
         self.inds = inds
+        self.precision = "fp32"  # "bf16": tcgen05 GEMM without autograd (2e-2 relative)
+        self._packed, self._packed_key = None, None
         self.self_init()
 
     def self_init(self):
@@ -21,6 +24,12 @@ class TensLinear(nn.Module):
         nn.init.normal_(self.W, std=fan_in ** -0.5)
 
     def forward(self, x):
+        if self.precision == "bf16" and not torch.is_grad_enabled() and x.is_cuda and self.W.shape[0] % 32 == 0 \
+                and self.W.shape[0] <= 512:
+            key = (self.W.data_ptr(), self.W._version)
+            if self._packed_key != key:
+                self._packed, self._packed_key = ops.pack_weights_bf16(self.W.detach().float()), key
+            return ops.linear_bf16_tc(x, self._packed, self.W.shape[0], None, ops.ACT_NONE, inds=self.inds)
         return tensor_linear(self.inds, self.W, x.contiguous())
 
 

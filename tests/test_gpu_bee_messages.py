@@ -97,7 +97,7 @@ def test_messages_tensor_core_vs_fp32(dims, B, N, r0, box):
     with torch.no_grad():
         graph = GL.Graph.radius_graph(r0, box, pos.cuda())
         ref = mes(graph, graph.rij, x_a.cuda(), x_v.cuda(), x_d.cuda())
-        mes.precision = "bf16"
+        bee.set_precision(mes, "bf16")
         got = mes(graph, graph.rij, x_a.cuda(), x_v.cuda(), x_d.cuda())
         got2 = mes(graph, graph.rij, x_a.cuda(), x_v.cuda(), x_d.cuda())
     torch.cuda.synchronize()
@@ -105,3 +105,21 @@ def test_messages_tensor_core_vs_fp32(dims, B, N, r0, box):
     for a, b in zip(got, ref):
         close(a, b, 2e-2)
     assert torch.equal(got[0], got2[0])
+
+
+def test_bee_denoiser_bf16_vs_fp32():
+    """whole l<=2 denoiser with the scalar channel and the node-level channel mixings on tcgen05; the
+    BF16 rounding of every layer compounds over depth, so the bar for the network output is 5e-2"""
+    from ld_b200 import bee, ops
+    torch.manual_seed(4)
+    dims = (128, 64, 32, 128)
+    dn = bee.BeeDenoiser(3.0, *dims, ntypes=5, depth=3).cuda()
+    g = torch.Generator().manual_seed(10)
+    x0 = torch.cumsum(torch.randn(4, 64, 3, generator=g) / 3 ** 0.5, dim=1).cuda()
+    x1 = x0 + 0.3 * torch.randn(4, 64, 3, generator=g).cuda()
+    types = torch.randint(0, 5, (64,), generator=g).cuda()
+    with torch.no_grad():
+        ref = dn(x0, x1, None, types)
+        got = bee.set_precision(dn, "bf16")(x0, x1, None, types)
+    assert int(ops.tc_status("cuda").item()) == 0
+    close(got, ref, 5e-2)
