@@ -127,6 +127,10 @@ long long ld_packed_weight_elems(int N, int K);
 int ld_pack_weights_bf16(const float* W, long long sw0, long long sw1, int N, int K, void* out, void* stream);
 int ld_linear_bf16_tc(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias, int N, int act,
                       float* y, int* status_dev, void* stream);
+/* same with a BF16 result written to y_bf16[r*ld_row + o*ld_col + s + off] (plain layout: ld_row = N*S,
+ * ld_col = S, off = 0); used to interleave the left operands of the l<=2 message layer per channel */
+int ld_linear_bf16_tc_out16(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias, int N,
+                            int act, void* y_bf16, long long ld_row, long long ld_col, int off, int* status_dev, void* stream);
 
 /* ld_painn_message_bf16_tc: ld_painn_message_f32 with the per-edge distance MLP on tcgen05
  * (BF16 operands, FP32 accumulation in tensor memory); same reference lines
@@ -143,10 +147,12 @@ int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, const float* ri
  * and edges_reduce_src (managan/graph_layers.py:54-59) in one pass over the CSR.
  * _vd: per-node sums of the five rank-1 and five rank-2 products (the Y maps are linear, so the
  * caller applies them per node with ld_tensor_linear over 5*chan inputs). _scalar: per-edge Y maps
- * and mlp_a, summed per node. `jacobi` = 8x9 coefficients of the shifted Jacobi(1,0) polynomials. */
+ * and mlp_a, summed per node. `jacobi` = 8x9 coefficients of the shifted Jacobi(1,0) polynomials.
+ * feat_bf16: 0 = L0/L1/L2 FP32; 1 = BF16; 2 = L0 alone points to the interleaved BF16 form
+ * [node][chan][16] = (l0, l1[3], l2[9], 3 unused) written by ld_linear_bf16_tc_out16. */
 int ld_bee_messages_vd_f32(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, float r0, const float* L0,
                            const float* L1, const float* L2, const float* enc_w, const float* enc_b, const float* jacobi,
-                           float scale, float* S_v, float* S_d, void* stream);
+                           float scale, float* S_v, float* S_d, int feat_bf16, void* stream);
 int ld_bee_messages_scalar_f32(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, int dim_a, float r0,
                                const float* L0, const float* L1, const float* L2, const float* enc_w, const float* enc_b,
                                const float* jacobi, const float* Yt, const float* W1t, const float* b1, const float* W2t,
@@ -159,7 +165,7 @@ int ld_bee_messages_scalar_bf16_tc(const int* row_ptr, const int* dst, const flo
                                    const float* L0, const float* L1, const float* L2, const float* enc_w, const float* enc_b,
                                    const float* jacobi, const void* Yp, const void* W1p, const float* b1, const void* W2p,
                                    const float* b2, const void* W3p, const float* b3, float scale, float* out_a,
-                                   int* status_dev, void* stream);
+                                   int feat_bf16, int* status_dev, void* stream);
 
 /* Diagnostics (no counterpart in the reference): per-phase cycle counters of the fused tensor-core
  * kernel, added into 16 device int64 by later launches; NULL switches them off. */

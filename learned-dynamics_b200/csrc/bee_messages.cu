@@ -18,8 +18,14 @@
 #include "common.cuh"
 #include "mlp_tile.cuh"
 #include "tp_math.h"
+#include <cuda_bf16.h>
+#include "tc05.cuh"
 
 namespace {
+
+__device__ __forceinline__ float bm_ld(const float* p, size_t i) { return __ldg(p + i); }
+__device__ __forceinline__ float bm_ld(const __nv_bfloat16* p, size_t i) { return __bfloat162float(p[i]); }
+
 
 constexpr int BM_TILE = 32;  // edges staged per step
 
@@ -95,8 +101,12 @@ __device__ __forceinline__ void edge_phi(const EdgeGeom& g, const float* w8, flo
 // S_v[node][k][c][3], k over (011,101,121,211,111); S_d[node][k][c][9], k over (022,202,112,222,212):
 // the layouts a channel mixing with 5*chan inputs expects. Thread = channel; a block walks its nodes
 // and stages the geometry of up to 32 edges at a time in shared memory.
+template <typename FT, bool PACKED>
 __global__ void __launch_bounds__(128)
 bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d, float scale) {
+  const FT* __restrict__ F0 = reinterpret_cast<const FT*>(P.L0);
+  const FT* __restrict__ F1 = reinterpret_cast<const FT*>(P.L1);
+  const FT* __restrict__ F2 = reinterpret_cast<const FT*>(P.L2);
   __shared__ EdgeGeom s_geom[BM_TILE];
   __shared__ int s_dst[BM_TILE];
   __shared__ float s_jac[72];
@@ -128,24 +138,47 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
         }
         __syncthreads();
         if (cok) {
-          for (int t = 0; t < cnt; t++) {
-            const size_t j = (size_t)s_dst[t] * C + c;
-            float l1[3], l2[9], pa, pv[3], pd[9];
-            const float l0 = __ldg(P.L0 + j);
+          constexpr int UNR = 4;  // neighbour rows in flight per thread
+          for (int tb = 0; tb < cnt; tb += UNR) {
+            uint32_t raw[UNR][8];
+            if (PACKED) {
 #pragma unroll
-            for (int k = 0; k < 3; k++) l1[k] = __ldg(P.L1 + j * 3 + k);
-#pragma unroll
-            for (int k = 0; k < 9; k++) l2[k] = __ldg(P.L2 + j * 9 + k);
-            edge_phi(s_geom[t], w8, wb, &pa, pv, pd);
-            BeeOut o;
-            bee_fwd_point(l0, l1, l2, pa, pv, pd, &o);
-#pragma unroll
-            for (int k = 0; k < 3; k++) {
-              av[k] += o.y011[k]; av[3 + k] += o.y101[k]; av[6 + k] += o.y121[k]; av[9 + k] += o.y211[k]; av[12 + k] += o.y111[k];
+              for (int u = 0; u < UNR; u++) {
+                const int t = min(tb + u, cnt - 1);
+                tc::ldg_raw8(reinterpret_cast<const __nv_bfloat16*>(P.L0) + ((size_t)s_dst[t] * C + c) * 16, raw[u]);
+              }
             }
 #pragma unroll
-            for (int k = 0; k < 9; k++) {
-              ad[k] += o.y022[k]; ad[9 + k] += o.y202[k]; ad[18 + k] += o.y112[k]; ad[27 + k] += o.y222[k]; ad[36 + k] += o.y212[k];
+            for (int u = 0; u < UNR; u++) {
+              const int t = tb + u;
+              if (t >= cnt) break;
+              const size_t j = (size_t)s_dst[t] * C + c;
+              float l1[3], l2[9], pa, pv[3], pd[9];
+              float l0;
+              if (PACKED) {
+                l0 = tc::bf16_at(raw[u], 0);
+#pragma unroll
+                for (int k = 0; k < 3; k++) l1[k] = tc::bf16_at(raw[u], 1 + k);
+#pragma unroll
+                for (int k = 0; k < 9; k++) l2[k] = tc::bf16_at(raw[u], 4 + k);
+              } else {
+                l0 = bm_ld(F0, j);
+#pragma unroll
+                for (int k = 0; k < 3; k++) l1[k] = bm_ld(F1, j * 3 + k);
+#pragma unroll
+                for (int k = 0; k < 9; k++) l2[k] = bm_ld(F2, j * 9 + k);
+              }
+              edge_phi(s_geom[t], w8, wb, &pa, pv, pd);
+              BeeOut o;
+              bee_fwd_point(l0, l1, l2, pa, pv, pd, &o);
+#pragma unroll
+              for (int k = 0; k < 3; k++) {
+                av[k] += o.y011[k]; av[3 + k] += o.y101[k]; av[6 + k] += o.y121[k]; av[9 + k] += o.y211[k]; av[12 + k] += o.y111[k];
+              }
+#pragma unroll
+              for (int k = 0; k < 9; k++) {
+                ad[k] += o.y022[k]; ad[9 + k] += o.y202[k]; ad[18 + k] += o.y112[k]; ad[27 + k] += o.y222[k]; ad[36 + k] += o.y212[k];
+              }
             }
           }
         }
@@ -285,18 +318,21 @@ bee_scalar_kernel(BeeScalarParams P) {
 
 // Per-node sums of the ten rank-1 / rank-2 Bee products of a Messages layer, times `scale`.
 // S_v: [Nt, 5*chan, 3] (product order 011,101,121,211,111), S_d: [Nt, 5*chan, 3, 3] (022,202,112,222,212).
-// L0/L1/L2 are the node-level left operands, enc_w [chan,8] / enc_b [chan] the radial read-in,
+// L0/L1/L2 are the node-level left operands: FP32 (feat_bf16 = 0), BF16 (1), or with feat_bf16 = 2
+// L0 alone points to the interleaved BF16 form [node][chan][16] = (l0, l1[3], l2[9], 3 unused); enc_w [chan,8] / enc_b [chan] the radial read-in,
 // jacobi the 8x9 coefficient matrix of the radial basis. Graph in CSR form sorted by source.
 extern "C" int ld_bee_messages_vd_f32(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, float r0,
                                       const float* L0, const float* L1, const float* L2, const float* enc_w,
                                       const float* enc_b, const float* jacobi, float scale, float* S_v, float* S_d,
-                                      void* stream) {
+                                      int feat_bf16, void* stream) {
   if (Nt < 0 || chan <= 0 || !(r0 > 0.f)) return LD_ERR_SHAPE;
   if (Nt == 0) return LD_OK;
   BeeEdgeParams P{row_ptr, dst, rij, Nt, chan, r0, L0, L1, L2, enc_w, enc_b, jacobi};
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  bee_vd_kernel<<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale);
+  if (feat_bf16 == 2) bee_vd_kernel<__nv_bfloat16, true><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale);
+  else if (feat_bf16) bee_vd_kernel<__nv_bfloat16, false><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale);
+  else bee_vd_kernel<float, false><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale);
   LD_LAUNCH_CHECK();
   return LD_OK;
 }

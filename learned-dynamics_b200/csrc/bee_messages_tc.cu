@@ -15,6 +15,8 @@
 #include "tc05.cuh"
 #include "tp_math.h"
 
+long long* ld_internal_phase_counters();  // diagnostics buffer set by ld_debug_set_phase_counters
+
 namespace {
 
 constexpr int BT_EDGES = 128;
@@ -24,8 +26,8 @@ constexpr int BT_MMA_WARP = BT_WORK_WARPS;
 constexpr int BT_PROD_WARP = BT_WORK_WARPS + 1;
 constexpr int BT_THREADS = (BT_WORK_WARPS + 2) * 32;
 constexpr int BT_SYNC_THREADS = (BT_WORK_WARPS + 1) * 32;
-constexpr int BT_STAGES = 4;        // weight ring: slabs of K = 32
-constexpr int BT_SLAB_KSTEPS = 2;
+constexpr int BT_STAGES = 3;        // weight ring: 32 KB slabs (a bulk copy costs about the same issue time whatever its size)
+constexpr int BT_SLAB_BYTES = 32 * 1024;
 constexpr int BT_LAYERS = 4;
 
 struct BtLayer {
@@ -33,6 +35,7 @@ struct BtLayer {
   const float* bias;        // may be null
   int a_panel;              // first 8-column panel of A this layer reads
   int ksteps;               // K / 16
+  int slab_ksteps;          // K-steps per weight slab: 32 KB / (N * 32 B)
   int N;                    // output width (multiple of 64, <= 256)
   int act;                  // 0 none, 2 LeakyReLU(0.1)
   int out_col;              // A column where the epilogue writes its BF16 result (-1: last layer)
@@ -47,8 +50,10 @@ struct BtParams {
   BtLayer layer[BT_LAYERS];
   unsigned stage_off, bias_off, slab_bytes;
   int seg_nodes;
+  int feat_bf16;            // 0: L0/L1/L2 FP32; 1: BF16; 2: L0 = interleaved BF16 [node][chan][16]
   float* out_a;
   int* status;
+  long long* prof;          // optional cycle counters: 0 geometry, 1 products, 2/4/6/8 waiting for layers, 3/5/7 epilogues, 9 staging, 10 sums
 };
 
 struct BtGeom { float rhat[3]; float enc[8]; };
@@ -177,9 +182,9 @@ bee_scalar_tc_kernel(BtParams P) {
         for (long long t = 0; t < ntiles && !fail; t++) {
           for (int l = 0; l < BT_LAYERS && !fail; l++) {
             const BtLayer& L = P.layer[l];
-            for (int ks = 0; ks < L.ksteps; ks += BT_SLAB_KSTEPS, loads++) {
+            for (int ks = 0; ks < L.ksteps; ks += L.slab_ksteps, loads++) {
               const uint32_t st = loads % BT_STAGES, use = loads / BT_STAGES;
-              const uint32_t bytes = (uint32_t)min(BT_SLAB_KSTEPS, L.ksteps - ks) * L.N * 32;
+              const uint32_t bytes = (uint32_t)min(L.slab_ksteps, L.ksteps - ks) * L.N * 32;
               if (use >= 1 && !tc::mbar_wait(&bar_empty[st], (use - 1) & 1)) { fail = 1; break; }
               tc::mbar_expect_tx(&bar_full[st], bytes);
               tc::bulk_g2s(b_smem + (size_t)st * slab, L.w + (size_t)ks * L.N * 16, bytes, &bar_full[st]);
@@ -205,12 +210,12 @@ bee_scalar_tc_kernel(BtParams P) {
           if (mma_lane && !fail) {
             tc::fence_after_sync();
             const BtLayer& L = P.layer[l];
-            for (int ks0 = 0; ks0 < L.ksteps; ks0 += BT_SLAB_KSTEPS, mmas++) {
+            for (int ks0 = 0; ks0 < L.ksteps; ks0 += L.slab_ksteps, mmas++) {
               const uint32_t st = mmas % BT_STAGES, use = mmas / BT_STAGES;
               if (!tc::mbar_wait(&bar_full[st], use & 1)) { fail = 1; break; }
               tc::fence_after_sync();
               const uint32_t b_base = tc::smem_u32(b_smem + (size_t)st * slab);
-              for (int kk = 0; kk < BT_SLAB_KSTEPS && ks0 + kk < L.ksteps; kk++) {
+              for (int kk = 0; kk < L.slab_ksteps && ks0 + kk < L.ksteps; kk++) {
                 const int ks = ks0 + kk;
                 const uint64_t ad = tc::smem_desc(a_base + (L.a_panel + ks * 2) * (BT_EDGES * 16), BT_EDGES * 16, 128);
                 const uint64_t bd = tc::smem_desc(b_base + kk * 2 * (L.N * 16), L.N * 16, 128);
@@ -230,6 +235,11 @@ bee_scalar_tc_kernel(BtParams P) {
   } else {
     // ===== working warps =========================================================================================
     uint32_t accum_phase = 0;
+    long long pc[12];
+#pragma unroll
+    for (int i = 0; i < 12; i++) pc[i] = 0;
+    long long tprev = clock64();
+    auto lap = [&](int i) { const long long t = clock64(); pc[i] += t - tprev; tprev = t; };
     auto flush_until = [&](int from, int next, float value) {
       if (tid < A)
         for (int v = from; v < next; v++) P.out_a[(size_t)v * A + tid] = (v == from ? value : 0.f) * P.scale;
@@ -271,38 +281,78 @@ bee_scalar_tc_kernel(BtParams P) {
           s_src[tid] = s;
         }
         if (bt_sync_or(fail)) { fail = 1; break; }                                        // [B1]
+        lap(0);
         // ---- 2. scalar products -> operand tile (columns c, C+c, 2C+c of row t) ------------------------------
         if (pc_h < pc_stride) {
-          for (int t = pc_h; t < BT_EDGES; t += pc_stride) {
-            float y0 = 0.f, y1 = 0.f, y2 = 0.f;
-            if (t < cnt) {
-              const BtGeom& g = s_geom[t];
-              float pa = wb;
+          const __nv_bfloat16* Lp = reinterpret_cast<const __nv_bfloat16*>(P.L0);
+          constexpr int UNR = 4;  // neighbour rows in flight per thread (the loop is bound by L2 latency otherwise)
+          for (int tb = pc_h; tb < BT_EDGES; tb += pc_stride * UNR) {
+            uint32_t raw[UNR][8];
+            if (P.feat_bf16 == 2) {
 #pragma unroll
-              for (int m = 0; m < 8; m++) pa = fmaf(g.enc[m], w8[m], pa);
-              const size_t j = (size_t)s_dst[t] * C + pc_c;
-              y0 = __ldg(P.L0 + j) * pa;
-              float dv = 0.f;
-#pragma unroll
-              for (int k = 0; k < 3; k++) dv = fmaf(__ldg(P.L1 + j * 3 + k), g.rhat[k], dv);
-              y1 = dv * pa;
-              float dd = 0.f;
-#pragma unroll
-              for (int x = 0; x < 3; x++)
-#pragma unroll
-                for (int y = 0; y < 3; y++) dd = fmaf(__ldg(P.L2 + j * 9 + x * 3 + y), g.rhat[x] * g.rhat[y], dd);
-              y2 = dd * pa;
+              for (int u = 0; u < UNR; u++) {
+                const int t = min(tb + u * pc_stride, max(cnt - 1, 0));   // clamped: the load is unconditional
+                tc::ldg_raw8(Lp + ((size_t)s_dst[t] * C + pc_c) * 16, raw[u]);
+              }
             }
-            unsigned short* arow = reinterpret_cast<unsigned short*>(a_smem + (size_t)t * 16);
-            const int k0 = pc_c, k1 = C + pc_c, k2 = 2 * C + pc_c;
-            arow[(size_t)(k0 >> 3) * (BT_EDGES * 8) + (k0 & 7)] = bt_bf16(y0);
-            arow[(size_t)(k1 >> 3) * (BT_EDGES * 8) + (k1 & 7)] = bt_bf16(y1);
-            arow[(size_t)(k2 >> 3) * (BT_EDGES * 8) + (k2 & 7)] = bt_bf16(y2);
+#pragma unroll
+            for (int u = 0; u < UNR; u++) {
+              const int t = tb + u * pc_stride;
+              if (t >= BT_EDGES) break;
+              float y0 = 0.f, y1 = 0.f, y2 = 0.f;
+              if (t < cnt) {
+                const BtGeom& g = s_geom[t];
+                float pa = wb;
+#pragma unroll
+                for (int m = 0; m < 8; m++) pa = fmaf(g.enc[m], w8[m], pa);
+                const size_t j = (size_t)s_dst[t] * C + pc_c;
+                float l0, l1[3], l2[9];
+                if (P.feat_bf16 == 2) {
+                  l0 = tc::bf16_at(raw[u], 0);
+#pragma unroll
+                  for (int k = 0; k < 3; k++) l1[k] = tc::bf16_at(raw[u], 1 + k);
+#pragma unroll
+                  for (int k = 0; k < 9; k++) l2[k] = tc::bf16_at(raw[u], 4 + k);
+                } else if (P.feat_bf16) {
+                  const __nv_bfloat16* F0 = reinterpret_cast<const __nv_bfloat16*>(P.L0);
+                  const __nv_bfloat16* F1 = reinterpret_cast<const __nv_bfloat16*>(P.L1);
+                  const __nv_bfloat16* F2 = reinterpret_cast<const __nv_bfloat16*>(P.L2);
+                  l0 = __bfloat162float(F0[j]);
+#pragma unroll
+                  for (int k = 0; k < 3; k++) l1[k] = __bfloat162float(F1[j * 3 + k]);
+#pragma unroll
+                  for (int k = 0; k < 9; k++) l2[k] = __bfloat162float(F2[j * 9 + k]);
+                } else {
+                  l0 = __ldg(P.L0 + j);
+#pragma unroll
+                  for (int k = 0; k < 3; k++) l1[k] = __ldg(P.L1 + j * 3 + k);
+#pragma unroll
+                  for (int k = 0; k < 9; k++) l2[k] = __ldg(P.L2 + j * 9 + k);
+                }
+                y0 = l0 * pa;
+                float dv = 0.f;
+#pragma unroll
+                for (int k = 0; k < 3; k++) dv = fmaf(l1[k], g.rhat[k], dv);
+                y1 = dv * pa;
+                float dd = 0.f;
+#pragma unroll
+                for (int x = 0; x < 3; x++)
+#pragma unroll
+                  for (int y = 0; y < 3; y++) dd = fmaf(l2[x * 3 + y], g.rhat[x] * g.rhat[y], dd);
+                y2 = dd * pa;
+              }
+              unsigned short* arow = reinterpret_cast<unsigned short*>(a_smem + (size_t)t * 16);
+              const int k0 = pc_c, k1 = C + pc_c, k2 = 2 * C + pc_c;
+              arow[(size_t)(k0 >> 3) * (BT_EDGES * 8) + (k0 & 7)] = bt_bf16(y0);
+              arow[(size_t)(k1 >> 3) * (BT_EDGES * 8) + (k1 & 7)] = bt_bf16(y1);
+              arow[(size_t)(k2 >> 3) * (BT_EDGES * 8) + (k2 & 7)] = bt_bf16(y2);
+            }
           }
         }
         tc::fence_async_smem();
         tc::fence_before_sync();
         if (bt_sync_or(fail)) { fail = 1; break; }                                        // [B2]
+        lap(1);
         // ---- 3. four layers ------------------------------------------------------------------------------------
         for (int l = 0; l < BT_LAYERS; l++) {
           {
@@ -313,6 +363,7 @@ bee_scalar_tc_kernel(BtParams P) {
           }
           accum_phase++;
           tc::fence_after_sync();
+          lap(2 + 2 * l);
           const int N = P.layer[l].N;
           if (!fail && l < BT_LAYERS - 1) {
             // bias, activation -> BF16 into the operand tile at out_col (this thread: row `row`, its half of the columns)
@@ -339,6 +390,7 @@ bee_scalar_tc_kernel(BtParams P) {
             tc::fence_before_sync();
           }
           if (bt_sync_or(fail)) { fail = 1; break; }                                      // [B3..B6]
+          if (l < BT_LAYERS - 1) lap(3 + 2 * l);
         }
         if (fail) break;
         // ---- 4. last layer's accumulators -> staging -> per-node sums -----------------------------------------
@@ -364,6 +416,7 @@ bee_scalar_tc_kernel(BtParams P) {
         }
         tc::fence_before_sync();
         bt_sync_workers();
+        lap(9);
         if (tid < A) {
           int c_node = tile_cur;
           float a_sum = acc;
@@ -394,9 +447,12 @@ bee_scalar_tc_kernel(BtParams P) {
           cur = c_node;
         }
         if (bt_sync_or(fail)) { fail = 1; break; }                                        // [B7]
+        lap(10);
       }
       if (!fail && n_begin < n_end) flush_until(cur, n_end, acc);
     }
+    if (P.prof != nullptr && tid == 0)
+      for (int i = 0; i < 12; i++) atomicAdd((unsigned long long*)&P.prof[i], (unsigned long long)pc[i]);
   }
   if (fail && lane == 0 && P.status != nullptr) atomicOr(P.status, LD_FLAG_TIMEOUT);
   __syncthreads();
@@ -412,8 +468,8 @@ extern "C" int ld_bee_messages_scalar_bf16_tc(const int* row_ptr, const int* dst
                                               int dim_a, float r0, const float* L0, const float* L1, const float* L2,
                                               const float* enc_w, const float* enc_b, const float* jacobi, const void* Yp,
                                               const void* W1p, const float* b1, const void* W2p, const float* b2,
-                                              const void* W3p, const float* b3, float scale, float* out_a, int* status_dev,
-                                              void* stream) {
+                                              const void* W3p, const float* b3, float scale, float* out_a, int feat_bf16,
+                                              int* status_dev, void* stream) {
   if (Nt < 0 || chan <= 0 || dim_a <= 0 || !(r0 > 0.f)) return LD_ERR_SHAPE;
   if (chan % 32 != 0 || chan > 256 || (dim_a != 64 && dim_a != 128)) {
     ld_set_last_message("bee messages (tensor-core path): chan must be a multiple of 32 up to 256, dim_a 64 or 128");
@@ -426,24 +482,25 @@ extern "C" int ld_bee_messages_scalar_bf16_tc(const int* row_ptr, const int* dst
   BtParams P;
   P.row_ptr = row_ptr; P.dst = dst; P.rij = rij; P.Nt = Nt; P.chan = C; P.dim_a = A; P.r0 = r0; P.scale = scale;
   P.L0 = L0; P.L1 = L1; P.L2 = L2; P.enc_w = enc_w; P.enc_b = enc_b; P.jacobi = jacobi;
-  P.layer[0] = BtLayer{(const __nv_bfloat16*)Yp, nullptr, 0, 3 * C / 16, A, 0, 2 * A};
-  P.layer[1] = BtLayer{(const __nv_bfloat16*)W1p, b1, 2 * A / 8, A / 16, 2 * A, 2, 0};
-  P.layer[2] = BtLayer{(const __nv_bfloat16*)W2p, b2, 0, 2 * A / 16, 2 * A, 2, 0};
-  P.layer[3] = BtLayer{(const __nv_bfloat16*)W3p, b3, 0, 3 * A / 16, A, 0, -1};
+  const int sk1 = BT_SLAB_BYTES / (A * 32), sk2 = BT_SLAB_BYTES / (2 * A * 32);
+  P.layer[0] = BtLayer{(const __nv_bfloat16*)Yp, nullptr, 0, 3 * C / 16, sk1, A, 0, 2 * A};
+  P.layer[1] = BtLayer{(const __nv_bfloat16*)W1p, b1, 2 * A / 8, A / 16, sk2, 2 * A, 2, 0};
+  P.layer[2] = BtLayer{(const __nv_bfloat16*)W2p, b2, 0, 2 * A / 16, sk2, 2 * A, 2, 0};
+  P.layer[3] = BtLayer{(const __nv_bfloat16*)W3p, b3, 0, 3 * A / 16, sk1, A, 0, -1};
   const int cols = 3 * (C > A ? C : A);
   const size_t a_bytes = (size_t)BT_EDGES * cols * 2;
   const size_t staging = (size_t)BT_EDGES * A * 4;
   const size_t front = a_bytes > staging ? a_bytes : staging;
-  P.slab_bytes = (unsigned)(BT_SLAB_KSTEPS * 2 * A * 32);
+  P.slab_bytes = (unsigned)BT_SLAB_BYTES;
   P.stage_off = (unsigned)front;
   P.bias_off = (unsigned)(front + (size_t)BT_STAGES * P.slab_bytes);
   const size_t smem = P.bias_off + (size_t)5 * A * 4 + 256;
   if (smem > 215 * 1024) { ld_set_last_message("bee messages (tensor-core path): shared-memory plan exceeds the limit"); return LD_ERR_UNSUPPORTED; }
   {
-    const long long seg = (40LL << 20) / (52LL * C);  // 13*chan floats gathered per neighbour
+    const long long seg = (40LL << 20) / ((feat_bf16 == 2 ? 32LL : feat_bf16 ? 26LL : 52LL) * C);  // 13*chan values gathered per neighbour
     P.seg_nodes = (int)(seg < 1024 ? 1024 : seg);
   }
-  P.out_a = out_a; P.status = status_dev;
+  P.out_a = out_a; P.status = status_dev; P.feat_bf16 = feat_bf16; P.prof = ld_internal_phase_counters();
   LD_CUDA_TRY(cudaFuncSetAttribute(bee_scalar_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

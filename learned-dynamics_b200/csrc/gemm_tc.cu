@@ -28,6 +28,9 @@ struct GemmParams {
   const float* bias;
   long long rows;            // logical rows = rows_outer * S
   int K, N, S, act;
+  int out_bf16;              // y is BF16 instead of FP32
+  long long y_ld_row, y_ld_col; // BF16 output addressing: element (r, o, s) at r*y_ld_row + o*y_ld_col + s + y_off
+  int y_off;
   int* status;
 };
 
@@ -131,14 +134,16 @@ gemm_tc_kernel(GemmParams P) {
     if (!ok) break;
     tc::fence_after_sync();
     float* yrow = P.y + (ro * N) * S + rs;
+    __nv_bfloat16* yrow16 = reinterpret_cast<__nv_bfloat16*>(P.y) + ro * P.y_ld_row + rs + P.y_off;
     for (int cb = 0; cb < N; cb += 32) {
       float v[32];
       tc::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + cb, v);
       if (row_ok) {
 #pragma unroll
         for (int j = 0; j < 32; j++) {
-          float t = v[j] + (P.bias != nullptr ? __ldg(P.bias + cb + j) : 0.f);
-          yrow[(size_t)(cb + j) * S] = act_apply(t, P.act);
+          const float t = act_apply(v[j] + (P.bias != nullptr ? __ldg(P.bias + cb + j) : 0.f), P.act);
+          if (P.out_bf16) yrow16[(size_t)(cb + j) * P.y_ld_col] = __float2bfloat16_rn(t);
+          else yrow[(size_t)(cb + j) * S] = t;
         }
       }
     }
@@ -195,20 +200,46 @@ extern "C" int ld_pack_weights_bf16(const float* W, long long sw0, long long sw1
 // y = act(x W^T + b) on the tensor cores. x: FP32 [rows_outer, K, S] contiguous, y: [rows_outer, N, S].
 // S in {1,3,9}; N a multiple of 32, N <= 512. wp from ld_pack_weights_bf16. status_dev: optional
 // device int32 that receives LD_FLAG_TIMEOUT if a bounded wait ran out.
-extern "C" int ld_linear_bf16_tc(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias,
-                                 int N, int act, float* y, int* status_dev, void* stream) {
+static int linear_tc_launch(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias, int N, int act,
+                            void* y, int out_bf16, long long ld_row, long long ld_col, int off, int* status_dev, void* stream) {
   if (rows_outer < 0 || K <= 0 || N <= 0 || (S != 1 && S != 3 && S != 9)) return LD_ERR_SHAPE;
   if (N % 32 != 0 || N > 512) { ld_set_last_message("tensor-core linear: N must be a multiple of 32, at most 512"); return LD_ERR_UNSUPPORTED; }
   if (((uintptr_t)wp) % 16 != 0) { ld_set_last_message("tensor-core linear: packed weights must be 16-byte aligned"); return LD_ERR_SHAPE; }
   if (rows_outer == 0) return LD_OK;
   GemmParams P;
-  P.x = x; P.y = y; P.wp = (const __nv_bfloat16*)wp; P.bias = bias; P.rows = rows_outer * S; P.K = K; P.N = N; P.S = S;
+  P.x = x; P.y = (float*)y; P.out_bf16 = out_bf16; P.y_ld_row = ld_row; P.y_ld_col = ld_col; P.y_off = off; P.wp = (const __nv_bfloat16*)wp; P.bias = bias; P.rows = rows_outer * S; P.K = K; P.N = N; P.S = S;
   P.act = act; P.status = status_dev;
   const size_t smem = 2 * GT_A_STAGE + 2 * (size_t)N * GT_KC * 2 + 1024;
   LD_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const long long ntiles = (P.rows + GT_ROWS - 1) / GT_ROWS;
-  const int grid = (int)(ntiles < gt_sm_count() ? ntiles : gt_sm_count());
+  // several blocks per SM hide the latency of the strided activation loads: as many as tensor memory
+  // (512 columns) and shared memory (about 220 KB) allow
+  int ncols = 32;
+  while (ncols < N) ncols <<= 1;
+  int per_sm = 512 / ncols;
+  const int by_smem = (int)((220 * 1024) / (smem + 2048));
+  if (per_sm > by_smem) per_sm = by_smem;
+  if (per_sm < 1) per_sm = 1;
+  if (per_sm > 4) per_sm = 4;
+  const long long slots = (long long)gt_sm_count() * per_sm;
+  const int grid = (int)(ntiles < slots ? ntiles : slots);
   gemm_tc_kernel<<<grid, GT_ROWS, smem, (cudaStream_t)stream>>>(P);
   LD_LAUNCH_CHECK();
   return LD_OK;
+}
+
+extern "C" int ld_linear_bf16_tc(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias,
+                                 int N, int act, float* y, int* status_dev, void* stream) {
+  return linear_tc_launch(x, rows_outer, K, S, wp, bias, N, act, y, 0, (long long)N * S, S, 0, status_dev, stream);
+}
+
+// same, with the result rounded to BF16 and free output addressing: element (r, o, s) is written to
+// y_bf16[r*ld_row + o*ld_col + s + off]. ld_row = N*S, ld_col = S, off = 0 gives the plain [rows, N, S]
+// layout; the l<=2 message layer uses ld_row = 16*N, ld_col = 16 and off = 0 / 1 / 4 to interleave its
+// rank-0/1/2 left operands as [node][channel][16] (32 bytes per channel: one load per edge and channel
+// in the fused edge kernels instead of thirteen).
+extern "C" int ld_linear_bf16_tc_out16(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias,
+                                       int N, int act, void* y_bf16, long long ld_row, long long ld_col, int off,
+                                       int* status_dev, void* stream) {
+  return linear_tc_launch(x, rows_outer, K, S, wp, bias, N, act, y_bf16, 1, ld_row, ld_col, off, status_dev, stream);
 }

@@ -479,6 +479,8 @@ long long* g_prof_buffer = nullptr;
 // Diagnostics: device buffer of 16 int64 that later ld_painn_message_bf16_tc launches add per-phase
 // cycle counts to (summed over blocks); NULL switches it off. Not thread safe.
 extern "C" int ld_debug_set_phase_counters(long long* device_buffer16) { g_prof_buffer = device_buffer16; return LD_OK; }
+// the same buffer for the other fused tensor-core kernels of this library
+long long* ld_internal_phase_counters() { return g_prof_buffer; }
 
 // Tensor-core variant of ld_painn_message_f32 (same graph / feature arguments). w1p/w2p/w3p are the
 // distance-MLP weights packed by ld_pack_weights_bf16 ([4n][n_rbf], [4n][4n], [4n][4n]); biases FP32.

@@ -183,6 +183,30 @@ __device__ __forceinline__ void ldg_v8(const float* p, float* v) {
                : "l"(p));
 }
 
+// 32-byte read-only load, raw words (lets several loads be in flight before any is unpacked)
+__device__ __forceinline__ void ldg_raw8(const void* p, uint32_t* w) {
+  asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+               : "l"(p));
+}
+// BF16 element i (0..15) of eight raw words, widened to FP32
+__device__ __forceinline__ float bf16_at(const uint32_t* w, int i) {
+  return (i & 1) ? __uint_as_float(w[i >> 1] & 0xffff0000u) : __uint_as_float(w[i >> 1] << 16);
+}
+
+// 32-byte read-only load of sixteen BF16 values, widened to FP32
+__device__ __forceinline__ void ldg_bf16x16(const void* p, float* v) {
+  uint32_t w[8];
+  asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+               : "l"(p));
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
 // SiLU through the hardware tanh: x*sigmoid(x) = h + h*tanh(h), h = x/2 (relative error ~1e-3,
 // used only where the result is rounded to BF16 afterwards)
 __device__ __forceinline__ float silu_fast(float x) {

@@ -35,10 +35,11 @@ SIGNATURES = {
     "ld_mlp3_rows": [P, LL, I, P, P, I, P, P, I, P, P, I, I, P, P, P],
     "ld_pack_weights_bf16": [P, LL, LL, I, I, P, P],
     "ld_linear_bf16_tc": [P, LL, I, I, P, P, I, I, P, P, P],
+    "ld_linear_bf16_tc_out16": [P, LL, I, I, P, P, I, I, P, LL, LL, I, P, P],
     "ld_painn_message_bf16_tc": [P, P, P, I, I, I, I, F, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P],
     "ld_debug_set_phase_counters": [P],
-    "ld_bee_messages_scalar_bf16_tc": [P, P, P, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P, P, P, F, P, P, P],
-    "ld_bee_messages_vd_f32": [P, P, P, I, I, F, P, P, P, P, P, P, F, P, P, P],
+    "ld_bee_messages_scalar_bf16_tc": [P, P, P, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P, P, P, F, P, I, P, P],
+    "ld_bee_messages_vd_f32": [P, P, P, I, I, F, P, P, P, P, P, P, F, P, P, I, P],
     "ld_bee_messages_scalar_f32": [P, P, P, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P, F, P, P],
     "ld_painn_message_f32": [P, P, P, I, I, I, I, F, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P],
 }

@@ -113,9 +113,20 @@ class Messages(nn.Module):
         batch, nodes = x_a.shape[0], x_a.shape[1]
         Nt, C, dev = batch * nodes, self.chan, x_a.device
         w = self._pack()
-        l0 = self.L0(x_a.reshape(Nt, -1))
-        l1 = self.L1(x_v.reshape(Nt, -1, 3))
-        l2 = self.L2(x_d.reshape(Nt, -1, 3, 3))
+        feat16 = self.precision == "bf16" and C % 32 == 0 and C <= 512
+        if feat16:
+            # left operands straight to BF16, interleaved per channel as [node][chan][16] = (l0, l1[3], l2[9], pad):
+            # the edge kernels fetch all thirteen values of a (neighbour, channel) with one 32-byte load
+            pk = lambda m: m._packed_for(ops)
+            lp = torch.empty(Nt, C, 16, dtype=torch.bfloat16, device=dev)
+            ops.linear_bf16_tc(x_a.reshape(Nt, -1), pk(self.L0), C, inds=0, out=lp, out_layout=(16 * C, 16, 0))
+            ops.linear_bf16_tc(x_v.reshape(Nt, -1, 3), pk(self.L1), C, inds=1, out=lp, out_layout=(16 * C, 16, 1))
+            ops.linear_bf16_tc(x_d.reshape(Nt, -1, 3, 3), pk(self.L2), C, inds=2, out=lp, out_layout=(16 * C, 16, 4))
+            l0 = l1 = l2 = lp
+        else:
+            l0 = self.L0(x_a.reshape(Nt, -1))
+            l1 = self.L1(x_v.reshape(Nt, -1, 3))
+            l2 = self.L2(x_d.reshape(Nt, -1, 3, 3))
         rij = r_ij.contiguous()
         S_v = torch.empty(Nt, 5 * C, 3, dtype=torch.float32, device=dev)
         S_d = torch.empty(Nt, 5 * C, 3, 3, dtype=torch.float32, device=dev)
@@ -124,14 +135,14 @@ class Messages(nn.Module):
         with KERNEL_TIMER.region("bee_messages_vd"):
             check(lib().ld_bee_messages_vd_f32(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, float(self.r0), ptr(l0),
                                                ptr(l1), ptr(l2), ptr(w["enc_w"]), ptr(w["enc_b"]), ptr(w["jac"]), 0.1,
-                                               ptr(S_v), ptr(S_d), st))
+                                               ptr(S_v), ptr(S_d), 2 if feat16 else 0, st))
         if self.precision == "bf16":
             with KERNEL_TIMER.region("bee_messages_scalar_tc"):
                 check(lib().ld_bee_messages_scalar_bf16_tc(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, self.dim_a,
                                                            float(self.r0), ptr(l0), ptr(l1), ptr(l2), ptr(w["enc_w"]),
                                                            ptr(w["enc_b"]), ptr(w["jac"]), ptr(w["Yp"]), ptr(w["W1p"]), ptr(w["b1"]),
                                                            ptr(w["W2p"]), ptr(w["b2"]), ptr(w["W3p"]), ptr(w["b3"]), 0.1, ptr(B_a),
-                                                           ptr(ops.tc_status(dev)), st))
+                                                           2 if feat16 else 0, ptr(ops.tc_status(dev)), st))
         else:
             with KERNEL_TIMER.region("bee_messages_scalar"):
                 check(lib().ld_bee_messages_scalar_f32(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, self.dim_a,

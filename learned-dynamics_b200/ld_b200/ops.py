@@ -245,8 +245,10 @@ def pack_weights_bf16(W):
     return out
 
 
-def linear_bf16_tc(x, W_packed, N, bias=None, act=ACT_NONE, inds=0):
-    """y[..., o, s] = act(sum_i W[o,i] x[..., i, s] + b[o]) on tcgen05 (BF16 operands, FP32 accumulate)."""
+def linear_bf16_tc(x, W_packed, N, bias=None, act=ACT_NONE, inds=0, out_bf16=False, out=None, out_layout=None):
+    """y[..., o, s] = act(sum_i W[o,i] x[..., i, s] + b[o]) on tcgen05 (BF16 operands, FP32 accumulate).
+    out_bf16: round the result to BF16. out / out_layout=(ld_row, ld_col, off): write BF16 element (r, o, s)
+    to out.flatten()[r*ld_row + o*ld_col + s + off] instead of a new tensor."""
     x = x.contiguous()
     require_cuda_f32(x, "x")
     S = 3 ** inds
@@ -257,10 +259,20 @@ def linear_bf16_tc(x, W_packed, N, bias=None, act=ACT_NONE, inds=0):
     for d in shape[:bd]:
         rows *= d
     shape[bd] = N
-    y = torch.empty(shape, dtype=torch.float32, device=x.device)
+    st, status = stream_ptr(x.device), ptr(tc_status(x.device))
     with KERNEL_TIMER.region("linear_bf16_tc"):
-        check(lib().ld_linear_bf16_tc(ptr(x), rows, K, S, ptr(W_packed), ptr(bias), N, act, ptr(y), ptr(tc_status(x.device)),
-                                      stream_ptr(x.device)))
+        if out is not None:
+            ld_row, ld_col, off = out_layout
+            check(lib().ld_linear_bf16_tc_out16(ptr(x), rows, K, S, ptr(W_packed), ptr(bias), N, act, ptr(out), ld_row, ld_col,
+                                                off, status, st))
+            return out
+        if out_bf16:
+            y = torch.empty(shape, dtype=torch.bfloat16, device=x.device)
+            check(lib().ld_linear_bf16_tc_out16(ptr(x), rows, K, S, ptr(W_packed), ptr(bias), N, act, ptr(y), N * S, S, 0,
+                                                status, st))
+            return y
+        y = torch.empty(shape, dtype=torch.float32, device=x.device)
+        check(lib().ld_linear_bf16_tc(ptr(x), rows, K, S, ptr(W_packed), ptr(bias), N, act, ptr(y), status, st))
     return y
 
 

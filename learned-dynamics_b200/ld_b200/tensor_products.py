@@ -23,13 +23,16 @@ class TensLinear(nn.Module):
         _, fan_in = self.W.shape
         nn.init.normal_(self.W, std=fan_in ** -0.5)
 
+    def _packed_for(self, ops_module):
+        key = (self.W.data_ptr(), self.W._version)
+        if self._packed_key != key:
+            self._packed, self._packed_key = ops_module.pack_weights_bf16(self.W.detach().float()), key
+        return self._packed
+
     def forward(self, x):
         if self.precision == "bf16" and not torch.is_grad_enabled() and x.is_cuda and self.W.shape[0] % 32 == 0 \
                 and self.W.shape[0] <= 512:
-            key = (self.W.data_ptr(), self.W._version)
-            if self._packed_key != key:
-                self._packed, self._packed_key = ops.pack_weights_bf16(self.W.detach().float()), key
-            return ops.linear_bf16_tc(x, self._packed, self.W.shape[0], None, ops.ACT_NONE, inds=self.inds)
+            return ops.linear_bf16_tc(x, self._packed_for(ops), self.W.shape[0], None, ops.ACT_NONE, inds=self.inds)
         return tensor_linear(self.inds, self.W, x.contiguous())
 
 
