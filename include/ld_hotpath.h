@@ -167,6 +167,30 @@ int ld_bee_messages_scalar_bf16_tc(const int* row_ptr, const int* dst, const flo
                                    const float* b2, const void* W3p, const float* b3, float scale, float* out_a,
                                    int feat_bf16, int* status_dev, void* stream);
 
+/* ---- dense-weight l<=2 products (Ant16) and the bare channel-wise product --------------------------
+ * Replace codegen_tensops_cuda.ant16_{o0,o1,o2,oc}_cuda and their _backward / _backleft / _wtsback
+ * companions (extensions/codegen_tensops/codegen_tensops.cpp:610-1517; einsum definitions
+ * managan/codegen_tensor_products.py:112-133) and the einsum of TensorProdBare
+ * (managan/tensor_products.py:91-108).
+ * product = position in 000,110,220,011,101,121,211,022,202,112,222,111,212. With
+ * U[b,(o,l),J] = sum_r P[o,l,r] x[b,r,J] (ld_tensor_linear with P viewed as [(o l), r]):
+ *   contract_left: y[b,o,K] (+)= sum_l c_IJK left[b,l,I] U[b,o,l,J]            (forward)
+ *   expand:        dU[b,o,l,J] = c_IJK left[b,l,I] dy[b,o,K]                    (dx = ld_tensor_linear(dU, P^T);
+ *                                                                               dP = ld_tensor_linear_dw(dU, x))
+ *   contract_out:  dleft[b,l,I] = sum_o c_IJK U[b,o,l,J] dy[b,o,K]
+ * c = the product's constant coupling (Kronecker deltas and the Levi-Civita symbol).
+ * ld_tensor_prod_bare: y[n, keep_l + keep_r] = sum_c a[n, keep_l + c] b[n, keep_r + c] with
+ * (inds_l + inds_r - inds_o) / 2 trailing indices contracted (mode 0); mode 1: a = dy, b = x_r -> dx_l;
+ * mode 2: a = dy, b = x_l -> dx_r. n counts (row, channel) pairs. */
+int ld_ant16_contract_left(int product, const float* left, const float* U, long long rows, int dim_o, int dim_l, float* y,
+                           int accumulate, void* stream);
+int ld_ant16_expand(int product, const float* left, const float* dy, long long rows, int dim_o, int dim_l, float* dU,
+                    void* stream);
+int ld_ant16_contract_out(int product, const float* U, const float* dy, long long rows, int dim_o, int dim_l, float* dleft,
+                          void* stream);
+int ld_tensor_prod_bare(int mode, int inds_l, int inds_r, int inds_o, const float* a, const float* b, long long n, float* out,
+                        void* stream);
+
 /* Diagnostics (no counterpart in the reference): per-phase cycle counters of the fused tensor-core
  * kernel, added into 16 device int64 by later launches; NULL switches them off. */
 int ld_debug_set_phase_counters(long long* device_buffer16);

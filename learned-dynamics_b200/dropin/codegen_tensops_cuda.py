@@ -1,11 +1,12 @@
-"""Drop-in for the Bee and Cow entry points of the reference's `codegen_tensops_cuda` module
-(extensions/codegen_tensops/codegen_tensops.cpp:1519-2011): same names, argument order and
-output order. The Ant16 family is not provided yet and raises on use."""
+"""Drop-in for the reference's `codegen_tensops_cuda` module
+(extensions/codegen_tensops/codegen_tensops.cpp:610-2011): the Bee, Cow and Ant16 entry points with
+the same names, argument order and output order (every function returns a list of tensors)."""
 import os
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from ld_b200 import ops as _ops  # noqa: E402
+from ld_b200 import ant16 as _ant16  # noqa: E402
 
 
 def set_kern_attributes():
@@ -49,14 +50,15 @@ def cow_o1_bwr_cuda(l_0, l_1, dy_011, dy_101, dy_111):
     return _ops.cow_o1_bw(False, l_0, l_1, dy_011, dy_101, dy_111)
 
 
-def _ant16_missing(name):
-    def f(*a, **k):
-        raise NotImplementedError(f"{name}: the Ant16 dense-P contraction kernels are not built in this library")
+def _ant16_entry(name, fn):
+    def f(*args):
+        return fn(*args)
     f.__name__ = name
+    f.__doc__ = fn.__doc__
     return f
 
 
 for _o in ("o0", "o1", "o2", "oc"):
     for _suffix in ("", "_backward", "_backleft", "_wtsback"):
         _n = f"ant16_{_o}{_suffix}_cuda"
-        globals()[_n] = _ant16_missing(_n)
+        globals()[_n] = _ant16_entry(_n, getattr(_ant16, f"ant16_{_o}{_suffix}"))

@@ -38,6 +38,10 @@ SIGNATURES = {
     "ld_linear_bf16_tc_out16": [P, LL, I, I, P, P, I, I, P, LL, LL, I, P, P],
     "ld_painn_message_bf16_tc": [P, P, P, I, I, I, I, F, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P],
     "ld_debug_set_phase_counters": [P],
+    "ld_ant16_contract_left": [I, P, P, LL, I, I, P, I, P],
+    "ld_ant16_expand": [I, P, P, LL, I, I, P, P],
+    "ld_ant16_contract_out": [I, P, P, LL, I, I, P, P],
+    "ld_tensor_prod_bare": [I, I, I, I, P, P, LL, P, P],
     "ld_bee_messages_scalar_bf16_tc": [P, P, P, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P, P, P, F, P, I, P, P],
     "ld_bee_messages_vd_f32": [P, P, P, I, I, F, P, P, P, P, P, P, F, P, P, I, P],
     "ld_bee_messages_scalar_f32": [P, P, P, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P, F, P, P],

@@ -116,6 +116,60 @@ def cow1(l_0, l_1, r_0, r_1):
             torch.einsum("bcx, bcy, xyz -> bcz", l_1, r_1, lc))
 
 
+def ant16(x_0, x_1, x_2, *pl):
+    """managan/codegen_tensor_products.py:112-133: the dense-weight products; pl = (P, left) pairs in the order
+    000,110,220, 011,101,121,211,111, 022,202,112,222,212 (Ant16.forward's argument order, :22-25)."""
+    lc = levi_civita().to(x_0.dtype)
+    (P_000, l_000, P_110, l_110, P_220, l_220, P_011, l_011, P_101, l_101, P_121, l_121, P_211, l_211, P_111, l_111,
+     P_022, l_022, P_202, l_202, P_112, l_112, P_222, l_222, P_212, l_212) = pl
+    y_0 = (torch.einsum("bl, br, olr -> bo", l_000, x_0, P_000) + torch.einsum("blx, brx, olr -> bo", l_110, x_1, P_110)
+           + torch.einsum("blxy, brxy, olr -> bo", l_220, x_2, P_220))
+    y_1 = (torch.einsum("bl, brx, olr -> box", l_011, x_1, P_011) + torch.einsum("blx, br, olr -> box", l_101, x_0, P_101)
+           + torch.einsum("blx, bryx, olr -> boy", l_121, x_2, P_121) + torch.einsum("blxy, bry, olr -> box", l_211, x_1, P_211)
+           + torch.einsum("blx, bry, olr, xyz -> boz", l_111, x_1, P_111, lc))
+    y_2 = (torch.einsum("bl, brxy, olr -> boxy", l_022, x_2, P_022) + torch.einsum("blxy, br, olr -> boxy", l_202, x_0, P_202)
+           + torch.einsum("blx, bry, olr -> boxy", l_112, x_1, P_112) + torch.einsum("blxy, brzy, olr -> boxz", l_222, x_2, P_222)
+           + torch.einsum("blxy, brz, olr, yzw -> boxw", l_212, x_1, P_212, lc))
+    return y_0, y_1, y_2
+
+
+def tensor_prod_bare(inds_l, inds_r, inds_o, x_l, x_r):
+    """managan/tensor_products.py:91-108: contract the trailing (inds_l + inds_r - inds_o) / 2 indices"""
+    contracts = (inds_l + inds_r - inds_o) // 2
+    letters = "ijklmn"[:inds_l + inds_r - contracts]
+    c, keep_l, keep_r = letters[:contracts], letters[contracts:inds_l], letters[inds_l:]
+    return torch.einsum(f"...{keep_l + c}, ...{keep_r + c} -> ...{keep_l + keep_r}", x_l, x_r)
+
+
+class OTensorProds(nn.Module):
+    """managan/tensor_products.py:111-123"""
+
+    def __init__(self, inds_l, inds_r, inds_o, dim_l, dim_r, dim_o, rank):
+        super().__init__()
+        self.ranks = (inds_l, inds_r, inds_o)
+        self.lin_l, self.lin_r, self.lin_o = OTensLinear(inds_l, dim_l, rank), OTensLinear(inds_r, dim_r, rank), OTensLinear(inds_o, rank, dim_o)
+
+    def forward(self, x_l, x_r):
+        return self.lin_o(tensor_prod_bare(*self.ranks, self.lin_l(x_l), self.lin_r(x_r)))
+
+
+class OAVDFullTensorProds(nn.Module):
+    """managan/tensor_products.py:250-265"""
+
+    def __init__(self, dim_a, dim_v, dim_d, rank):
+        super().__init__()
+        dims = {0: dim_a, 1: dim_v, 2: dim_d}
+        for code in ("000", "101", "110", "112", "202", "211", "220", "222"):
+            l, r, o = (int(ch) for ch in code)
+            setattr(self, "tp" + code, OTensorProds(l, r, o, dims[l], dims[r], dims[o], rank))
+
+    def forward(self, x_a, x_v, x_d):
+        y_a = self.tp000(x_a, x_a) + self.tp110(x_v, x_v) + self.tp220(x_d, x_d)
+        y_v = self.tp101(x_v, x_a) + self.tp211(x_d, x_v)
+        y_d = self.tp112(x_v, x_v) + self.tp202(x_d, x_a) + self.tp222(x_d, x_d)
+        return y_a, y_v, y_d
+
+
 # ---- radial encodings ---------------------------------------------------------------------------
 def radial_encode_painn(r, n, rmax):
     """archs/meanflow_painn8.py:25-35"""

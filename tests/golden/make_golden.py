@@ -174,6 +174,29 @@ def main():
         B_a, B_v, B_d = mes(graph, r_ij, y_a, y_v, y_d)
     gold["bee_messages"] = {"dims": (16, 8, 8, 16), "x_a": y_a, "x_v": y_v, "x_d": y_d, "state": mes.state_dict(),
                             "out": (B_a, B_v, B_d)}
+    # --- Ant16 dense-weight products: the reference's einsum refimpl (managan/codegen_tensor_products.py:112-133)
+    #     with autograd gradients for seeded cotangents; (P, left) pairs in Ant16.forward's argument order ----
+    nb, d0, d1, d2, dl = 5, 8, 6, 4, 3
+    sfx = {0: (), 1: (3,), 2: (3, 3)}
+    dims = {0: d0, 1: d1, 2: d2}
+    order = ["000", "110", "220", "011", "101", "121", "211", "111", "022", "202", "112", "222", "212"]
+    a_in = [torch.randn(nb, dims[r], *sfx[r], generator=g, requires_grad=True) for r in (0, 1, 2)]
+    for name in order:
+        rl, rr, ro = int(name[0]), int(name[1]), int(name[2])
+        a_in.append(torch.randn(dims[ro], dl, dims[rr], generator=g, requires_grad=True))
+        a_in.append(torch.randn(nb, dl, *sfx[rl], generator=g, requires_grad=True))
+    a_out = refimpl_ns["ant16_refimpl"](*a_in)
+    cot = [torch.randn(t.shape, generator=g) for t in a_out]
+    a_grads = torch.autograd.grad(sum((y * c).sum() for y, c in zip(a_out, cot)), a_in)
+    gold["ant16"] = {"inputs": [t.detach() for t in a_in], "outputs": [t.detach() for t in a_out], "cotangents": cot,
+                     "grads": list(a_grads)}
+    # --- AVDFullTensorProds (managan/tensor_products.py:250-265), dims (8, 6, 4), rank 5 -----------------
+    torch.manual_seed(13)
+    avd = tp.AVDFullTensorProds(8, 6, 4, 5)
+    z_a, z_v, z_d = (torch.randn(2, 7, dims[r], *sfx[r], generator=g) for r in (0, 1, 2))
+    with torch.no_grad():
+        avd_out = avd(z_a, z_v, z_d)
+    gold["avd_tensor_prods"] = {"dims": (8, 6, 4, 5), "inputs": (z_a, z_v, z_d), "state": avd.state_dict(), "out": avd_out}
     # --- the reference's own hand-computed graph test (managan/graph_layers.py:80-124) ------------
     gold["graph_kat"] = {
         "positions": torch.tensor([[[0., 0., -1.], [1., 0., 0.], [3., 0., 0.], [2., 1., 0.], [8., 0., 0.]]]),

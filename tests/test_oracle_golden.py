@@ -106,3 +106,25 @@ def test_bee_messages_layer(golden):
     for inds, key, x in ((1, "tgn1_out", n["xv"]), (2, "tgn2_out", n["xd"])):
         gn = R.OTensGroupNorm(inds, 8, 4 if inds == 1 else 2)
         assert torch.allclose(gn(x), n[key], rtol=1e-5, atol=1e-6)
+
+
+def test_ant16_against_reference_einsums(golden):
+    """outputs and all 29 gradients of the dense-weight products vs the reference's own einsum refimpl"""
+    a = golden["ant16"]
+    ins = [t.clone().requires_grad_(True) for t in a["inputs"]]
+    outs = R.ant16(*ins)
+    for mine, ref in zip(outs, a["outputs"]):
+        assert torch.allclose(mine, ref, rtol=1e-5, atol=1e-5)
+    grads = torch.autograd.grad(sum((y * c).sum() for y, c in zip(outs, a["cotangents"])), ins)
+    for mine, ref in zip(grads, a["grads"]):
+        assert torch.allclose(mine, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_avd_tensor_prods(golden):
+    a = golden["avd_tensor_prods"]
+    mod = R.OAVDFullTensorProds(*a["dims"])
+    mod.load_state_dict(a["state"])
+    with torch.no_grad():
+        outs = mod(*a["inputs"])
+    for mine, ref in zip(outs, a["out"]):
+        assert torch.allclose(mine, ref, rtol=1e-5, atol=1e-5)
