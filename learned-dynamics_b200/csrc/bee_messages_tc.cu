@@ -3,7 +3,7 @@
 //   psi_e = [y_000 | y_110 | y_220] Y^T ;  out_e = psi_e + lin_direct(psi_e) + layers(psi_e)
 //   B_a[i] = scale * sum_{e: src_e = i} out_e
 // as four tcgen05 GEMMs per 128-edge tile (BF16 operands, FP32 accumulation in tensor memory;
-// 2e-2 relative). Same block structure as the fused PaiNN kernel (painn_message_tc.cu): 8 working
+// 2e-2 relative). Same block structure as the fused PaiNN kernel (painn_message_tc.cu): 16 working
 // warps build the operand tile and run the epilogues, one warp issues MMAs, one warp streams
 // weight slabs from L2 with bulk copies; node-aligned CSR slices, one write per node, no atomics.
 //
@@ -20,7 +20,7 @@ long long* ld_internal_phase_counters();  // diagnostics buffer set by ld_debug_
 namespace {
 
 constexpr int BT_EDGES = 128;
-constexpr int BT_WORK_WARPS = 8;
+constexpr int BT_WORK_WARPS = 16;     // four warps per 32-lane quarter of tensor memory; each takes a quarter of the columns
 constexpr int BT_WORK_THREADS = BT_WORK_WARPS * 32;
 constexpr int BT_MMA_WARP = BT_WORK_WARPS;
 constexpr int BT_PROD_WARP = BT_WORK_WARPS + 1;
@@ -131,6 +131,7 @@ __device__ __forceinline__ unsigned short bt_bf16(float v) {
   return *reinterpret_cast<unsigned short*>(&h);
 }
 
+template <bool PROF>
 __global__ void __launch_bounds__(BT_THREADS, 1)
 bee_scalar_tc_kernel(BtParams P) {
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -145,7 +146,7 @@ bee_scalar_tc_kernel(BtParams P) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool mma_lane = warp == BT_MMA_WARP && lane == 0;
   const bool prod_lane = warp == BT_PROD_WARP && lane == 0;
-  const int quarter = warp & 3, half = (warp >> 2) & 1;
+  const int quarter = warp & 3, part = (warp >> 2) & 3;  // TMEM lane quarter (fixed by the warp id), column part
   const int row = quarter * 32 + lane;
   const int C = P.chan, A = P.dim_a;
   unsigned char* a_smem = smem;                                   // 128 x max(3C, 3A) BF16, overlaid by the staging tile
@@ -235,16 +236,18 @@ bee_scalar_tc_kernel(BtParams P) {
   } else {
     // ===== working warps =========================================================================================
     uint32_t accum_phase = 0;
-    long long pc[12];
+    long long pc[PROF ? 12 : 1];
 #pragma unroll
-    for (int i = 0; i < 12; i++) pc[i] = 0;
-    long long tprev = clock64();
-    auto lap = [&](int i) { const long long t = clock64(); pc[i] += t - tprev; tprev = t; };
+    for (int i = 0; i < (PROF ? 12 : 1); i++) pc[i] = 0;
+    long long tprev = PROF ? clock64() : 0;
+    auto lap = [&](int i) {
+      if (PROF) { const long long t = clock64(); pc[i] += t - tprev; tprev = t; }
+    };
     auto flush_until = [&](int from, int next, float value) {
       if (tid < A)
         for (int v = from; v < next; v++) P.out_a[(size_t)v * A + tid] = (v == from ? value : 0.f) * P.scale;
     };
-    // product role: channel c, every second edge (both halves of a warp-uniform edge stay coalesced)
+    // product role: channel c, every pc_stride-th edge (the lanes of a warp share the edge, so loads stay coalesced)
     const int pc_c = tid % C, pc_h = tid / C, pc_stride = BT_WORK_THREADS / C;
     float w8[8], wb = 0.f;
     if (pc_h < pc_stride) {
@@ -369,7 +372,8 @@ bee_scalar_tc_kernel(BtParams P) {
             // bias, activation -> BF16 into the operand tile at out_col (this thread: row `row`, its half of the columns)
             const float* bias = l == 0 ? nullptr : s_bias + (l - 1) * 2 * A;
             const int act = P.layer[l].act, oc = P.layer[l].out_col;
-            for (int cb = half * (N / 2); cb < (half + 1) * (N / 2); cb += 32) {
+            const int cpp = max(N / 4, 32);  // columns per part
+            for (int cb = part * cpp; cb < min((part + 1) * cpp, N); cb += 32) {
               float v[32];
               tc::tmem_ld32(tmem_row + cb, v);
 #pragma unroll
@@ -399,7 +403,8 @@ bee_scalar_tc_kernel(BtParams P) {
         if (tid <= BT_EDGES) s_rowwin[tid] = P.row_ptr[min(node_lo + tid, n_end)];
         {
           const float* bias = s_bias + 4 * A;
-          for (int cb = half * (A / 2); cb < (half + 1) * (A / 2); cb += 32) {
+          const int cpp = max(A / 4, 32);
+          for (int cb = part * cpp; cb < min((part + 1) * cpp, A); cb += 32) {
             float v[32];
             tc::tmem_ld32(tmem_row + cb, v);
 #pragma unroll
@@ -451,7 +456,7 @@ bee_scalar_tc_kernel(BtParams P) {
       }
       if (!fail && n_begin < n_end) flush_until(cur, n_end, acc);
     }
-    if (P.prof != nullptr && tid == 0)
+    if (PROF && P.prof != nullptr && tid == 0)
       for (int i = 0; i < 12; i++) atomicAdd((unsigned long long*)&P.prof[i], (unsigned long long)pc[i]);
   }
   if (fail && lane == 0 && P.status != nullptr) atomicOr(P.status, LD_FLAG_TIMEOUT);
@@ -501,10 +506,11 @@ extern "C" int ld_bee_messages_scalar_bf16_tc(const int* row_ptr, const int* dst
     P.seg_nodes = (int)(seg < 1024 ? 1024 : seg);
   }
   P.out_a = out_a; P.status = status_dev; P.feat_bf16 = feat_bf16; P.prof = ld_internal_phase_counters();
-  LD_CUDA_TRY(cudaFuncSetAttribute(bee_scalar_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  auto kern = P.prof != nullptr ? bee_scalar_tc_kernel<true> : bee_scalar_tc_kernel<false>;
+  LD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  bee_scalar_tc_kernel<<<sms, BT_THREADS, smem, (cudaStream_t)stream>>>(P);
+  kern<<<sms, BT_THREADS, smem, (cudaStream_t)stream>>>(P);
   LD_LAUNCH_CHECK();
   return LD_OK;
 }
