@@ -26,7 +26,7 @@
 namespace {
 
 constexpr int MT_EDGES = 128;          // edges per tile = MMA M
-constexpr int MT_WORK_WARPS = 8;       // TMEM lane quarter = warp % 4, column half = warp / 4
+constexpr int MT_WORK_WARPS = 16;      // TMEM lane quarter = warp % 4, column part = warp / 4
 constexpr int MT_WORK_THREADS = MT_WORK_WARPS * 32;
 constexpr int MT_MMA_WARP = MT_WORK_WARPS;
 constexpr int MT_PROD_WARP = MT_WORK_WARPS + 1;
@@ -110,6 +110,7 @@ __device__ __forceinline__ int sync_or(int flag) {
 // barrier 2: working warps only
 __device__ __forceinline__ void sync_workers() { asm volatile("barrier.cta.sync 2, %0;" ::"n"(MT_WORK_THREADS) : "memory"); }
 
+template <bool PROF>
 __global__ void __launch_bounds__(MT_THREADS_TC, 1)
 painn_message_tc_kernel(TcMessageParams P) {
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -124,7 +125,7 @@ painn_message_tc_kernel(TcMessageParams P) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool mma_lane = warp == MT_MMA_WARP && lane == 0;
   const bool prod_lane = warp == MT_PROD_WARP && lane == 0;
-  const int quarter = warp & 3, half = (warp >> 2) & 1;
+  const int quarter = warp & 3, part = (warp >> 2) & 3;
   const int row = quarter * 32 + lane;  // edge slot / TMEM lane owned in the epilogues
   const int n = P.n, N = 4 * n;
   // dynamic shared memory: [ A operand tile, overlaid by the reduction staging | weight ring | biases ]
@@ -155,9 +156,9 @@ painn_message_tc_kernel(TcMessageParams P) {
   const int seg_nodes = P.seg_nodes > 0 ? P.seg_nodes : P.Nt;
   const int k0steps = P.k0p / 16, ksteps = N / 16;
   const int npass = (n + MT_CG - 1) / MT_CG;
-  long long pc[MT_PROF_SLOTS];
+  long long pc[PROF ? MT_PROF_SLOTS : 1];
 #pragma unroll
-  for (int i = 0; i < MT_PROF_SLOTS; i++) pc[i] = 0;
+  for (int i = 0; i < (PROF ? MT_PROF_SLOTS : 1); i++) pc[i] = 0;
   int fail = 0;
 
   if (warp == MT_PROD_WARP) {
@@ -173,9 +174,9 @@ painn_message_tc_kernel(TcMessageParams P) {
           for (int ks = 0; ks < steps; ks += MT_SLAB_KSTEPS, loads++) {
             const uint32_t st = loads % nst, use = loads / nst;
             const uint32_t bytes = (uint32_t)min(MT_SLAB_KSTEPS, steps - ks) * N * 32;
-            const long long t0 = clock64();
+            const long long t0 = PROF ? clock64() : 0;
             if (use >= 1 && !tc::mbar_wait(&bar_empty[st], (use - 1) & 1)) { fail = 1; break; }  // MMAs that read it are done
-            pc[10] += clock64() - t0;
+            if (PROF) pc[10] += clock64() - t0;
             tc::mbar_expect_tx(&bar_full[st], bytes);
             tc::bulk_g2s(b_smem + (size_t)st * slab, wp + (size_t)ks * N * 16, bytes, &bar_full[st]);
           }
@@ -203,9 +204,9 @@ painn_message_tc_kernel(TcMessageParams P) {
           const int steps = layer == 0 ? k0steps : ksteps;
           for (int ks0 = 0; ks0 < steps; ks0 += MT_SLAB_KSTEPS, mmas++) {
             const uint32_t st = mmas % nst, use = mmas / nst;
-            const long long t0 = clock64();
+            const long long t0 = PROF ? clock64() : 0;
             if (!tc::mbar_wait(&bar_full[st], use & 1)) { fail = 1; break; }
-            pc[9] += clock64() - t0;
+            if (PROF) pc[9] += clock64() - t0;
             tc::fence_after_sync();
             const uint32_t b_base = tc::smem_u32(b_smem + (size_t)st * slab);
             for (int kk = 0; kk < MT_SLAB_KSTEPS && ks0 + kk < steps; kk++) {
@@ -232,14 +233,17 @@ painn_message_tc_kernel(TcMessageParams P) {
     // ===== working warps =========================================================================================
     // reduction role: column `tid` of the staging tile = (channel tid/4 of the pass, component tid%4)
     const int red_c = (tid >> 2) & (MT_CG - 1), red_k = tid & 3;
-    long long tprev = clock64();
-    auto lap = [&](int i) { const long long t = clock64(); pc[i] += t - tprev; tprev = t; };
+    long long tprev = PROF ? clock64() : 0;
+    auto lap = [&](int i) {
+      if (PROF) { const long long t = clock64(); pc[i] += t - tprev; tprev = t; }
+    };
     uint32_t accum_phase = 0;
+    const bool reducer = tid < MT_CG * 4;  // the staging tile has MT_CG * 4 columns, one per reducing thread
 
     auto flush_until = [&](int pass, int from, int next, float value) {
       // write node `from` (value), zero-fill (from, next) for this pass's channel
       const int c = pass * MT_CG + red_c;
-      if (c >= n) return;
+      if (c >= n || !reducer) return;
       for (int v = from; v < next; v++) {
         float val = (v == from) ? value : 0.f;
         if (red_k < 3) {
@@ -343,13 +347,14 @@ painn_message_tc_kernel(TcMessageParams P) {
         tc::fence_after_sync();
         lap(2 + 2 * layer);
         if (!fail && layer < 2) {
-          // bias + SiLU -> next operand tile (this thread: row `row`, columns of its half)
+          // bias + SiLU -> next operand tile (this thread: row `row`, columns of its part)
           const float* bias = s_bias + layer * N;
-          for (int cb = half * (N / 2); cb < (half + 1) * (N / 2); cb += 64) {
-            float v[64];
-            tc::tmem_ld64(tmem_row + cb, v);
+          const int cpp = ((N / 4 + 31) / 32) * 32;  // columns per part (N is a multiple of 32)
+          for (int cb = part * cpp; cb < min((part + 1) * cpp, N); cb += 32) {
+            float v[32];
+            tc::tmem_ld32(tmem_row + cb, v);
 #pragma unroll
-            for (int g8 = 0; g8 < 8; g8++) {
+            for (int g8 = 0; g8 < 4; g8++) {
               float t[8];
 #pragma unroll
               for (int j = 0; j < 8; j++) t[j] = tc::silu_fast(v[g8 * 8 + j] + bias[cb + g8 * 8 + j]);
@@ -378,9 +383,9 @@ painn_message_tc_kernel(TcMessageParams P) {
       // stage the row_ptr window of the next tile (read after the barrier that ends this tile)
       if (tid <= MT_EDGES) s_rowwin[tid] = P.row_ptr[min(node_lo + tid, n_end)];
       for (int pass = 0; pass < npass; pass++) {
-        // this thread: edge `row`, channels [pass*CG + half*CG/2, +CG/2) in groups of 8
-        for (int g8 = 0; g8 < MT_CG / 16; g8++) {
-          const int c0 = pass * MT_CG + half * (MT_CG / 2) + g8 * 8;
+        // this thread: edge `row`, channels [pass*CG + part*CG/4, +CG/4) in groups of 8
+        for (int g8 = 0; g8 < MT_CG / 32; g8++) {
+          const int c0 = pass * MT_CG + part * (MT_CG / 4) + g8 * 8;
           if (c0 < n) {  // n is a multiple of 8: a group is entirely valid or entirely not
             // 32-byte loads: every fetched sector is requested exactly once
             float a[32];
@@ -389,15 +394,18 @@ painn_message_tc_kernel(TcMessageParams P) {
             float xv[24];
 #pragma unroll
             for (int q8 = 0; q8 < 3; q8++) tc::ldg_v8(Xj + (size_t)c0 * 3 + 8 * q8, xv + 8 * q8);
-            float d[32];
-            tc::tmem_ld8x4(tmem_row + c0, (uint32_t)n, d);  // D[.., c0 + k*n + j] at d[k*8 + j]
+            // p_k = (D_k + b3_k) * actv_k in place, one 8-column read of tensor memory per k (keeps registers low)
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+              float d8[8];
+              tc::tmem_ld8(tmem_row + c0 + k * n, d8);
+#pragma unroll
+              for (int j = 0; j < 8; j++) a[k * 8 + j] *= d8[j] + b3[k * n + c0 + j];
+            }
 #pragma unroll
             for (int j = 0; j < 8; j++) {
               const int c = c0 + j;
-              const float p0 = (d[j] + b3[c]) * a[j];
-              const float p1 = (d[8 + j] + b3[n + c]) * a[8 + j];
-              const float p2 = (d[16 + j] + b3[2 * n + c]) * a[16 + j];
-              const float p3 = (d[24 + j] + b3[3 * n + c]) * a[24 + j];
+              const float p0 = a[j], p1 = a[8 + j], p2 = a[16 + j], p3 = a[24 + j];
               const float x0 = xv[3 * j], x1 = xv[3 * j + 1], x2 = xv[3 * j + 2];
               float4 m;
               m.x = x0 * p0 + (x1 * dir2 - x2 * dir1) * p1 + dir0 * p2;
@@ -415,7 +423,7 @@ painn_message_tc_kernel(TcMessageParams P) {
         sync_workers();
         lap(8);
         // sum per source node, in edge order; thread = one (channel, component) column
-        {
+        if (reducer) {
           int c_node = tile_cur;
           float a_sum = acc[pass];
           const int slot = red_c;
@@ -463,7 +471,7 @@ painn_message_tc_kernel(TcMessageParams P) {
     if (!fail && P.edge_counter != nullptr && tid == 0 && edges_done > 0)
       atomicAdd((unsigned long long*)P.edge_counter, (unsigned long long)edges_done);
   }
-  if (P.prof != nullptr && (tid == 0 || mma_lane || prod_lane)) {
+  if (PROF && P.prof != nullptr && (tid == 0 || mma_lane || prod_lane)) {
     for (int i = 0; i < MT_PROF_SLOTS; i++)
       if (pc[i]) atomicAdd((unsigned long long*)&P.prof[i], (unsigned long long)pc[i]);
   }
@@ -525,10 +533,11 @@ extern "C" int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, cons
   P.stage_off = (unsigned)front;
   P.bias_off = (unsigned)(front + ring);
   const size_t smem = front + ring + (size_t)3 * N * 4 + 1024;
-  LD_CUDA_TRY(cudaFuncSetAttribute(painn_message_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  auto kern = P.prof != nullptr ? painn_message_tc_kernel<true> : painn_message_tc_kernel<false>;
+  LD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  painn_message_tc_kernel<<<sms, MT_THREADS_TC, smem, (cudaStream_t)stream>>>(P);
+  kern<<<sms, MT_THREADS_TC, smem, (cudaStream_t)stream>>>(P);
   LD_LAUNCH_CHECK();
   return LD_OK;
 }
