@@ -134,12 +134,17 @@ int ld_linear_bf16_tc_out16(const float* x, long long rows_outer, int K, int S, 
 
 /* ld_painn_message_bf16_tc: ld_painn_message_f32 with the per-edge distance MLP on tcgen05
  * (BF16 operands, FP32 accumulation in tensor memory); same reference lines
- * (archs/meanflow_painn8.py:77-100). Weights packed by ld_pack_weights_bf16. 2e-2 relative. */
+ * (archs/meanflow_painn8.py:77-100). Weights packed by ld_pack_weights_bf16. 2e-2 relative.
+ * gather16 (optional, else NULL): the node features of the neighbours as BF16 records made by
+ * ld_painn_pack_gather from actv [Nt][4n] and x_v [Nt][n][3]; [Nt][n/8][64] BF16, per 8 channels the four
+ * actv planes, the 24 vector components and 8 unused values (128 bytes, four 32-byte loads per thread).
+ * With gather16 the kernel does not read actv / x_v. */
+int ld_painn_pack_gather(const float* actv, const float* x_v, int Nt, int n, void* out_bf16, void* stream);
 int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, const float* rij, int Nt, int n, int n_rbf, int radial_kind,
                              float rmax, float eps, const void* w1p, const float* b1, const void* w2p, const float* b2,
-                             const void* w3p, const float* b3, const float* actv, const float* x_v, const float* res_a,
-                             const float* res_v, float* out_a, float* out_v, long long* edge_counter, int* status_dev,
-                             void* stream);
+                             const void* w3p, const float* b3, const float* actv, const float* x_v, const void* gather16,
+                             const float* res_a, const float* res_v, float* out_a, float* out_v, long long* edge_counter,
+                             int* status_dev, void* stream);
 
 /* ---- fused l<=2 message layer ------------------------------------------------------------------------
  * Messages.forward (archs/diffuser_atoms15.py:227-253) without edge-sized tensors: the radial

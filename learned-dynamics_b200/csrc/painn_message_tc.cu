@@ -53,6 +53,7 @@ struct TcMessageParams {
   const __nv_bfloat16* w1; const __nv_bfloat16* w2; const __nv_bfloat16* w3;  // packed panels [K/8][4n][8]
   const float* b1; const float* b2; const float* b3;
   const float* actv; const float* x_v; const float* res_a; const float* res_v;
+  const uint32_t* g16;   // optional packed BF16 gather records [Nt][n/8][64] (see ld_painn_pack_gather); replaces actv / x_v
   float* out_a; float* out_v;
   long long* edge_counter;
   int* status;
@@ -110,7 +111,7 @@ __device__ __forceinline__ int sync_or(int flag) {
 // barrier 2: working warps only
 __device__ __forceinline__ void sync_workers() { asm volatile("barrier.cta.sync 2, %0;" ::"n"(MT_WORK_THREADS) : "memory"); }
 
-template <bool PROF>
+template <bool PROF, bool G16>
 __global__ void __launch_bounds__(MT_THREADS_TC, 1)
 painn_message_tc_kernel(TcMessageParams P) {
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -389,11 +390,23 @@ painn_message_tc_kernel(TcMessageParams P) {
           if (c0 < n) {  // n is a multiple of 8: a group is entirely valid or entirely not
             // 32-byte loads: every fetched sector is requested exactly once
             float a[32];
-#pragma unroll
-            for (int k = 0; k < 4; k++) tc::ldg_v8(Aj + k * n + c0, a + 8 * k);
             float xv[24];
+            if (G16) {
+              // one 128-byte BF16 record per (neighbour, 8 channels): actv planes 0..3 (8 values each), x_v (24), 8 unused
+              uint32_t raw[32];
+              const uint32_t* rec = P.g16 + ((size_t)j_node * (n >> 3) + (c0 >> 3)) * 32;
 #pragma unroll
-            for (int q8 = 0; q8 < 3; q8++) tc::ldg_v8(Xj + (size_t)c0 * 3 + 8 * q8, xv + 8 * q8);
+              for (int q = 0; q < 4; q++) tc::ldg_raw8(rec + 8 * q, raw + 8 * q);
+#pragma unroll
+              for (int i = 0; i < 32; i++) a[i] = tc::bf16_at(raw, i);
+#pragma unroll
+              for (int i = 0; i < 24; i++) xv[i] = tc::bf16_at(raw + 16, i);
+            } else {
+#pragma unroll
+              for (int k = 0; k < 4; k++) tc::ldg_v8(Aj + k * n + c0, a + 8 * k);
+#pragma unroll
+              for (int q8 = 0; q8 < 3; q8++) tc::ldg_v8(Xj + (size_t)c0 * 3 + 8 * q8, xv + 8 * q8);
+            }
             // p_k = (D_k + b3_k) * actv_k in place, one 8-column read of tensor memory per k (keeps registers low)
 #pragma unroll
             for (int k = 0; k < 4; k++) {
@@ -480,6 +493,32 @@ painn_message_tc_kernel(TcMessageParams P) {
   if (warp == 0) tc::tmem_dealloc(tmem_base, ncols);
 }
 
+// actv [Nt][4n] and x_v [Nt][n][3] (FP32) -> BF16 records [Nt][n/8][64]: for 8 consecutive channels c0..c0+7 the four
+// actv planes (8 values each, plane k = columns k*n + c), the 24 vector components, 8 unused values. 128 bytes, so a
+// fused-message thread fetches everything it needs of a neighbour with four 32-byte loads.
+__global__ void painn_pack_gather_kernel(const float* __restrict__ actv, const float* __restrict__ x_v, long long groups,
+                                         int n, uint4* __restrict__ out) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= groups) return;
+  const int gpn = n >> 3;
+  const long long node = idx / gpn;
+  const int c0 = (int)(idx % gpn) * 8;
+  float v[64];
+#pragma unroll
+  for (int k = 0; k < 4; k++) tc::ldg_v8(actv + node * 4 * n + k * n + c0, v + 8 * k);
+#pragma unroll
+  for (int q = 0; q < 3; q++) tc::ldg_v8(x_v + (node * n + c0) * 3 + 8 * q, v + 32 + 8 * q);
+#pragma unroll
+  for (int i = 56; i < 64; i++) v[i] = 0.f;
+#pragma unroll
+  for (int q = 0; q < 8; q++) {
+    uint4 w;
+    w.x = tc::pack_bf16x2(v[8 * q], v[8 * q + 1]); w.y = tc::pack_bf16x2(v[8 * q + 2], v[8 * q + 3]);
+    w.z = tc::pack_bf16x2(v[8 * q + 4], v[8 * q + 5]); w.w = tc::pack_bf16x2(v[8 * q + 6], v[8 * q + 7]);
+    out[idx * 8 + q] = w;
+  }
+}
+
 long long* g_prof_buffer = nullptr;
 
 }  // namespace
@@ -490,18 +529,36 @@ extern "C" int ld_debug_set_phase_counters(long long* device_buffer16) { g_prof_
 // the same buffer for the other fused tensor-core kernels of this library
 long long* ld_internal_phase_counters() { return g_prof_buffer; }
 
+extern "C" int ld_painn_pack_gather(const float* actv, const float* x_v, int Nt, int n, void* out_bf16, void* stream) {
+  if (Nt < 0 || n <= 0 || n % 8 != 0) return LD_ERR_SHAPE;
+  if ((((uintptr_t)actv | (uintptr_t)x_v | (uintptr_t)out_bf16) % 32) != 0) return LD_ERR_SHAPE;
+  const long long groups = (long long)Nt * (n / 8);
+  if (groups == 0) return LD_OK;
+  painn_pack_gather_kernel<<<(unsigned)((groups + 127) / 128), 128, 0, (cudaStream_t)stream>>>(actv, x_v, groups, n, (uint4*)out_bf16);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}
+
 // Tensor-core variant of ld_painn_message_f32 (same graph / feature arguments). w1p/w2p/w3p are the
 // distance-MLP weights packed by ld_pack_weights_bf16 ([4n][n_rbf], [4n][4n], [4n][4n]); biases FP32.
 // n a multiple of 8, n <= 128. status_dev receives LD_FLAG_TIMEOUT if a bounded wait ran out.
+// gather16 (optional): the node features as BF16 records written by ld_painn_pack_gather; the kernel then reads
+// 2 KB per neighbour (n = 128) instead of 3.5 KB and actv / x_v are not touched.
 extern "C" int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, const float* rij, int Nt, int n, int n_rbf,
                                         int radial_kind, float rmax, float eps, const void* w1p, const float* b1,
                                         const void* w2p, const float* b2, const void* w3p, const float* b3,
-                                        const float* actv, const float* x_v, const float* res_a, const float* res_v,
-                                        float* out_a, float* out_v, long long* edge_counter, int* status_dev, void* stream) {
+                                        const float* actv, const float* x_v, const void* gather16, const float* res_a,
+                                        const float* res_v, float* out_a, float* out_v, long long* edge_counter,
+                                        int* status_dev, void* stream) {
   if (Nt < 0 || n <= 0 || n_rbf <= 0) return LD_ERR_SHAPE;
   if (n % 8 != 0 || n > 128) { ld_set_last_message("painn message (tensor-core path): n must be a multiple of 8, at most 128"); return LD_ERR_UNSUPPORTED; }
   if (b1 == nullptr || b2 == nullptr || b3 == nullptr) { ld_set_last_message("painn message: biases are required"); return LD_ERR_SHAPE; }
-  if ((((uintptr_t)w1p | (uintptr_t)w2p | (uintptr_t)w3p) % 16) != 0 || (((uintptr_t)actv | (uintptr_t)x_v) % 32) != 0) {
+  if (gather16 == nullptr && (actv == nullptr || x_v == nullptr)) {
+    ld_set_last_message("painn message (tensor-core path): pass either actv and x_v or the packed gather records");
+    return LD_ERR_SHAPE;
+  }
+  if ((((uintptr_t)w1p | (uintptr_t)w2p | (uintptr_t)w3p) % 16) != 0 ||
+      (((uintptr_t)actv | (uintptr_t)x_v | (uintptr_t)gather16) % 32) != 0) {
     ld_set_last_message("painn message (tensor-core path): packed weights must be 16-byte, node features 32-byte aligned");
     return LD_ERR_SHAPE;
   }
@@ -510,7 +567,7 @@ extern "C" int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, cons
   P.row_ptr = row_ptr; P.dst = dst; P.rij = rij; P.Nt = Nt; P.n = n; P.n_rbf = n_rbf; P.k0p = (n_rbf + 15) / 16 * 16;
   P.radial_kind = radial_kind; P.rmax = rmax; P.pi_over_rmax = (float)(3.14159265358979323846 / (double)rmax); P.eps = eps;
   P.w1 = (const __nv_bfloat16*)w1p; P.w2 = (const __nv_bfloat16*)w2p; P.w3 = (const __nv_bfloat16*)w3p;
-  P.b1 = b1; P.b2 = b2; P.b3 = b3; P.actv = actv; P.x_v = x_v; P.res_a = res_a; P.res_v = res_v;
+  P.b1 = b1; P.b2 = b2; P.b3 = b3; P.actv = actv; P.x_v = x_v; P.g16 = (const uint32_t*)gather16; P.res_a = res_a; P.res_v = res_v;
   P.out_a = out_a; P.out_v = out_v; P.edge_counter = edge_counter; P.status = status_dev; P.prof = g_prof_buffer;
   const int N = 4 * n;
   if (P.k0p > N) { ld_set_last_message("painn message (tensor-core path): n_rbf above 4n is not supported"); return LD_ERR_UNSUPPORTED; }
@@ -533,7 +590,8 @@ extern "C" int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, cons
   P.stage_off = (unsigned)front;
   P.bias_off = (unsigned)(front + ring);
   const size_t smem = front + ring + (size_t)3 * N * 4 + 1024;
-  auto kern = P.prof != nullptr ? painn_message_tc_kernel<true> : painn_message_tc_kernel<false>;
+  auto kern = gather16 != nullptr ? (P.prof != nullptr ? painn_message_tc_kernel<true, true> : painn_message_tc_kernel<false, true>)
+                                  : (P.prof != nullptr ? painn_message_tc_kernel<true, false> : painn_message_tc_kernel<false, false>);
   LD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

@@ -36,7 +36,8 @@ SIGNATURES = {
     "ld_pack_weights_bf16": [P, LL, LL, I, I, P, P],
     "ld_linear_bf16_tc": [P, LL, I, I, P, P, I, I, P, P, P],
     "ld_linear_bf16_tc_out16": [P, LL, I, I, P, P, I, I, P, LL, LL, I, P, P],
-    "ld_painn_message_bf16_tc": [P, P, P, I, I, I, I, F, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P],
+    "ld_painn_message_bf16_tc": [P, P, P, I, I, I, I, F, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P],
+    "ld_painn_pack_gather": [P, P, I, I, P, P],
     "ld_debug_set_phase_counters": [P],
     "ld_ant16_contract_left": [I, P, P, LL, I, I, P, I, P],
     "ld_ant16_expand": [I, P, P, LL, I, I, P, P],
