@@ -36,6 +36,7 @@ struct BeeEdgeParams {
   const float* L0; const float* L1; const float* L2;   // [Nt,chan], [Nt,chan,3], [Nt,chan,9]
   const float* enc_w; const float* enc_b;               // lin_enc: [chan,8], [chan]
   const float* jacobi;                                  // [8][9] polynomial coefficients
+  int seg_nodes;                                        // nodes per scheduling segment (0: the whole range at once)
 };
 
 // first node v in [lo, hi] whose preceding work (edges + nodes) reaches target
@@ -48,12 +49,13 @@ __device__ __forceinline__ int bm_work_lower_bound(const int* __restrict__ row_p
   return lo;
 }
 
-__device__ __forceinline__ void bm_block_range(const int* __restrict__ row_ptr, int Nt, int* n_begin, int* n_end) {
-  const long long work = (long long)row_ptr[Nt] + Nt;
+// this block's slice of the node range [lo, hi), balanced over edges + nodes
+__device__ __forceinline__ void bm_block_range(const int* __restrict__ row_ptr, int lo, int hi, int* n_begin, int* n_end) {
+  const long long work = ((long long)row_ptr[hi] - row_ptr[lo]) + (hi - lo);
   long long per = (work + gridDim.x - 1) / gridDim.x;
   if (per < 1) per = 1;
-  *n_begin = blockIdx.x == 0 ? 0 : bm_work_lower_bound(row_ptr, 0, Nt, per * blockIdx.x);
-  *n_end = blockIdx.x == gridDim.x - 1 ? Nt : bm_work_lower_bound(row_ptr, 0, Nt, per * (blockIdx.x + 1));
+  *n_begin = blockIdx.x == 0 ? lo : bm_work_lower_bound(row_ptr, lo, hi, per * blockIdx.x);
+  *n_end = blockIdx.x == gridDim.x - 1 ? hi : bm_work_lower_bound(row_ptr, lo, hi, per * (blockIdx.x + 1));
 }
 
 // per-edge geometry shared by all channels: rhat[3] and the eight radial features
@@ -112,9 +114,13 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
   __shared__ float s_jac[72];
   for (int i = threadIdx.x; i < 72; i += blockDim.x) s_jac[i] = P.jacobi[i];
   __syncthreads();
-  int n_begin, n_end;
-  bm_block_range(P.row_ptr, P.Nt, &n_begin, &n_end);
   const int C = P.chan;
+  // all blocks walk the node range segment by segment, so that the neighbour rows a segment gathers (its nodes'
+  // neighbours are nearby nodes) stay resident in L2 while its edges are processed
+  const int seg_nodes = P.seg_nodes > 0 ? P.seg_nodes : P.Nt;
+  for (int seg_lo = 0; seg_lo < P.Nt; seg_lo += seg_nodes) {
+  int n_begin, n_end;
+  bm_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt), &n_begin, &n_end);
   for (int c0 = 0; c0 < C; c0 += blockDim.x) {   // channel groups (one pass when chan <= 128)
     const int c = c0 + threadIdx.x;
     const bool cok = c < C;
@@ -196,6 +202,7 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
       }
     }
   }
+  }
 }
 
 
@@ -231,7 +238,7 @@ bee_scalar_kernel(BeeScalarParams P) {
   const int ldo = A + 1;
   for (int i = tid; i < 72; i += MT_THREADS) s_jac[i] = P.g.jacobi[i];
   int n_begin, n_end;
-  bm_block_range(P.g.row_ptr, P.g.Nt, &n_begin, &n_end);
+  bm_block_range(P.g.row_ptr, 0, P.g.Nt, &n_begin, &n_end);
   if (n_begin >= n_end) return;
   const long long e_begin = P.g.row_ptr[n_begin], e_end = P.g.row_ptr[n_end];
   __syncthreads();
@@ -327,7 +334,9 @@ extern "C" int ld_bee_messages_vd_f32(const int* row_ptr, const int* dst, const 
                                       int feat_bf16, void* stream) {
   if (Nt < 0 || chan <= 0 || !(r0 > 0.f)) return LD_ERR_SHAPE;
   if (Nt == 0) return LD_OK;
-  BeeEdgeParams P{row_ptr, dst, rij, Nt, chan, r0, L0, L1, L2, enc_w, enc_b, jacobi};
+  // segment = about 40 MB of gathered rows (13 * chan values per node, 32 bytes per channel when interleaved)
+  const long long seg = (40LL << 20) / ((feat_bf16 == 2 ? 32LL : feat_bf16 ? 26LL : 52LL) * chan);
+  BeeEdgeParams P{row_ptr, dst, rij, Nt, chan, r0, L0, L1, L2, enc_w, enc_b, jacobi, (int)(seg < 1024 ? 1024 : seg)};
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (feat_bf16 == 2) bee_vd_kernel<__nv_bfloat16, true><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale);
@@ -350,7 +359,7 @@ extern "C" int ld_bee_messages_scalar_f32(const int* row_ptr, const int* dst, co
   if ((((uintptr_t)Yt | (uintptr_t)W1t | (uintptr_t)W2t | (uintptr_t)W3t) % 16) != 0) return LD_ERR_SHAPE;
   if (Nt == 0) return LD_OK;
   BeeScalarParams P;
-  P.g = BeeEdgeParams{row_ptr, dst, rij, Nt, chan, r0, L0, L1, L2, enc_w, enc_b, jacobi};
+  P.g = BeeEdgeParams{row_ptr, dst, rij, Nt, chan, r0, L0, L1, L2, enc_w, enc_b, jacobi, 0};
   P.dim_a = dim_a; P.Yt = Yt; P.W1t = W1t; P.b1 = b1; P.W2t = W2t; P.b2 = b2; P.W3t = W3t; P.b3 = b3; P.Wdt = Wdt;
   P.scale = scale; P.out_a = out_a;
   const size_t floats = (size_t)3 * chan * BM_LDH + (size_t)dim_a * MT_ROWS + (size_t)4 * dim_a * MT_ROWS +
