@@ -159,7 +159,7 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
               const int t = tb + u;
               if (t >= cnt) break;
               const size_t j = (size_t)s_dst[t] * C + c;
-              float l1[3], l2[9], pa, pv[3], pd[9];
+              float l1[3], l2[9], pa;
               float l0;
               if (PACKED) {
                 l0 = tc::bf16_at(raw[u], 0);
@@ -174,16 +174,45 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
 #pragma unroll
                 for (int k = 0; k < 9; k++) l2[k] = bm_ld(F2, j * 9 + k);
               }
-              edge_phi(s_geom[t], w8, wb, &pa, pv, pd);
-              BeeOut o;
-              bee_fwd_point(l0, l1, l2, pa, pv, pd, &o);
+              // phi_a = pa, phi_v = pa * rhat, phi_d = pa * rhat rhat^T: with q = pa * l every product is a short
+              // expression in q and rhat (e.g. 222: l_xy phi_zy = (q_x . rhat) rhat_z), about 100 operations for
+              // the 60 sums instead of 150 for general right operands
+              const EdgeGeom& g = s_geom[t];
+              pa = wb;
 #pragma unroll
-              for (int k = 0; k < 3; k++) {
-                av[k] += o.y011[k]; av[3 + k] += o.y101[k]; av[6 + k] += o.y121[k]; av[9 + k] += o.y211[k]; av[12 + k] += o.y111[k];
+              for (int m = 0; m < 8; m++) pa = fmaf(g.enc[m], w8[m], pa);
+              const float rh[3] = {g.rhat[0], g.rhat[1], g.rhat[2]};
+              const float q0 = l0 * pa;
+              float q1[3], q2[9], m2[3], t0[3];
+#pragma unroll
+              for (int x = 0; x < 3; x++) q1[x] = l1[x] * pa;
+#pragma unroll
+              for (int x = 0; x < 9; x++) q2[x] = l2[x] * pa;
+              const float d1 = q1[0] * rh[0] + q1[1] * rh[1] + q1[2] * rh[2];
+#pragma unroll
+              for (int x = 0; x < 3; x++) {
+                m2[x] = q2[x * 3] * rh[0] + q2[x * 3 + 1] * rh[1] + q2[x * 3 + 2] * rh[2];
+                t0[x] = q0 * rh[x];
+                av[x] += t0[x];                                   // 011: l phi_x
+                av[3 + x] += q1[x];                               // 101
+                av[6 + x] = fmaf(d1, rh[x], av[6 + x]);           // 121: l_x phi_yx -> y
+                av[9 + x] += m2[x];                               // 211: l_xy phi_y -> x
               }
+              av[12] += q1[1] * rh[2] - q1[2] * rh[1];            // 111: l x phi
+              av[13] += q1[2] * rh[0] - q1[0] * rh[2];
+              av[14] += q1[0] * rh[1] - q1[1] * rh[0];
 #pragma unroll
-              for (int k = 0; k < 9; k++) {
-                ad[k] += o.y022[k]; ad[9 + k] += o.y202[k]; ad[18 + k] += o.y112[k]; ad[27 + k] += o.y222[k]; ad[36 + k] += o.y212[k];
+              for (int x = 0; x < 3; x++) {
+#pragma unroll
+                for (int y = 0; y < 3; y++) {
+                  ad[x * 3 + y] = fmaf(t0[x], rh[y], ad[x * 3 + y]);             // 022
+                  ad[9 + x * 3 + y] += q2[x * 3 + y];                            // 202
+                  ad[18 + x * 3 + y] = fmaf(q1[x], rh[y], ad[18 + x * 3 + y]);   // 112
+                  ad[27 + x * 3 + y] = fmaf(m2[x], rh[y], ad[27 + x * 3 + y]);   // 222: l_xy phi_zy -> xz
+                }
+                ad[36 + x * 3 + 0] += q2[x * 3 + 1] * rh[2] - q2[x * 3 + 2] * rh[1];   // 212: row x of l cross phi
+                ad[36 + x * 3 + 1] += q2[x * 3 + 2] * rh[0] - q2[x * 3 + 0] * rh[2];
+                ad[36 + x * 3 + 2] += q2[x * 3 + 0] * rh[1] - q2[x * 3 + 1] * rh[0];
               }
             }
           }
