@@ -93,6 +93,14 @@ int ld_tensor_linear_dw(int inds, const float* dy, const float* x, float* dW, lo
  * HOST arrays of 13 device pointers in the order 000,110,220,011,101,121,211,022,202,112,222,111,212. */
 int ld_bee_fwd(const float* l0, const float* l1, const float* l2, const float* r0, const float* r1, const float* r2,
                long long rows, int chan, float* const* out13, void* stream);
+/* Node-local products of SelfTensProds (archs/diffuser_atoms15.py:59-95) for ONE channel mixing per rank on either
+ * side: inputs lr0 [rows][2*chan], lr1 [rows][2*chan][3], lr2 [rows][2*chan][3][3] hold the left operands in channels
+ * [0, chan) and the right operands in [chan, 2*chan) (one linear per rank with 2*chan outputs); outputs are the 13
+ * Bee products concatenated per rank, P_a [rows][3*chan] = (000|110|220), P_v [rows][5*chan][3] =
+ * (011|101|121|211|111), P_d [rows][5*chan][3][3] = (022|202|112|222|212), the K dimension of the concatenated Y maps.
+ * chan a multiple of 32. Same arithmetic as ld_bee_fwd. */
+int ld_bee_self_products(const float* lr0, const float* lr1, const float* lr2, long long rows, int chan, float* P_a,
+                         float* P_v, float* P_d, void* stream);
 int ld_bee_bw(int left, const float* o0, const float* o1, const float* o2, const float* const* grads13, long long rows,
               int chan, float* d0, float* d1, float* d2, void* stream);
 int ld_cow_o0_fwd(const float* l0, const float* l1, const float* r0, const float* r1, long long rows, int chan,

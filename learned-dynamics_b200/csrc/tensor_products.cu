@@ -130,7 +130,89 @@ inline int grid_for(size_t n) {
   return (int)(b < cap ? (b ? b : 1) : cap);
 }
 
+// Node-local products of SelfTensProds (archs/diffuser_atoms15.py:59-95) in the layout its Y maps want as ONE
+// channel mixing per rank: left and right operands come from one linear per rank with 2*chan outputs
+// (lr[row][0:chan] = left, [chan:2chan] = right), the 13 products are written concatenated,
+//   P_a[row][3*chan]      = (000 | 110 | 220)
+//   P_v[row][5*chan][3]   = (011 | 101 | 121 | 211 | 111)
+//   P_d[row][5*chan][3][3] = (022 | 202 | 112 | 222 | 212).
+// A warp owns (row, 32 channels). Rank-1/2 operands and results have a stride of 3 or 9 floats per channel; they
+// pass through a per-warp shared-memory buffer so that every global access of the warp is a contiguous 128 bytes
+// (strides 3 and 9 are coprime with the 32 banks: no conflicts).
+constexpr int SP_WARPS = 4;
+
+template <int S>
+__device__ __forceinline__ void sp_load(const float* __restrict__ g, float* wbuf, int lane, float* v) {
+#pragma unroll
+  for (int j = 0; j < S; j++) wbuf[lane + 32 * j] = __ldg(g + lane + 32 * j);
+  __syncwarp();
+#pragma unroll
+  for (int s = 0; s < S; s++) v[s] = wbuf[lane * S + s];
+  __syncwarp();
+}
+template <int S>
+__device__ __forceinline__ void sp_store(float* __restrict__ g, float* wbuf, int lane, const float* v) {
+#pragma unroll
+  for (int s = 0; s < S; s++) wbuf[lane * S + s] = v[s];
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < S; j++) g[lane + 32 * j] = wbuf[lane + 32 * j];
+  __syncwarp();
+}
+
+__global__ void __launch_bounds__(SP_WARPS * 32)
+bee_self_products_kernel(const float* __restrict__ lr0, const float* __restrict__ lr1, const float* __restrict__ lr2,
+                         long long rows, int C, float* __restrict__ P_a, float* __restrict__ P_v, float* __restrict__ P_d) {
+  __shared__ float s_buf[SP_WARPS][288];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  float* wbuf = s_buf[w];
+  const int groups = C >> 5;
+  const long long items = rows * groups;
+  for (long long it = (long long)blockIdx.x * SP_WARPS + w; it < items; it += (long long)gridDim.x * SP_WARPS) {
+    const long long row = it / groups;
+    const int c0 = (int)(it - row * groups) * 32;
+    const size_t in = (size_t)row * 2 * C + c0;     // left operand of channel c0 (right: + C)
+    float l1[3], l2[9], r1[3], r2[9];
+    const float l0 = __ldg(lr0 + in + lane), r0 = __ldg(lr0 + in + C + lane);
+    sp_load<3>(lr1 + in * 3, wbuf, lane, l1);
+    sp_load<3>(lr1 + (in + C) * 3, wbuf, lane, r1);
+    sp_load<9>(lr2 + in * 9, wbuf, lane, l2);
+    sp_load<9>(lr2 + (in + C) * 9, wbuf, lane, r2);
+    BeeOut o;
+    bee_fwd_point(l0, l1, l2, r0, r1, r2, &o);
+    float* pa = P_a + (size_t)row * 3 * C + c0 + lane;
+    pa[0] = o.y000; pa[C] = o.y110; pa[2 * C] = o.y220;
+    float* pv = P_v + ((size_t)row * 5 * C + c0) * 3;
+    sp_store<3>(pv, wbuf, lane, o.y011);
+    sp_store<3>(pv + (size_t)C * 3, wbuf, lane, o.y101);
+    sp_store<3>(pv + (size_t)2 * C * 3, wbuf, lane, o.y121);
+    sp_store<3>(pv + (size_t)3 * C * 3, wbuf, lane, o.y211);
+    sp_store<3>(pv + (size_t)4 * C * 3, wbuf, lane, o.y111);
+    float* pd = P_d + ((size_t)row * 5 * C + c0) * 9;
+    sp_store<9>(pd, wbuf, lane, o.y022);
+    sp_store<9>(pd + (size_t)C * 9, wbuf, lane, o.y202);
+    sp_store<9>(pd + (size_t)2 * C * 9, wbuf, lane, o.y112);
+    sp_store<9>(pd + (size_t)3 * C * 9, wbuf, lane, o.y222);
+    sp_store<9>(pd + (size_t)4 * C * 9, wbuf, lane, o.y212);
+  }
+}
+
 }  // namespace
+
+// lr0 [rows][2*chan], lr1 [rows][2*chan][3], lr2 [rows][2*chan][3][3]: left operands in channels [0, chan), right in
+// [chan, 2*chan). Outputs as described at bee_self_products_kernel. chan a multiple of 32.
+extern "C" int ld_bee_self_products(const float* lr0, const float* lr1, const float* lr2, long long rows, int chan, float* P_a,
+                                    float* P_v, float* P_d, void* stream) {
+  if (rows < 0 || chan <= 0) return LD_ERR_SHAPE;
+  if (chan % 32 != 0) { ld_set_last_message("bee self products: chan must be a multiple of 32"); return LD_ERR_UNSUPPORTED; }
+  if (rows == 0) return LD_OK;
+  const long long items = rows * (chan / 32);
+  long long blocks = (items + SP_WARPS - 1) / SP_WARPS;
+  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  bee_self_products_kernel<<<(unsigned)blocks, SP_WARPS * 32, 0, (cudaStream_t)stream>>>(lr0, lr1, lr2, rows, chan, P_a, P_v, P_d);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}
 
 // rows*chan elements per rank-0 operand; operands are contiguous [rows, chan, (3,)^l] float32.
 extern "C" int ld_bee_fwd(const float* l0, const float* l1, const float* l2, const float* r0, const float* r1,

@@ -27,6 +27,7 @@ SIGNATURES = {
     "ld_tensor_linear_dw_workspace": [I, LL, I, I, P],
     "ld_tensor_linear_dw": [I, P, P, P, LL, I, I, P, SZ, P],
     "ld_bee_fwd": [P, P, P, P, P, P, LL, I, P, P],
+    "ld_bee_self_products": [P, P, P, LL, I, P, P, P, P],
     "ld_bee_bw": [I, P, P, P, P, LL, I, P, P, P, P],
     "ld_cow_o0_fwd": [P, P, P, P, LL, I, P, P, P],
     "ld_cow_o0_bw": [P, P, P, P, LL, I, P, P, P],

@@ -213,6 +213,30 @@ class SelfTensProds(nn.Module):
         self.gn_a = TensGroupNorm(0, dim_a, groups)
         self.gn_v = TensGroupNorm(1, dim_v, groups)
         self.gn_d = TensGroupNorm(2, dim_d, groups)
+        self.chan = chan
+        self._cat, self._cat_key = None, None
+
+    def _cat_weights(self):
+        """left|right weights stacked per rank and the Y maps concatenated along their inputs (cached)"""
+        key = tuple((p.data_ptr(), p._version) for p in self.parameters()) + (self.L0.precision,)
+        if self._cat_key != key:
+            f = lambda t: t.detach().float().contiguous()
+            c = {"LR0": f(torch.cat([self.L0.W, self.R0.W], dim=0)), "LR1": f(torch.cat([self.L1.W, self.R1.W], dim=0)),
+                 "LR2": f(torch.cat([self.L2.W, self.R2.W], dim=0)),
+                 "Ya": f(torch.cat([self.Y_000.W, self.Y_110.W, self.Y_220.W], dim=1)),
+                 "Yv": f(torch.cat([getattr(self, "Y_" + n).W for n in V_ORDER], dim=1)),
+                 "Yd": f(torch.cat([getattr(self, "Y_" + n).W for n in D_ORDER], dim=1))}
+            if self.L0.precision == "bf16":
+                for k in list(c):
+                    c[k + "p"] = ops.pack_weights_bf16(c[k])
+            self._cat, self._cat_key = c, key
+        return self._cat
+
+    def _mix(self, c, name, inds, x):
+        W = c[name]
+        if name + "p" in c and W.shape[0] % 32 == 0 and W.shape[0] <= 512:
+            return ops.linear_bf16_tc(x, c[name + "p"], W.shape[0], None, ops.ACT_NONE, inds=inds)
+        return ops.tensor_linear_fwd(inds, W, x.contiguous())
 
     def forward(self, x_a, x_v, x_d):
         rest = x_a.shape[:-1]
@@ -220,6 +244,13 @@ class SelfTensProds(nn.Module):
         for d in rest:
             n *= d
         xa, xv, xd = x_a.reshape(n, -1), x_v.reshape(n, -1, 3), x_d.reshape(n, -1, 3, 3)
+        if not torch.is_grad_enabled() and x_a.is_cuda and self.chan % 32 == 0:
+            # three channel mixings in (left|right stacked), one product kernel, three channel mixings out
+            c = self._cat_weights()
+            P_a, P_v, P_d = ops.bee_self_products(self._mix(c, "LR0", 0, xa), self._mix(c, "LR1", 1, xv), self._mix(c, "LR2", 2, xd))
+            y_a, y_v, y_d = self._mix(c, "Ya", 0, P_a), self._mix(c, "Yv", 1, P_v), self._mix(c, "Yd", 2, P_d)
+            return (self.gn_a(y_a.reshape(*rest, -1)), self.gn_v(y_v.reshape(*rest, -1, 3)),
+                    self.gn_d(y_d.reshape(*rest, -1, 3, 3)))
         y = Bee.apply(self.L0(xa), self.L1(xv), self.L2(xd), self.R0(xa), self.R1(xv), self.R2(xd))
         (y_000, y_110, y_220, y_011, y_101, y_121, y_211, y_022, y_202, y_112, y_222, y_111, y_212) = y
         y_a = self.Y_000(y_000) + self.Y_110(y_110) + self.Y_220(y_220)

@@ -113,6 +113,24 @@ def bee_fwd(l_0, l_1, l_2, r_0, r_1, r_2):
     return outs
 
 
+def bee_self_products(lr_0, lr_1, lr_2):
+    """13 Bee products of left = lr[:, :chan], right = lr[:, chan:], concatenated per rank:
+    P_a [rows, 3*chan], P_v [rows, 5*chan, 3], P_d [rows, 5*chan, 3, 3] (the inputs of concatenated Y maps)."""
+    for name, t in (("lr_0", lr_0), ("lr_1", lr_1), ("lr_2", lr_2)):
+        require_cuda_f32(t, name)
+    rows, chan = lr_0.shape[0], lr_0.shape[1] // 2
+    if lr_0.shape != (rows, 2 * chan) or lr_1.shape != (rows, 2 * chan, 3) or lr_2.shape != (rows, 2 * chan, 3, 3):
+        raise RuntimeError("bee_self_products: expected [rows, 2*chan], [rows, 2*chan, 3], [rows, 2*chan, 3, 3]")
+    dev = lr_0.device
+    P_a = torch.empty(rows, 3 * chan, dtype=torch.float32, device=dev)
+    P_v = torch.empty(rows, 5 * chan, 3, dtype=torch.float32, device=dev)
+    P_d = torch.empty(rows, 5 * chan, 3, 3, dtype=torch.float32, device=dev)
+    with KERNEL_TIMER.region("bee_self_products"):
+        check(lib().ld_bee_self_products(ptr(lr_0), ptr(lr_1), ptr(lr_2), rows, chan, ptr(P_a), ptr(P_v), ptr(P_d),
+                                         stream_ptr(dev)))
+    return P_a, P_v, P_d
+
+
 def bee_bw(left, o_0, o_1, o_2, grads):
     names = ("r_0", "r_1", "r_2") if left else ("l_0", "l_1", "l_2")
     batch, chan = _check_operands(names, (o_0, o_1, o_2), (0, 1, 2))

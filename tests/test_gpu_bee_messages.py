@@ -123,3 +123,26 @@ def test_bee_denoiser_bf16_vs_fp32():
         got = bee.set_precision(dn, "bf16")(x0, x1, None, types)
     assert int(ops.tc_status("cuda").item()) == 0
     close(got, ref, 5e-2)
+
+
+@pytest.mark.parametrize("dims,rows", [((128, 64, 32, 128), (3, 50)), ((16, 8, 8, 32), (1, 7)), ((64, 32, 16, 96), (2, 33))])
+def test_self_tens_prods_fused_vs_reference_sequence(dims, rows):
+    """node-local products: three stacked channel mixings + one product kernel + three concatenated Y maps against
+    the reference's op sequence (six linears, Bee, thirteen Y maps) on the unfused kernels and against the oracle"""
+    from ld_b200 import bee
+    from oracle import reference_math as R
+    torch.manual_seed(sum(dims))
+    mod = bee.SelfTensProds(*dims).cuda()
+    g = torch.Generator().manual_seed(3)
+    da, dv, dd, _ = dims
+    x_a, x_v, x_d = (torch.randn(*rows, da, generator=g), torch.randn(*rows, dv, 3, generator=g),
+                     torch.randn(*rows, dd, 3, 3, generator=g))
+    ref_mod = R.OSelfTensProds(*dims)
+    ref_mod.load_state_dict(mod.state_dict())
+    with torch.no_grad():
+        ref = ref_mod(x_a, x_v, x_d)
+        fused = mod(x_a.cuda(), x_v.cuda(), x_d.cuda())
+    unfused = mod(x_a.cuda(), x_v.cuda(), x_d.cuda())   # autograd enabled: the reference's op sequence
+    for a, b, c in zip(fused, unfused, ref):
+        close(a, b.detach(), 2e-5)
+        close(a, c, 5e-5)
