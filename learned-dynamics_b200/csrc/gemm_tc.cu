@@ -40,6 +40,8 @@ __device__ __forceinline__ float act_apply(float v, int act) {
   return v;
 }
 
+// UNIT: rows are plain rows (S = 1) with K a multiple of 4: 16-byte activation loads and staged, coalesced stores
+template <bool UNIT>
 __global__ void __launch_bounds__(GT_ROWS, 1)
 gemm_tc_kernel(GemmParams P) {
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -92,13 +94,23 @@ gemm_tc_kernel(GemmParams P) {
       }
       // activations: this thread's row, 8 panels of 8 columns
       const int k0 = c * GT_KC;
+      constexpr bool row_vec = UNIT;   // 16-byte loads along the row
 #pragma unroll
       for (int p = 0; p < GT_PANELS; p++) {
         float v[8];
+        if (row_vec) {
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-          const int k = k0 + p * 8 + j;
-          v[j] = (row_ok && k < K) ? __ldg(xrow + (size_t)k * S) : 0.f;
+          for (int h = 0; h < 2; h++) {
+            const int k = k0 + p * 8 + h * 4;
+            const float4 q4 = (row_ok && k < K) ? __ldg(reinterpret_cast<const float4*>(xrow + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v[h * 4] = q4.x; v[h * 4 + 1] = q4.y; v[h * 4 + 2] = q4.z; v[h * 4 + 3] = q4.w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const int k = k0 + p * 8 + j;
+            v[j] = (row_ok && k < K) ? __ldg(xrow + (size_t)k * S) : 0.f;
+          }
         }
         uint4 q;
         q.x = tc::pack_bf16x2(v[0], v[1]); q.y = tc::pack_bf16x2(v[2], v[3]);
@@ -135,15 +147,35 @@ gemm_tc_kernel(GemmParams P) {
     tc::fence_after_sync();
     float* yrow = P.y + (ro * N) * S + rs;
     __nv_bfloat16* yrow16 = reinterpret_cast<__nv_bfloat16*>(P.y) + ro * P.y_ld_row + rs + P.y_off;
+    // S == 1 with the plain [rows][N] layout: a thread owns a row, so direct stores would put every 4-byte value
+    // of a warp into a different sector; 32-column slices go through shared memory (the operand stages are idle
+    // once the accumulators are complete) and leave as 128-byte rows
+    const bool staged = UNIT && (!P.out_bf16 || (P.y_ld_col == 1 && P.y_ld_row == N && P.y_off == 0));
+    float* stage_f = reinterpret_cast<float*>(smem);   // [128 rows][33]
     for (int cb = 0; cb < N; cb += 32) {
       float v[32];
       tc::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + cb, v);
-      if (row_ok) {
+#pragma unroll
+      for (int j = 0; j < 32; j++) v[j] = act_apply(v[j] + (P.bias != nullptr ? __ldg(P.bias + cb + j) : 0.f), P.act);
+      if (staged) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) stage_f[tid * 33 + j] = v[j];
+        __syncthreads();
+        const long long R0 = tile * GT_ROWS;
+        const int lane = tid & 31;
+        for (int r = warp; r < GT_ROWS; r += GT_ROWS / 32) {
+          if (R0 + r < P.rows) {
+            const float t = stage_f[r * 33 + lane];
+            const long long idx = (R0 + r) * N + cb + lane;
+            if (P.out_bf16) reinterpret_cast<__nv_bfloat16*>(P.y)[idx] = __float2bfloat16_rn(t); else P.y[idx] = t;
+          }
+        }
+        __syncthreads();
+      } else if (row_ok) {
 #pragma unroll
         for (int j = 0; j < 32; j++) {
-          const float t = act_apply(v[j] + (P.bias != nullptr ? __ldg(P.bias + cb + j) : 0.f), P.act);
-          if (P.out_bf16) yrow16[(size_t)(cb + j) * P.y_ld_col] = __float2bfloat16_rn(t);
-          else yrow[(size_t)(cb + j) * S] = t;
+          if (P.out_bf16) yrow16[(size_t)(cb + j) * P.y_ld_col] = __float2bfloat16_rn(v[j]);
+          else yrow[(size_t)(cb + j) * S] = v[j];
         }
       }
     }
@@ -210,7 +242,9 @@ static int linear_tc_launch(const float* x, long long rows_outer, int K, int S, 
   P.x = x; P.y = (float*)y; P.out_bf16 = out_bf16; P.y_ld_row = ld_row; P.y_ld_col = ld_col; P.y_off = off; P.wp = (const __nv_bfloat16*)wp; P.bias = bias; P.rows = rows_outer * S; P.K = K; P.N = N; P.S = S;
   P.act = act; P.status = status_dev;
   const size_t smem = 2 * GT_A_STAGE + 2 * (size_t)N * GT_KC * 2 + 1024;
-  LD_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const bool unit = S == 1 && (K & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  auto kern = unit ? gemm_tc_kernel<true> : gemm_tc_kernel<false>;
+  LD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const long long ntiles = (P.rows + GT_ROWS - 1) / GT_ROWS;
   // several blocks per SM hide the latency of the strided activation loads: as many as tensor memory
   // (512 columns) and shared memory (about 220 KB) allow
@@ -223,7 +257,7 @@ static int linear_tc_launch(const float* x, long long rows_outer, int K, int S, 
   if (per_sm > 4) per_sm = 4;
   const long long slots = (long long)gt_sm_count() * per_sm;
   const int grid = (int)(ntiles < slots ? ntiles : slots);
-  gemm_tc_kernel<<<grid, GT_ROWS, smem, (cudaStream_t)stream>>>(P);
+  kern<<<grid, GT_ROWS, smem, (cudaStream_t)stream>>>(P);
   LD_LAUNCH_CHECK();
   return LD_OK;
 }
