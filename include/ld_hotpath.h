@@ -98,9 +98,9 @@ int ld_bee_fwd(const float* l0, const float* l1, const float* l2, const float* r
  * [0, chan) and the right operands in [chan, 2*chan) (one linear per rank with 2*chan outputs); outputs are the 13
  * Bee products concatenated per rank, P_a [rows][3*chan] = (000|110|220), P_v [rows][5*chan][3] =
  * (011|101|121|211|111), P_d [rows][5*chan][3][3] = (022|202|112|222|212), the K dimension of the concatenated Y maps.
- * chan a multiple of 32. Same arithmetic as ld_bee_fwd. */
+ * chan a multiple of 32. Same arithmetic as ld_bee_fwd. out_bf16: P_v and P_d are stored as BF16. */
 int ld_bee_self_products(const float* lr0, const float* lr1, const float* lr2, long long rows, int chan, float* P_a,
-                         float* P_v, float* P_d, void* stream);
+                         void* P_v, void* P_d, int out_bf16, void* stream);
 int ld_bee_bw(int left, const float* o0, const float* o1, const float* o2, const float* const* grads13, long long rows,
               int chan, float* d0, float* d1, float* d2, void* stream);
 int ld_cow_o0_fwd(const float* l0, const float* l1, const float* r0, const float* r1, long long rows, int chan,
@@ -135,6 +135,10 @@ long long ld_packed_weight_elems(int N, int K);
 int ld_pack_weights_bf16(const float* W, long long sw0, long long sw1, int N, int K, void* out, void* stream);
 int ld_linear_bf16_tc(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias, int N, int act,
                       float* y, int* status_dev, void* stream);
+/* same with the activations already stored as BF16 ([rows_outer, K, S] contiguous); the MMA operands are BF16 in
+ * any case, so the result equals that of the same values passed as FP32 */
+int ld_linear_bf16_tc_in16(const void* x_bf16, long long rows_outer, int K, int S, const void* wp, const float* bias, int N,
+                           int act, float* y, int* status_dev, void* stream);
 /* same with a BF16 result written to y_bf16[r*ld_row + o*ld_col + s + off] (plain layout: ld_row = N*S,
  * ld_col = S, off = 0); used to interleave the left operands of the l<=2 message layer per channel */
 int ld_linear_bf16_tc_out16(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias, int N,
@@ -162,10 +166,11 @@ int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, const float* ri
  * caller applies them per node with ld_tensor_linear over 5*chan inputs). _scalar: per-edge Y maps
  * and mlp_a, summed per node. `jacobi` = 8x9 coefficients of the shifted Jacobi(1,0) polynomials.
  * feat_bf16: 0 = L0/L1/L2 FP32; 1 = BF16; 2 = L0 alone points to the interleaved BF16 form
- * [node][chan][16] = (l0, l1[3], l2[9], 3 unused) written by ld_linear_bf16_tc_out16. */
+ * [node][chan][16] = (l0, l1[3], l2[9], 3 unused) written by ld_linear_bf16_tc_out16.
+ * out_bf16 (vd): S_v / S_d are stored as BF16 (same shapes), the input form of ld_linear_bf16_tc_in16. */
 int ld_bee_messages_vd_f32(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, float r0, const float* L0,
                            const float* L1, const float* L2, const float* enc_w, const float* enc_b, const float* jacobi,
-                           float scale, float* S_v, float* S_d, int feat_bf16, void* stream);
+                           float scale, void* S_v, void* S_d, int feat_bf16, int out_bf16, void* stream);
 int ld_bee_messages_scalar_f32(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, int dim_a, float r0,
                                const float* L0, const float* L1, const float* L2, const float* enc_w, const float* enc_b,
                                const float* jacobi, const float* Yt, const float* W1t, const float* b1, const float* W2t,

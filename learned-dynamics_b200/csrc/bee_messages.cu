@@ -105,7 +105,7 @@ __device__ __forceinline__ void edge_phi(const EdgeGeom& g, const float* w8, flo
 // and stages the geometry of up to 32 edges at a time in shared memory.
 template <typename FT, bool PACKED>
 __global__ void __launch_bounds__(128)
-bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d, float scale) {
+bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d, float scale, int out_bf16) {
   const FT* __restrict__ F0 = reinterpret_cast<const FT*>(P.L0);
   const FT* __restrict__ F1 = reinterpret_cast<const FT*>(P.L1);
   const FT* __restrict__ F2 = reinterpret_cast<const FT*>(P.L2);
@@ -219,14 +219,29 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
         }
       }
       if (cok) {
-        float* sv = S_v + (size_t)v * 5 * C * 3;
-        float* sd = S_d + (size_t)v * 5 * C * 9;
+        if (out_bf16) {
+          // the sums feed a tensor-core channel mixing that rounds its operands to BF16 anyway: store them rounded
+          // component-major [node][3 | 9][5*chan]: consecutive channels are consecutive addresses, and a (node,
+          // component) row is the contiguous K dimension of that channel mixing
+          __nv_bfloat16* sv = reinterpret_cast<__nv_bfloat16*>(S_v) + (size_t)v * 3 * 5 * C + c;
+          __nv_bfloat16* sd = reinterpret_cast<__nv_bfloat16*>(S_d) + (size_t)v * 9 * 5 * C + c;
 #pragma unroll
-        for (int k = 0; k < 5; k++) {
+          for (int k = 0; k < 5; k++) {
 #pragma unroll
-          for (int x = 0; x < 3; x++) sv[((size_t)k * C + c) * 3 + x] = av[k * 3 + x] * scale;
+            for (int x = 0; x < 3; x++) sv[(size_t)x * 5 * C + k * C] = __float2bfloat16_rn(av[k * 3 + x] * scale);
 #pragma unroll
-          for (int x = 0; x < 9; x++) sd[((size_t)k * C + c) * 9 + x] = ad[k * 9 + x] * scale;
+            for (int x = 0; x < 9; x++) sd[(size_t)x * 5 * C + k * C] = __float2bfloat16_rn(ad[k * 9 + x] * scale);
+          }
+        } else {
+          float* sv = S_v + (size_t)v * 5 * C * 3;
+          float* sd = S_d + (size_t)v * 5 * C * 9;
+#pragma unroll
+          for (int k = 0; k < 5; k++) {
+#pragma unroll
+            for (int x = 0; x < 3; x++) sv[((size_t)k * C + c) * 3 + x] = av[k * 3 + x] * scale;
+#pragma unroll
+            for (int x = 0; x < 9; x++) sd[((size_t)k * C + c) * 9 + x] = ad[k * 9 + x] * scale;
+          }
         }
       }
     }
@@ -357,10 +372,14 @@ bee_scalar_kernel(BeeScalarParams P) {
 // L0/L1/L2 are the node-level left operands: FP32 (feat_bf16 = 0), BF16 (1), or with feat_bf16 = 2
 // L0 alone points to the interleaved BF16 form [node][chan][16] = (l0, l1[3], l2[9], 3 unused); enc_w [chan,8] / enc_b [chan] the radial read-in,
 // jacobi the 8x9 coefficient matrix of the radial basis. Graph in CSR form sorted by source.
+// out_bf16: S_v / S_d are stored as BF16, component-major ([Nt][3][5*chan] and [Nt][9][5*chan]), the input form of
+// ld_linear_bf16_tc_in16.
 extern "C" int ld_bee_messages_vd_f32(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, float r0,
                                       const float* L0, const float* L1, const float* L2, const float* enc_w,
-                                      const float* enc_b, const float* jacobi, float scale, float* S_v, float* S_d,
-                                      int feat_bf16, void* stream) {
+                                      const float* enc_b, const float* jacobi, float scale, void* S_v_, void* S_d_,
+                                      int feat_bf16, int out_bf16, void* stream) {
+  float* S_v = (float*)S_v_;
+  float* S_d = (float*)S_d_;
   if (Nt < 0 || chan <= 0 || !(r0 > 0.f)) return LD_ERR_SHAPE;
   if (Nt == 0) return LD_OK;
   // segment = about 40 MB of gathered rows (13 * chan values per node, 32 bytes per channel when interleaved)
@@ -368,9 +387,9 @@ extern "C" int ld_bee_messages_vd_f32(const int* row_ptr, const int* dst, const 
   BeeEdgeParams P{row_ptr, dst, rij, Nt, chan, r0, L0, L1, L2, enc_w, enc_b, jacobi, (int)(seg < 1024 ? 1024 : seg)};
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (feat_bf16 == 2) bee_vd_kernel<__nv_bfloat16, true><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale);
-  else if (feat_bf16) bee_vd_kernel<__nv_bfloat16, false><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale);
-  else bee_vd_kernel<float, false><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale);
+  if (feat_bf16 == 2) bee_vd_kernel<__nv_bfloat16, true><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale, out_bf16);
+  else if (feat_bf16) bee_vd_kernel<__nv_bfloat16, false><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale, out_bf16);
+  else bee_vd_kernel<float, false><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale, out_bf16);
   LD_LAUNCH_CHECK();
   return LD_OK;
 }

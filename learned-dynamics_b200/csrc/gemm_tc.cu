@@ -24,6 +24,7 @@ constexpr int GT_A_STAGE = GT_ROWS * GT_KC * 2;  // bytes
 
 struct GemmParams {
   const float* x; float* y;
+  int in_bf16;               // x holds BF16 values laid out [rows_outer][S][K] (K contiguous per GEMM row, K % 8 == 0)
   const __nv_bfloat16* wp;   // packed weights [nchunks][8 panels][N][8]
   const float* bias;
   long long rows;            // logical rows = rows_outer * S
@@ -41,7 +42,9 @@ __device__ __forceinline__ float act_apply(float v, int act) {
 }
 
 // UNIT: rows are plain rows (S = 1) with K a multiple of 4: 16-byte activation loads and staged, coalesced stores
-template <bool UNIT>
+// IN16: the activations are stored as BF16, component-major ([rows_outer][S][K]): a GEMM row is K contiguous values,
+// and eight of them are exactly one 16-byte piece of the operand layout, so they are copied without conversion
+template <bool UNIT, bool IN16>
 __global__ void __launch_bounds__(GT_ROWS, 1)
 gemm_tc_kernel(GemmParams P) {
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -81,6 +84,7 @@ gemm_tc_kernel(GemmParams P) {
     const long long ro = row_ok ? row / S : 0;
     const int rs = row_ok ? (int)(row - ro * S) : 0;
     const float* xrow = P.x + (ro * K) * S + rs;
+    const __nv_bfloat16* xrow16 = reinterpret_cast<const __nv_bfloat16*>(P.x) + row * K;
     for (int c = 0; c < nchunks; c++, g++) {
       const int st = g & 1;
       const uint32_t use = g >> 1;
@@ -95,6 +99,16 @@ gemm_tc_kernel(GemmParams P) {
       // activations: this thread's row, 8 panels of 8 columns
       const int k0 = c * GT_KC;
       constexpr bool row_vec = UNIT;   // 16-byte loads along the row
+      if (IN16) {
+        uint4 q[GT_PANELS];
+#pragma unroll
+        for (int p = 0; p < GT_PANELS; p++) {
+          const int k = k0 + p * 8;
+          q[p] = (row_ok && k < K) ? __ldg(reinterpret_cast<const uint4*>(xrow16 + k)) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int p = 0; p < GT_PANELS; p++) *reinterpret_cast<uint4*>(a_smem[st] + p * (GT_ROWS * 16) + tid * 16) = q[p];
+      } else {
 #pragma unroll
       for (int p = 0; p < GT_PANELS; p++) {
         float v[8];
@@ -116,6 +130,7 @@ gemm_tc_kernel(GemmParams P) {
         q.x = tc::pack_bf16x2(v[0], v[1]); q.y = tc::pack_bf16x2(v[2], v[3]);
         q.z = tc::pack_bf16x2(v[4], v[5]); q.w = tc::pack_bf16x2(v[6], v[7]);
         *reinterpret_cast<uint4*>(a_smem[st] + p * (GT_ROWS * 16) + tid * 16) = q;
+      }
       }
       tc::fence_async_smem();
       __syncthreads();
@@ -232,18 +247,22 @@ extern "C" int ld_pack_weights_bf16(const float* W, long long sw0, long long sw1
 // y = act(x W^T + b) on the tensor cores. x: FP32 [rows_outer, K, S] contiguous, y: [rows_outer, N, S].
 // S in {1,3,9}; N a multiple of 32, N <= 512. wp from ld_pack_weights_bf16. status_dev: optional
 // device int32 that receives LD_FLAG_TIMEOUT if a bounded wait ran out.
-static int linear_tc_launch(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias, int N, int act,
+static int linear_tc_launch(const float* x, int in_bf16, long long rows_outer, int K, int S, const void* wp, const float* bias, int N, int act,
                             void* y, int out_bf16, long long ld_row, long long ld_col, int off, int* status_dev, void* stream) {
   if (rows_outer < 0 || K <= 0 || N <= 0 || (S != 1 && S != 3 && S != 9)) return LD_ERR_SHAPE;
   if (N % 32 != 0 || N > 512) { ld_set_last_message("tensor-core linear: N must be a multiple of 32, at most 512"); return LD_ERR_UNSUPPORTED; }
   if (((uintptr_t)wp) % 16 != 0) { ld_set_last_message("tensor-core linear: packed weights must be 16-byte aligned"); return LD_ERR_SHAPE; }
+  if (in_bf16 && ((K & 7) != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0)) {
+    ld_set_last_message("tensor-core linear: BF16 activations need K a multiple of 8 and a 16-byte aligned base");
+    return LD_ERR_UNSUPPORTED;
+  }
   if (rows_outer == 0) return LD_OK;
   GemmParams P;
-  P.x = x; P.y = (float*)y; P.out_bf16 = out_bf16; P.y_ld_row = ld_row; P.y_ld_col = ld_col; P.y_off = off; P.wp = (const __nv_bfloat16*)wp; P.bias = bias; P.rows = rows_outer * S; P.K = K; P.N = N; P.S = S;
+  P.x = x; P.in_bf16 = in_bf16; P.y = (float*)y; P.out_bf16 = out_bf16; P.y_ld_row = ld_row; P.y_ld_col = ld_col; P.y_off = off; P.wp = (const __nv_bfloat16*)wp; P.bias = bias; P.rows = rows_outer * S; P.K = K; P.N = N; P.S = S;
   P.act = act; P.status = status_dev;
   const size_t smem = 2 * GT_A_STAGE + 2 * (size_t)N * GT_KC * 2 + 1024;
-  const bool unit = S == 1 && (K & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
-  auto kern = unit ? gemm_tc_kernel<true> : gemm_tc_kernel<false>;
+  const bool unit = !in_bf16 && S == 1 && (K & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  auto kern = unit ? gemm_tc_kernel<true, false> : (in_bf16 ? gemm_tc_kernel<false, true> : gemm_tc_kernel<false, false>);
   LD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const long long ntiles = (P.rows + GT_ROWS - 1) / GT_ROWS;
   // several blocks per SM hide the latency of the strided activation loads: as many as tensor memory
@@ -264,7 +283,7 @@ static int linear_tc_launch(const float* x, long long rows_outer, int K, int S, 
 
 extern "C" int ld_linear_bf16_tc(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias,
                                  int N, int act, float* y, int* status_dev, void* stream) {
-  return linear_tc_launch(x, rows_outer, K, S, wp, bias, N, act, y, 0, (long long)N * S, S, 0, status_dev, stream);
+  return linear_tc_launch(x, 0, rows_outer, K, S, wp, bias, N, act, y, 0, (long long)N * S, S, 0, status_dev, stream);
 }
 
 // same, with the result rounded to BF16 and free output addressing: element (r, o, s) is written to
@@ -275,5 +294,14 @@ extern "C" int ld_linear_bf16_tc(const float* x, long long rows_outer, int K, in
 extern "C" int ld_linear_bf16_tc_out16(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias,
                                        int N, int act, void* y_bf16, long long ld_row, long long ld_col, int off,
                                        int* status_dev, void* stream) {
-  return linear_tc_launch(x, rows_outer, K, S, wp, bias, N, act, y_bf16, 1, ld_row, ld_col, off, status_dev, stream);
+  return linear_tc_launch(x, 0, rows_outer, K, S, wp, bias, N, act, y_bf16, 1, ld_row, ld_col, off, status_dev, stream);
+}
+
+// ld_linear_bf16_tc with the activations already stored as BF16, component-major: x_bf16 [rows_outer][S][K] (K
+// contiguous, a multiple of 8). The MMA operands are BF16 in any case, so the result is identical to passing the same
+// values as FP32 [rows_outer][K][S]; the read traffic halves and the rows are copied into the operand layout as they are.
+extern "C" int ld_linear_bf16_tc_in16(const void* x_bf16, long long rows_outer, int K, int S, const void* wp, const float* bias,
+                                      int N, int act, float* y, int* status_dev, void* stream) {
+  return linear_tc_launch((const float*)x_bf16, 1, rows_outer, K, S, wp, bias, N, act, y, 0, (long long)N * S, S, 0, status_dev,
+                          stream);
 }

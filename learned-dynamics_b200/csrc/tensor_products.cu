@@ -5,6 +5,7 @@
 // rank-1 / rank-2 operands touch 96 / 288 consecutive floats (every fetched sector is used).
 // These ops are HBM bound: 26 floats in, 63 out per (row, channel) for the forward Bee set.
 #include "common.cuh"
+#include <cuda_bf16.h>
 #include "tp_math.h"
 
 namespace {
@@ -150,19 +151,20 @@ __device__ __forceinline__ void sp_load(const float* __restrict__ g, float* wbuf
   for (int s = 0; s < S; s++) v[s] = wbuf[lane * S + s];
   __syncwarp();
 }
-template <int S>
-__device__ __forceinline__ void sp_store(float* __restrict__ g, float* wbuf, int lane, const float* v) {
+template <int S, typename OT>
+__device__ __forceinline__ void sp_store(OT* __restrict__ g, float* wbuf, int lane, const float* v) {
 #pragma unroll
   for (int s = 0; s < S; s++) wbuf[lane * S + s] = v[s];
   __syncwarp();
 #pragma unroll
-  for (int j = 0; j < S; j++) g[lane + 32 * j] = wbuf[lane + 32 * j];
+  for (int j = 0; j < S; j++) g[lane + 32 * j] = (OT)wbuf[lane + 32 * j];
   __syncwarp();
 }
 
+template <typename OT>
 __global__ void __launch_bounds__(SP_WARPS * 32)
 bee_self_products_kernel(const float* __restrict__ lr0, const float* __restrict__ lr1, const float* __restrict__ lr2,
-                         long long rows, int C, float* __restrict__ P_a, float* __restrict__ P_v, float* __restrict__ P_d) {
+                         long long rows, int C, float* __restrict__ P_a, OT* __restrict__ P_v, OT* __restrict__ P_d) {
   __shared__ float s_buf[SP_WARPS][288];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   float* wbuf = s_buf[w];
@@ -182,18 +184,33 @@ bee_self_products_kernel(const float* __restrict__ lr0, const float* __restrict_
     bee_fwd_point(l0, l1, l2, r0, r1, r2, &o);
     float* pa = P_a + (size_t)row * 3 * C + c0 + lane;
     pa[0] = o.y000; pa[C] = o.y110; pa[2 * C] = o.y220;
-    float* pv = P_v + ((size_t)row * 5 * C + c0) * 3;
-    sp_store<3>(pv, wbuf, lane, o.y011);
-    sp_store<3>(pv + (size_t)C * 3, wbuf, lane, o.y101);
-    sp_store<3>(pv + (size_t)2 * C * 3, wbuf, lane, o.y121);
-    sp_store<3>(pv + (size_t)3 * C * 3, wbuf, lane, o.y211);
-    sp_store<3>(pv + (size_t)4 * C * 3, wbuf, lane, o.y111);
-    float* pd = P_d + ((size_t)row * 5 * C + c0) * 9;
-    sp_store<9>(pd, wbuf, lane, o.y022);
-    sp_store<9>(pd + (size_t)C * 9, wbuf, lane, o.y202);
-    sp_store<9>(pd + (size_t)2 * C * 9, wbuf, lane, o.y112);
-    sp_store<9>(pd + (size_t)3 * C * 9, wbuf, lane, o.y222);
-    sp_store<9>(pd + (size_t)4 * C * 9, wbuf, lane, o.y212);
+    if (sizeof(OT) == 2) {
+      // BF16 outputs are component-major, [row][3 | 9][5*chan]: lanes are consecutive addresses, no staging needed
+      OT* pv = P_v + (size_t)row * 3 * 5 * C + c0 + lane;
+      OT* pd = P_d + (size_t)row * 9 * 5 * C + c0 + lane;
+      const float* vs[5] = {o.y011, o.y101, o.y121, o.y211, o.y111};
+      const float* ds[5] = {o.y022, o.y202, o.y112, o.y222, o.y212};
+#pragma unroll
+      for (int q = 0; q < 5; q++) {
+#pragma unroll
+        for (int x = 0; x < 3; x++) pv[(size_t)x * 5 * C + q * C] = (OT)vs[q][x];
+#pragma unroll
+        for (int x = 0; x < 9; x++) pd[(size_t)x * 5 * C + q * C] = (OT)ds[q][x];
+      }
+    } else {
+      OT* pv = P_v + ((size_t)row * 5 * C + c0) * 3;
+      sp_store<3>(pv, wbuf, lane, o.y011);
+      sp_store<3>(pv + (size_t)C * 3, wbuf, lane, o.y101);
+      sp_store<3>(pv + (size_t)2 * C * 3, wbuf, lane, o.y121);
+      sp_store<3>(pv + (size_t)3 * C * 3, wbuf, lane, o.y211);
+      sp_store<3>(pv + (size_t)4 * C * 3, wbuf, lane, o.y111);
+      OT* pd = P_d + ((size_t)row * 5 * C + c0) * 9;
+      sp_store<9>(pd, wbuf, lane, o.y022);
+      sp_store<9>(pd + (size_t)C * 9, wbuf, lane, o.y202);
+      sp_store<9>(pd + (size_t)2 * C * 9, wbuf, lane, o.y112);
+      sp_store<9>(pd + (size_t)3 * C * 9, wbuf, lane, o.y222);
+      sp_store<9>(pd + (size_t)4 * C * 9, wbuf, lane, o.y212);
+    }
   }
 }
 
@@ -201,15 +218,22 @@ bee_self_products_kernel(const float* __restrict__ lr0, const float* __restrict_
 
 // lr0 [rows][2*chan], lr1 [rows][2*chan][3], lr2 [rows][2*chan][3][3]: left operands in channels [0, chan), right in
 // [chan, 2*chan). Outputs as described at bee_self_products_kernel. chan a multiple of 32.
+// out_bf16: P_v and P_d are BF16 and component-major, [rows][3][5*chan] and [rows][9][5*chan] (the input form of
+// ld_linear_bf16_tc_in16); P_a stays FP32.
 extern "C" int ld_bee_self_products(const float* lr0, const float* lr1, const float* lr2, long long rows, int chan, float* P_a,
-                                    float* P_v, float* P_d, void* stream) {
+                                    void* P_v, void* P_d, int out_bf16, void* stream) {
   if (rows < 0 || chan <= 0) return LD_ERR_SHAPE;
   if (chan % 32 != 0) { ld_set_last_message("bee self products: chan must be a multiple of 32"); return LD_ERR_UNSUPPORTED; }
   if (rows == 0) return LD_OK;
   const long long items = rows * (chan / 32);
   long long blocks = (items + SP_WARPS - 1) / SP_WARPS;
   if (blocks > 148LL * 16) blocks = 148LL * 16;
-  bee_self_products_kernel<<<(unsigned)blocks, SP_WARPS * 32, 0, (cudaStream_t)stream>>>(lr0, lr1, lr2, rows, chan, P_a, P_v, P_d);
+  if (out_bf16)
+    bee_self_products_kernel<__nv_bfloat16><<<(unsigned)blocks, SP_WARPS * 32, 0, (cudaStream_t)stream>>>(
+        lr0, lr1, lr2, rows, chan, P_a, (__nv_bfloat16*)P_v, (__nv_bfloat16*)P_d);
+  else
+    bee_self_products_kernel<float><<<(unsigned)blocks, SP_WARPS * 32, 0, (cudaStream_t)stream>>>(lr0, lr1, lr2, rows, chan, P_a,
+                                                                                                  (float*)P_v, (float*)P_d);
   LD_LAUNCH_CHECK();
   return LD_OK;
 }

@@ -27,7 +27,8 @@ SIGNATURES = {
     "ld_tensor_linear_dw_workspace": [I, LL, I, I, P],
     "ld_tensor_linear_dw": [I, P, P, P, LL, I, I, P, SZ, P],
     "ld_bee_fwd": [P, P, P, P, P, P, LL, I, P, P],
-    "ld_bee_self_products": [P, P, P, LL, I, P, P, P, P],
+    "ld_bee_self_products": [P, P, P, LL, I, P, P, P, I, P],
+    "ld_linear_bf16_tc_in16": [P, LL, I, I, P, P, I, I, P, P, P],
     "ld_bee_bw": [I, P, P, P, P, LL, I, P, P, P, P],
     "ld_cow_o0_fwd": [P, P, P, P, LL, I, P, P, P],
     "ld_cow_o0_bw": [P, P, P, P, LL, I, P, P, P],
@@ -45,7 +46,7 @@ SIGNATURES = {
     "ld_ant16_contract_out": [I, P, P, LL, I, I, P, P],
     "ld_tensor_prod_bare": [I, I, I, I, P, P, LL, P, P],
     "ld_bee_messages_scalar_bf16_tc": [P, P, P, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P, P, P, F, P, I, P, P],
-    "ld_bee_messages_vd_f32": [P, P, P, I, I, F, P, P, P, P, P, P, F, P, P, I, P],
+    "ld_bee_messages_vd_f32": [P, P, P, I, I, F, P, P, P, P, P, P, F, P, P, I, I, P],
     "ld_bee_messages_scalar_f32": [P, P, P, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P, F, P, P],
     "ld_painn_message_f32": [P, P, P, I, I, I, I, F, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P],
 }

@@ -128,14 +128,18 @@ class Messages(nn.Module):
             l1 = self.L1(x_v.reshape(Nt, -1, 3))
             l2 = self.L2(x_d.reshape(Nt, -1, 3, 3))
         rij = r_ij.contiguous()
-        S_v = torch.empty(Nt, 5 * C, 3, dtype=torch.float32, device=dev)
-        S_d = torch.empty(Nt, 5 * C, 3, 3, dtype=torch.float32, device=dev)
+        # the per-node product sums feed tensor-core channel mixings on the bf16 path, which round them to BF16 anyway
+        sums16 = self.precision == "bf16" and self.dim_v % 32 == 0 and self.dim_d % 32 == 0
+        sdt = torch.bfloat16 if sums16 else torch.float32
+        # (BF16 sums are component-major, [Nt][3 | 9][5C]: a (node, component) row is the GEMM's contiguous K)
+        S_v = torch.empty((Nt, 3, 5 * C) if sums16 else (Nt, 5 * C, 3), dtype=sdt, device=dev)
+        S_d = torch.empty((Nt, 9, 5 * C) if sums16 else (Nt, 5 * C, 3, 3), dtype=sdt, device=dev)
         B_a = torch.empty(Nt, self.dim_a, dtype=torch.float32, device=dev)
         st = stream_ptr(dev)
         with KERNEL_TIMER.region("bee_messages_vd"):
             check(lib().ld_bee_messages_vd_f32(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, float(self.r0), ptr(l0),
                                                ptr(l1), ptr(l2), ptr(w["enc_w"]), ptr(w["enc_b"]), ptr(w["jac"]), 0.1,
-                                               ptr(S_v), ptr(S_d), 2 if feat16 else 0, st))
+                                               ptr(S_v), ptr(S_d), 2 if feat16 else 0, 1 if sums16 else 0, st))
         if self.precision == "bf16":
             with KERNEL_TIMER.region("bee_messages_scalar_tc"):
                 check(lib().ld_bee_messages_scalar_bf16_tc(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, self.dim_a,
@@ -150,9 +154,9 @@ class Messages(nn.Module):
                                                        ptr(w["enc_b"]), ptr(w["jac"]), ptr(w["Yt"]), ptr(w["W1t"]), ptr(w["b1"]),
                                                        ptr(w["W2t"]), ptr(w["b2"]), ptr(w["W3t"]), ptr(w["b3"]), ptr(w["Wdt"]),
                                                        0.1, ptr(B_a), st))
-        if self.precision == "bf16" and self.dim_v % 32 == 0 and self.dim_d % 32 == 0:
-            B_v = ops.linear_bf16_tc(S_v, w["Yvp"], self.dim_v, None, ops.ACT_NONE, inds=1)
-            B_d = ops.linear_bf16_tc(S_d, w["Ydp"], self.dim_d, None, ops.ACT_NONE, inds=2)
+        if sums16:
+            B_v = ops.linear_bf16_tc_cm(S_v, w["Yvp"], self.dim_v, 1)
+            B_d = ops.linear_bf16_tc_cm(S_d, w["Ydp"], self.dim_d, 2)
         else:
             B_v = ops.tensor_linear(1, w["Yv"], S_v)
             B_d = ops.tensor_linear(2, w["Yd"], S_d)
@@ -247,8 +251,15 @@ class SelfTensProds(nn.Module):
         if not torch.is_grad_enabled() and x_a.is_cuda and self.chan % 32 == 0:
             # three channel mixings in (left|right stacked), one product kernel, three channel mixings out
             c = self._cat_weights()
-            P_a, P_v, P_d = ops.bee_self_products(self._mix(c, "LR0", 0, xa), self._mix(c, "LR1", 1, xv), self._mix(c, "LR2", 2, xd))
-            y_a, y_v, y_d = self._mix(c, "Ya", 0, P_a), self._mix(c, "Yv", 1, P_v), self._mix(c, "Yd", 2, P_d)
+            tc_out = all(n + "p" in c and c[n].shape[0] % 32 == 0 for n in ("Yv", "Yd"))  # BF16 products for tcgen05 Y maps
+            P_a, P_v, P_d = ops.bee_self_products(self._mix(c, "LR0", 0, xa), self._mix(c, "LR1", 1, xv), self._mix(c, "LR2", 2, xd),
+                                                  out_bf16=tc_out)
+            y_a = self._mix(c, "Ya", 0, P_a)
+            if tc_out:
+                y_v = ops.linear_bf16_tc_cm(P_v, c["Yvp"], c["Yv"].shape[0], 1)
+                y_d = ops.linear_bf16_tc_cm(P_d, c["Ydp"], c["Yd"].shape[0], 2)
+            else:
+                y_v, y_d = self._mix(c, "Yv", 1, P_v), self._mix(c, "Yd", 2, P_d)
             return (self.gn_a(y_a.reshape(*rest, -1)), self.gn_v(y_v.reshape(*rest, -1, 3)),
                     self.gn_d(y_d.reshape(*rest, -1, 3, 3)))
         y = Bee.apply(self.L0(xa), self.L1(xv), self.L2(xd), self.R0(xa), self.R1(xv), self.R2(xd))

@@ -113,9 +113,11 @@ def bee_fwd(l_0, l_1, l_2, r_0, r_1, r_2):
     return outs
 
 
-def bee_self_products(lr_0, lr_1, lr_2):
+def bee_self_products(lr_0, lr_1, lr_2, out_bf16=False):
     """13 Bee products of left = lr[:, :chan], right = lr[:, chan:], concatenated per rank:
-    P_a [rows, 3*chan], P_v [rows, 5*chan, 3], P_d [rows, 5*chan, 3, 3] (the inputs of concatenated Y maps)."""
+    P_a [rows, 3*chan], P_v [rows, 5*chan, 3], P_d [rows, 5*chan, 3, 3] (the inputs of concatenated Y maps).
+    out_bf16: P_v [rows, 3, 5*chan] and P_d [rows, 9, 5*chan] as BF16, component-major (for linear_bf16_tc_cm, which
+    rounds its operands to BF16 anyway)."""
     for name, t in (("lr_0", lr_0), ("lr_1", lr_1), ("lr_2", lr_2)):
         require_cuda_f32(t, name)
     rows, chan = lr_0.shape[0], lr_0.shape[1] // 2
@@ -123,11 +125,12 @@ def bee_self_products(lr_0, lr_1, lr_2):
         raise RuntimeError("bee_self_products: expected [rows, 2*chan], [rows, 2*chan, 3], [rows, 2*chan, 3, 3]")
     dev = lr_0.device
     P_a = torch.empty(rows, 3 * chan, dtype=torch.float32, device=dev)
-    P_v = torch.empty(rows, 5 * chan, 3, dtype=torch.float32, device=dev)
-    P_d = torch.empty(rows, 5 * chan, 3, 3, dtype=torch.float32, device=dev)
+    odt = torch.bfloat16 if out_bf16 else torch.float32
+    P_v = torch.empty((rows, 3, 5 * chan) if out_bf16 else (rows, 5 * chan, 3), dtype=odt, device=dev)
+    P_d = torch.empty((rows, 9, 5 * chan) if out_bf16 else (rows, 5 * chan, 3, 3), dtype=odt, device=dev)
     with KERNEL_TIMER.region("bee_self_products"):
         check(lib().ld_bee_self_products(ptr(lr_0), ptr(lr_1), ptr(lr_2), rows, chan, ptr(P_a), ptr(P_v), ptr(P_d),
-                                         stream_ptr(dev)))
+                                         1 if out_bf16 else 0, stream_ptr(dev)))
     return P_a, P_v, P_d
 
 
@@ -291,6 +294,20 @@ def linear_bf16_tc(x, W_packed, N, bias=None, act=ACT_NONE, inds=0, out_bf16=Fal
             return y
         y = torch.empty(shape, dtype=torch.float32, device=x.device)
         check(lib().ld_linear_bf16_tc(ptr(x), rows, K, S, ptr(W_packed), ptr(bias), N, act, ptr(y), status, st))
+    return y
+
+
+def linear_bf16_tc_cm(x16, W_packed, N, inds, bias=None, act=ACT_NONE):
+    """linear_bf16_tc for activations stored as BF16 in component-major form, x16 [rows, 3**inds, K] (K contiguous,
+    a multiple of 8): returns y [rows, N, (3,)*inds] FP32. Same result as the FP32 [rows, K, (3,)*inds] form of the
+    same values (the MMA operands are BF16 either way)."""
+    if not x16.is_cuda or x16.dtype != torch.bfloat16 or not x16.is_contiguous() or x16.dim() != 3 or x16.shape[1] != 3 ** inds:
+        raise RuntimeError("linear_bf16_tc_cm: expected a contiguous CUDA BF16 tensor [rows, 3**inds, K]")
+    rows, S, K = x16.shape
+    y = torch.empty((rows, N) + (3,) * inds, dtype=torch.float32, device=x16.device)
+    with KERNEL_TIMER.region("linear_bf16_tc"):
+        check(lib().ld_linear_bf16_tc_in16(ptr(x16), rows, K, S, ptr(W_packed), ptr(bias), N, act, ptr(y),
+                                           ptr(tc_status(x16.device)), stream_ptr(x16.device)))
     return y
 
 

@@ -173,3 +173,20 @@ def test_denoiser_bf16_vs_oracle():
         got = mine((s_.cuda(), t_.cuda()), x0.cuda(), x1.cuda(), box, types.cuda(), painn.empty_bond_graph(B, N, "cuda"))
     _status_ok()
     close(got, want, 2e-2)
+
+
+@pytest.mark.parametrize("inds,rows,K,N", [(1, 700, 640, 64), (2, 129, 640, 32), (0, 300, 64, 128), (2, 5, 8, 32)])
+def test_linear_component_major_bf16_input_matches_fp32_input(inds, rows, K, N):
+    """BF16 activations stored [rows, 3**inds, K] give bit-identical results to the same values passed as FP32
+    [rows, K, (3,)*inds]: the tensor-core path rounds its operands to BF16 either way"""
+    from ld_b200 import ops
+    g = torch.Generator().manual_seed(K + N + inds)
+    S = 3 ** inds
+    x16 = torch.randn(rows, S, K, generator=g).to(torch.bfloat16).cuda()
+    W = (torch.randn(N, K, generator=g) * K ** -0.5).cuda()
+    Wp = ops.pack_weights_bf16(W)
+    x32 = x16.float().permute(0, 2, 1).reshape(rows, K, *([3] * inds)).contiguous()
+    a = ops.linear_bf16_tc_cm(x16, Wp, N, inds)
+    b = ops.linear_bf16_tc(x32, Wp, N, inds=inds)
+    assert a.shape == b.shape and torch.equal(a, b)
+    assert int(ops.tc_status("cuda").item()) == 0
