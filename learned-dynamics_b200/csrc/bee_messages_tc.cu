@@ -104,8 +104,7 @@ __device__ __forceinline__ int bt_sync_or(int flag) {
 }
 __device__ __forceinline__ void bt_sync_workers() { asm volatile("barrier.cta.sync 2, %0;" ::"n"(BT_WORK_THREADS) : "memory"); }
 
-__device__ __forceinline__ void bt_geometry(const float* __restrict__ rij, long long e, float r0, const float* jac, BtGeom* g) {
-  const float x = rij[e * 3], y = rij[e * 3 + 1], z = rij[e * 3 + 2];
+__device__ __forceinline__ void bt_geometry(float x, float y, float z, float r0, const float* jac, BtGeom* g) {
   const float d = sqrtf(x * x + y * y + z * z);
   const float zz = d / r0;
   float pw[9];
@@ -262,16 +261,28 @@ bee_scalar_tc_kernel(BtParams P) {
       int cur = n_begin, node_lo = n_begin;
       bt_sync_workers();
       if (tid <= BT_EDGES) s_rowwin[tid] = P.row_ptr[min(node_lo + tid, n_end > n_begin ? n_end : n_begin)];
+      float pre_x = 0.f, pre_y = 0.f, pre_z = 0.f;
+      int pre_j = 0;
+      if (tid < BT_EDGES && br.e_begin + tid < br.e_end) {
+        const long long en = br.e_begin + tid;
+        pre_x = P.rij[en * 3]; pre_y = P.rij[en * 3 + 1]; pre_z = P.rij[en * 3 + 2]; pre_j = P.dst[en];
+      }
       bt_sync_workers();
       for (long long e0 = br.e_begin; e0 < br.e_end; e0 += BT_EDGES) {
         const int cnt = (int)((br.e_end - e0) < BT_EDGES ? (br.e_end - e0) : BT_EDGES);
-        // ---- 1. edge geometry ----------------------------------------------------------------------------
+        // ---- 1. edge geometry (the displacement and neighbour index of this tile were fetched one tile ahead) ------
         if (tid < BT_EDGES) {
           int j = 0, s = -1;
+          const float gx = pre_x, gy = pre_y, gz = pre_z;
+          const int gj = pre_j;
+          {
+            const long long en = e0 + BT_EDGES + tid;   // next tile's edge for this thread
+            if (en < br.e_end) { pre_x = P.rij[en * 3]; pre_y = P.rij[en * 3 + 1]; pre_z = P.rij[en * 3 + 2]; pre_j = P.dst[en]; }
+          }
           if (tid < cnt) {
             const long long e = e0 + tid;
-            bt_geometry(P.rij, e, P.r0, s_jac, &s_geom[tid]);
-            j = P.dst[e];
+            bt_geometry(gx, gy, gz, P.r0, s_jac, &s_geom[tid]);
+            j = gj;
             if ((long long)s_rowwin[BT_EDGES] > e) {
               int lo = 0, hi = BT_EDGES;
               while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if ((long long)s_rowwin[mid] > e) hi = mid; else lo = mid; }
