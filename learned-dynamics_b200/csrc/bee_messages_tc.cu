@@ -141,6 +141,7 @@ bee_scalar_tc_kernel(BtParams P) {
   __shared__ int s_src[BT_EDGES];
   __shared__ int s_rowwin[BT_EDGES + 1];
   __shared__ float s_jac[72];
+  __shared__ float s_head[4][128], s_tail[4][128];   // partial per-node sums of the four row quarters
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool mma_lane = warp == BT_MMA_WARP && lane == 0;
@@ -433,30 +434,62 @@ bee_scalar_tc_kernel(BtParams P) {
         tc::fence_before_sync();
         bt_sync_workers();
         lap(9);
+        // Per-node sums in two steps. (a) Thread (column, row quarter) adds up its 32 rows in edge order: the sum for
+        // the quarter's first node goes to s_head, for its last node (when different) to s_tail, nodes strictly inside
+        // the quarter are complete and written at once. (b) One thread per column joins the four quarters with the sum
+        // carried over from earlier tiles. Every addition happens in a fixed order.
+        {
+          const int col = tid & 127, rq = tid >> 7;
+          const int r_lo = rq * 32, r_hi = min(r_lo + 32, cnt);
+          if (col < A && r_lo < cnt) {
+            const int slot = col >> 2, sub = col & 3;
+            int c_node = s_src[r_lo];
+            float sum = 0.f, head = 0.f;
+            bool first = true;
+            for (int eb = r_lo; eb < r_hi; eb += 8) {
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; i++) {   // rows beyond cnt hold zeros
+                const int e = eb + i;
+                const int sw = (slot & ~7) | ((slot ^ e) & 7);
+                v[i] = stage_f[(size_t)e * A + sw * 4 + sub];
+              }
+              const int last = min(eb + 7, r_hi - 1);
+              if (s_src[eb] == c_node && s_src[last] == c_node) {
+                sum += ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                  if (eb + i < r_hi) {
+                    const int s = s_src[eb + i];
+                    if (s != c_node) {
+                      if (first) { head = sum; first = false; }
+                      else P.out_a[(size_t)c_node * A + col] = sum * P.scale;
+                      for (int z = c_node + 1; z < s; z++) P.out_a[(size_t)z * A + col] = 0.f;   // nodes without edges
+                      sum = 0.f;
+                      c_node = s;
+                    }
+                    sum += v[i];
+                  }
+                }
+              }
+            }
+            s_head[rq][col] = first ? sum : head;
+            s_tail[rq][col] = first ? 0.f : sum;
+          }
+        }
+        bt_sync_workers();
         if (tid < A) {
           int c_node = tile_cur;
           float a_sum = acc;
-          const int slot = tid >> 2, sub = tid & 3;
-          for (int eb = 0; eb < cnt; eb += 8) {
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-              const int e = eb + i;
-              const int sw = (slot & ~7) | ((slot ^ e) & 7);
-              v[i] = stage_f[(size_t)e * A + sw * 4 + sub];
-            }
-            const int last = min(eb + 7, cnt - 1);
-            if (s_src[eb] == c_node && s_src[last] == c_node) {
-              a_sum += ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; i++) {
-                if (eb + i < cnt) {
-                  const int s = s_src[eb + i];
-                  if (s != c_node) { flush_until(c_node, s, a_sum); a_sum = 0.f; c_node = s; }
-                  a_sum += v[i];
-                }
-              }
+          for (int q = 0; q < 4 && q * 32 < cnt; q++) {
+            const int f = s_src[q * 32], l = s_src[min(q * 32 + 31, cnt - 1)];
+            if (f != c_node) { flush_until(c_node, f, a_sum); a_sum = 0.f; c_node = f; }
+            a_sum += s_head[q][tid];
+            if (l != f) {
+              P.out_a[(size_t)f * A + tid] = a_sum * P.scale;   // gaps after f were zero-filled by the quarter's thread
+              a_sum = s_tail[q][tid];
+              c_node = l;
             }
           }
           acc = a_sum;

@@ -81,9 +81,11 @@ def test_bee_denoiser_vs_oracle():
 
 
 @pytest.mark.parametrize("dims,B,N,r0,box", [((128, 64, 32, 128), 2, 300, 3.0, (9.0, 9.0, 9.5)), ((64, 32, 16, 96), 3, 50, 5.0, None),
-                                             ((128, 8, 8, 32), 1, 6, 1.0, None)])
+                                             ((128, 8, 8, 32), 1, 6, 1.0, None), ((128, 64, 32, 128), 8, 256, 5.0, None),
+                                             ((64, 32, 32, 128), 3, 40, 0.9, None), ((64, 32, 32, 64), 2, 20, 0.01, None)])
 def test_messages_tensor_core_vs_fp32(dims, B, N, r0, box):
-    """scalar channel on tcgen05 (BF16 operands) against the FP32 fused kernels: 2e-2 relative"""
+    """scalar channel on tcgen05 (BF16 operands) against the FP32 fused kernels: 2e-2 relative. The last rows cover
+    many tiles and node segments, a sparse graph with nodes without neighbours, and a graph without any edge."""
     from ld_b200 import bee, graph_layers as GL, ops
     torch.manual_seed(sum(dims) + 1)
     mes = bee.Messages(r0, *dims).cuda()
@@ -104,7 +106,8 @@ def test_messages_tensor_core_vs_fp32(dims, B, N, r0, box):
     assert int(ops.tc_status("cuda").item()) == 0
     for a, b in zip(got, ref):
         close(a, b, 2e-2)
-    assert torch.equal(got[0], got2[0])
+    for a, b in zip(got, got2):
+        assert torch.equal(a, b)  # fixed summation order: run-to-run identical
 
 
 def test_bee_denoiser_bf16_vs_fp32():
