@@ -122,6 +122,7 @@ painn_message_tc_kernel(TcMessageParams P) {
   __shared__ int s_dst[MT_EDGES];
   __shared__ int s_src[MT_EDGES];
   __shared__ int s_rowwin[MT_EDGES + 1];  // row_ptr[node_lo .. node_lo+128] of the coming tile
+  __shared__ float s_head[2][MT_CG * 4], s_tail[2][MT_CG * 4];   // partial per-node sums of the two row halves
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool mma_lane = warp == MT_MMA_WARP && lane == 0;
@@ -435,36 +436,73 @@ painn_message_tc_kernel(TcMessageParams P) {
         }
         sync_workers();
         lap(8);
-        // sum per source node, in edge order; thread = one (channel, component) column
+        // Sum per source node in edge order, in two steps. (a) Thread (column, row half) adds up its 64 rows: the sum
+        // for the half's first node goes to s_head, for its last node (when different) to s_tail, nodes strictly
+        // inside the half are complete and written at once. (b) One thread per column joins the two halves with the
+        // sum carried over from earlier tiles. Column = (channel, component); every addition is in a fixed order.
+        {
+          const int col = tid & (MT_CG * 4 - 1), rh = tid / (MT_CG * 4);   // 256 columns x 2 row halves
+          const int r_lo = rh * (MT_EDGES / 2), r_hi = min(r_lo + MT_EDGES / 2, cnt);
+          const int c_chan = pass * MT_CG + ((col >> 2) & (MT_CG - 1)), c_k = col & 3;
+          if (rh < 2 && r_lo < cnt && c_chan < n) {
+            const int slot = (col >> 2) & (MT_CG - 1);
+            auto write_node = [&](int v, float val) {
+              if (c_k < 3) {
+                const size_t off = ((size_t)v * n + c_chan) * 3 + c_k;
+                P.out_v[off] = P.res_v != nullptr ? val + P.res_v[off] : val;
+              } else {
+                const size_t off = (size_t)v * n + c_chan;
+                P.out_a[off] = P.res_a != nullptr ? val + P.res_a[off] : val;
+              }
+            };
+            int c_node = s_src[r_lo];
+            float sum = 0.f, head = 0.f;
+            bool first = true;
+            for (int eb = r_lo; eb < r_hi; eb += 8) {
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; i++) {  // rows beyond cnt hold zeros
+                const int e = eb + i;
+                const int sw = (slot & ~7) | ((slot ^ e) & 7);
+                v[i] = stage_f[(size_t)e * (MT_CG * 4) + sw * 4 + c_k];
+              }
+              const int last = min(eb + 7, r_hi - 1);
+              if (s_src[eb] == c_node && s_src[last] == c_node) {
+                sum += ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                  if (eb + i < r_hi) {
+                    const int s = s_src[eb + i];
+                    if (s != c_node) {
+                      if (first) { head = sum; first = false; }
+                      else write_node(c_node, sum);
+                      for (int z = c_node + 1; z < s; z++) write_node(z, 0.f);   // nodes without edges
+                      sum = 0.f;
+                      c_node = s;
+                    }
+                    sum += v[i];
+                  }
+                }
+              }
+            }
+            s_head[rh][col] = first ? sum : head;
+            s_tail[rh][col] = first ? 0.f : sum;
+          }
+        }
+        sync_workers();
         if (reducer) {
           int c_node = tile_cur;
           float a_sum = acc[pass];
-          const int slot = red_c;
-          for (int eb = 0; eb < cnt; eb += 8) {
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) {  // rows beyond cnt hold zeros
-              const int e = eb + i;
-              const int sw = (slot & ~7) | ((slot ^ e) & 7);
-              v[i] = stage_f[(size_t)e * (MT_CG * 4) + sw * 4 + red_k];
-            }
-            const int last = min(eb + 7, cnt - 1);
-            if (s_src[eb] == c_node && s_src[last] == c_node) {
-              // whole group belongs to the current node (src is sorted): fixed-shape tree sum
-              a_sum += ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; i++) {
-                if (eb + i < cnt) {
-                  const int s = s_src[eb + i];
-                  if (s != c_node) {
-                    flush_until(pass, c_node, s, a_sum);
-                    a_sum = 0.f;
-                    c_node = s;
-                  }
-                  a_sum += v[i];
-                }
-              }
+          const bool live = pass * MT_CG + red_c < n;
+          for (int q = 0; q < 2 && q * (MT_EDGES / 2) < cnt; q++) {
+            const int f = s_src[q * (MT_EDGES / 2)], l = s_src[min(q * (MT_EDGES / 2) + MT_EDGES / 2 - 1, cnt - 1)];
+            if (f != c_node) { flush_until(pass, c_node, f, a_sum); a_sum = 0.f; c_node = f; }
+            if (live) a_sum += s_head[q][tid];
+            if (l != f) {
+              flush_until(pass, f, f + 1, a_sum);   // node f alone: the gaps after it were filled by the half's thread
+              a_sum = live ? s_tail[q][tid] : 0.f;
+              c_node = l;
             }
           }
           acc[pass] = a_sum;
