@@ -29,6 +29,9 @@ constexpr int BT_SYNC_THREADS = (BT_WORK_WARPS + 1) * 32;
 constexpr int BT_STAGES = 3;        // weight ring: 32 KB slabs (a bulk copy costs about the same issue time whatever its size)
 constexpr int BT_SLAB_BYTES = 32 * 1024;
 constexpr int BT_LAYERS = 4;
+// Byte stride between the 8-column panels of the operand tile: 128 rows x 16 bytes plus one 16-byte pad, so that the
+// panels a warp of the product phase writes to (32 channels = 4 panels, same row) fall into different banks
+constexpr int BT_PANEL = BT_EDGES * 16 + 16;
 
 struct BtLayer {
   const __nv_bfloat16* w;   // packed panels [K/8][N][8]
@@ -218,7 +221,7 @@ bee_scalar_tc_kernel(BtParams P) {
               const uint32_t b_base = tc::smem_u32(b_smem + (size_t)st * slab);
               for (int kk = 0; kk < L.slab_ksteps && ks0 + kk < L.ksteps; kk++) {
                 const int ks = ks0 + kk;
-                const uint64_t ad = tc::smem_desc(a_base + (L.a_panel + ks * 2) * (BT_EDGES * 16), BT_EDGES * 16, 128);
+                const uint64_t ad = tc::smem_desc(a_base + (L.a_panel + ks * 2) * BT_PANEL, BT_PANEL, 128);
                 const uint64_t bd = tc::smem_desc(b_base + kk * 2 * (L.N * 16), L.N * 16, 128);
                 tc::mma_bf16(tmem_base, ad, bd, tc::idesc_bf16(BT_EDGES, L.N), ks > 0 ? 1u : 0u);
               }
@@ -358,9 +361,9 @@ bee_scalar_tc_kernel(BtParams P) {
               }
               unsigned short* arow = reinterpret_cast<unsigned short*>(a_smem + (size_t)t * 16);
               const int k0 = pc_c, k1 = C + pc_c, k2 = 2 * C + pc_c;
-              arow[(size_t)(k0 >> 3) * (BT_EDGES * 8) + (k0 & 7)] = bt_bf16(y0);
-              arow[(size_t)(k1 >> 3) * (BT_EDGES * 8) + (k1 & 7)] = bt_bf16(y1);
-              arow[(size_t)(k2 >> 3) * (BT_EDGES * 8) + (k2 & 7)] = bt_bf16(y2);
+              arow[(size_t)(k0 >> 3) * (BT_PANEL / 2) + (k0 & 7)] = bt_bf16(y0);
+              arow[(size_t)(k1 >> 3) * (BT_PANEL / 2) + (k1 & 7)] = bt_bf16(y1);
+              arow[(size_t)(k2 >> 3) * (BT_PANEL / 2) + (k2 & 7)] = bt_bf16(y2);
             }
           }
         }
@@ -399,7 +402,7 @@ bee_scalar_tc_kernel(BtParams P) {
                 uint4 q;
                 q.x = tc::pack_bf16x2(t8[0], t8[1]); q.y = tc::pack_bf16x2(t8[2], t8[3]);
                 q.z = tc::pack_bf16x2(t8[4], t8[5]); q.w = tc::pack_bf16x2(t8[6], t8[7]);
-                *reinterpret_cast<uint4*>(a_smem + (size_t)(((oc + cb) >> 3) + g8) * (BT_EDGES * 16) + row * 16) = q;
+                *reinterpret_cast<uint4*>(a_smem + (size_t)(((oc + cb) >> 3) + g8) * BT_PANEL + row * 16) = q;
               }
             }
             tc::fence_async_smem();
@@ -537,7 +540,7 @@ extern "C" int ld_bee_messages_scalar_bf16_tc(const int* row_ptr, const int* dst
   P.layer[2] = BtLayer{(const __nv_bfloat16*)W2p, b2, 0, 2 * A / 16, sk2, 2 * A, 2, 0};
   P.layer[3] = BtLayer{(const __nv_bfloat16*)W3p, b3, 0, 3 * A / 16, sk1, A, 0, -1};
   const int cols = 3 * (C > A ? C : A);
-  const size_t a_bytes = (size_t)BT_EDGES * cols * 2;
+  const size_t a_bytes = (size_t)(cols / 8) * BT_PANEL;
   const size_t staging = (size_t)BT_EDGES * A * 4;
   const size_t front = a_bytes > staging ? a_bytes : staging;
   P.slab_bytes = (unsigned)BT_SLAB_BYTES;
