@@ -59,7 +59,7 @@ struct BtParams {
   long long* prof;          // optional cycle counters: 0 geometry, 1 products, 2/4/6/8 waiting for layers, 3/5/7 epilogues, 9 staging, 10 sums
 };
 
-struct BtGeom { float rhat[3]; float enc[8]; };
+struct __align__(16) BtGeom { float enc[8]; float rhat[3]; float pad; };   // 48 bytes: three 16-byte shared-memory loads
 
 __device__ __forceinline__ int bt_lb_row(const int* __restrict__ row_ptr, int lo, int hi, long long target) {
   while (lo < hi) {
@@ -252,6 +252,9 @@ bee_scalar_tc_kernel(BtParams P) {
     };
     // product role: channel c, every pc_stride-th edge (the lanes of a warp share the edge, so loads stay coalesced)
     const int pc_c = tid % C, pc_h = tid / C, pc_stride = BT_WORK_THREADS / C;
+    // this thread's three columns of the operand tile (element offsets within a row's panels)
+    const int a_off0 = (pc_c >> 3) * (BT_PANEL / 2) + (pc_c & 7), a_off1 = ((C + pc_c) >> 3) * (BT_PANEL / 2) + (pc_c & 7),
+              a_off2 = ((2 * C + pc_c) >> 3) * (BT_PANEL / 2) + (pc_c & 7);
     float w8[8], wb = 0.f;
     if (pc_h < pc_stride) {
 #pragma unroll
@@ -319,10 +322,12 @@ bee_scalar_tc_kernel(BtParams P) {
               if (t >= BT_EDGES) break;
               float y0 = 0.f, y1 = 0.f, y2 = 0.f;
               if (t < cnt) {
-                const BtGeom& g = s_geom[t];
+                const float4* gp = reinterpret_cast<const float4*>(&s_geom[t]);
+                const float4 e0 = gp[0], e1 = gp[1], rr = gp[2];
                 float pa = wb;
-#pragma unroll
-                for (int m = 0; m < 8; m++) pa = fmaf(g.enc[m], w8[m], pa);
+                pa = fmaf(e0.x, w8[0], pa); pa = fmaf(e0.y, w8[1], pa); pa = fmaf(e0.z, w8[2], pa); pa = fmaf(e0.w, w8[3], pa);
+                pa = fmaf(e1.x, w8[4], pa); pa = fmaf(e1.y, w8[5], pa); pa = fmaf(e1.z, w8[6], pa); pa = fmaf(e1.w, w8[7], pa);
+                const float rh[3] = {rr.x, rr.y, rr.z};
                 const size_t j = (size_t)s_dst[t] * C + pc_c;
                 float l0, l1[3], l2[9];
                 if (P.feat_bf16 == 2) {
@@ -348,22 +353,17 @@ bee_scalar_tc_kernel(BtParams P) {
                   for (int k = 0; k < 9; k++) l2[k] = __ldg(P.L2 + j * 9 + k);
                 }
                 y0 = l0 * pa;
-                float dv = 0.f;
-#pragma unroll
-                for (int k = 0; k < 3; k++) dv = fmaf(l1[k], g.rhat[k], dv);
-                y1 = dv * pa;
-                float dd = 0.f;
-#pragma unroll
-                for (int x = 0; x < 3; x++)
-#pragma unroll
-                  for (int y = 0; y < 3; y++) dd = fmaf(l2[x * 3 + y], g.rhat[x] * g.rhat[y], dd);
-                y2 = dd * pa;
+                y1 = (l1[0] * rh[0] + l1[1] * rh[1] + l1[2] * rh[2]) * pa;
+                // r^T l2 r, row by row
+                const float m0 = l2[0] * rh[0] + l2[1] * rh[1] + l2[2] * rh[2];
+                const float m1 = l2[3] * rh[0] + l2[4] * rh[1] + l2[5] * rh[2];
+                const float m2 = l2[6] * rh[0] + l2[7] * rh[1] + l2[8] * rh[2];
+                y2 = (m0 * rh[0] + m1 * rh[1] + m2 * rh[2]) * pa;
               }
               unsigned short* arow = reinterpret_cast<unsigned short*>(a_smem + (size_t)t * 16);
-              const int k0 = pc_c, k1 = C + pc_c, k2 = 2 * C + pc_c;
-              arow[(size_t)(k0 >> 3) * (BT_PANEL / 2) + (k0 & 7)] = bt_bf16(y0);
-              arow[(size_t)(k1 >> 3) * (BT_PANEL / 2) + (k1 & 7)] = bt_bf16(y1);
-              arow[(size_t)(k2 >> 3) * (BT_PANEL / 2) + (k2 & 7)] = bt_bf16(y2);
+              arow[a_off0] = bt_bf16(y0);
+              arow[a_off1] = bt_bf16(y1);
+              arow[a_off2] = bt_bf16(y2);
             }
           }
         }
