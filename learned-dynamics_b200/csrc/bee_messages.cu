@@ -59,7 +59,7 @@ __device__ __forceinline__ void bm_block_range(const int* __restrict__ row_ptr, 
 }
 
 // per-edge geometry shared by all channels: rhat[3] and the eight radial features
-struct EdgeGeom { float rhat[3]; float enc[8]; };
+struct __align__(16) EdgeGeom { float enc[8]; float rhat[3]; float pad; };   // 48 bytes: three 16-byte shared-memory loads
 
 __device__ __forceinline__ void edge_geometry(const float* __restrict__ rij, long long e, float r0,
                                               const float* __restrict__ jac, EdgeGeom* g) {
@@ -104,7 +104,7 @@ __device__ __forceinline__ void edge_phi(const EdgeGeom& g, const float* w8, flo
 // the layouts a channel mixing with 5*chan inputs expects. Thread = channel; a block walks its nodes
 // and stages the geometry of up to 32 edges at a time in shared memory.
 template <typename FT, bool PACKED>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)   // four blocks per SM: at most 128 registers
 bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d, float scale, int out_bf16) {
   const FT* __restrict__ F0 = reinterpret_cast<const FT*>(P.L0);
   const FT* __restrict__ F1 = reinterpret_cast<const FT*>(P.L1);
@@ -177,11 +177,12 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
               // phi_a = pa, phi_v = pa * rhat, phi_d = pa * rhat rhat^T: with q = pa * l every product is a short
               // expression in q and rhat (e.g. 222: l_xy phi_zy = (q_x . rhat) rhat_z), about 100 operations for
               // the 60 sums instead of 150 for general right operands
-              const EdgeGeom& g = s_geom[t];
+              const float4* gp = reinterpret_cast<const float4*>(&s_geom[t]);
+              const float4 e0 = gp[0], e1 = gp[1], rr = gp[2];
               pa = wb;
-#pragma unroll
-              for (int m = 0; m < 8; m++) pa = fmaf(g.enc[m], w8[m], pa);
-              const float rh[3] = {g.rhat[0], g.rhat[1], g.rhat[2]};
+              pa = fmaf(e0.x, w8[0], pa); pa = fmaf(e0.y, w8[1], pa); pa = fmaf(e0.z, w8[2], pa); pa = fmaf(e0.w, w8[3], pa);
+              pa = fmaf(e1.x, w8[4], pa); pa = fmaf(e1.y, w8[5], pa); pa = fmaf(e1.z, w8[6], pa); pa = fmaf(e1.w, w8[7], pa);
+              const float rh[3] = {rr.x, rr.y, rr.z};
               const float q0 = l0 * pa;
               float q1[3], q2[9], m2[3], t0[3];
 #pragma unroll
