@@ -213,17 +213,25 @@ bee_scalar_tc_kernel(BtParams P) {
         for (int l = 0; l < BT_LAYERS; l++) {
           if (mma_lane && !fail) {
             tc::fence_after_sync();
-            const BtLayer& L = P.layer[l];
-            for (int ks0 = 0; ks0 < L.ksteps; ks0 += L.slab_ksteps, mmas++) {
+            // everything that is constant over the layer is computed once: the issuing thread runs alone in its warp,
+            // so every instruction between two MMAs is exposed latency
+            const int l_ksteps = P.layer[l].ksteps, l_slab = P.layer[l].slab_ksteps, l_N = P.layer[l].N;
+            const uint32_t idesc = tc::idesc_bf16(BT_EDGES, l_N);
+            uint64_t ad = tc::smem_desc(a_base + P.layer[l].a_panel * BT_PANEL, BT_PANEL, 128);
+            const uint64_t a_step = (uint64_t)((2 * BT_PANEL) >> 4), b_step = (uint64_t)((2 * l_N * 16) >> 4);
+            uint32_t accumulate = 0u;
+            for (int ks0 = 0; ks0 < l_ksteps; ks0 += l_slab, mmas++) {
               const uint32_t st = mmas % BT_STAGES, use = mmas / BT_STAGES;
               if (!tc::mbar_wait(&bar_full[st], use & 1)) { fail = 1; break; }
               tc::fence_after_sync();
-              const uint32_t b_base = tc::smem_u32(b_smem + (size_t)st * slab);
-              for (int kk = 0; kk < L.slab_ksteps && ks0 + kk < L.ksteps; kk++) {
-                const int ks = ks0 + kk;
-                const uint64_t ad = tc::smem_desc(a_base + (L.a_panel + ks * 2) * BT_PANEL, BT_PANEL, 128);
-                const uint64_t bd = tc::smem_desc(b_base + kk * 2 * (L.N * 16), L.N * 16, 128);
-                tc::mma_bf16(tmem_base, ad, bd, tc::idesc_bf16(BT_EDGES, L.N), ks > 0 ? 1u : 0u);
+              uint64_t bd = tc::smem_desc(tc::smem_u32(b_smem + (size_t)st * slab), l_N * 16, 128);
+              const int nk = min(l_slab, l_ksteps - ks0);
+#pragma unroll 4
+              for (int kk = 0; kk < nk; kk++) {
+                tc::mma_bf16(tmem_base, ad, bd, idesc, accumulate);
+                accumulate = 1u;
+                ad += a_step;   // the address field of a descriptor counts 16-byte units: next K-step = two panels on
+                bd += b_step;
               }
               tc::mma_commit(&bar_empty[st]);
             }

@@ -203,22 +203,29 @@ painn_message_tc_kernel(TcMessageParams P) {
       for (int layer = 0; layer < 3; layer++) {
         if (mma_lane && !fail) {
           tc::fence_after_sync();
+          // everything that is constant over the layer is computed once: the issuing thread runs alone in its warp,
+          // so every instruction between two MMAs is exposed latency
           const int steps = layer == 0 ? k0steps : ksteps;
+          uint64_t ad = tc::smem_desc(a_base, MT_EDGES * 16, 128);
+          const uint64_t a_step = (uint64_t)((2 * MT_EDGES * 16) >> 4), b_step = (uint64_t)((2 * N * 16) >> 4);
+          const int n_lo = min(256, N), n_hi = N - n_lo;                       // N = 4n <= 512: one or two instructions per K-step
+          const uint32_t idesc_lo = tc::idesc_bf16(MT_EDGES, n_lo), idesc_hi = tc::idesc_bf16(MT_EDGES, n_hi > 0 ? n_hi : 8);
+          const uint64_t b_hi = (uint64_t)((256 * 16) >> 4);
+          uint32_t accumulate = 0u;
           for (int ks0 = 0; ks0 < steps; ks0 += MT_SLAB_KSTEPS, mmas++) {
             const uint32_t st = mmas % nst, use = mmas / nst;
             const long long t0 = PROF ? clock64() : 0;
             if (!tc::mbar_wait(&bar_full[st], use & 1)) { fail = 1; break; }
             if (PROF) pc[9] += clock64() - t0;
             tc::fence_after_sync();
-            const uint32_t b_base = tc::smem_u32(b_smem + (size_t)st * slab);
-            for (int kk = 0; kk < MT_SLAB_KSTEPS && ks0 + kk < steps; kk++) {
-              const int ks = ks0 + kk;
-              const uint64_t ad = tc::smem_desc(a_base + ks * 2 * (MT_EDGES * 16), MT_EDGES * 16, 128);
-              for (int n0 = 0; n0 < N; n0 += 256) {
-                const int n1 = min(256, N - n0);
-                const uint64_t bd = tc::smem_desc(b_base + kk * 2 * (N * 16) + n0 * 16, N * 16, 128);
-                tc::mma_bf16(tmem_base + n0, ad, bd, tc::idesc_bf16(MT_EDGES, n1), ks > 0 ? 1u : 0u);
-              }
+            uint64_t bd = tc::smem_desc(tc::smem_u32(b_smem + (size_t)st * slab), N * 16, 128);
+            const int nk = min(MT_SLAB_KSTEPS, steps - ks0);
+            for (int kk = 0; kk < nk; kk++) {
+              tc::mma_bf16(tmem_base, ad, bd, idesc_lo, accumulate);
+              if (n_hi > 0) tc::mma_bf16(tmem_base + 256, ad, bd + b_hi, idesc_hi, accumulate);
+              accumulate = 1u;
+              ad += a_step;   // the address field of a descriptor counts 16-byte units: next K-step = two panels on
+              bd += b_step;
             }
             tc::mma_commit(&bar_empty[st]);
           }
