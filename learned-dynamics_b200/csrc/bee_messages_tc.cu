@@ -402,10 +402,16 @@ bee_scalar_tc_kernel(BtParams P) {
 #pragma unroll
               for (int g8 = 0; g8 < 4; g8++) {
                 float t8[8];
+                float b8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                if (bias != nullptr) {   // two 16-byte shared-memory loads for eight biases
+                  const float4 ba = *reinterpret_cast<const float4*>(bias + cb + g8 * 8);
+                  const float4 bb = *reinterpret_cast<const float4*>(bias + cb + g8 * 8 + 4);
+                  b8[0] = ba.x; b8[1] = ba.y; b8[2] = ba.z; b8[3] = ba.w; b8[4] = bb.x; b8[5] = bb.y; b8[6] = bb.z; b8[7] = bb.w;
+                }
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
-                  float u = v[g8 * 8 + j] + (bias != nullptr ? bias[cb + g8 * 8 + j] : 0.f);
-                  t8[j] = (act == 2) ? (u > 0.f ? u : 0.1f * u) : u;
+                  const float u = v[g8 * 8 + j] + b8[j];
+                  t8[j] = (act == 2) ? fmaxf(u, 0.1f * u) : u;   // LeakyReLU(0.1) = max(u, 0.1 u)
                 }
                 uint4 q;
                 q.x = tc::pack_bf16x2(t8[0], t8[1]); q.y = tc::pack_bf16x2(t8[2], t8[3]);

@@ -365,8 +365,11 @@ painn_message_tc_kernel(TcMessageParams P) {
 #pragma unroll
             for (int g8 = 0; g8 < 4; g8++) {
               float t[8];
+              const float4 ba = *reinterpret_cast<const float4*>(bias + cb + g8 * 8);       // eight biases, two 16-byte loads
+              const float4 bb = *reinterpret_cast<const float4*>(bias + cb + g8 * 8 + 4);
+              const float b8[8] = {ba.x, ba.y, ba.z, ba.w, bb.x, bb.y, bb.z, bb.w};
 #pragma unroll
-              for (int j = 0; j < 8; j++) t[j] = tc::silu_fast(v[g8 * 8 + j] + bias[cb + g8 * 8 + j]);
+              for (int j = 0; j < 8; j++) t[j] = tc::silu_fast(v[g8 * 8 + j] + b8[j]);
               uint4 q;
               q.x = tc::pack_bf16x2(t[0], t[1]); q.y = tc::pack_bf16x2(t[2], t[3]);
               q.z = tc::pack_bf16x2(t[4], t[5]); q.w = tc::pack_bf16x2(t[6], t[7]);
@@ -420,8 +423,11 @@ painn_message_tc_kernel(TcMessageParams P) {
             for (int k = 0; k < 4; k++) {
               float d8[8];
               tc::tmem_ld8(tmem_row + c0 + k * n, d8);
+              const float4 ba = *reinterpret_cast<const float4*>(b3 + k * n + c0);
+              const float4 bb = *reinterpret_cast<const float4*>(b3 + k * n + c0 + 4);
+              const float b8[8] = {ba.x, ba.y, ba.z, ba.w, bb.x, bb.y, bb.z, bb.w};
 #pragma unroll
-              for (int j = 0; j < 8; j++) a[k * 8 + j] *= d8[j] + b3[k * n + c0 + j];
+              for (int j = 0; j < 8; j++) a[k * 8 + j] *= d8[j] + b8[j];
             }
 #pragma unroll
             for (int j = 0; j < 8; j++) {
