@@ -504,6 +504,7 @@ painn_message_tc_kernel(TcMessageParams P) {
           }
         }
         sync_workers();
+        lap(11);
         if (reducer) {
           int c_node = tile_cur;
           float a_sum = acc[pass];

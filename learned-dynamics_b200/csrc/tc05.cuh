@@ -30,18 +30,22 @@ __device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+// One bounded wait: the thread may be suspended by the hardware until the phase completes or about
+// TC_WAIT_HINT_NS have passed (a waiting thread that is parked does not compete for issue slots with the
+// warps that do the work, unlike a tight polling loop).
+constexpr uint32_t TC_WAIT_HINT_NS = 1000;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(TC_WAIT_HINT_NS)
       : "memory");
   return ok != 0;
 }
-// returns false if the phase did not complete within the poll limit
+// returns false if the phase did not complete within the poll limit (about a second at most: 2^20 waits of up to 1 us)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   for (uint32_t i = 0; i < TC_WAIT_LIMIT; i++)
     if (mbar_try_wait(bar, parity)) return true;

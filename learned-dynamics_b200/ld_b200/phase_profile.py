@@ -14,8 +14,8 @@ import torch
 from . import _lib, graph_layers as GL
 
 PAINN_LABELS = ["geometry", "radial features", "wait layer 1 MMAs", "epilogue 1", "wait layer 2 MMAs", "epilogue 2",
-                "wait layer 3 MMAs", "per-node sums", "gather + message staging", "MMA lane: waiting for weights",
-                "producer: waiting for a free stage"]
+                "wait layer 3 MMAs", "per-node sums: join + barrier", "gather + message staging", "MMA lane: waiting for weights",
+                "producer: waiting for a free stage", "per-node sums: row halves"]
 BEE_LABELS = ["geometry", "products (gather)", "wait Y MMAs", "epilogue Y", "wait layer 1 MMAs", "epilogue 1",
               "wait layer 2 MMAs", "epilogue 2", "wait layer 3 MMAs", "staging", "per-node sums"]
 
@@ -50,7 +50,7 @@ def painn():
     with torch.no_grad():
         graph = GL.Graph.radius_graph(r0, box, pos)
     vals, ms = _run(lambda: msg(graph, x_a, x_v, graph.rij), PAINN_LABELS, 9)
-    return graph.src.numel(), vals, ms, PAINN_LABELS, 9
+    return graph.src.numel(), vals, ms, PAINN_LABELS, (0, 1, 2, 3, 4, 5, 6, 7, 8, 11)
 
 
 def bee():
@@ -66,7 +66,7 @@ def bee():
     with torch.no_grad():
         graph = GL.Graph.radius_graph(r0, None, pos)
     vals, ms = _run(lambda: mes(graph, graph.rij, x_a, x_v, x_d), BEE_LABELS, 11)
-    return graph.src.numel(), vals, ms, BEE_LABELS, 11
+    return graph.src.numel(), vals, ms, BEE_LABELS, tuple(range(11))
 
 
 def main(argv):
@@ -77,7 +77,7 @@ def main(argv):
     for i, lab in enumerate(labels):
         print(f"  {lab:36s} {vals[i] / tiles:9.0f}")
     total_label = "sum over the working warps' phases"
-    print(f"  {total_label:36s} {sum(vals[:nworker]) / tiles:9.0f}")
+    print(f"  {total_label:36s} {sum(vals[i] for i in nworker) / tiles:9.0f}")
 
 
 if __name__ == "__main__":
