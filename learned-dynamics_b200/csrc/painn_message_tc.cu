@@ -471,14 +471,14 @@ painn_message_tc_kernel(TcMessageParams P) {
             int c_node = s_src[r_lo];
             float sum = 0.f, head = 0.f;
             bool first = true;
-            for (int eb = r_lo; eb < r_hi; eb += 8) {
+            // row e keeps this column at slot (slot & ~7) | ((slot ^ e) & 7); eb is a multiple of 8, so within a group
+            // of eight rows the offsets are loop-invariant
+            const float* sp = stage_f + (size_t)r_lo * (MT_CG * 4) + (slot & ~7) * 4 + c_k;
+            const int sx = slot & 7;
+            for (int eb = r_lo; eb < r_hi; eb += 8, sp += 8 * (MT_CG * 4)) {
               float v[8];
 #pragma unroll
-              for (int i = 0; i < 8; i++) {  // rows beyond cnt hold zeros
-                const int e = eb + i;
-                const int sw = (slot & ~7) | ((slot ^ e) & 7);
-                v[i] = stage_f[(size_t)e * (MT_CG * 4) + sw * 4 + c_k];
-              }
+              for (int i = 0; i < 8; i++) v[i] = sp[i * (MT_CG * 4) + ((sx ^ i) << 2)];   // rows beyond cnt hold zeros
               const int last = min(eb + 7, r_hi - 1);
               if (s_src[eb] == c_node && s_src[last] == c_node) {
                 sum += ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
