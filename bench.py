@@ -45,7 +45,7 @@ DEFAULT_WORKLOAD = "polymers_l2_1024x256"
 # DRAM bytes per processed edge of the dominant kernel, from the committed profiler captures of a smaller case
 # (profiles/): read + write bytes of one launch / its edge count. Traffic is dominated by per-edge inputs (rij, dst)
 # and by one pass over the node features, both proportional to the edge count at fixed degree.
-DRAM_BYTES_PER_EDGE = {"bee_scalar_tc_kernel": 63.6, "painn_message_tc_kernel": 35.1}
+DRAM_BYTES_PER_EDGE = {"bee_scalar_tc_kernel": 64.1, "painn_message_tc_kernel": 33.8}
 
 
 def make_positions(w, systems, seed):
