@@ -1,7 +1,7 @@
 """Generates tests/golden/*.pt by running the REFERENCE's own Python classes on CPU.
 
-Run in a container that has the reference checkout (default /root/reference):
-    python tests/golden/make_golden.py [/path/to/learned-dynamics]
+Run where a checkout of the reference is available:
+    python tests/golden/make_golden.py /path/to/learned-dynamics      (or set LD_REFERENCE_DIR)
 The reference cannot be imported as-is without a GPU (its extension modules are CUDA-only and
 some modules create CUDA tensors at import time), so this script
   * registers stub modules for tensor_ops_cuda (the reference's own einsum form), torch_scatter
@@ -20,7 +20,9 @@ import types
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("LD_REFERENCE_DIR", "")
+if not os.path.isdir(os.path.join(REF, "managan")):
+    sys.exit("usage: make_golden.py /path/to/learned-dynamics (a checkout of the reference repository)")
 OUT = os.path.dirname(os.path.abspath(__file__))
 sys.dont_write_bytecode = True
 sys.path.insert(0, REF)
