@@ -27,7 +27,8 @@ __device__ __forceinline__ float bm_ld(const float* p, size_t i) { return __ldg(
 __device__ __forceinline__ float bm_ld(const __nv_bfloat16* p, size_t i) { return __bfloat162float(p[i]); }
 
 
-constexpr int BM_TILE = 32;  // edges staged per step
+constexpr int BM_TILE = 32;  // edges staged per step (scalar kernel: the rows of its MLP tile)
+constexpr int BV_TILE = 64;  // edges staged per step in the product-sum kernel (two block barriers per step)
 
 struct BeeEdgeParams {
   const int* row_ptr; const int* dst; const float* rij;
@@ -109,8 +110,8 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
   const FT* __restrict__ F0 = reinterpret_cast<const FT*>(P.L0);
   const FT* __restrict__ F1 = reinterpret_cast<const FT*>(P.L1);
   const FT* __restrict__ F2 = reinterpret_cast<const FT*>(P.L2);
-  __shared__ EdgeGeom s_geom[BM_TILE];
-  __shared__ int s_dst[BM_TILE];
+  __shared__ EdgeGeom s_geom[BV_TILE];
+  __shared__ int s_dst[BV_TILE];
   __shared__ float s_jac[72];
   for (int i = threadIdx.x; i < 72; i += blockDim.x) s_jac[i] = P.jacobi[i];
   __syncthreads();
@@ -135,8 +136,8 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
 #pragma unroll
       for (int i = 0; i < 45; i++) ad[i] = 0.f;
       const int e_lo = P.row_ptr[v], e_hi = P.row_ptr[v + 1];
-      for (int eb = e_lo; eb < e_hi; eb += BM_TILE) {
-        const int cnt = min(BM_TILE, e_hi - eb);
+      for (int eb = e_lo; eb < e_hi; eb += BV_TILE) {
+        const int cnt = min(BV_TILE, e_hi - eb);
         __syncthreads();  // previous tile's readers are done
         if (threadIdx.x < cnt) {
           edge_geometry(P.rij, (long long)eb + threadIdx.x, P.r0, s_jac, &s_geom[threadIdx.x]);
