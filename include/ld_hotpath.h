@@ -185,6 +185,15 @@ int ld_bee_messages_scalar_bf16_tc(const int* row_ptr, const int* dst, const flo
                                    const float* b2, const void* W3p, const float* b3, float scale, float* out_a,
                                    int feat_bf16, int* status_dev, void* stream);
 
+/* ---- group norms of node-level activations ----------------------------------------------------------
+ * Replace ScalGroupNorm (managan/layers_common.py:201-223; center = 1, S = 1: y = beta + gamma (x - mean) /
+ * sqrt(eps + var), statistics over the nodes of a system and the channels of a group) and TensGroupNorm
+ * (managan/tensor_products.py:215-232; center = 0, beta = NULL: y = gamma x / sqrt(eps + m2), m2 = mean over
+ * nodes and group channels of the squared norm over the S = 3^inds components). x, y: [B][N][C][S] float32.
+ * workspace: 98 * B * groups floats of device memory (statistics and chunk partials). */
+int ld_group_norm(const float* x, int B, int N, int C, int S, int groups, int center, float eps, const float* gamma,
+                  const float* beta, float* y, void* workspace, void* stream);
+
 /* ---- dense-weight l<=2 products (Ant16) and the bare channel-wise product --------------------------
  * Replace codegen_tensops_cuda.ant16_{o0,o1,o2,oc}_cuda and their _backward / _backleft / _wtsback
  * companions (extensions/codegen_tensops/codegen_tensops.cpp:610-1517; einsum definitions

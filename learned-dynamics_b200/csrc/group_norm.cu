@@ -1,0 +1,125 @@
+// Group norms of the node-level activations, per system and channel group:
+//   ScalGroupNorm (managan/layers_common.py:201-223): y = beta + gamma * (x - mean) / sqrt(eps + var), mean and
+//     variance over (nodes, channels of the group);
+//   TensGroupNorm (managan/tensor_products.py:215-232): y = gamma * x / sqrt(eps + m2), m2 = mean over (nodes, channels
+//     of the group) of the squared norm over the 3^inds Cartesian components; no mean is subtracted.
+// x: [B][N][C][S] float32 (S = 3^inds; S = 1 for scalars). Blocks per (system, group, chunk of nodes) compute partial
+// statistics (two passes over the chunk for the squared deviations), a small kernel joins them, a third applies them.
+#include <cuda_runtime.h>
+#include "common.cuh"
+
+namespace {
+
+constexpr int GN_THREADS = 256;
+
+__device__ __forceinline__ float gn_block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();   // red may still be read from the previous use
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < GN_THREADS / 32; i++) t += red[i];   // same order in every thread
+  return t;
+}
+
+// One block per (system, group, chunk of nodes): count, mean and sum of squared deviations from that mean of the chunk
+// (two passes over the chunk; not centred: mean = 0). part[((b*G + g)*nchunks + k)*3 + {0,1,2}].
+__global__ void __launch_bounds__(GN_THREADS) gn_partial_kernel(const float* __restrict__ x, int N, int C, int S, int G, int center,
+                                                               int nchunks, float* __restrict__ part) {
+  __shared__ float red[GN_THREADS / 32];
+  const int bg = blockIdx.x, b = bg / G, g = bg % G, kc = blockIdx.y;
+  const int cpg = C / G, slab = cpg * S;            // contiguous floats per node
+  const int per = (N + nchunks - 1) / nchunks;
+  const int n0 = kc * per, n1 = min(N, n0 + per);
+  const long long total = (long long)max(n1 - n0, 0) * slab;
+  const float* base = x + (((size_t)b * N + n0) * C + (size_t)g * cpg) * S;
+  float mean = 0.f;
+  if (center && total > 0) {
+    float s = 0.f;
+    for (long long i = threadIdx.x; i < total; i += GN_THREADS) {
+      const long long n = i / slab;
+      s += base[(size_t)n * C * S + (i - n * slab)];
+    }
+    mean = gn_block_sum(s, red) / (float)total;
+  }
+  float q = 0.f;
+  for (long long i = threadIdx.x; i < total; i += GN_THREADS) {
+    const long long n = i / slab;
+    const float d = base[(size_t)n * C * S + (i - n * slab)] - mean;
+    q = fmaf(d, d, q);
+  }
+  q = gn_block_sum(q, red);
+  if (threadIdx.x == 0) {
+    float* o = part + ((size_t)bg * nchunks + kc) * 3;
+    o[0] = (float)total; o[1] = mean; o[2] = q;
+  }
+}
+
+// Joins the chunks of a (system, group) in a fixed order (pairwise update of mean and squared deviations):
+// stats[(b*G + g)*2] = mean (0 when not centred), [.. + 1] = 1/sqrt(eps + second moment)
+__global__ void gn_finalize_kernel(const float* __restrict__ part, int BG, int nchunks, int center, long long norm_count, float eps,
+                                   float* __restrict__ stats) {
+  const int bg = blockIdx.x * blockDim.x + threadIdx.x;
+  if (bg >= BG) return;
+  float n = 0.f, mean = 0.f, m2 = 0.f;
+  for (int k = 0; k < nchunks; k++) {
+    const float* p = part + ((size_t)bg * nchunks + k) * 3;
+    const float nk = p[0];
+    if (nk <= 0.f) continue;
+    const float delta = p[1] - mean, nn = n + nk;
+    mean += delta * (nk / nn);
+    m2 += p[2] + delta * delta * (n * nk / nn);
+    n = nn;
+  }
+  // centred: variance over all elements; else: mean over (node, channel) of the squared norm over the S components
+  const float second = m2 / (float)(center ? (long long)n : norm_count);
+  stats[(size_t)bg * 2] = center ? mean : 0.f;
+  stats[(size_t)bg * 2 + 1] = 1.0f / sqrtf(eps + second);
+}
+
+__global__ void __launch_bounds__(256) gn_apply_kernel(const float* __restrict__ x, long long total, int N, int C, int S, int G,
+                                                       const float* __restrict__ stats, const float* __restrict__ gamma,
+                                                       const float* __restrict__ beta, float* __restrict__ y) {
+  const int cpg = C / G;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long cs = i / S;              // (b, n, c)
+    const int c = (int)(cs % C);
+    const long long b = cs / ((long long)N * C);
+    const float* st = stats + ((size_t)b * G + c / cpg) * 2;
+    const float v = (x[i] - st[0]) * st[1] * gamma[c];
+    y[i] = beta != nullptr ? v + beta[c] : v;
+  }
+}
+
+}  // namespace
+
+// x, y: [B][N][C][S]; gamma [C]; beta [C] or NULL; center != 0 subtracts the group mean (ScalGroupNorm, S = 1).
+// workspace: 98 * B * groups floats of device memory (statistics per system and group + up to 32 chunk partials).
+extern "C" int ld_group_norm(const float* x, int B, int N, int C, int S, int groups, int center, float eps, const float* gamma,
+                             const float* beta, float* y, void* workspace, void* stream) {
+  if (B < 0 || N <= 0 || C <= 0 || S <= 0 || groups <= 0 || C % groups != 0) return LD_ERR_SHAPE;
+  if (center && S != 1) { ld_set_last_message("group norm: the centred form is defined for scalars (S = 1)"); return LD_ERR_SHAPE; }
+  if (B == 0) return LD_OK;
+  if (workspace == nullptr) return LD_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  float* stats = (float*)workspace;
+  float* part = stats + (size_t)2 * B * groups;
+  // enough blocks to fill the device even for a few large systems: split the nodes of a (system, group) into chunks
+  int nchunks = (148 * 4 + B * groups - 1) / (B * groups);
+  if (nchunks > 32) nchunks = 32;
+  if (nchunks > N) nchunks = N;
+  if (nchunks < 1) nchunks = 1;
+  gn_partial_kernel<<<dim3(B * groups, nchunks), GN_THREADS, 0, st>>>(x, N, C, S, groups, center, nchunks, part);
+  LD_LAUNCH_CHECK();
+  gn_finalize_kernel<<<(B * groups + 127) / 128, 128, 0, st>>>(part, B * groups, nchunks, center, (long long)N * (C / groups), eps, stats);
+  LD_LAUNCH_CHECK();
+  const long long total = (long long)B * N * C * S;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  gn_apply_kernel<<<(unsigned)blocks, 256, 0, st>>>(x, total, N, C, S, groups, stats, gamma, beta, y);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}

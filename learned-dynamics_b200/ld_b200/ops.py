@@ -337,3 +337,25 @@ def painn_message_bf16_tc(row_ptr, dst, rij, mlp_dist, actv, x_v, rmax, eps=0.1,
                                              ptr(w[2]), ptr(mlp_dist.b[2]), ptr(actv), ptr(x_v), ptr(g16), ptr(res_a), ptr(res_v),
                                              ptr(out_a), ptr(out_v), ptr(edge_counter), ptr(tc_status(x_v.device)), st))
     return out_a, out_v
+
+
+def group_norm(x, groups, eps, gamma, beta=None, center=False):
+    """Per-system group norm of x [B, N, C, (3,)*inds] (fused statistics + apply kernels).
+    center=True: ScalGroupNorm (mean subtracted, beta added; scalars only); center=False: TensGroupNorm (x is divided
+    by the root of the group's mean squared norm, gamma applied, no beta)."""
+    require_cuda_f32(x, "x")
+    x = x.contiguous()
+    B, N, C = x.shape[0], x.shape[1], x.shape[2]
+    S = 1
+    for d in x.shape[3:]:
+        S *= d
+    if C % groups != 0:
+        raise RuntimeError("group_norm: channels must divide into the groups")
+    y = torch.empty_like(x)
+    ws = torch.empty(max(98 * B * groups, 1), dtype=torch.float32, device=x.device)
+    g = gamma.detach().reshape(-1).float().contiguous()
+    b = None if beta is None else beta.detach().reshape(-1).float().contiguous()
+    with KERNEL_TIMER.region("group_norm"):
+        check(lib().ld_group_norm(ptr(x), B, N, C, S, groups, 1 if center else 0, float(eps), ptr(g), ptr(b), ptr(y), ptr(ws),
+                                  stream_ptr(x.device)))
+    return y

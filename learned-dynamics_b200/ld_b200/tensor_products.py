@@ -52,6 +52,8 @@ class TensGroupNorm(nn.Module):
         self.gamma = nn.Parameter(torch.ones(chan, *[1] * inds))
 
     def forward(self, x):
+        if not torch.is_grad_enabled() and x.is_cuda and x.dim() == 3 + self.inds and x.dtype == torch.float32:
+            return ops.group_norm(x, self.groups, self.epsilon, self.gamma, None, center=False)
         batch, nodes = x.shape[0], x.shape[1]
         xg = x.reshape(batch, nodes, self.groups, -1, 3 ** self.inds)
         moment2 = (xg ** 2).sum(-1, keepdim=True).mean([1, 3], keepdim=True)

@@ -191,3 +191,43 @@ def test_drop_in_neighbour_grid_module():
         ng.get_edges(48, 64, 7., *box, x)
     with pytest.raises(RuntimeError, match="overflow"):
         ng.get_neighbours(32, 2, 7., *box, x)
+
+
+def test_group_norms_fused_against_reference_golden(golden):
+    """ScalGroupNorm / TensGroupNorm as the fused statistics + apply kernels (no autograd) against outputs of the
+    reference's own classes, and against the torch formulation used under autograd"""
+    from ld_b200.painn import ScalGroupNorm
+    from ld_b200.tensor_products import TensGroupNorm
+    n = golden["norms"]
+    sgn = ScalGroupNorm(16, 4, epsilon=1.).cuda()
+    sgn.load_state_dict(n["sgn_state"])
+    tgn1, tgn2 = TensGroupNorm(1, 8, 4).cuda(), TensGroupNorm(2, 8, 2).cuda()
+    x, xv, xd = n["x"].cuda(), n["xv"].cuda(), n["xd"].cuda()
+    with torch.no_grad():
+        close(sgn(x), n["sgn_out"], rel=2e-5)
+        close(tgn1(xv), n["tgn1_out"], rel=2e-5)
+        close(tgn2(xd), n["tgn2_out"], rel=2e-5)
+        fused = [sgn(x), tgn1(xv), tgn2(xd)]
+    for a, b in zip(fused, [sgn(x), tgn1(xv), tgn2(xd)]):   # autograd enabled: torch formulation
+        close(a, b, rel=2e-5)
+
+
+@pytest.mark.parametrize("shape,groups,inds", [((3, 257, 64), 4, 0), ((2, 100, 32, 3), 8, 1), ((5, 33, 16, 3, 3), 2, 2), ((1, 1, 8), 8, 0)])
+def test_group_norm_shapes(shape, groups, inds):
+    from ld_b200 import ops
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(*shape, generator=g) * 3 + (0.7 if inds == 0 else 0.0)
+    C = shape[2]
+    gamma, beta = torch.randn(C, generator=g), torch.randn(C, generator=g)
+    B, N = shape[0], shape[1]
+    xg = x.reshape(B, N, groups, C // groups, -1)
+    if inds == 0:
+        mean = xg.mean([1, 3, 4], keepdim=True)
+        var = ((xg - mean) ** 2).mean([1, 3, 4], keepdim=True)
+        ref = beta + gamma * ((xg - mean) / torch.sqrt(1e-3 + var)).reshape(shape)
+        got = ops.group_norm(x.cuda(), groups, 1e-3, gamma.cuda(), beta.cuda(), center=True)
+    else:
+        m2 = (xg ** 2).sum(-1, keepdim=True).mean([1, 3], keepdim=True)
+        ref = gamma.reshape(C, *[1] * inds) * (xg / torch.sqrt(1e-3 + m2)).reshape(shape)
+        got = ops.group_norm(x.cuda(), groups, 1e-3, gamma.cuda(), None, center=False)
+    close(got, ref, rel=2e-5)
