@@ -392,7 +392,7 @@ bee_scalar_tc_kernel(BtParams P) {
           lap(2 + 2 * l);
           const int N = P.layer[l].N;
           if (!fail && l < BT_LAYERS - 1) {
-            // bias, activation -> BF16 into the operand tile at out_col (this thread: row `row`, its half of the columns)
+            // bias, activation -> BF16 into the operand tile at out_col (this thread: row `row`, its quarter of the columns)
             const float* bias = l == 0 ? nullptr : s_bias + (l - 1) * 2 * A;
             const int act = P.layer[l].act, oc = P.layer[l].out_col;
             const int cpp = max(N / 4, 32);  // columns per part

@@ -5,15 +5,16 @@
 //
 // A block owns a node-aligned, contiguous slice of the CSR and walks it 128 edges at a time.
 // Three roles (warp specialised):
-//   * 8 working warps: edge geometry, radial features -> BF16 operand tile A in shared memory;
+//   * 16 working warps (four per 32-lane quarter of tensor memory, each a quarter of the columns): edge geometry,
+//     radial features -> BF16 operand tile A in shared memory;
 //     between layers they read the accumulators (tcgen05.ld), add bias, apply SiLU and write the
 //     next operand tile over A; after the last layer: accumulator x gathered neighbour activation
 //     -> vector/scalar messages, staged in shared memory and summed per source node in edge order.
 //     Sums of a node that spans tiles stay in registers; every node is written once (no atomics,
 //     fixed summation order).
-//   * 1 MMA warp (lane 0): per layer, waits for the operand tile and for each K=16 weight slab,
-//     issues the [128 x 4n x 16] MMAs into 128 lanes x 4n columns of TMEM, commits stage release
-//     and layer completion to mbarriers.
+//   * 1 MMA warp (lane 0): per layer, waits for the operand tile and for each 32 KB weight slab,
+//     issues the [128 x 4n x 16] MMAs into 128 lanes x 4n columns of TMEM (descriptors built once per
+//     layer, one add per K-step), commits stage release and layer completion to mbarriers.
 //   * 1 producer warp (lane 0): streams the pre-packed BF16 weight slabs from L2 with bulk
 //     asynchronous copies through a ring of stages; weights do not depend on the data, so it runs
 //     ahead across layers and tiles as far as the ring allows.
