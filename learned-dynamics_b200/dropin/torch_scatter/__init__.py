@@ -7,6 +7,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 from ld_b200 import graph as _graph  # noqa: E402
+from ld_b200.graph_layers import _GatherFn  # noqa: E402
 
 
 class _SegmentCoo(torch.autograd.Function):
@@ -18,8 +19,8 @@ class _SegmentCoo(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad):
-        index, = ctx.saved_tensors
-        return _graph.gather_rows(grad.contiguous(), index), None, None
+        index, = ctx.saved_tensors  # gather through an autograd function: differentiable again
+        return _GatherFn.apply(grad.contiguous(), index.to(torch.int32), index.to(torch.int64)), None, None
 
 
 def segment_coo(src, index, out=None, dim_size=None, reduce="sum"):

@@ -58,15 +58,18 @@ class _GatherFn(torch.autograd.Function):
 
 
 class _SegmentSumFn(torch.autograd.Function):
+    """The gradient of the per-node sum is the gather by source node, taken through _GatherFn so that
+    it can be differentiated again."""
+
     @staticmethod
-    def forward(ctx, x_edge, row_ptr, src32, n):
-        ctx.save_for_backward(src32)
+    def forward(ctx, x_edge, row_ptr, src32, src64, n):
+        ctx.save_for_backward(src32, src64)
         return _g.segment_sum(x_edge, row_ptr, n)
 
     @staticmethod
     def backward(ctx, grad):
-        src32, = ctx.saved_tensors
-        return _g.gather_rows(grad.contiguous(), src32), None, None, None
+        src32, src64 = ctx.saved_tensors
+        return _GatherFn.apply(grad.contiguous(), src32, src64), None, None, None, None
 
 
 def edges_read(graph, x_node):
@@ -85,7 +88,7 @@ def edges_read_dst(graph, x_node):
 def edges_reduce_src(graph, x_edge):
     """sum edge data onto source nodes: (edges, ...) -> (batch, nodes, ...)"""
     n = graph.batch * graph.nodes
-    ans = _SegmentSumFn.apply(x_edge.contiguous(), graph.row_ptr, graph.src32, n)
+    ans = _SegmentSumFn.apply(x_edge.contiguous(), graph.row_ptr, graph.src32, graph.src, n)
     return ans.reshape(graph.batch, graph.nodes, *ans.shape[1:])
 
 

@@ -57,7 +57,10 @@ def tensor_linear_dw(inds, dy, x, dim_out, dim_in):
 
 class TensorLinearFn(torch.autograd.Function):
     """Same split as the reference's C++ autograd function (extensions/tensor_ops/tensor_ops.cpp:31-170):
-    dx is the forward kernel on W transposed (swapped strides), dW is its own kernel."""
+    dx is the forward kernel on W transposed (swapped strides), dW is its own kernel. Unlike the
+    reference, the backward is itself built from autograd functions, so gradients of any order exist
+    (the double backward of torch.autograd.functional.jvp(create_graph=True), as the meanflow
+    training step uses at archs/meanflow_painn8.py:274-282)."""
 
     @staticmethod
     def forward(ctx, inds, W, x):
@@ -71,10 +74,33 @@ class TensorLinearFn(torch.autograd.Function):
         dy = dy.contiguous()
         dx = dW = None
         if ctx.needs_input_grad[2]:
-            dx = tensor_linear_fwd(ctx.inds, W.t(), dy)
+            dx = TensorLinearFn.apply(ctx.inds, W.t(), dy)
         if ctx.needs_input_grad[1]:
-            dW = tensor_linear_dw(ctx.inds, dy, x, W.shape[0], W.shape[1])
+            dW = TensorLinearDwFn.apply(ctx.inds, dy, x)
         return None, dW, dx
+
+
+class TensorLinearDwFn(torch.autograd.Function):
+    """dW[o,i] = sum over rows and tensor components of dy[.,o,s] x[.,i,s]; its own gradients are two
+    tensor_linear calls: d(dy) = G x, d(x) = G^T dy for an incoming G of W's shape."""
+
+    @staticmethod
+    def forward(ctx, inds, dy, x):
+        ctx.inds = inds
+        ctx.save_for_backward(dy, x)
+        bd = x.dim() - (1 + inds)
+        return tensor_linear_dw(inds, dy, x, dy.shape[bd], x.shape[bd])
+
+    @staticmethod
+    def backward(ctx, G):
+        dy, x = ctx.saved_tensors
+        G = G.contiguous()
+        g_dy = g_x = None
+        if ctx.needs_input_grad[1]:
+            g_dy = TensorLinearFn.apply(ctx.inds, G, x)
+        if ctx.needs_input_grad[2]:
+            g_x = TensorLinearFn.apply(ctx.inds, G.t(), dy)
+        return None, g_dy, g_x
 
 
 def tensor_linear(inds, W, x):

@@ -167,6 +167,14 @@ class Message(nn.Module):
 def graph_setup(r0, box, pos):
     """radius graph + wrapped displacements; box=None means open boundaries."""
     graph = Graph.radius_graph(r0, box, pos)
+    if torch.is_grad_enabled() and pos.requires_grad:
+        # the reference's form (archs/meanflow_painn8.py:167-172): differentiable in the positions,
+        # which the meanflow training step needs for its Jacobian-vector product
+        pos_src, pos_dst = edges_read(graph, pos)
+        delta = pos_dst - pos_src
+        if box is None:
+            return graph, delta
+        return graph, boxwrap(torch.as_tensor(box, dtype=pos.dtype, device=pos.device), delta)
     return graph, graph.rij
 
 
@@ -295,7 +303,7 @@ def set_precision(module, precision):
 
 
 class Meanflow:
-    """Inference side of the reference's Meanflow wrapper (generate/predict, :302-318)."""
+    """The reference's Meanflow wrapper: generate/predict (:302-318) and the training objective (:269-297)."""
 
     def __init__(self, dn, box, sigma_0, types, graph_bond):
         self.dn, self.box, self.sigma_0, self.types, self.graph_bond = dn, box, sigma_0, types, graph_bond
@@ -313,4 +321,27 @@ class Meanflow:
         v_pred = self.dn(st, x_0, z_1, self.box, self.types, self.graph_bond, counter)
         return (z_1 - v_pred).reshape(*lead, atoms, 3)
 
-    predict = generate
+    def predict(self, state, counter=None):
+        """state: a ModelState (the reference's calling convention, :316-318) or a position tensor"""
+        x = state if isinstance(state, torch.Tensor) else state.x
+        return self.generate(x, counter=counter)
+
+    def set_eval(self, bool_eval):
+        self.dn.train(not bool_eval)
+
+    def diffuser_loss(self, x_prev, z_0, z_1, s, t, loss_wt="ph"):
+        """The meanflow training objective of the reference's _diffuser_step
+        (archs/meanflow_painn8.py:269-297) with the random draws (z_1, s, t) passed in and the
+        optimiser left to the caller: v_target = v - (t - s) * d/dt dn along (v, 1), taken as a
+        Jacobian-vector product with create_graph=True, so the loss gradient is a double backward
+        through every kernel-backed autograd function of this library."""
+        tt = t[:, None, None]
+        z_t, v = tt * z_1 + (1 - tt) * z_0, z_1 - z_0
+        f = lambda z, tau: self.dn((s, tau), x_prev, z, self.box, self.types, self.graph_bond)  # noqa: E731
+        _, jvp = torch.autograd.functional.jvp(f, (z_t, t), (v, torch.ones_like(t)), create_graph=True)
+        v_target = v - (t - s)[:, None, None] * jvp
+        v_pred = f(z_t, t)
+        d_sq = ((v_pred - v_target) ** 2).mean((1, 2))
+        if loss_wt == "ph":
+            d_sq = d_sq / (0.5 + d_sq.detach()) ** 0.7
+        return d_sq.mean()

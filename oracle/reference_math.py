@@ -351,7 +351,13 @@ class OCPaiNN(nn.Module):
     def forward(self, pos, graph_bond, x_a, x_v, box, types):
         x_a = x_a + self.atom_embed(types)[None]
         g = radius_graph(pos, self.r0, box)
-        graph = (g["src"], g["dst"], g["rij"])
+        rij = g["rij"]
+        if torch.is_grad_enabled() and pos.requires_grad:  # graph_setup's differentiable form (:167-172)
+            flat = pos.reshape(-1, 3)
+            rij = flat[g["dst"].long()] - flat[g["src"].long()]
+            if box is not None:
+                rij = boxwrap(torch.as_tensor(box, dtype=pos.dtype), rij)
+        graph = (g["src"], g["dst"], rij)
         for blk in self.blocks:
             x_a, x_v = blk(graph, graph_bond, x_a, x_v)
         return x_a, x_v, g["E"]
@@ -427,6 +433,21 @@ def meanflow_generate(dn, x_0, noise, sigma_0, box, types, bond_src, bond_dst):
     with torch.no_grad():
         v_pred = dn(st, x_0, z_1, box, types, bond_src, bond_dst)
     return z_1 - v_pred
+
+
+def meanflow_loss(dn, x_prev, z_0, z_1, s, t, box, types, bond_src, bond_dst, loss_wt="ph"):
+    """archs/meanflow_painn8.py:269-297 (_get_pos_and_vel, _get_jvp, _diffuser_step) with the random
+    draws passed in and without the optimiser step"""
+    tt = t[:, None, None]
+    z_t, v = tt * z_1 + (1 - tt) * z_0, z_1 - z_0
+    f = lambda z, tau: dn((s, tau), x_prev, z, box, types, bond_src, bond_dst)  # noqa: E731
+    _, jvp = torch.autograd.functional.jvp(f, (z_t, t), (v, torch.ones_like(t)), create_graph=True)
+    v_target = v - (t - s)[:, None, None] * jvp
+    v_pred = f(z_t, t)
+    d_sq = ((v_pred - v_target) ** 2).mean((1, 2))
+    if loss_wt == "ph":
+        d_sq = d_sq / (0.5 + d_sq.detach()) ** 0.7
+    return d_sq.mean()
 
 
 def chain_bonds(batch, nodes):

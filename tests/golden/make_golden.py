@@ -113,6 +113,79 @@ def brute_graph(pos, r0, box):
     return torch.cat(srcs), torch.cat(dsts)
 
 
+def get_edges(listmax, neighboursmax, cutoff, bx, by, bz, x):
+    """stand-in for the extension's get_edges on CPU: same outputs, membership by float64 brute force"""
+    src, dst = brute_graph(x.detach(), cutoff, (bx, by, bz))
+    counts = torch.bincount(src // x.shape[1], minlength=x.shape[0])
+    return src.to(torch.int32), dst.to(torch.int32), torch.cumsum(counts, 0).to(torch.int32)
+
+
+sys.modules["neighbour_grid_cuda"].get_edges = get_edges
+NTYPES = 4
+
+
+class TypeEmbed(torch.nn.Module):
+    """plain type-embedding table in place of ResidueAtomEmbed (protein metadata is out of scope);
+    `metadata` is the int64 type index per atom"""
+
+    def __init__(self, dim):
+        super().__init__()
+        self.weight = torch.nn.Parameter(torch.randn(NTYPES, dim))
+
+    def forward(self, metadata):
+        return self.weight[metadata]
+
+
+def chain_bond_graph(batch, metadata, device):
+    """get_bond_graph for a linear chain: bonds (i, i+1) both ways, sorted by src, replicated over the batch"""
+    atoms = metadata.shape[0]
+    i = torch.arange(atoms - 1)
+    bs, bd = torch.cat([i, i + 1]), torch.cat([i + 1, i])
+    order = torch.argsort(bs, stable=True)
+    return gl.expand_graph(gl.Graph(bs[order], bd[order], None, 1, atoms), batch)
+
+
+class NoOptim:
+    def zero_grad(self):
+        pass
+
+    def step(self):
+        pass
+
+
+def meanflow_training_step(g):
+    """the reference's own Meanflow._diffuser_step (archs/meanflow_painn8.py:283-301) on its own
+    SE3ITO, with the optimiser replaced by a no-op so that the parameter gradients stay readable; the
+    random draws are replayed from the same seed and stored"""
+    painn.ResidueAtomEmbed, painn.get_bond_graph = TypeEmbed, chain_bond_graph
+    r0, n, B, N, L, box, sigma_0 = 2.5, 16, 2, 10, 2, (30., 30., 30.), 0.3
+    torch.manual_seed(23)
+    dn = painn.SE3ITO(r0, n, N, 1, 2)
+    with torch.no_grad():   # the reference initialises the table to zeros; make it count
+        for emb in (dn.cpainn_0.atom_embed, dn.cpainn_1.atom_embed):
+            emb.weight.copy_(torch.randn(NTYPES, n, generator=g))
+    types = torch.randint(0, NTYPES, (N,), generator=g)
+    x = 10. + torch.cumsum(torch.randn(L, B, N, 3, generator=g) / 3 ** 0.5, dim=2)
+    x[1] = x[0] + 0.2 * torch.randn(B, N, 3, generator=g)
+    me = types_ns(dn=dn, box=box, sigma_0=sigma_0, config={"loss_wt": "ph"}, optim=NoOptim())
+    for name in ("_get_pos_and_vel", "_get_jvp"):
+        setattr(me, name, getattr(painn.Meanflow, name).__get__(me))
+    torch.manual_seed(29)
+    loss = painn.Meanflow._diffuser_step(me, x, types)
+    grads = {k: p.grad.clone() for k, p in dn.named_parameters() if p.grad is not None}
+    torch.manual_seed(29)   # replay _diffuser_step's draws (:288-290)
+    x_prev = x[:-1].reshape((L - 1) * B, N, 3)
+    z_1 = x_prev + sigma_0 * torch.randn_like(x_prev)
+    t = torch.rand((L - 1) * B)
+    s = t * (1 - torch.relu(4 * torch.rand((L - 1) * B) - 3))
+    return {"r0": r0, "n": n, "box": box, "sigma_0": sigma_0, "types": types, "x": x, "z_1": z_1, "t": t, "s": s,
+            "blks": (1, 2), "state": dn.state_dict(), "loss": loss, "grads": grads}
+
+
+def types_ns(**kw):
+    return types.SimpleNamespace(**kw)
+
+
 def main():
     g = torch.Generator().manual_seed(20240)
     gold = {}
@@ -199,6 +272,17 @@ def main():
     with torch.no_grad():
         avd_out = avd(z_a, z_v, z_d)
     gold["avd_tensor_prods"] = {"dims": (8, 6, 4, 5), "inputs": (z_a, z_v, z_d), "state": avd.state_dict(), "out": avd_out}
+    # --- one meanflow training step: loss and parameter gradients (JVP + double backward) ------------
+    gold["meanflow_step"] = meanflow_training_step(g)
+    # --- trajectory file image written by the reference's own save_state_to_file --------------------
+    sf = importlib.import_module("managan.statefiles")
+    pred = importlib.import_module("managan.predictor")
+    import io
+    traj = torch.randn(3, 2, 5, 3, generator=g)
+    buf = io.BytesIO()
+    sf.save_state_to_file(buf, pred.ModelState((5, 3), traj, metadata={"seq": "AG", "note": 7}))
+    gold["statefile"] = {"x": traj, "shape": (5, 3), "metadata": {"seq": "AG", "note": 7},
+                         "image": np.frombuffer(buf.getvalue(), dtype=np.uint8).copy()}
     # --- the reference's own hand-computed graph test (managan/graph_layers.py:80-124) ------------
     gold["graph_kat"] = {
         "positions": torch.tensor([[[0., 0., -1.], [1., 0., 0.], [3., 0., 0.], [2., 1., 0.], [8., 0., 0.]]]),

@@ -214,3 +214,82 @@ def test_message_rotation_equivariance_full_width():
     assert graph.src.numel() == graph2.src.numel()
     close(a2, a1, rel=1e-4)
     close(v2, v1.cpu() @ rot.T, rel=1e-4)
+
+
+def test_meanflow_training_step_against_reference_golden(golden):
+    """One meanflow training step on the kernels: the Jacobian-vector product is taken with
+    create_graph=True, so the parameter gradients are a double backward through the kernel-backed
+    autograd functions (tensor_linear, gather, per-node sum). Compared with the loss and gradients
+    the reference's own _diffuser_step produced. FP32, 2e-4 of each gradient's largest entry."""
+    from ld_b200 import painn
+    m = golden["meanflow_step"]
+    L, B, N, _ = m["x"].shape
+    dn = painn.SE3ITO(m["r0"], m["n"], N, 4, *m["blks"])
+    dn.load_state_dict(m["state"])
+    dn.cuda()
+    x_prev, z_0 = m["x"][:-1].reshape(-1, N, 3).cuda(), m["x"][1:].reshape(-1, N, 3).cuda()
+    mf = painn.Meanflow(dn, m["box"], m["sigma_0"], m["types"].cuda(), painn.chain_bond_graph(x_prev.shape[0], N, "cuda"))
+    loss = mf.diffuser_loss(x_prev, z_0, m["z_1"].cuda(), m["s"].cuda(), m["t"].cuda())
+    assert abs(loss.item() - m["loss"]) <= 2e-5 * abs(m["loss"])
+    loss.backward()
+    grads = {k: p.grad for k, p in dn.named_parameters() if p.grad is not None}
+    assert set(grads) == set(m["grads"])
+    for k, ref in m["grads"].items():
+        scale = ref.abs().max().item()
+        assert (grads[k].cpu() - ref).abs().max().item() <= 2e-4 * scale + 1e-9, k
+
+
+@pytest.mark.parametrize("inds", [0, 1, 2])
+def test_tensor_linear_second_order(inds):
+    """gradient of a gradient through tensor_linear: d/dW and d/dx of |d y / d x|^2-style scalars
+    against the einsum form on the CPU"""
+    from ld_b200 import ops
+    torch.manual_seed(40 + inds)
+    W = torch.randn(12, 20, requires_grad=True)
+    x = torch.randn(7, 20, *([3] * inds), requires_grad=True)
+    c = torch.randn(7, 12, *([3] * inds))
+
+    def scalar(fn, W, x, c):
+        y = fn(inds, W, x)
+        gW, gx = torch.autograd.grad((y.tanh() * c).sum(), (W, x), create_graph=True)
+        return (gW ** 2).sum() + (gx ** 3).sum()
+
+    want = torch.autograd.grad(scalar(R.tensor_linear, W, x, c), (W, x))
+    Wg, xg = W.detach().cuda().requires_grad_(True), x.detach().cuda().requires_grad_(True)
+    got = torch.autograd.grad(scalar(ops.tensor_linear, Wg, xg, c.cuda()), (Wg, xg))
+    for a, b in zip(got, want):
+        close(a, b, rel=2e-5)
+
+
+def test_model_predictor_rollout_and_host_frames():
+    """ModelPredictor.predict (the reference's rollout loop): mutates the state, returns (L, batch, ...)
+    frames equal to the same steps taken by hand with the same random stream, and the frames streamed
+    to pinned host memory on the side stream are the same bits."""
+    from ld_b200 import painn, predictor as P
+    n, B, N, r0, L = 32, 3, 40, 2.5, 5
+    ref, mine = _denoiser_pair(r0, n, N, 4, (1, 1), seed=9)
+    g = torch.Generator().manual_seed(3)
+    x0 = torch.cumsum(torch.randn(B, N, 3, generator=g) / 3 ** 0.5, dim=1).cuda()
+    types = torch.randint(0, 4, (N,), generator=g).cuda()
+    mf = painn.Meanflow(mine, None, 0.3, types, painn.chain_bond_graph(B, N, "cuda"))
+    torch.manual_seed(77)
+    by_hand, x = [], x0.clone()
+    for _ in range(L):
+        x = mf.generate(x)
+        by_hand.append(x.clone())
+    by_hand = torch.stack(by_hand)
+    for host_frames in (False, True):
+        state = P.ModelState((N, 3), x0.clone(), metadata={"k": 1})
+        pred = P.ModelPredictor(mf, host_frames=host_frames)
+        torch.manual_seed(77)
+        traj = pred.predict(L, state)
+        assert traj.size == (L, B) and traj.shape == (N, 3) and traj.metadata == {"k": 1}
+        assert torch.equal(traj.x, by_hand)
+        assert torch.equal(state.x, by_hand[-1])
+        if host_frames:
+            assert pred.last_host_trajectory.is_pinned()
+            assert torch.equal(pred.last_host_trajectory, by_hand.cpu())
+    state = P.ModelState((N, 3), x0.clone())
+    torch.manual_seed(77)
+    assert P.ModelPredictor(mf).predict(L, state, ret=False) is None
+    assert torch.equal(state.x, by_hand[-1])

@@ -128,3 +128,22 @@ def test_avd_tensor_prods(golden):
         outs = mod(*a["inputs"])
     for mine, ref in zip(outs, a["out"]):
         assert torch.allclose(mine, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_meanflow_training_step(golden):
+    """loss and every parameter gradient of one meanflow training step (Jacobian-vector product with
+    create_graph, then backward) vs the reference's own Meanflow._diffuser_step on its own SE3ITO"""
+    m = golden["meanflow_step"]
+    L, B, N, _ = m["x"].shape
+    dn = R.OSE3ITO(m["r0"], m["n"], N, 4, *m["blks"])
+    dn.load_state_dict(m["state"])
+    x_prev, z_0 = m["x"][:-1].reshape(-1, N, 3), m["x"][1:].reshape(-1, N, 3)
+    bs, bd = R.chain_bonds(x_prev.shape[0], N)
+    loss = R.meanflow_loss(dn, x_prev, z_0, m["z_1"], m["s"], m["t"], m["box"], m["types"], bs, bd)
+    assert abs(loss.item() - m["loss"]) <= 1e-5 * abs(m["loss"])
+    loss.backward()
+    grads = {k: p.grad for k, p in dn.named_parameters() if p.grad is not None}
+    assert set(grads) == set(m["grads"])
+    for k, ref in m["grads"].items():
+        scale = ref.abs().max().item()
+        assert (grads[k] - ref).abs().max().item() <= 1e-4 * scale + 1e-9, k
