@@ -194,6 +194,22 @@ int ld_bee_messages_scalar_bf16_tc(const int* row_ptr, const int* dst, const flo
 int ld_group_norm(const float* x, int B, int N, int C, int S, int groups, int center, float eps, const float* gamma,
                   const float* beta, float* y, void* workspace, void* stream);
 
+/* ---- dense proximity attention ---------------------------------------------------------------------
+ * Replace the Triton operators proxattn (managan/triton_kernels/proxattn.py:239-311: _fwd_kernel :30-83,
+ * _bwd_kernel_kvy :86-164, _bwd_kernel_qx :167-236) and proxattn_periodic (proxattn_periodic.py, same layout plus
+ * the box), defined by refimpl_proxattn (proxattn.py:9-27, proxattn_periodic.py:9-28):
+ *   out[z,m,:] = sum_n r0sq[z % heads] / (r0sq[z % heads] + dist2(X[z,m], Y[z,n])) * (Q[z,m] . K[z,n]) * V[z,n,:]
+ * Q, K, V, out, d_out, dQ, dK, dV: [Z][N][dim] float32, dim in {16, 32, 64, 128}; X, Y, dX, dY: [Z][N][3];
+ * r0sq: [heads] on the device, Z a multiple of heads (r0sq receives no gradient, as in the reference).
+ * periodic = 0: dist2 = |x - y|^2; periodic = 1: sum_a (1 - cos(2 pi (x_a - y_a) / box_a)) box_a^2 / (2 pi^2).
+ * ld_proxattn_bwd writes all five gradients (two kernels: one per key tile, one per query tile). */
+int ld_proxattn_fwd(const float* Q, const float* K, const float* V, const float* X, const float* Y, const float* r0sq,
+                    int heads, int Z, int N, int dim, int periodic, float box_x, float box_y, float box_z, float* out,
+                    void* stream);
+int ld_proxattn_bwd(const float* Q, const float* K, const float* V, const float* X, const float* Y, const float* r0sq,
+                    int heads, int Z, int N, int dim, int periodic, float box_x, float box_y, float box_z,
+                    const float* d_out, float* dQ, float* dK, float* dV, float* dX, float* dY, void* stream);
+
 /* ---- dense-weight l<=2 products (Ant16) and the bare channel-wise product --------------------------
  * Replace codegen_tensops_cuda.ant16_{o0,o1,o2,oc}_cuda and their _backward / _backleft / _wtsback
  * companions (extensions/codegen_tensops/codegen_tensops.cpp:610-1517; einsum definitions

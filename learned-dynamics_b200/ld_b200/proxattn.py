@@ -1,0 +1,111 @@
+"""Host-side mirror of the reference's dense proximity-attention operators
+(managan/triton_kernels/proxattn.py:239-311 `proxattn`, managan/triton_kernels/proxattn_periodic.py
+`proxattn`): same argument order, shapes and restrictions (dim in {16, 32, 64, 128}, every tensor
+contiguous and on the GPU, Z a multiple of the number of heads), with gradients for Q, K, V, X and
+Y and none for r0sq (and none for the box).
+
+    proxattn(Q, K, V, X, Y, r0sq)               -> out (Z, N, dim)
+    proxattn_periodic(Q, K, V, X, Y, r0sq, box) -> out (Z, N, dim), box = (Lx, Ly, Lz)
+
+Both run the FP32 kernels ld_proxattn_fwd / ld_proxattn_bwd."""
+import torch
+
+from ._lib import lib, check, ptr, stream_ptr, require_cuda_f32, KERNEL_TIMER
+
+
+def _check(Q, K, V, X, Y, r0sq):
+    for name, t in (("Q", Q), ("K", K), ("V", V), ("X", X), ("Y", Y), ("r0sq", r0sq)):
+        require_cuda_f32(t, name)
+        if not t.is_contiguous():
+            raise RuntimeError(f"proxattn: {name} must be contiguous")
+    if Q.dim() != 3:
+        raise RuntimeError("proxattn: Q must be (Z, N, dim)")
+    Z, N, dim = Q.shape
+    if tuple(K.shape) != (Z, N, dim) or tuple(V.shape) != (Z, N, dim):
+        raise RuntimeError("proxattn: K and V must have Q's shape")
+    if tuple(X.shape) != (Z, N, 3) or tuple(Y.shape) != (Z, N, 3):
+        raise RuntimeError("proxattn: X and Y must be (Z, N, 3)")
+    if dim not in (16, 32, 64, 128):
+        raise RuntimeError("proxattn: dim must be one of 16, 32, 64, 128")
+    if r0sq.dim() != 1 or Z % r0sq.shape[0] != 0:
+        raise RuntimeError("proxattn: Z must be a multiple of the number of heads")
+    return Z, N, dim, r0sq.shape[0]
+
+
+def _box_args(box):
+    if box is None:
+        return 0, 0.0, 0.0, 0.0
+    bx, by, bz = (float(b) for b in box)
+    return 1, bx, by, bz
+
+
+class _ProxAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, Q, K, V, X, Y, r0sq, box):
+        Z, N, dim, heads = _check(Q, K, V, X, Y, r0sq)
+        out = torch.empty_like(Q)
+        with KERNEL_TIMER.region("proxattn_fwd"):
+            check(lib().ld_proxattn_fwd(ptr(Q), ptr(K), ptr(V), ptr(X), ptr(Y), ptr(r0sq), heads, Z, N, dim, *_box_args(box),
+                                        ptr(out), stream_ptr(Q.device)))
+        ctx.save_for_backward(Q, K, V, X, Y, r0sq)
+        ctx.box = box
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, d_out):
+        Q, K, V, X, Y, r0sq = ctx.saved_tensors
+        Z, N, dim = Q.shape
+        d_out = d_out.contiguous()
+        dQ, dK, dV = torch.empty_like(Q), torch.empty_like(K), torch.empty_like(V)
+        dX, dY = torch.empty_like(X), torch.empty_like(Y)
+        with KERNEL_TIMER.region("proxattn_bwd"):
+            check(lib().ld_proxattn_bwd(ptr(Q), ptr(K), ptr(V), ptr(X), ptr(Y), ptr(r0sq), r0sq.shape[0], Z, N, dim,
+                                        *_box_args(ctx.box), ptr(d_out), ptr(dQ), ptr(dK), ptr(dV), ptr(dX), ptr(dY),
+                                        stream_ptr(Q.device)))
+        return dQ, dK, dV, dX, dY, None, None
+
+
+def proxattn(Q, K, V, X, Y, r0sq):
+    return _ProxAttn.apply(Q, K, V, X, Y, r0sq, None)
+
+
+def proxattn_periodic(Q, K, V, X, Y, r0sq, box):
+    if isinstance(box, torch.Tensor):
+        box = tuple(box.tolist())
+    return _ProxAttn.apply(Q, K, V, X, Y, r0sq, tuple(box))
+
+
+def _time_case(Z=32, N=4096, dim=64, heads=4, periodic=False, reps=5):
+    """python -m ld_b200.proxattn [Z N dim]: device time of the forward and of the backward pass"""
+    g = torch.Generator().manual_seed(0)
+    q, k, v, d_out = (torch.randn(Z, N, dim, generator=g).cuda() for _ in range(4))
+    x, y = (4 * torch.rand(Z, N, 3, generator=g)).cuda(), (4 * torch.rand(Z, N, 3, generator=g)).cuda()
+    r0sq = (0.2 + torch.rand(heads, generator=g)).cuda()
+    box = (4.0, 4.0, 4.0) if periodic else None
+    ins = [t.requires_grad_(True) for t in (q, k, v, x, y)]
+    times = []
+    for backward in (False, True):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        out = _ProxAttn.apply(*ins, r0sq, box)
+        for i in range(reps + 2):
+            if i == 2:
+                e0.record()
+            if backward:
+                torch.autograd.grad(out, ins, d_out, retain_graph=True)
+            else:
+                out = _ProxAttn.apply(*ins, r0sq, box)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / reps)
+    pair_flops = 2.0 * Z * N * N * dim
+    print(f"proximity attention Z={Z} N={N} dim={dim} periodic={periodic}: forward {times[0]:.3f} ms "
+          f"({2 * pair_flops / times[0] * 1e-9:.1f} TFLOP/s FP32), backward {times[1]:.3f} ms "
+          f"({7 * pair_flops / times[1] * 1e-9:.1f} TFLOP/s FP32)")
+
+
+if __name__ == "__main__":
+    import sys
+    a = [int(v) for v in sys.argv[1:4]]
+    _time_case(*a)
+    _time_case(*a, periodic=True)

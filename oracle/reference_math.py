@@ -450,6 +450,23 @@ def meanflow_loss(dn, x_prev, z_0, z_1, s, t, box, types, bond_src, bond_dst, lo
     return d_sq.mean()
 
 
+def proxattn(Q, K, V, X, Y, r0sq, box=None):
+    """refimpl_proxattn of managan/triton_kernels/proxattn.py:9-27 (box=None) and of
+    managan/triton_kernels/proxattn_periodic.py:9-28 (box = 3 lengths)"""
+    Z = Q.shape[0]
+    heads = r0sq.shape[0]
+    assert Z % heads == 0
+    r0 = r0sq[None].expand(Z // heads, -1).reshape(Z)[:, None, None]
+    QK = torch.einsum("zmd, znd -> zmn", Q, K)
+    R = X[:, :, None] - Y[:, None, :]
+    if box is None:
+        dist2 = (R ** 2).sum(-1)
+    else:
+        box = torch.as_tensor(box, dtype=Q.dtype)
+        dist2 = ((1. - torch.cos(2 * torch.pi * R / box)) * box ** 2 / (2 * torch.pi * torch.pi)).sum(-1)
+    return torch.einsum("zmn, znd -> zmd", r0 * QK / (r0 + dist2), V)
+
+
 def chain_bonds(batch, nodes):
     i = torch.arange(nodes - 1)
     src = torch.cat([i, i + 1]); dst = torch.cat([i + 1, i])

@@ -274,6 +274,22 @@ def main():
     gold["avd_tensor_prods"] = {"dims": (8, 6, 4, 5), "inputs": (z_a, z_v, z_d), "state": avd.state_dict(), "out": avd_out}
     # --- one meanflow training step: loss and parameter gradients (JVP + double backward) ------------
     gold["meanflow_step"] = meanflow_training_step(g)
+    # --- dense proximity attention: the reference's own torch definitions with autograd gradients --------
+    pa = importlib.import_module("managan.triton_kernels.proxattn")
+    pap = importlib.import_module("managan.triton_kernels.proxattn_periodic")
+    Zp, Np, dp = 6, 37, 16
+    pa_in = [torch.randn(Zp, Np, dp, generator=g, requires_grad=True) for _ in range(3)] + \
+            [(2 * torch.rand(Zp, Np, 3, generator=g)).requires_grad_(True) for _ in range(2)]
+    pa_r0sq = torch.tensor([0.2, 0.5, 1.3])
+    pa_box = (1.7, 2.1, 2.6)
+    pa_cot = torch.randn(Zp, Np, dp, generator=g)
+    pa_out = pa.refimpl_proxattn(*pa_in, pa_r0sq)
+    pa_grads = torch.autograd.grad((pa_out * pa_cot).sum(), pa_in)
+    pap_out = pap.refimpl_proxattn(*pa_in, pa_r0sq, torch.tensor(pa_box))
+    pap_grads = torch.autograd.grad((pap_out * pa_cot).sum(), pa_in)
+    gold["proxattn"] = {"inputs": [t.detach() for t in pa_in], "r0sq": pa_r0sq, "box": pa_box, "cotangent": pa_cot,
+                        "out": pa_out.detach(), "grads": list(pa_grads), "out_periodic": pap_out.detach(),
+                        "grads_periodic": list(pap_grads)}
     # --- trajectory file image written by the reference's own save_state_to_file --------------------
     sf = importlib.import_module("managan.statefiles")
     pred = importlib.import_module("managan.predictor")

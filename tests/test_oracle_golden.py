@@ -147,3 +147,15 @@ def test_meanflow_training_step(golden):
     for k, ref in m["grads"].items():
         scale = ref.abs().max().item()
         assert (grads[k] - ref).abs().max().item() <= 1e-4 * scale + 1e-9, k
+
+
+def test_proximity_attention(golden):
+    """open-space and periodic proximity attention with all five gradients vs the reference's refimpl"""
+    p = golden["proxattn"]
+    for box, ko, kg in ((None, "out", "grads"), (p["box"], "out_periodic", "grads_periodic")):
+        ins = [t.clone().requires_grad_(True) for t in p["inputs"]]
+        out = R.proxattn(*ins, p["r0sq"], box)
+        assert torch.allclose(out, p[ko], rtol=1e-5, atol=1e-5)
+        grads = torch.autograd.grad((out * p["cotangent"]).sum(), ins)
+        for mine, ref in zip(grads, p[kg]):
+            assert torch.allclose(mine, ref, rtol=1e-4, atol=1e-4)
