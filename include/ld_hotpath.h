@@ -206,6 +206,11 @@ int ld_group_norm(const float* x, int B, int N, int C, int S, int groups, int ce
 int ld_proxattn_fwd(const float* Q, const float* K, const float* V, const float* X, const float* Y, const float* r0sq,
                     int heads, int Z, int N, int dim, int periodic, float box_x, float box_y, float box_z, float* out,
                     void* stream);
+/* The same forward on the tensor cores in TF32 (tcgen05.mma kind::tf32, accumulators in TMEM) - the precision of the
+ * Triton kernel's tl.dot on FP32 inputs. status_dev: optional device word, LD_FLAG_TIMEOUT if a bounded wait ran out. */
+int ld_proxattn_fwd_tf32_tc(const float* Q, const float* K, const float* V, const float* X, const float* Y, const float* r0sq,
+                            int heads, int Z, int N, int dim, int periodic, float box_x, float box_y, float box_z, float* out,
+                            int* status_dev, void* stream);
 int ld_proxattn_bwd(const float* Q, const float* K, const float* V, const float* X, const float* Y, const float* r0sq,
                     int heads, int Z, int N, int dim, int periodic, float box_x, float box_y, float box_z,
                     const float* d_out, float* dQ, float* dK, float* dV, float* dX, float* dY, void* stream);

@@ -43,6 +43,7 @@ SIGNATURES = {
     "ld_debug_set_phase_counters": [P],
     "ld_group_norm": [P, I, I, I, I, I, I, F, P, P, P, P, P],
     "ld_proxattn_fwd": [P, P, P, P, P, P, I, I, I, I, I, F, F, F, P, P],
+    "ld_proxattn_fwd_tf32_tc": [P, P, P, P, P, P, I, I, I, I, I, F, F, F, P, P, P],
     "ld_proxattn_bwd": [P, P, P, P, P, P, I, I, I, I, I, F, F, F, P, P, P, P, P, P, P],
     "ld_ant16_contract_left": [I, P, P, LL, I, I, P, I, P],
     "ld_ant16_expand": [I, P, P, LL, I, I, P, P],

@@ -7,10 +7,13 @@ Y and none for r0sq (and none for the box).
     proxattn(Q, K, V, X, Y, r0sq)               -> out (Z, N, dim)
     proxattn_periodic(Q, K, V, X, Y, r0sq, box) -> out (Z, N, dim), box = (Lx, Ly, Lz)
 
-Both run the FP32 kernels ld_proxattn_fwd / ld_proxattn_bwd."""
+precision="fp32" (default): the FP32 kernels ld_proxattn_fwd / ld_proxattn_bwd, 2e-5 against the einsum
+definition. precision="tf32": the forward runs on the tensor cores (ld_proxattn_fwd_tf32_tc, the precision of
+the reference's Triton kernel, about 1e-3); the backward stays FP32."""
 import torch
 
 from ._lib import lib, check, ptr, stream_ptr, require_cuda_f32, KERNEL_TIMER
+from .ops import tc_status
 
 
 def _check(Q, K, V, X, Y, r0sq):
@@ -41,12 +44,18 @@ def _box_args(box):
 
 class _ProxAttn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, Q, K, V, X, Y, r0sq, box):
+    def forward(ctx, Q, K, V, X, Y, r0sq, box, precision):
         Z, N, dim, heads = _check(Q, K, V, X, Y, r0sq)
+        if precision not in ("fp32", "tf32"):
+            raise RuntimeError("proxattn: precision must be 'fp32' or 'tf32'")
         out = torch.empty_like(Q)
         with KERNEL_TIMER.region("proxattn_fwd"):
-            check(lib().ld_proxattn_fwd(ptr(Q), ptr(K), ptr(V), ptr(X), ptr(Y), ptr(r0sq), heads, Z, N, dim, *_box_args(box),
-                                        ptr(out), stream_ptr(Q.device)))
+            if precision == "tf32":
+                check(lib().ld_proxattn_fwd_tf32_tc(ptr(Q), ptr(K), ptr(V), ptr(X), ptr(Y), ptr(r0sq), heads, Z, N, dim,
+                                                    *_box_args(box), ptr(out), ptr(tc_status(Q.device)), stream_ptr(Q.device)))
+            else:
+                check(lib().ld_proxattn_fwd(ptr(Q), ptr(K), ptr(V), ptr(X), ptr(Y), ptr(r0sq), heads, Z, N, dim,
+                                            *_box_args(box), ptr(out), stream_ptr(Q.device)))
         ctx.save_for_backward(Q, K, V, X, Y, r0sq)
         ctx.box = box
         return out
@@ -63,20 +72,20 @@ class _ProxAttn(torch.autograd.Function):
             check(lib().ld_proxattn_bwd(ptr(Q), ptr(K), ptr(V), ptr(X), ptr(Y), ptr(r0sq), r0sq.shape[0], Z, N, dim,
                                         *_box_args(ctx.box), ptr(d_out), ptr(dQ), ptr(dK), ptr(dV), ptr(dX), ptr(dY),
                                         stream_ptr(Q.device)))
-        return dQ, dK, dV, dX, dY, None, None
+        return dQ, dK, dV, dX, dY, None, None, None
 
 
-def proxattn(Q, K, V, X, Y, r0sq):
-    return _ProxAttn.apply(Q, K, V, X, Y, r0sq, None)
+def proxattn(Q, K, V, X, Y, r0sq, precision="fp32"):
+    return _ProxAttn.apply(Q, K, V, X, Y, r0sq, None, precision)
 
 
-def proxattn_periodic(Q, K, V, X, Y, r0sq, box):
+def proxattn_periodic(Q, K, V, X, Y, r0sq, box, precision="fp32"):
     if isinstance(box, torch.Tensor):
         box = tuple(box.tolist())
-    return _ProxAttn.apply(Q, K, V, X, Y, r0sq, tuple(box))
+    return _ProxAttn.apply(Q, K, V, X, Y, r0sq, tuple(box), precision)
 
 
-def _time_case(Z=32, N=4096, dim=64, heads=4, periodic=False, reps=5):
+def _time_case(Z=32, N=4096, dim=64, heads=4, periodic=False, reps=5, precision="fp32"):
     """python -m ld_b200.proxattn [Z N dim]: device time of the forward and of the backward pass"""
     g = torch.Generator().manual_seed(0)
     q, k, v, d_out = (torch.randn(Z, N, dim, generator=g).cuda() for _ in range(4))
@@ -87,20 +96,20 @@ def _time_case(Z=32, N=4096, dim=64, heads=4, periodic=False, reps=5):
     times = []
     for backward in (False, True):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        out = _ProxAttn.apply(*ins, r0sq, box)
+        out = _ProxAttn.apply(*ins, r0sq, box, precision)
         for i in range(reps + 2):
             if i == 2:
                 e0.record()
             if backward:
                 torch.autograd.grad(out, ins, d_out, retain_graph=True)
             else:
-                out = _ProxAttn.apply(*ins, r0sq, box)
+                out = _ProxAttn.apply(*ins, r0sq, box, precision)
         e1.record()
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1) / reps)
     pair_flops = 2.0 * Z * N * N * dim
-    print(f"proximity attention Z={Z} N={N} dim={dim} periodic={periodic}: forward {times[0]:.3f} ms "
-          f"({2 * pair_flops / times[0] * 1e-9:.1f} TFLOP/s FP32), backward {times[1]:.3f} ms "
+    print(f"proximity attention Z={Z} N={N} dim={dim} periodic={periodic} forward in {precision}: forward {times[0]:.3f} ms "
+          f"({2 * pair_flops / times[0] * 1e-9:.1f} TFLOP/s), backward {times[1]:.3f} ms "
           f"({7 * pair_flops / times[1] * 1e-9:.1f} TFLOP/s FP32)")
 
 
@@ -109,3 +118,5 @@ if __name__ == "__main__":
     a = [int(v) for v in sys.argv[1:4]]
     _time_case(*a)
     _time_case(*a, periodic=True)
+    _time_case(*a, precision="tf32")
+    _time_case(*a, periodic=True, precision="tf32")

@@ -79,3 +79,30 @@ def test_deterministic_and_linear_in_v():
     assert torch.equal(a, PA.proxattn(q, k, v1, x, y, r0sq))
     b = PA.proxattn(q, k, v2, x, y, r0sq)
     close(PA.proxattn(q, k, v1 + v2, x, y, r0sq), a + b, rel=1e-5)
+
+
+@pytest.mark.parametrize("dim", [16, 32, 64, 128])
+@pytest.mark.parametrize("Z,N,heads", [(5, 1, 5), (4, 128, 2), (3, 130, 1), (6, 517, 3)])
+@pytest.mark.parametrize("periodic", [False, True])
+def test_tf32_tensor_core_forward(dim, Z, N, heads, periodic):
+    """forward on the tensor cores in TF32 (10-bit mantissas on both products): 3e-3 of the largest output,
+    the accuracy class of the reference's Triton kernel; the backward of that call is the FP32 one"""
+    from ld_b200 import ops, proxattn as PA
+    g = torch.Generator().manual_seed(77 * dim + N + int(periodic))
+    ins = [torch.randn(Z, N, dim, generator=g) for _ in range(3)] + [2 * torch.rand(Z, N, 3, generator=g) for _ in range(2)]
+    r0sq = 0.2 + torch.rand(heads, generator=g)
+    box = (2.2, 1.9, 2.7) if periodic else None
+    want = R.proxattn(*ins, r0sq, box)
+    g_in = [t.cuda().requires_grad_(True) for t in ins]
+    if periodic:
+        got = PA.proxattn_periodic(*g_in, r0sq.cuda(), box, precision="tf32")
+    else:
+        got = PA.proxattn(*g_in, r0sq.cuda(), precision="tf32")
+    close(got, want, rel=3e-3)
+    assert int(ops.tc_status(got.device).item()) == 0
+    cot = torch.randn(Z, N, dim, generator=g)
+    grads = torch.autograd.grad((got * cot.cuda()).sum(), g_in)
+    ref_in = [t.clone().requires_grad_(True) for t in ins]
+    ref_grads = torch.autograd.grad((R.proxattn(*ref_in, r0sq, box) * cot).sum(), ref_in)
+    for mine, ref in zip(grads, ref_grads):
+        close(mine, ref, rel=5e-5)
