@@ -3,14 +3,16 @@
 // Same operator as ld_proxattn_fwd (FP32 FMA); this is the precision the reference's Triton kernel computes
 // in (its tl.dot calls on FP32 inputs run as TF32; managan/triton_kernels/proxattn.py:30-83).
 //
-// A block owns 128 queries (one TMEM lane each) and walks the keys in steps of TN (128, or 64 at dim 128):
+// A block owns 128 queries (one TMEM lane each) and walks the keys in steps of TN = 64; up to dim 64 two blocks
+// share an SM (shared memory about 100 KB, 128 TMEM columns each), so that one block's staging and weights
+// overlap the other's MMAs:
 //   1. K, V and the key positions of the step are staged in shared memory as K-major, no-swizzle operand
 //      panels of 32-bit elements: element (row, k) at (k / 4) * LBO + row * 16 + (k % 4) * 4 bytes. For V the
 //      "row" is the feature and k the key, so the staging transposes 4 keys per 16-byte store.
 //   2. one thread issues S = Q K^T (dim / 8 MMAs of 128 x TN x 8) into TMEM columns [0, TN)
 //   3. all 256 threads (thread = query row x column half) read their part of S, multiply by the pair
 //      weights and store P = w o S as the A-operand panel of the second product
-//   4. one thread issues O += P V (TN / 8 MMAs of 128 x dim x 8) into TMEM columns [128, 128 + dim)
+//   4. one thread issues O += P V (TN / 8 MMAs of 128 x dim x 8) into TMEM columns [TN, TN + dim)
 // Rows past N are zero-filled, so they contribute nothing; only the final store is masked. Every wait on an
 // mbarrier is bounded; on a timeout the block sets LD_FLAG_TIMEOUT in the status word, frees its TMEM and returns.
 #include <cuda_runtime.h>
@@ -45,9 +47,18 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint6
       : "memory");
 }
 
+// round to nearest TF32 (the MMA itself would drop the low mantissa bits)
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
 template <int D>
 struct Ptc {
-  static constexpr int TN = (D == 128) ? 64 : 128;          // keys per step
+  static constexpr int TN = 64;                               // keys per step
+  static constexpr int TMEM_COLS = (D <= 64) ? 128 : 256;     // S in columns [0, 64), O in [64, 64 + D)
+  static constexpr int MIN_BLOCKS = (D <= 64) ? 2 : 1;        // two blocks per SM overlap each other's phases
   static constexpr int LBO_Q = QT * 16 + PANEL_PAD;         // bytes between K-groups of the Q panel (rows = queries)
   static constexpr int LBO_K = TN * 16 + PANEL_PAD;         // K panel (rows = keys)
   static constexpr int LBO_V = D * 16 + PANEL_PAD;          // V panel (rows = features, K-groups = 4 keys)
@@ -68,7 +79,7 @@ __device__ __forceinline__ void ptc_stage_rows(uint8_t* __restrict__ panel, int 
     const int r = idx / G, k4 = idx % G;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (row0 + r < N) v = __ldg(reinterpret_cast<const float4*>(g + (size_t)(row0 + r) * D) + k4);
-    *reinterpret_cast<float4*>(panel + (size_t)k4 * lbo + r * 16) = v;
+    *reinterpret_cast<float4*>(panel + (size_t)k4 * lbo + r * 16) = make_float4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
   }
 }
 
@@ -81,7 +92,7 @@ __device__ __forceinline__ void ptc_stage_v(uint8_t* __restrict__ panel, int lbo
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const int n = row0 + 4 * n4 + j;
-      e[j] = (n < N) ? __ldg(g + (size_t)n * D + d) : 0.f;
+      e[j] = (n < N) ? to_tf32(__ldg(g + (size_t)n * D + d)) : 0.f;
     }
     *reinterpret_cast<float4*>(panel + (size_t)n4 * lbo + d * 16) = make_float4(e[0], e[1], e[2], e[3]);
   }
@@ -121,7 +132,7 @@ __device__ __forceinline__ float ptc_weight(const float* x, const float* y, floa
 }
 
 template <int D, bool PER>
-__global__ void __launch_bounds__(PTC_THREADS, 1) proxattn_fwd_tc_kernel(PtcArgs p) {
+__global__ void __launch_bounds__(PTC_THREADS, Ptc<D>::MIN_BLOCKS) proxattn_fwd_tc_kernel(PtcArgs p) {
   using C = Ptc<D>;
   constexpr int TN = C::TN, TNH = TN / 2, PS = PER ? 6 : 3;
   extern __shared__ __align__(128) uint8_t smem[];
@@ -146,12 +157,12 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) proxattn_fwd_tc_kernel(PtcArgs
     tc::mbar_init(bar_o, 1);
     tc::mbar_init_fence();
   }
-  if (warp == 0) { tc::tmem_alloc(tmem_slot, 256); tc::tmem_relinquish(); }
+  if (warp == 0) { tc::tmem_alloc(tmem_slot, C::TMEM_COLS); tc::tmem_relinquish(); }
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + TN;
   const uint32_t lane_bits = (uint32_t)(32 * (warp & 3)) << 16;
 
   ptc_stage_rows<D, QT>(sQ, C::LBO_Q, p.Q + zf, m0, N);
@@ -197,10 +208,10 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) proxattn_fwd_tc_kernel(PtcArgs
       for (int c = 0; c < 32; c += 4) {
         const int n = half * TNH + c0 + c;
         float4 o;
-        o.x = s[c + 0] * ptc_weight<PER>(xq, sY + (n + 0) * PS, r0sq, kc);
-        o.y = s[c + 1] * ptc_weight<PER>(xq, sY + (n + 1) * PS, r0sq, kc);
-        o.z = s[c + 2] * ptc_weight<PER>(xq, sY + (n + 2) * PS, r0sq, kc);
-        o.w = s[c + 3] * ptc_weight<PER>(xq, sY + (n + 3) * PS, r0sq, kc);
+        o.x = to_tf32(s[c + 0] * ptc_weight<PER>(xq, sY + (n + 0) * PS, r0sq, kc));
+        o.y = to_tf32(s[c + 1] * ptc_weight<PER>(xq, sY + (n + 1) * PS, r0sq, kc));
+        o.z = to_tf32(s[c + 2] * ptc_weight<PER>(xq, sY + (n + 2) * PS, r0sq, kc));
+        o.w = to_tf32(s[c + 3] * ptc_weight<PER>(xq, sY + (n + 3) * PS, r0sq, kc));
         *reinterpret_cast<float4*>(sP + (size_t)(n >> 2) * C::LBO_P + row * 16) = o;
       }
     }
@@ -240,7 +251,7 @@ __global__ void __launch_bounds__(PTC_THREADS, 1) proxattn_fwd_tc_kernel(PtcArgs
   }
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc::tmem_dealloc(tmem_base, 256);
+  if (warp == 0) tc::tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
 template <int D, bool PER>
