@@ -6,7 +6,8 @@
 // A block owns 128 queries (one TMEM lane each) and walks the keys in steps of TN = 64; up to dim 64 two blocks
 // share an SM (shared memory about 100 KB, 128 TMEM columns each), so that one block's staging and weights
 // overlap the other's MMAs:
-//   1. K, V and the key positions of the step are staged in shared memory as K-major, no-swizzle operand
+//   1. K, V and the key positions of the step are staged in shared memory (K by asynchronous copies issued during
+//      the weights of the step before, V while the score product runs) as K-major, no-swizzle operand
 //      panels of 32-bit elements: element (row, k) at (k / 4) * LBO + row * 16 + (k % 4) * 4 bytes. For V the
 //      "row" is the feature and k the key, so the staging transposes 4 keys per 16-byte store.
 //   2. one thread issues S = Q K^T (dim / 8 MMAs of 128 x TN x 8) into TMEM columns [0, TN)
@@ -81,6 +82,22 @@ __device__ __forceinline__ void ptc_stage_rows(uint8_t* __restrict__ panel, int 
     if (row0 + r < N) v = __ldg(reinterpret_cast<const float4*>(g + (size_t)(row0 + r) * D) + k4);
     *reinterpret_cast<float4*>(panel + (size_t)k4 * lbo + r * 16) = make_float4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
   }
+}
+
+// the same panel filled by 16-byte asynchronous copies (rows past N are zero-filled by a zero source size); the
+// MMA then drops the low mantissa bits of these operands instead of rounding them
+template <int D, int ROWS>
+__device__ __forceinline__ void ptc_stage_rows_async(uint32_t panel_addr, int lbo, const float* __restrict__ g, int row0, int N) {
+  constexpr int G = D / 4;
+  for (int idx = threadIdx.x; idx < ROWS * G; idx += PTC_THREADS) {
+    const int r = idx / G, k4 = idx % G;
+    const bool in = row0 + r < N;
+    const float* src = g + (size_t)(in ? row0 + r : 0) * D + 4 * k4;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(panel_addr + (uint32_t)(k4 * lbo + r * 16)), "l"(src),
+                 "r"(in ? 16 : 0)
+                 : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
 // rows [row0, row0 + TN) of V [N][D] -> panel whose rows are features and whose K-groups are 4 consecutive keys
@@ -166,25 +183,18 @@ __global__ void __launch_bounds__(PTC_THREADS, Ptc<D>::MIN_BLOCKS) proxattn_fwd_
   const uint32_t lane_bits = (uint32_t)(32 * (warp & 3)) << 16;
 
   ptc_stage_rows<D, QT>(sQ, C::LBO_Q, p.Q + zf, m0, N);
+  ptc_stage_rows<D, TN>(sK, C::LBO_K, p.K + zf, 0, N);
   float xq[PS];
   ptc_point<PER>(p.X + zp, m0 + row, N, p, xq);
+  tc::fence_async_smem();
+  __syncthreads();
 
   const uint32_t q_addr = tc::smem_u32(sQ), k_addr = tc::smem_u32(sK), v_addr = tc::smem_u32(sV), p_addr = tc::smem_u32(sP);
   const int ntiles = (N + TN - 1) / TN;
   bool ok = true;
   for (int t = 0; t < ntiles && ok; t++) {
     const int n0 = t * TN;
-    if (t > 0) {   // the second product of the previous step still reads sP and sV
-      const bool w = tc::mbar_wait(bar_o, (t - 1) & 1);
-      ok = __syncthreads_and(w);
-      if (!ok) break;
-    }
-    ptc_stage_rows<D, TN>(sK, C::LBO_K, p.K + zf, n0, N);
-    ptc_stage_v<D, TN>(sV, C::LBO_V, p.V + zf, n0, N);
-    if (tid < TN) ptc_point<PER>(p.Y + zp, n0 + tid, N, p, sY + tid * PS);
-    tc::fence_async_smem();
-    __syncthreads();
-    if (tid == 0) {
+    if (tid == 0) {   // K of this step is in shared memory (prologue, or the asynchronous copies of the previous step)
       tc::fence_after_sync();
 #pragma unroll
       for (int ks = 0; ks < D / 8; ks++) {
@@ -194,11 +204,19 @@ __global__ void __launch_bounds__(PTC_THREADS, Ptc<D>::MIN_BLOCKS) proxattn_fwd_
       }
       tc::mma_commit(bar_s);
     }
-    {
-      const bool w = tc::mbar_wait(bar_s, t & 1);
+    if (t > 0) {   // the second product of the previous step still reads sP and sV
+      const bool w = tc::mbar_wait(bar_o, (t - 1) & 1);
       ok = __syncthreads_and(w);
       if (!ok) break;
     }
+    ptc_stage_v<D, TN>(sV, C::LBO_V, p.V + zf, n0, N);   // while the score product runs
+    if (tid < TN) ptc_point<PER>(p.Y + zp, n0 + tid, N, p, sY + tid * PS);
+    {
+      const bool w = tc::mbar_wait(bar_s, t & 1);
+      ok = __syncthreads_and(w);   // also orders the position stores before the weights below
+      if (!ok) break;
+    }
+    if (t + 1 < ntiles) ptc_stage_rows_async<D, TN>(k_addr, C::LBO_K, p.K + zf, n0 + TN, N);   // sK is free: lands during the weights
     tc::fence_after_sync();
 #pragma unroll
     for (int c0 = 0; c0 < TNH; c0 += 32) {
@@ -215,6 +233,7 @@ __global__ void __launch_bounds__(PTC_THREADS, Ptc<D>::MIN_BLOCKS) proxattn_fwd_
         *reinterpret_cast<float4*>(sP + (size_t)(n >> 2) * C::LBO_P + row * 16) = o;
       }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
