@@ -6,8 +6,8 @@
 // A block owns 128 queries (one TMEM lane each) and walks the keys in steps of TN = 64; up to dim 64 two blocks
 // share an SM (shared memory about 100 KB, 128 TMEM columns each), so that one block's staging and weights
 // overlap the other's MMAs:
-//   1. K, V and the key positions of the step are staged in shared memory (K by asynchronous copies issued during
-//      the weights of the step before, V while the score product runs) as K-major, no-swizzle operand
+//   1. K, V and the key positions of the step are staged in shared memory (K by asynchronous copies and V through registers, both
+//      issued during the weights of the step before) as K-major, no-swizzle operand
 //      panels of 32-bit elements: element (row, k) at (k / 4) * LBO + row * 16 + (k % 4) * 4 bytes. For V the
 //      "row" is the feature and k the key, so the staging transposes 4 keys per 16-byte store.
 //   2. one thread issues S = Q K^T (dim / 8 MMAs of 128 x TN x 8) into TMEM columns [0, TN)
@@ -100,18 +100,28 @@ __device__ __forceinline__ void ptc_stage_rows_async(uint32_t panel_addr, int lb
   asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
-// rows [row0, row0 + TN) of V [N][D] -> panel whose rows are features and whose K-groups are 4 consecutive keys
+// rows [row0, row0 + TN) of V [N][D] -> panel whose rows are features and whose K-groups are 4 consecutive keys.
+// In two halves, so that the loads of the next step can be in flight while this step's weights are computed:
+// ptc_load_v reads 4 keys x one feature per thread and iteration into registers, ptc_store_v rounds and stores them.
 template <int D, int TN>
-__device__ __forceinline__ void ptc_stage_v(uint8_t* __restrict__ panel, int lbo, const float* __restrict__ g, int row0, int N) {
-  for (int idx = threadIdx.x; idx < (TN / 4) * D; idx += PTC_THREADS) {
-    const int d = idx % D, n4 = idx / D;
-    float e[4];
+__device__ __forceinline__ void ptc_load_v(float (&e)[D / 16][4], const float* __restrict__ g, int row0, int N) {
+#pragma unroll
+  for (int it = 0; it < D / 16; it++) {
+    const int idx = threadIdx.x + it * PTC_THREADS, d = idx % D, n4 = idx / D;
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const int n = row0 + 4 * n4 + j;
-      e[j] = (n < N) ? to_tf32(__ldg(g + (size_t)n * D + d)) : 0.f;
+      e[it][j] = (n < N) ? __ldg(g + (size_t)n * D + d) : 0.f;
     }
-    *reinterpret_cast<float4*>(panel + (size_t)n4 * lbo + d * 16) = make_float4(e[0], e[1], e[2], e[3]);
+  }
+}
+template <int D, int TN>
+__device__ __forceinline__ void ptc_store_v(uint8_t* __restrict__ panel, int lbo, const float (&e)[D / 16][4]) {
+#pragma unroll
+  for (int it = 0; it < D / 16; it++) {
+    const int idx = threadIdx.x + it * PTC_THREADS, d = idx % D, n4 = idx / D;
+    *reinterpret_cast<float4*>(panel + (size_t)n4 * lbo + d * 16) =
+        make_float4(to_tf32(e[it][0]), to_tf32(e[it][1]), to_tf32(e[it][2]), to_tf32(e[it][3]));
   }
 }
 
@@ -184,6 +194,8 @@ __global__ void __launch_bounds__(PTC_THREADS, Ptc<D>::MIN_BLOCKS) proxattn_fwd_
 
   ptc_stage_rows<D, QT>(sQ, C::LBO_Q, p.Q + zf, m0, N);
   ptc_stage_rows<D, TN>(sK, C::LBO_K, p.K + zf, 0, N);
+  float vreg[D / 16][4];
+  ptc_load_v<D, TN>(vreg, p.V + zf, 0, N);
   float xq[PS];
   ptc_point<PER>(p.X + zp, m0 + row, N, p, xq);
   tc::fence_async_smem();
@@ -209,14 +221,17 @@ __global__ void __launch_bounds__(PTC_THREADS, Ptc<D>::MIN_BLOCKS) proxattn_fwd_
       ok = __syncthreads_and(w);
       if (!ok) break;
     }
-    ptc_stage_v<D, TN>(sV, C::LBO_V, p.V + zf, n0, N);   // while the score product runs
+    ptc_store_v<D, TN>(sV, C::LBO_V, vreg);   // loaded during the weights of the previous step
     if (tid < TN) ptc_point<PER>(p.Y + zp, n0 + tid, N, p, sY + tid * PS);
     {
       const bool w = tc::mbar_wait(bar_s, t & 1);
       ok = __syncthreads_and(w);   // also orders the position stores before the weights below
       if (!ok) break;
     }
-    if (t + 1 < ntiles) ptc_stage_rows_async<D, TN>(k_addr, C::LBO_K, p.K + zf, n0 + TN, N);   // sK is free: lands during the weights
+    if (t + 1 < ntiles) {   // sK is free; both land during the weights
+      ptc_stage_rows_async<D, TN>(k_addr, C::LBO_K, p.K + zf, n0 + TN, N);
+      ptc_load_v<D, TN>(vreg, p.V + zf, n0 + TN, N);
+    }
     tc::fence_after_sync();
 #pragma unroll
     for (int c0 = 0; c0 < TNH; c0 += 32) {
