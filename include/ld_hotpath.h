@@ -27,7 +27,7 @@ enum {
 };
 
 /* bits OR-ed by kernels into the caller's device status word */
-enum { LD_FLAG_CAPACITY = 1, LD_FLAG_NONFINITE = 2, LD_FLAG_TIMEOUT = 4 };
+enum { LD_FLAG_CAPACITY = 1, LD_FLAG_NONFINITE = 2, LD_FLAG_TIMEOUT = 4, LD_FLAG_OVERFLOW = 8 };
 
 /* activation codes for the dense layers */
 enum { LD_ACT_NONE = 0, LD_ACT_SILU = 1, LD_ACT_LEAKY01 = 2 };
@@ -58,10 +58,10 @@ int ld_radius_graph_fill(const float* pos, int batch, int nodes, int periodic, f
                          int open_cells_cap, void* workspace, size_t workspace_bytes, const int* row_ptr,
                          long long capacity, int* src, int* dst, int* shift, float* rij, int* status_dev, void* stream);
 
-/* Allocation-free variant (no counterpart in the reference, whose build allocates and frees three
- * device buffers per call, neighbour_grid_kern.cu:174-176,220-222): count + fill in one call with the
+/* Allocation-free variant. It has no counterpart in the reference. Count + fill in one call with the
  * scratch space in a fixed 8 MiB device array inside the library, for callers that may not allocate
- * device memory where they need the graph. Refuses larger problems with LD_ERR_WORKSPACE. The first
+ * device memory where they need the graph (a plugin called from inside an engine's time-step loop, a
+ * service whose allocator is frozen after start-up). Refuses larger problems with LD_ERR_WORKSPACE. The first
  * call per device resolves the array's address and should precede any stream capture; calls that
  * overlap on one device race on the shared array. */
 int ld_radius_graph_build_noalloc(const float* pos, int batch, int nodes, int periodic, float cutoff, const float* box,
@@ -143,6 +143,28 @@ int ld_linear_bf16_tc_in16(const void* x_bf16, long long rows_outer, int K, int 
  * ld_col = S, off = 0); used to interleave the left operands of the l<=2 message layer per channel */
 int ld_linear_bf16_tc_out16(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias, int N,
                             int act, void* y_bf16, long long ld_row, long long ld_col, int off, int* status_dev, void* stream);
+
+/* Self-test of the bounded waits (no counterpart in the reference): ld_linear_bf16_tc (S = 1, no bias) on a launch
+ * whose weight panels are never requested and whose waits give up after 64 polls. Every block leaves through the
+ * failure path: *status_dev receives LD_FLAG_TIMEOUT, tensor memory is released, y stays unwritten, the device stays
+ * usable. rows_outer <= 1024. */
+int ld_linear_bf16_tc_selftest_timeout(const float* x, long long rows_outer, int K, const void* wp, int N, float* y,
+                                       int* status_dev, void* stream);
+
+/* ---- edge radial encodings as an operator of their own: r [rows, 3] (kind 3: r [rows]) -> out [rows, n] -------
+ * kind 0: radial_encode of archs/meanflow_painn8.py:25-35; kind 1: Gaussian basis x cosine cutoff (benchmark spec,
+ * not in the reference); kind 2: radial_encode_edge of archs/diffuser_atoms5.py:25-30; kind 3: radial_encode of
+ * managan/layers_common.py:122-126 (rmax unused); kind 4: radial_encode_8 of managan/jacobi_radenc.py:27-33
+ * (n = 8, coeff = its 8x9 coefficient matrix; NULL for the other kinds). */
+int ld_radial_encode(int kind, const float* r, long long rows, int n, float rmax, const float* coeff, float* out,
+                     void* stream);
+
+/* Counter-based Gaussian noise for sharded rollouts (the reference draws torch.randn_like per step,
+ * archs/meanflow_painn8.py:302-310, whose stream depends on how the batch is split): out[i] = base[i] + scale *
+ * z(seed, step, first_element + i), z ~ N(0,1) a pure function of its three arguments (splitmix64 hash + Box-Muller),
+ * so a rank owning systems [b0, b1) draws what a single GPU draws for them. base may be NULL. */
+int ld_counter_noise(float* out, const float* base, float scale, long long first_element, long long count,
+                     unsigned long long seed, unsigned long long step, void* stream);
 
 /* ld_painn_message_bf16_tc: ld_painn_message_f32 with the per-edge distance MLP on tcgen05
  * (BF16 operands, FP32 accumulation in tensor memory); same reference lines
@@ -238,10 +260,6 @@ int ld_ant16_contract_out(int product, const float* U, const float* dy, long lon
                           void* stream);
 int ld_tensor_prod_bare(int mode, int inds_l, int inds_r, int inds_o, const float* a, const float* b, long long n, float* out,
                         void* stream);
-
-/* Diagnostics (no counterpart in the reference): per-phase cycle counters of the fused tensor-core
- * kernel, added into 16 device int64 by later launches; NULL switches them off. */
-int ld_debug_set_phase_counters(long long* device_buffer16);
 
 #ifdef __cplusplus
 }

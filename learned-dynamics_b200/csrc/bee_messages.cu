@@ -67,18 +67,8 @@ __device__ __forceinline__ void edge_geometry(const float* __restrict__ rij, lon
   const float x = rij[e * 3], y = rij[e * 3 + 1], z = rij[e * 3 + 2];
   const float d = sqrtf(x * x + y * y + z * z);
   const float zz = d / r0;
-  float pw[9];
-  pw[0] = 1.f;
-#pragma unroll
-  for (int p = 1; p < 9; p++) pw[p] = pw[p - 1] * zz;
   const float env = fmaxf(1.f - zz, 0.f);
-#pragma unroll
-  for (int m = 0; m < 8; m++) {
-    float a = 0.f;
-#pragma unroll
-    for (int p = 0; p < 9; p++) a = fmaf(pw[p], jac[m * 9 + p], a);
-    g->enc[m] = a * env;
-  }
+  ld_radial_poly8(zz, env, jac, g->enc);
   const float s = 7.f / r0;
   const float ux = x * s, uy = y * s, uz = z * s;
   const float inv = 1.0f / sqrtf(1.f + ux * ux + uy * uy + uz * uz);

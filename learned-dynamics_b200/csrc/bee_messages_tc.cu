@@ -15,7 +15,9 @@
 #include "tc05.cuh"
 #include "tp_math.h"
 
-long long* ld_internal_phase_counters();  // diagnostics buffer set by ld_debug_set_phase_counters
+#ifdef LD_PHASE_COUNTERS
+long long* ld_internal_phase_counters();  // diagnostics build only: buffer set by ld_debug_set_phase_counters
+#endif
 
 namespace {
 
@@ -110,18 +112,8 @@ __device__ __forceinline__ void bt_sync_workers() { asm volatile("barrier.cta.sy
 __device__ __forceinline__ void bt_geometry(float x, float y, float z, float r0, const float* jac, BtGeom* g) {
   const float d = sqrtf(x * x + y * y + z * z);
   const float zz = d / r0;
-  float pw[9];
-  pw[0] = 1.f;
-#pragma unroll
-  for (int p = 1; p < 9; p++) pw[p] = pw[p - 1] * zz;
   const float env = fmaxf(1.f - zz, 0.f);
-#pragma unroll
-  for (int m = 0; m < 8; m++) {
-    float a = 0.f;
-#pragma unroll
-    for (int p = 0; p < 9; p++) a = fmaf(pw[p], jac[m * 9 + p], a);
-    g->enc[m] = a * env;
-  }
+  ld_radial_poly8(zz, env, jac, g->enc);
   const float s = 7.f / r0;
   const float ux = x * s, uy = y * s, uz = z * s;
   const float inv = rsqrtf(1.f + ux * ux + uy * uy + uz * uz);
@@ -566,8 +558,14 @@ extern "C" int ld_bee_messages_scalar_bf16_tc(const int* row_ptr, const int* dst
     const long long seg = (40LL << 20) / ((feat_bf16 == 2 ? 32LL : feat_bf16 ? 26LL : 52LL) * C);  // 13*chan values gathered per neighbour
     P.seg_nodes = (int)(seg < 1024 ? 1024 : seg);
   }
-  P.out_a = out_a; P.status = status_dev; P.feat_bf16 = feat_bf16; P.prof = ld_internal_phase_counters();
+  P.out_a = out_a; P.status = status_dev; P.feat_bf16 = feat_bf16;
+#ifdef LD_PHASE_COUNTERS
+  P.prof = ld_internal_phase_counters();
   auto kern = P.prof != nullptr ? bee_scalar_tc_kernel<true> : bee_scalar_tc_kernel<false>;
+#else
+  P.prof = nullptr;
+  auto kern = bee_scalar_tc_kernel<false>;
+#endif
   LD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

@@ -19,6 +19,7 @@
 #define LD_FLAG_CAPACITY 1
 #define LD_FLAG_NONFINITE 2
 #define LD_FLAG_TIMEOUT 4
+#define LD_FLAG_OVERFLOW 8
 
 #define LD_CUDA_TRY(expr)                          \
   do {                                             \

@@ -33,6 +33,8 @@ struct GemmParams {
   long long y_ld_row, y_ld_col; // BF16 output addressing: element (r, o, s) at r*y_ld_row + o*y_ld_col + s + y_off
   int y_off;
   int* status;
+  uint32_t wait_limit;       // polls per bounded wait (tc::TC_WAIT_LIMIT in production)
+  int selftest_no_weights;   // self-test only: the weight panels are never requested, so the first wait for them runs out
 };
 
 __device__ __forceinline__ float act_apply(float v, int act) {
@@ -89,10 +91,10 @@ gemm_tc_kernel(GemmParams P) {
       const int st = g & 1;
       const uint32_t use = g >> 1;
       bool w = true;
-      if (use >= 1) w = tc::mbar_wait(&bar_empty[st], (use - 1) & 1);  // MMAs that read this stage are done
+      if (use >= 1) w = tc::mbar_wait(&bar_empty[st], (use - 1) & 1, P.wait_limit);  // MMAs that read this stage are done
       ok = __syncthreads_and(w && !s_abort);
       if (!ok) break;
-      if (tid == 0) {
+      if (tid == 0 && !P.selftest_no_weights) {
         tc::mbar_expect_tx(&bar_full[st], b_stage);
         tc::bulk_g2s(b_smem[st], P.wp + (size_t)c * N * GT_KC, b_stage, &bar_full[st]);
       }
@@ -135,7 +137,7 @@ gemm_tc_kernel(GemmParams P) {
       tc::fence_async_smem();
       __syncthreads();
       if (tid == 0) {
-        if (tc::mbar_wait(&bar_full[st], use & 1)) {
+        if (tc::mbar_wait(&bar_full[st], use & 1, P.wait_limit)) {
           tc::fence_after_sync();
           const int kc = min(GT_KC, K - k0);
           const int ksteps = (kc + 15) / 16;
@@ -156,7 +158,7 @@ gemm_tc_kernel(GemmParams P) {
       }
     }
     if (!ok) break;
-    bool w = tc::mbar_wait(&bar_accum, tile_it & 1);
+    bool w = tc::mbar_wait(&bar_accum, tile_it & 1, P.wait_limit);
     ok = __syncthreads_and(w && !s_abort);
     if (!ok) break;
     tc::fence_after_sync();
@@ -201,7 +203,7 @@ gemm_tc_kernel(GemmParams P) {
   // every MMA and copy this block issued has been waited for on the success path; on the failure
   // path give outstanding work a bounded chance to land before releasing TMEM
   if (!ok && tid == 0) {
-    for (int s = 0; s < 2; s++) tc::mbar_wait(&bar_full[s], ((g >> 1) & 1));
+    for (int s = 0; s < 2 && !P.selftest_no_weights; s++) tc::mbar_wait(&bar_full[s], ((g >> 1) & 1), P.wait_limit);
   }
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem_base, ncols);
@@ -248,7 +250,8 @@ extern "C" int ld_pack_weights_bf16(const float* W, long long sw0, long long sw1
 // S in {1,3,9}; N a multiple of 32, N <= 512. wp from ld_pack_weights_bf16. status_dev: optional
 // device int32 that receives LD_FLAG_TIMEOUT if a bounded wait ran out.
 static int linear_tc_launch(const float* x, int in_bf16, long long rows_outer, int K, int S, const void* wp, const float* bias, int N, int act,
-                            void* y, int out_bf16, long long ld_row, long long ld_col, int off, int* status_dev, void* stream) {
+                            void* y, int out_bf16, long long ld_row, long long ld_col, int off, int* status_dev, void* stream,
+                            uint32_t wait_limit = tc::TC_WAIT_LIMIT, int selftest_no_weights = 0) {
   if (rows_outer < 0 || K <= 0 || N <= 0 || (S != 1 && S != 3 && S != 9)) return LD_ERR_SHAPE;
   if (N % 32 != 0 || N > 512) { ld_set_last_message("tensor-core linear: N must be a multiple of 32, at most 512"); return LD_ERR_UNSUPPORTED; }
   if (((uintptr_t)wp) % 16 != 0) { ld_set_last_message("tensor-core linear: packed weights must be 16-byte aligned"); return LD_ERR_SHAPE; }
@@ -259,7 +262,7 @@ static int linear_tc_launch(const float* x, int in_bf16, long long rows_outer, i
   if (rows_outer == 0) return LD_OK;
   GemmParams P;
   P.x = x; P.in_bf16 = in_bf16; P.y = (float*)y; P.out_bf16 = out_bf16; P.y_ld_row = ld_row; P.y_ld_col = ld_col; P.y_off = off; P.wp = (const __nv_bfloat16*)wp; P.bias = bias; P.rows = rows_outer * S; P.K = K; P.N = N; P.S = S;
-  P.act = act; P.status = status_dev;
+  P.act = act; P.status = status_dev; P.wait_limit = wait_limit; P.selftest_no_weights = selftest_no_weights;
   const size_t smem = 2 * GT_A_STAGE + 2 * (size_t)N * GT_KC * 2 + 1024;
   const bool unit = !in_bf16 && S == 1 && (K & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
   auto kern = unit ? gemm_tc_kernel<true, false> : (in_bf16 ? gemm_tc_kernel<false, true> : gemm_tc_kernel<false, false>);
@@ -304,4 +307,14 @@ extern "C" int ld_linear_bf16_tc_in16(const void* x_bf16, long long rows_outer, 
                                       int N, int act, float* y, int* status_dev, void* stream) {
   return linear_tc_launch((const float*)x_bf16, 1, rows_outer, K, S, wp, bias, N, act, y, 0, (long long)N * S, S, 0, status_dev,
                           stream);
+}
+
+// Self-test of the bounded-wait exit path: ld_linear_bf16_tc on a launch whose weight panels are never requested and
+// whose waits give up after 64 polls (about 64 microseconds each). Every block must leave through the failure path:
+// LD_FLAG_TIMEOUT in *status_dev, tensor memory released, y left unwritten, and the next launch on the device
+// unaffected. Nothing waits without a limit and nothing traps. Keep rows_outer small (one or two tiles).
+extern "C" int ld_linear_bf16_tc_selftest_timeout(const float* x, long long rows_outer, int K, const void* wp, int N, float* y,
+                                                  int* status_dev, void* stream) {
+  if (rows_outer > 1024) return LD_ERR_SHAPE;
+  return linear_tc_launch(x, 0, rows_outer, K, 1, wp, nullptr, N, 0, y, 0, (long long)N, 1, 0, status_dev, stream, 64u, 1);
 }

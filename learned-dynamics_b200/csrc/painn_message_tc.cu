@@ -572,15 +572,19 @@ __global__ void painn_pack_gather_kernel(const float* __restrict__ actv, const f
   }
 }
 
+#ifdef LD_PHASE_COUNTERS
 long long* g_prof_buffer = nullptr;
+#endif
 
 }  // namespace
 
-// Diagnostics: device buffer of 16 int64 that later ld_painn_message_bf16_tc launches add per-phase
-// cycle counts to (summed over blocks); NULL switches it off. Not thread safe.
+#ifdef LD_PHASE_COUNTERS
+// Diagnostics build only (-DLD_PHASE_COUNTERS; not part of the library's interface): device buffer of 16 int64 that
+// later launches of the fused tensor-core kernels add per-phase cycle counts to; NULL switches it off. Process-wide
+// and not thread safe, which is why the regular build has neither this switch nor the counting kernel instances.
 extern "C" int ld_debug_set_phase_counters(long long* device_buffer16) { g_prof_buffer = device_buffer16; return LD_OK; }
-// the same buffer for the other fused tensor-core kernels of this library
 long long* ld_internal_phase_counters() { return g_prof_buffer; }
+#endif
 
 extern "C" int ld_painn_pack_gather(const float* actv, const float* x_v, int Nt, int n, void* out_bf16, void* stream) {
   if (Nt < 0 || n <= 0 || n % 8 != 0) return LD_ERR_SHAPE;
@@ -621,7 +625,12 @@ extern "C" int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, cons
   P.radial_kind = radial_kind; P.rmax = rmax; P.pi_over_rmax = (float)(3.14159265358979323846 / (double)rmax); P.eps = eps;
   P.w1 = (const __nv_bfloat16*)w1p; P.w2 = (const __nv_bfloat16*)w2p; P.w3 = (const __nv_bfloat16*)w3p;
   P.b1 = b1; P.b2 = b2; P.b3 = b3; P.actv = actv; P.x_v = x_v; P.g16 = (const uint32_t*)gather16; P.res_a = res_a; P.res_v = res_v;
-  P.out_a = out_a; P.out_v = out_v; P.edge_counter = edge_counter; P.status = status_dev; P.prof = g_prof_buffer;
+  P.out_a = out_a; P.out_v = out_v; P.edge_counter = edge_counter; P.status = status_dev;
+#ifdef LD_PHASE_COUNTERS
+  P.prof = g_prof_buffer;
+#else
+  P.prof = nullptr;
+#endif
   const int N = 4 * n;
   if (P.k0p > N) { ld_set_last_message("painn message (tensor-core path): n_rbf above 4n is not supported"); return LD_ERR_UNSUPPORTED; }
   // the staging tile overlays only the operand tile, never the weight ring (the producer runs ahead)
@@ -643,8 +652,12 @@ extern "C" int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, cons
   P.stage_off = (unsigned)front;
   P.bias_off = (unsigned)(front + ring);
   const size_t smem = front + ring + (size_t)3 * N * 4 + 1024;
+#ifdef LD_PHASE_COUNTERS
   auto kern = gather16 != nullptr ? (P.prof != nullptr ? painn_message_tc_kernel<true, true> : painn_message_tc_kernel<false, true>)
                                   : (P.prof != nullptr ? painn_message_tc_kernel<true, false> : painn_message_tc_kernel<false, false>);
+#else
+  auto kern = gather16 != nullptr ? painn_message_tc_kernel<false, true> : painn_message_tc_kernel<false, false>;
+#endif
   LD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

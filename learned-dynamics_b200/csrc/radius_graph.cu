@@ -342,6 +342,8 @@ neighbour_kernel(const float* __restrict__ pos, GraphParams P, const GridDesc* _
                   sz = -(int)floorf(__fdiv_rn(__fadd_rn(ddz, hz), P.bz));
                 }
                 shift[e] = (sx & 0xff) | ((sy & 0xff) << 8) | ((sz & 0xff) << 16);
+                // three signed bytes: positions more than 127 box lengths apart do not fit
+                if ((abs(sx) > 127 || abs(sy) > 127 || abs(sz) > 127) && status != nullptr) atomicOr(status, LD_FLAG_OVERFLOW);
               }
               if (rij != nullptr) {
                 if (P.periodic) {
@@ -426,7 +428,11 @@ int make_params(int batch, int nodes, int periodic, float cutoff, const float* b
       if (mode == 1) {
         nd[a] = ceil_div;  // reference grid: cell edge may be < cutoff, pairs two cells apart are missed
       } else {
-        nd[a] = (int)floorf(box[a] / (cutoff * 1.00001f));  // cell edge >= cutoff: 27 cells cover the sphere
+        // cell edge >= cutoff with a margin for the float32 rounding of the cell index: (int)(n*p/box) is off by up to
+        // about n*1.2e-7 cells, so the margin grows with the number of cells per axis (n <= 1024)
+        float est = box[a] / cutoff;
+        if (est > 1024.f) est = 1024.f;
+        nd[a] = (int)floorf(box[a] / (cutoff * (1.00001f + 4.f * est * 1.1920929e-7f)));
         if (nd[a] < 1) nd[a] = 1;
       }
       if (nd[a] > 1024) nd[a] = 1024;
@@ -443,6 +449,24 @@ int make_params(int batch, int nodes, int periodic, float cutoff, const float* b
   return LD_OK;
 }
 
+}  // namespace
+
+namespace {
+// sum of the degrees in 64 bits; more than INT_MAX edges cannot be addressed by the int32 row offsets
+__global__ void degree_overflow_kernel(const int* __restrict__ degree, int Nt, int* status) {
+  __shared__ unsigned long long s_sum;
+  if (threadIdx.x == 0) s_sum = 0ull;
+  __syncthreads();
+  unsigned long long t = 0ull;
+  for (int i = threadIdx.x; i < Nt; i += blockDim.x) t += (unsigned long long)degree[i];
+  atomicAdd(&s_sum, t);
+  __syncthreads();
+  if (threadIdx.x == 0 && s_sum > 0x7fffffffull && status != nullptr) atomicOr(status, LD_FLAG_OVERFLOW);
+}
+
+__global__ void capacity_flag_kernel(const int* __restrict__ row_ptr, int Nt, int* status) {
+  if (status != nullptr && row_ptr[Nt] > 0) atomicOr(status, LD_FLAG_CAPACITY);
+}
 }  // namespace
 
 extern "C" int ld_radius_graph_workspace_size(int batch, int nodes, int periodic, float cutoff, const float* box,
@@ -496,6 +520,11 @@ extern "C" int ld_radius_graph_count(const float* pos, int batch, int nodes, int
   LD_LAUNCH_CHECK();
   rc = ld_scan_exclusive(w.degree, row_ptr, (long long)Nt, w.scan, stream);
   if (rc != LD_OK) return rc;
+  // row_ptr is int32: only problems whose edge count could pass 2^31-1 pay for the 64-bit check of the degree sum
+  if ((long long)Nt * (nodes - 1) > 0x7fffffffLL) {
+    degree_overflow_kernel<<<1, 256, 0, stream>>>(w.degree, Nt, status_dev);
+    LD_LAUNCH_CHECK();
+  }
   if (edge_counts != nullptr) {
     edge_counts_kernel<<<ld_cdiv(batch, 256), 256, 0, stream>>>(row_ptr, batch, nodes, edge_counts);
     LD_LAUNCH_CHECK();
@@ -520,7 +549,12 @@ extern "C" int ld_radius_graph_fill(const float* pos, int batch, int nodes, int 
   plan(P, workspace, &w);
   if (workspace == nullptr || workspace_bytes < w.bytes) { ld_set_last_message("radius graph: workspace too small"); return LD_ERR_WORKSPACE; }
   const int Nt = batch * nodes;
-  if (Nt == 0 || capacity <= 0) return LD_OK;
+  if (Nt == 0) return LD_OK;
+  if (capacity <= 0) {   // nothing can be written: still report edges that do not fit
+    capacity_flag_kernel<<<1, 1, 0, stream>>>(row_ptr, Nt, status_dev);
+    LD_LAUNCH_CHECK();
+    return LD_OK;
+  }
   neighbour_kernel<true><<<ld_cdiv(Nt, NB_WARPS), NB_WARPS * 32, 0, stream>>>(
       pos, P, w.desc, w.cell_start, w.sorted, w.sorted_cell, nullptr, row_ptr, capacity, src, dst, shift, rij, status_dev);
   LD_LAUNCH_CHECK();

@@ -46,8 +46,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // returns false if the phase did not complete within the poll limit (about a second at most: 2^20 waits of up to 1 us)
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < TC_WAIT_LIMIT; i++)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = TC_WAIT_LIMIT) {
+  for (uint32_t i = 0; i < limit; i++)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }

@@ -135,3 +135,17 @@ LD_HD float radial_feature(int kind, int m, int n, float d, float rmax, float pi
 }
 
 LD_HD float silu_f(float x) { return x / (1.0f + expf(-x)); }
+
+// Polynomial radial basis of managan/jacobi_radenc.py:27-33: enc[m] = env * sum_p coeff[m][p] z^p for an 8x9
+// coefficient matrix (the shifted Jacobi(1,0) polynomials there). The coefficients reach 2.7e4 with alternating
+// signs, so a float32 power sum loses four digits to cancellation (the reference's own float32 evaluation is
+// 2.4e-4 off the exact value of a basis function of size 1). Evaluated here by Horner's rule in double, once per
+// edge (72 double FMAs), which leaves only the final rounding to float32.
+LD_HD void ld_radial_poly8(float z, float env, const float* coeff, float* enc) {
+  const double zd = (double)z;
+  for (int m = 0; m < 8; m++) {
+    double a = (double)coeff[m * 9 + 8];
+    for (int p = 7; p >= 0; p--) a = fma(a, zd, (double)coeff[m * 9 + p]);
+    enc[m] = (float)(a * (double)env);
+  }
+}

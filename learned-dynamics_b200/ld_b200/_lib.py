@@ -11,7 +11,7 @@ c_void_p, c_int, c_float, c_size_t, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes
 
 LD_OK, LD_ERR_SHAPE, LD_ERR_CAPACITY, LD_ERR_BOX_TOO_SMALL = 0, -1, -2, -3
 LD_ERR_NONFINITE, LD_ERR_TIMEOUT, LD_ERR_CUDA, LD_ERR_WORKSPACE, LD_ERR_UNSUPPORTED = -4, -5, -6, -7, -8
-LD_FLAG_CAPACITY, LD_FLAG_NONFINITE, LD_FLAG_TIMEOUT = 1, 2, 4
+LD_FLAG_CAPACITY, LD_FLAG_NONFINITE, LD_FLAG_TIMEOUT, LD_FLAG_OVERFLOW = 1, 2, 4, 8
 
 # name -> argtypes ; every entry point declared in include/ld_hotpath.h
 P, I, F, LL, SZ = c_void_p, c_int, c_float, c_ll, c_size_t
@@ -40,7 +40,9 @@ SIGNATURES = {
     "ld_linear_bf16_tc_out16": [P, LL, I, I, P, P, I, I, P, LL, LL, I, P, P],
     "ld_painn_message_bf16_tc": [P, P, P, I, I, I, I, F, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P],
     "ld_painn_pack_gather": [P, P, I, I, P, P],
-    "ld_debug_set_phase_counters": [P],
+    "ld_radial_encode": [I, P, LL, I, F, P, P, P],
+    "ld_linear_bf16_tc_selftest_timeout": [P, LL, I, P, I, P, P, P],
+    "ld_counter_noise": [P, P, F, LL, LL, ctypes.c_ulonglong, ctypes.c_ulonglong, P],
     "ld_group_norm": [P, I, I, I, I, I, I, F, P, P, P, P, P],
     "ld_proxattn_fwd": [P, P, P, P, P, P, I, I, I, I, I, F, F, F, P, P],
     "ld_proxattn_fwd_tf32_tc": [P, P, P, P, P, P, I, I, I, I, I, F, F, F, P, P, P],

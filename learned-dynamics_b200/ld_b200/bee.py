@@ -38,11 +38,12 @@ def jacobi_matrix(dim=8):
 
 
 def radial_encode_8(r, rmax):
-    """r: (..., 3) -> (..., 8)"""
-    A = jacobi_matrix(8).to(r.device)
+    """r: (..., 3) -> (..., 8). The power sum is evaluated in float64 (as the fused kernels do): the coefficients reach
+    2.7e4 with alternating signs, and in float32 the cancellation costs four digits."""
+    A = jacobi_matrix(8).to(device=r.device, dtype=torch.float64)
     z = (torch.linalg.vector_norm(r, dim=-1) / rmax)[..., None]
-    pows = z ** torch.arange(A.shape[1], device=r.device)
-    return torch.nn.functional.linear(pows, A) * torch.relu(1. - z)
+    pows = z.double() ** torch.arange(A.shape[1], device=r.device)
+    return (torch.nn.functional.linear(pows, A) * torch.relu(1. - z).double()).to(r.dtype)
 
 
 class MLP(nn.Module):
@@ -298,21 +299,24 @@ class BeeDenoiser(nn.Module):
         self.v_readin = TensLinear(1, 1, dim_v)
         self.blocks = nn.ModuleList([BeeBlock(r0, dim_a, dim_v, dim_d, chan) for _ in range(depth)])
         self.readout = TensLinear(1, dim_v, 1)
+        self.graph_cache = None   # set by painn.enable_rollout_graphs: fixed-capacity graph buffers for rollouts
 
     def forward(self, x0, x1, box, types, counter=None):
         from .graph_layers import Graph
         batch, nodes, _ = x0.shape
-        graph = Graph.radius_graph(self.r0, box, x1.contiguous())
+        graph = Graph.radius_graph(self.r0, box, x1.contiguous(), cache=self.graph_cache)
         x_a = self.type_embed(types)[None].expand(batch, -1, -1).contiguous()
         x_v = self.v_readin((x1 - x0)[..., None, :].contiguous())
         x_d = torch.zeros(batch, nodes, self.dim_d, 3, 3, device=x0.device)
         for blk in self.blocks:
             x_a, x_v, x_d = blk(graph, graph.rij, x_a, x_v, x_d)
         if counter is not None:
-            counter += graph.src.numel() * len(self.blocks)
+            graph.count_edges(counter, len(self.blocks))
         return self.readout(x_v).squeeze(-2)
 
     @torch.no_grad()
     def generate(self, x_0, noise, sigma_0, box, types, counter=None):
         z_1 = x_0 + sigma_0 * noise
-        return z_1 - self.forward(x_0, z_1, box, types, counter)
+        out = z_1 - self.forward(x_0, z_1, box, types, counter)
+        ops.check_tc_status(x_0.device, block=False)   # a kernel that gave up on a wait is reported, not passed on
+        return out

@@ -74,6 +74,77 @@ class RadiusGraphBuilder:
         self.fill(pos, capacity, src, dst, shift, rij)
 
 
+class RolloutGraphCache:
+    """Edge buffers of a fixed capacity reused over the steps of a rollout, so that no step waits for the device to
+    learn its edge count (the reference's get_edges reads it back with .item() on every build,
+    neighbour_grid.cpp:180-194). The first build is the ordinary one and fixes the capacity at `margin` times its edge
+    count. Later builds run count + fill back to back at that capacity; the kernels downstream take their ranges from
+    row_ptr, so the unused tail of the buffers is never read. After every build the edge count and the status word
+    are copied to pinned host memory without waiting; a later build looks at the copies that have arrived, grows the
+    buffers when the count comes within 10 % of the capacity, and raises if a build did overflow (the steps since
+    then are invalid and must be redone: use a larger margin)."""
+
+    def __init__(self, margin=1.25):
+        self.margin = float(margin)
+        self.builder = None
+        self.capacity = 0
+        self.buffers = None
+        self._host = None
+        self._event = None
+
+    def _allocate(self, capacity, device):
+        self.capacity = int(capacity)
+        self.buffers = (torch.empty(self.capacity, dtype=torch.int32, device=device),
+                        torch.empty(self.capacity, dtype=torch.int32, device=device),
+                        torch.empty(self.capacity, 3, dtype=torch.float32, device=device))
+
+    def _poll(self, block=False):
+        if self._event is None or not (block or self._event.query()):
+            return
+        if block:
+            self._event.synchronize()
+        edges, flags = int(self._host[0]), int(self._host[1])
+        self._event = None
+        if flags != 0:
+            self.builder.status.zero_()
+            if flags & _lib.LD_FLAG_CAPACITY:
+                need = int(edges * self.margin) + 1024
+                self._allocate(need, self.builder.device)
+                raise _lib.HotpathError(_lib.LD_ERR_CAPACITY, f"a fixed-capacity graph build overflowed ({edges} edges); the buffers "
+                                        f"were grown to {need}, the steps since that build must be redone")
+            check_status_flags(torch.tensor([flags]))
+        if edges * 1.1 > self.capacity:
+            self._allocate(int(edges * self.margin) + 1024, self.builder.device)
+
+    def build(self, r0, box, pos, mode=MODE_EXACT):
+        batch, nodes, _ = pos.shape
+        key = (batch, nodes, float(r0), None if box is None else tuple(float(b) for b in box), mode, pos.device)
+        if self.builder is None or self._key != key:
+            self.builder = RadiusGraphBuilder(batch, nodes, r0, box, mode=mode, device=pos.device)
+            self._key = key
+            g = self.builder.build(pos, want_rij=True)            # ordinary build: learns the edge count
+            check_status_flags(self.builder.status)
+            self._allocate(int(g["E"] * self.margin) + 1024, pos.device)
+            self._host = torch.zeros(2, dtype=torch.int32).pin_memory()
+            self._event = None
+        else:
+            self._poll()
+        b = self.builder
+        src, dst, rij = self.buffers
+        b.build_fixed(pos, self.capacity, src, dst, None, rij)
+        # edge count and status of this build, on their way to the host while the step goes on
+        self._host[0:1].copy_(b.row_ptr[-1:], non_blocking=True)
+        self._host[1:2].copy_(b.status, non_blocking=True)
+        self._event = torch.cuda.Event()
+        self._event.record(torch.cuda.current_stream(pos.device))
+        return {"src": src, "dst": dst, "rij": rij, "row_ptr": b.row_ptr, "edge_counts": b.edge_counts,
+                "num_edges": b.row_ptr[-1:]}
+
+    def finish(self):
+        """wait for the last build's report (end of a rollout): raises if it overflowed"""
+        self._poll(block=True)
+
+
 def unpack_shift(shift):
     """int32 packed lattice shift -> [E,3] int32"""
     s = shift.to(torch.int32)
@@ -87,6 +158,8 @@ def check_status_flags(status):
         raise RuntimeError("some positions are NaN!")
     if flags & _lib.LD_FLAG_CAPACITY:
         raise RuntimeError("Neighbour list overflow occurred. Try increasing the edge capacity.")
+    if flags & _lib.LD_FLAG_OVERFLOW:
+        raise RuntimeError("radius graph: more than 2^31-1 edges, or a lattice shift beyond 127 box lengths")
     if flags & _lib.LD_FLAG_TIMEOUT:
         raise RuntimeError("device-side wait ran out")
 

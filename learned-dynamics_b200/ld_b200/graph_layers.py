@@ -10,16 +10,41 @@ from . import graph as _g
 class Graph:
     """Batch of graphs with the same node count; edges flat, src non-decreasing (reference :9-24)."""
 
-    def __init__(self, src, dst, edge_indices, batch, nodes, row_ptr=None, rij=None):
-        self.src32 = src.to(torch.int32).contiguous()
-        self.dst32 = dst.to(torch.int32).contiguous()
-        self.src = src.to(torch.int64)
-        self.dst = dst.to(torch.int64)
+    def __init__(self, src, dst, edge_indices, batch, nodes, row_ptr=None, rij=None, num_edges=None):
+        self.src32 = src if src.dtype == torch.int32 and src.is_contiguous() else src.to(torch.int32).contiguous()
+        self.dst32 = dst if dst.dtype == torch.int32 and dst.is_contiguous() else dst.to(torch.int32).contiguous()
+        self._src64 = src if src.dtype == torch.int64 else None
+        self._dst64 = dst if dst.dtype == torch.int64 else None
         self.edge_indices = edge_indices
         self.batch = batch
         self.nodes = nodes
         self._row_ptr = row_ptr
         self.rij = rij  # wrapped displacement per edge when built by radius_graph
+        # fixed-capacity graphs (rollouts): the buffers are longer than the edge list and the count lives on the device
+        self.num_edges_dev = num_edges
+
+    def _trim(self, t):
+        return t if self.num_edges_dev is None else t[: int(self.num_edges_dev.item())]
+
+    @property
+    def src(self):
+        """int64 view, as the reference exposes (managan/graph_layers.py:19-20); made on first use"""
+        if self._src64 is None:
+            self._src64 = self._trim(self.src32).to(torch.int64)
+        return self._src64
+
+    @property
+    def dst(self):
+        if self._dst64 is None:
+            self._dst64 = self._trim(self.dst32).to(torch.int64)
+        return self._dst64
+
+    def count_edges(self, counter, times=1):
+        """counter (device int64[1]) += times * number of edges, without a host read"""
+        if self.num_edges_dev is not None:
+            counter += self.num_edges_dev.to(torch.int64) * times
+        else:
+            counter += self.src32.numel() * times
 
     @property
     def row_ptr(self):
@@ -28,12 +53,20 @@ class Graph:
         return self._row_ptr
 
     @staticmethod
-    def radius_graph(r0, box, pos, celllist_max=32, neighbours_max=64, mode=_g.MODE_EXACT):
+    def radius_graph(r0, box, pos, celllist_max=32, neighbours_max=64, mode=_g.MODE_EXACT, cache=None):
         """Nodes within r0 are connected. box: (bx,by,bz) periodic, or None for open boundaries
         (the reference has periodic only). celllist_max / neighbours_max are accepted and unused:
-        the CSR build has no capacities to overflow."""
+        the CSR build has no capacities to overflow. cache: a graph.RolloutGraphCache; the build then reuses its
+        buffers at a fixed capacity and does not wait for the device (inference loops only: src / dst are then longer
+        than the edge list, row_ptr delimits it)."""
         batch, nodes, three = pos.shape
         assert three == 3
+        if cache is not None and not torch.is_grad_enabled():
+            g = cache.build(r0, box, pos.contiguous(), mode)
+            ans = Graph(g["src"], g["dst"], g["edge_counts"], batch, nodes, row_ptr=g["row_ptr"], rij=g["rij"],
+                        num_edges=g["num_edges"])
+            ans.box = box
+            return ans
         builder = _g.RadiusGraphBuilder(batch, nodes, r0, box, mode=mode, device=pos.device)
         g = builder.build(pos.contiguous(), want_rij=True)
         _g.check_status_flags(builder.status)  # NaN positions raise, as the reference's assert does

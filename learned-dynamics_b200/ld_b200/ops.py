@@ -7,7 +7,7 @@ from ._lib import lib, check, ptr, stream_ptr, require_cuda_f32, KERNEL_TIMER
 
 ACT_NONE, ACT_SILU, ACT_LEAKY01 = 0, 1, 2
 KERNEL_TIMER = KERNEL_TIMER  # re-exported for bench.py
-RADIAL_PAINN, RADIAL_GAUSSIAN = 0, 1
+RADIAL_PAINN, RADIAL_GAUSSIAN, RADIAL_EDGE, RADIAL_COS, RADIAL_JACOBI8 = 0, 1, 2, 3, 4
 
 BEE_SUFFIX = ("", "", "", (3,), (3,), (3,), (3,), (3, 3), (3, 3), (3, 3), (3, 3), (3,), (3, 3))
 
@@ -105,6 +105,14 @@ class TensorLinearDwFn(torch.autograd.Function):
 
 def tensor_linear(inds, W, x):
     return TensorLinearFn.apply(inds, W, x)
+
+
+def radial_encode(kind, r, rows, n, rmax, out, coeff=None):
+    """out[rows, n] = radial encoding `kind` (RADIAL_*) of r[rows, 3] (r[rows] for RADIAL_COS)"""
+    require_cuda_f32(r, "r")
+    with KERNEL_TIMER.region("radial_encode"):
+        check(lib().ld_radial_encode(kind, ptr(r), rows, n, float(rmax), ptr(coeff), ptr(out), stream_ptr(r.device)))
+    return out
 
 
 def _ptr_array(tensors):
@@ -281,6 +289,46 @@ def tc_status(device):
     if key not in _TC_STATUS:
         _TC_STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _TC_STATUS[key]
+
+
+_TC_WATCH = {}
+
+
+def check_tc_status(device, block=True):
+    """Raise HotpathError(LD_ERR_TIMEOUT) if a tensor-core kernel on `device` gave up on a bounded wait (its outputs are
+    then incomplete), and clear the status word. block=True reads the word now (synchronises the device).
+    block=False is for rollout loops: it looks at the copy of the word requested by the previous call, if that copy
+    has arrived, and requests a new one on the current stream without waiting for it; a timeout is then reported one or
+    two steps late, but no step waits for the device. ModelPredictor.predict and the generate() loops call it this way
+    every step and with block=True once at the end."""
+    from ._lib import HotpathError, LD_ERR_TIMEOUT
+    dev = torch.device(device)
+    key = dev.index or 0
+    word = tc_status(dev)
+
+    def report(value):
+        if value != 0:
+            word.zero_()
+            _TC_WATCH.pop(key, None)
+            raise HotpathError(LD_ERR_TIMEOUT, f"a tensor-core kernel gave up on a bounded wait (status flags {value:#x}); "
+                                               "the outputs of the affected step are incomplete")
+
+    pending = _TC_WATCH.get(key)
+    if block:
+        _TC_WATCH.pop(key, None)
+        report(int(word.item()))
+        return
+    if pending is not None:
+        host, ev = pending
+        if not ev.query():
+            return
+        report(int(host[0]))
+    else:
+        host = torch.zeros(1, dtype=torch.int32).pin_memory()
+    host.copy_(word, non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(dev))
+    _TC_WATCH[key] = (host, ev)
 
 
 def pack_weights_bf16(W):

@@ -164,9 +164,10 @@ class Message(nn.Module):
         return d_a, d_v
 
 
-def graph_setup(r0, box, pos):
-    """radius graph + wrapped displacements; box=None means open boundaries."""
-    graph = Graph.radius_graph(r0, box, pos)
+def graph_setup(r0, box, pos, cache=None):
+    """radius graph + wrapped displacements; box=None means open boundaries. cache: optional
+    graph.RolloutGraphCache (fixed-capacity buffers, no wait for the edge count; inference only)."""
+    graph = Graph.radius_graph(r0, box, pos, cache=cache)
     if torch.is_grad_enabled() and pos.requires_grad:
         # the reference's form (archs/meanflow_painn8.py:167-172): differentiable in the positions,
         # which the meanflow training step needs for its Jacobian-vector product
@@ -188,13 +189,14 @@ class Block(nn.Module):
         self.update = Update(n)
         if self.pos_mutable:
             self.lin_push_pos = TensLinear(1, n, 1)
+        self.graph_cache = None   # set by enable_rollout_graphs
 
     def forward(self, tup):
         pos, graph, r_ij, graph_bond, r_ij_bond, x_a, x_v, box = tup[:8]
         counter = tup[8] if len(tup) > 8 else None
         if graph is None:
-            graph, r_ij = graph_setup(self.r0, box, pos)
-        if graph_bond.src.numel() > 0:  # a bond graph without edges contributes exactly zero
+            graph, r_ij = graph_setup(self.r0, box, pos, self.graph_cache)
+        if graph_bond.src32.numel() > 0:  # a bond graph without edges contributes exactly zero
             x_a, x_v = self.message_bond(graph_bond, x_a, x_v, r_ij_bond, residual=True, edge_counter=counter)
         x_a, x_v = self.message(graph, x_a, x_v, r_ij, residual=True, edge_counter=counter)
         dx_a, dx_v = self.update(x_a, x_v)
@@ -203,6 +205,24 @@ class Block(nn.Module):
             pos = pos + self.lin_push_pos(x_v).squeeze(-2)
             graph, r_ij = None, None
         return (pos, graph, r_ij, graph_bond, r_ij_bond, x_a, x_v, box) + ((counter,) if len(tup) > 8 else ())
+
+
+def enable_rollout_graphs(module, margin=1.25):
+    """Give every layer of `module` that builds a radius graph a graph.RolloutGraphCache: inside torch.no_grad() its
+    builds then reuse edge buffers of a fixed capacity (margin x the first build's edge count, grown when the count
+    comes close) and do not read the edge count back, so a rollout loop never waits for the device."""
+    from .graph import RolloutGraphCache
+    for m in module.modules():
+        if hasattr(m, "graph_cache"):
+            m.graph_cache = RolloutGraphCache(margin)
+    return module
+
+
+def finish_rollout_graphs(module):
+    """wait for the reports of the last builds (end of a rollout); raises if one overflowed its capacity"""
+    for m in module.modules():
+        if getattr(m, "graph_cache", None) is not None and m.graph_cache.builder is not None:
+            m.graph_cache.finish()
 
 
 class CPaiNN(nn.Module):
@@ -319,6 +339,8 @@ class Meanflow:
         z_1 = x_0 + self.sigma_0 * noise.reshape(batch, atoms, 3)
         st = (torch.zeros(batch, device=x_0.device), torch.ones(batch, device=x_0.device))
         v_pred = self.dn(st, x_0, z_1, self.box, self.types, self.graph_bond, counter)
+        if x_0.is_cuda:
+            ops.check_tc_status(x_0.device, block=False)   # a kernel that gave up on a wait is reported, not passed on
         return (z_1 - v_pred).reshape(*lead, atoms, 3)
 
     def predict(self, state, counter=None):

@@ -119,6 +119,9 @@ class ModelPredictor:
         if host is not None:
             self._copy_stream.synchronize()
             self.last_host_trajectory = host
+        if x.is_cuda:
+            from . import ops
+            ops.check_tc_status(x.device, block=True)   # the trajectory is only handed out if no kernel gave up on a wait
         if ret:
             return ModelState(state.shape, trajectory, **state.kwargs)
 

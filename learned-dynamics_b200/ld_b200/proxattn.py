@@ -83,40 +83,3 @@ def proxattn_periodic(Q, K, V, X, Y, r0sq, box, precision="fp32"):
     if isinstance(box, torch.Tensor):
         box = tuple(box.tolist())
     return _ProxAttn.apply(Q, K, V, X, Y, r0sq, tuple(box), precision)
-
-
-def _time_case(Z=32, N=4096, dim=64, heads=4, periodic=False, reps=5, precision="fp32"):
-    """python -m ld_b200.proxattn [Z N dim]: device time of the forward and of the backward pass"""
-    g = torch.Generator().manual_seed(0)
-    q, k, v, d_out = (torch.randn(Z, N, dim, generator=g).cuda() for _ in range(4))
-    x, y = (4 * torch.rand(Z, N, 3, generator=g)).cuda(), (4 * torch.rand(Z, N, 3, generator=g)).cuda()
-    r0sq = (0.2 + torch.rand(heads, generator=g)).cuda()
-    box = (4.0, 4.0, 4.0) if periodic else None
-    ins = [t.requires_grad_(True) for t in (q, k, v, x, y)]
-    times = []
-    for backward in (False, True):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        out = _ProxAttn.apply(*ins, r0sq, box, precision)
-        for i in range(reps + 2):
-            if i == 2:
-                e0.record()
-            if backward:
-                torch.autograd.grad(out, ins, d_out, retain_graph=True)
-            else:
-                out = _ProxAttn.apply(*ins, r0sq, box, precision)
-        e1.record()
-        torch.cuda.synchronize()
-        times.append(e0.elapsed_time(e1) / reps)
-    pair_flops = 2.0 * Z * N * N * dim
-    print(f"proximity attention Z={Z} N={N} dim={dim} periodic={periodic} forward in {precision}: forward {times[0]:.3f} ms "
-          f"({2 * pair_flops / times[0] * 1e-9:.1f} TFLOP/s), backward {times[1]:.3f} ms "
-          f"({7 * pair_flops / times[1] * 1e-9:.1f} TFLOP/s FP32)")
-
-
-if __name__ == "__main__":
-    import sys
-    a = [int(v) for v in sys.argv[1:4]]
-    _time_case(*a)
-    _time_case(*a, periodic=True)
-    _time_case(*a, precision="tf32")
-    _time_case(*a, periodic=True, precision="tf32")

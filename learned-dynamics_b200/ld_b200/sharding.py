@@ -12,9 +12,55 @@ def shard_range(systems, rank, world):
     return begin, begin + base + (1 if rank < extra else 0)
 
 
-def noise_seed(global_system_index, step, base_seed=777):
-    """per-(system, step) seed: results do not depend on the number of ranks"""
-    return (base_seed * 1000003 + global_system_index) * 1000003 + step
+_M1, _M2 = -4658895280553007687, -7723592293110705685      # 0xBF58476D1CE4E5B9, 0x94D049BB133111EB as int64
+_K1 = -7046029254386353131                                  # 0x9E3779B97F4A7C15 as int64
+
+
+def _wrap64(v):
+    """Python integer -> the int64 with the same low 64 bits"""
+    v &= (1 << 64) - 1
+    return v - (1 << 64) if v >= (1 << 63) else v
+
+
+def _lsr(x, k):
+    """logical right shift of int64 tensors (torch's >> is arithmetic)"""
+    return (x >> k) & ((1 << (64 - k)) - 1)
+
+
+def counter_noise_torch(first_element, count, seed, step, device="cpu"):
+    """N(0,1) values number first_element .. first_element+count-1 of the noise field of (seed, step): the arithmetic of
+    ld_counter_noise in torch integer operations (64-bit wrapping multiply, splitmix64 finaliser, Box-Muller).
+    Element numbering of a batch [systems, nodes, 3]: ((system * nodes) + node) * 3 + component, so a shard's values
+    are a contiguous range and do not depend on how the batch is split over ranks."""
+    key = _wrap64(seed * 0x9E3779B97F4A7C15 + step * 0xBF58476D1CE4E5B9)
+    x = torch.arange(first_element, first_element + count, dtype=torch.int64, device=device) + key
+    x = (x ^ _lsr(x, 30)) * _M1
+    x = (x ^ _lsr(x, 27)) * _M2
+    x = x ^ _lsr(x, 31)
+    u1 = (_lsr(x, 40) + 1).to(torch.float32) * (1.0 / 16777216.0)
+    u2 = (_lsr(x, 16) & 0xFFFFFF).to(torch.float32) * (1.0 / 16777216.0)
+    return torch.sqrt(-2.0 * torch.log(u1)) * torch.cos(6.283185307179586 * u2)
+
+
+def shard_noise(shape, first_system, seed, step, device, base=None, scale=1.0):
+    """base + scale * noise for the systems [first_system, first_system + shape[0]) of a batch whose per-system shape is
+    shape[1:] (one kernel launch on a CUDA device). The values are those a single rank owning the whole batch draws."""
+    per = 1
+    for d in shape[1:]:
+        per *= d
+    count, first = shape[0] * per, first_system * per
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        z = counter_noise_torch(first, count, seed, step, dev).reshape(shape)
+        return z * scale if base is None else base + scale * z
+    from ._lib import lib, check, ptr, stream_ptr, KERNEL_TIMER
+    out = torch.empty(shape, dtype=torch.float32, device=dev)
+    if base is not None:
+        base = base.contiguous()
+        assert base.shape == out.shape and base.dtype == torch.float32
+    with KERNEL_TIMER.region("counter_noise"):
+        check(lib().ld_counter_noise(ptr(out), ptr(base), float(scale), first, count, seed, step, stream_ptr(dev)))
+    return out
 
 
 def gather_positions(x_local, systems, dst=0):

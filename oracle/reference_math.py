@@ -37,11 +37,8 @@ def _c():
 
 
 # ---- radius graph -----------------------------------------------------------------------------
-def radius_graph(pos, cutoff, box=None, mode=0):
-    """pos [B,N,3] float32 (CPU). Returns dict(src, dst, shift[E,3], rij[E,3], degree[B*N]) with
-    edges ordered by (system, i, j). Membership: neighbour_grid_kern.cu:39-48, 95-150; edge order
-    neighbour_grid.cpp:180-194; rij is graph_setup's boxwrap (managan/graph_layers.py:62-66)."""
-    pos = np.ascontiguousarray(pos.detach().cpu().numpy(), dtype=np.float32)
+def _radius_graph_block(pos, cutoff, box, mode):
+    """one call of the C brute force on pos [B,N,3] (numpy float32); node ids are local to the block"""
     B, N, _ = pos.shape
     periodic = 0 if box is None else 1
     boxarr = np.asarray(box if box is not None else (0, 0, 0), dtype=np.float32)
@@ -52,6 +49,27 @@ def radius_graph(pos, cutoff, box=None, mode=0):
     shift = np.zeros(E, dtype=np.int32); rij = np.zeros((E, 3), dtype=np.float32)
     _c().oracle_radius_graph(pos.ctypes.data, B, N, periodic, ctypes.c_float(cutoff), boxarr.ctypes.data, mode, E,
                              src.ctypes.data, dst.ctypes.data, shift.ctypes.data, rij.ctypes.data, deg.ctypes.data)
+    return src, dst, shift, rij, deg
+
+
+def radius_graph(pos, cutoff, box=None, mode=0):
+    """pos [B,N,3] float32 (CPU). Returns dict(src, dst, shift[E,3], rij[E,3], degree[B*N]) with
+    edges ordered by (system, i, j). Membership: neighbour_grid_kern.cu:39-48, 95-150; edge order
+    neighbour_grid.cpp:180-194; rij is graph_setup's boxwrap (managan/graph_layers.py:62-66).
+    Systems are independent, so large batches are handed to the C routine one system per host thread."""
+    pos = np.ascontiguousarray(pos.detach().cpu().numpy(), dtype=np.float32)
+    B, N, _ = pos.shape
+    if B > 1 and B * N * N > (1 << 24):
+        from concurrent.futures import ThreadPoolExecutor
+        _c()
+        with ThreadPoolExecutor(max_workers=len(os.sched_getaffinity(0))) as pool:
+            parts = list(pool.map(lambda b: _radius_graph_block(pos[b:b + 1], cutoff, box, mode), range(B)))
+        src = np.concatenate([p[0] + b * N for b, p in enumerate(parts)])
+        dst = np.concatenate([p[1] + b * N for b, p in enumerate(parts)])
+        shift, rij, deg = (np.concatenate([p[k] for p in parts]) for k in (2, 3, 4))
+    else:
+        src, dst, shift, rij, deg = _radius_graph_block(pos, cutoff, box, mode)
+    E = src.shape[0]
     sh = np.stack([((shift >> (8 * a)) & 0xFF).astype(np.int32) for a in range(3)], axis=1)
     sh = np.where(sh >= 128, sh - 256, sh)
     return {"src": torch.from_numpy(src), "dst": torch.from_numpy(dst), "shift": torch.from_numpy(sh),
@@ -190,6 +208,23 @@ def radial_encode_gaussian(r, n, rmax):
     return torch.exp(-0.5 * ((d - mu) / width) ** 2) * env
 
 
+def radial_encode_edge(r, n, rmax):
+    """archs/diffuser_atoms5.py:25-30"""
+    npi = torch.pi * torch.arange(0, n)
+    x_sq = (r ** 2).sum(-1) / rmax
+    return torch.cos(npi * torch.sqrt(x_sq)[..., None]) * torch.relu(1. - x_sq)[..., None]
+
+
+def radial_encode_cos(r, n, rmax):
+    """managan/layers_common.py:122-126 (radial_encode there; rmax is unused)"""
+    return torch.cos(torch.pi * torch.arange(0, n) * r[..., None])
+
+
+def vec_linear(W, v):
+    """managan/layers_common.py:81-89 (VecLinear.forward)"""
+    return torch.einsum("oi, ...ik -> ...ok", W, v)
+
+
 def jacobi_matrix(dim):
     """managan/jacobi_radenc.py:8-24: coefficients of shifted Jacobi(1,0) polynomials on [0,1]"""
     import sympy as sp
@@ -213,7 +248,7 @@ def radial_encode_8(r, rmax):
         _A8 = jacobi_matrix(8)
     z = (torch.linalg.vector_norm(r, dim=-1) / rmax)[..., None]
     pows = z ** torch.arange(_A8.shape[1])
-    return F.linear(pows, _A8) * torch.relu(1. - z)
+    return F.linear(pows, _A8.to(r.dtype)) * torch.relu(1. - z)   # float64 inputs give the float64 oracle
 
 
 def tens_sigmoid(inds, x):
@@ -614,12 +649,13 @@ class OBeeDenoiser(nn.Module):
 
     def forward(self, x0, x1, box, types):
         batch, nodes, _ = x0.shape
-        g = radius_graph(x1, self.r0, box)
+        g = radius_graph(x1, self.r0, box)   # membership and r_ij in float32, as the graph builder defines them
         x_a = self.type_embed(types)[None].expand(batch, -1, -1)
         x_v = self.v_readin((x1 - x0)[..., None, :])
-        x_d = torch.zeros(batch, nodes, self.dim_d, 3, 3)
+        x_d = torch.zeros(batch, nodes, self.dim_d, 3, 3, dtype=x0.dtype)
+        rij = g["rij"].to(x0.dtype)
         for blk in self.blocks:
-            x_a, x_v, x_d = blk(g["src"], g["dst"], g["rij"], x_a, x_v, x_d)
+            x_a, x_v, x_d = blk(g["src"], g["dst"], rij, x_a, x_v, x_d)
         self.edges_last = g["E"] * len(self.blocks)
         return self.readout(x_v).squeeze(-2)
 

@@ -135,9 +135,9 @@ def test_deterministic_order():
     assert torch.equal(g1["dst"], g2["dst"]) and torch.equal(g1["rij"], g2["rij"])
 
 
-def test_benchmark_config_1_one_system_and_full_properties():
-    """32 periodic boxes L=16 x 4096 uniform particles, cutoff 2.5: one system against the
-    oracle, the whole batch through size-independent properties (symmetry, degree sums)."""
+def test_benchmark_config_1_all_systems_and_full_properties():
+    """32 periodic boxes L=16 x 4096 uniform particles, cutoff 2.5: all 32 systems bit-exact against the brute-force
+    oracle (edge set, lattice shifts, displacements), then size-independent properties (symmetry, degree sums)."""
     gen = torch.Generator().manual_seed(1001)
     pos = torch.rand(32, 4096, 3, generator=gen) * 16.0
     box = (16.0, 16.0, 16.0)
@@ -145,12 +145,13 @@ def test_benchmark_config_1_one_system_and_full_properties():
     b = G.RadiusGraphBuilder(32, 4096, 2.5, box)
     g = b.build(pos.cuda(), want_shift=True)
     G.check_status_flags(b.status)
-    o = R.radius_graph(pos[5:6], 2.5, box)
-    lo, hi = int(g["edge_counts"][4]), int(g["edge_counts"][5])
-    k1, s1, r1 = _canon(g["src"][lo:hi].cpu() - 5 * 4096, g["dst"][lo:hi].cpu() - 5 * 4096,
-                        G.unpack_shift(g["shift"][lo:hi]).cpu(), g["rij"][lo:hi].cpu())
+    o = R.radius_graph(pos, 2.5, box)
+    assert g["E"] == o["E"]
+    k1, s1, r1 = _canon(g["src"].cpu(), g["dst"].cpu(), G.unpack_shift(g["shift"]).cpu(), g["rij"].cpu())
     k2, s2, r2 = _canon(o["src"], o["dst"], o["shift"], o["rij"])
     assert torch.equal(k1, k2) and torch.equal(s1, s2) and torch.equal(r1, r2)
+    per_system = torch.bincount(o["src"].long() // 4096, minlength=32)
+    assert torch.equal(torch.cumsum(per_system, 0).to(torch.int32), g["edge_counts"].cpu())
     # symmetry of the whole batch: the multiset of (min,max) pairs has every pair exactly twice
     s, d = g["src"].long(), g["dst"].long()
     fwd = torch.sort(s * (1 << 32) + d).values

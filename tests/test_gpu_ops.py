@@ -231,3 +231,52 @@ def test_group_norm_shapes(shape, groups, inds):
         ref = gamma.reshape(C, *[1] * inds) * (xg / torch.sqrt(1e-3 + m2)).reshape(shape)
         got = ops.group_norm(x.cuda(), groups, 1e-3, gamma.cuda(), None, center=False)
     close(got, ref, rel=2e-5)
+
+
+def _golden_radial():
+    import os
+    return torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_golden_radial.pt"),
+                      weights_only=False)
+
+
+def test_older_radial_encodings_against_reference_golden():
+    """radial_encode_edge (archs/diffuser_atoms5.py:25-30) and layers_common.radial_encode (:122-126) on the GPU against
+    the outputs of the reference's own functions and against the oracle on a larger seeded input"""
+    from ld_b200 import layers_common as LC
+    from oracle import reference_math as R
+    g = _golden_radial()
+    with torch.no_grad():
+        close(LC.radial_encode_edge(g["r_vec"].cuda(), 8, 4.0), g["edge_n8_rmax4"], 1e-5)
+        close(LC.radial_encode_edge(g["r_vec"].cuda(), 16, 2.5), g["edge_n16_rmax2p5"], 1e-5)
+        close(LC.radial_encode(g["r_len"].cuda(), 8, 1.0), g["cos_n8"], 1e-5)
+        close(LC.radial_encode(g["r_len"].cuda(), 12, 3.0), g["cos_n12"], 1e-5)
+        gen = torch.Generator().manual_seed(11)
+        r = torch.randn(4, 1000, 3, generator=gen)
+        close(LC.radial_encode_edge(r.cuda(), 12, 3.0), R.radial_encode_edge(r, 12, 3.0), 1e-5)
+        d = torch.rand(7, 333, generator=gen)
+        close(LC.radial_encode(d.cuda(), 10, 1.0), R.radial_encode_cos(d, 10, 1.0), 1e-5)
+        assert LC.radial_encode_edge(torch.zeros(0, 3, device="cuda"), 8, 1.0).shape == (0, 8)
+    # with autograd the torch formulation runs; same values
+    rg = g["r_vec"].cuda().requires_grad_(True)
+    close(LC.radial_encode_edge(rg, 8, 4.0), g["edge_n8_rmax4"], 1e-5)
+
+
+def test_vec_linear_against_reference_golden():
+    """VecLinear (managan/layers_common.py:81-89): the reference's state dict loads, forward and gradients match"""
+    from ld_b200 import layers_common as LC
+    from oracle import reference_math as R
+    g = _golden_radial()
+    vl = LC.VecLinear(24, 40)
+    vl.load_state_dict(g["veclinear_state"])
+    vl.cuda()
+    with torch.no_grad():
+        close(vl(g["veclinear_in"].cuda()), g["veclinear_out"], 1e-5)
+    x = g["veclinear_in"].cuda().requires_grad_(True)
+    y = vl(x)
+    cot = torch.randn(y.shape, generator=torch.Generator().manual_seed(2))
+    gx, gw = torch.autograd.grad(y, (x, vl.W), cot.cuda())
+    xr = g["veclinear_in"].clone().requires_grad_(True)
+    Wr = g["veclinear_state"]["W"].clone().requires_grad_(True)
+    rx, rw = torch.autograd.grad(R.vec_linear(Wr, xr), (xr, Wr), cot)
+    close(gx, rx, 1e-5)
+    close(gw, rw, 1e-5)

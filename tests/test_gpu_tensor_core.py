@@ -190,3 +190,41 @@ def test_linear_component_major_bf16_input_matches_fp32_input(inds, rows, K, N):
     b = ops.linear_bf16_tc(x32, Wp, N, inds=inds)
     assert a.shape == b.shape and torch.equal(a, b)
     assert int(ops.tc_status("cuda").item()) == 0
+
+
+def test_bounded_wait_runs_out_and_returns():
+    """A launch of the tensor-core linear whose weight panels are never requested: every wait gives up after 64 polls,
+    all blocks leave through the failure path (status flag set, tensor memory released, no trap), the host check
+    raises and clears the word, and the next launch on the same device is correct."""
+    from ld_b200 import ops
+    from ld_b200._lib import lib, check, ptr, stream_ptr, HotpathError, LD_ERR_TIMEOUT, LD_FLAG_TIMEOUT
+    torch.cuda.synchronize()
+    ops.check_tc_status("cuda")                       # clean before
+    g = torch.Generator().manual_seed(5)
+    rows, K, N = 200, 128, 64
+    W = torch.randn(N, K, generator=g) / K ** 0.5
+    x = torch.randn(rows, K, generator=g).cuda()
+    wp = ops.pack_weights_bf16(W.cuda())
+    y = torch.full((rows, N), 7.0, device="cuda")
+    status = ops.tc_status("cuda")
+    check(lib().ld_linear_bf16_tc_selftest_timeout(ptr(x), rows, K, ptr(wp), N, ptr(y), ptr(status), stream_ptr(x.device)))
+    torch.cuda.synchronize()                          # the kernel returned by itself
+    assert int(status.item()) & LD_FLAG_TIMEOUT
+    assert torch.all(y == 7.0)                        # nothing was written
+    with pytest.raises(HotpathError) as err:
+        ops.check_tc_status("cuda")
+    assert err.value.status == LD_ERR_TIMEOUT
+    assert int(status.item()) == 0                    # reported once, then cleared
+    # tensor memory was released and the context is intact: the regular launch works, several times over
+    for _ in range(3):
+        got = ops.linear_bf16_tc(x, wp, N)
+    torch.cuda.synchronize()
+    _status_ok()
+    close(got, x.cpu() @ W.t(), 2e-2)
+    # the non-blocking form used inside rollout loops reports a flagged step on a later call
+    check(lib().ld_linear_bf16_tc_selftest_timeout(ptr(x), rows, K, ptr(wp), N, ptr(y), ptr(status), stream_ptr(x.device)))
+    ops.check_tc_status("cuda", block=False)          # requests a copy of the word
+    torch.cuda.synchronize()
+    with pytest.raises(HotpathError):
+        ops.check_tc_status("cuda", block=False)      # the copy has arrived and shows the flag
+    assert int(status.item()) == 0

@@ -159,3 +159,31 @@ def test_proximity_attention(golden):
         grads = torch.autograd.grad((out * p["cotangent"]).sum(), ins)
         for mine, ref in zip(grads, p[kg]):
             assert torch.allclose(mine, ref, rtol=1e-4, atol=1e-4)
+
+
+def _golden_radial():
+    import os
+    return torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_golden_radial.pt"),
+                      weights_only=False)
+
+
+def test_older_radial_encodings_and_vec_linear():
+    """radial_encode_edge (archs/diffuser_atoms5.py), radial_encode and VecLinear (managan/layers_common.py)"""
+    g = _golden_radial()
+    assert torch.allclose(R.radial_encode_edge(g["r_vec"], 8, 4.0), g["edge_n8_rmax4"], **TOL)
+    assert torch.allclose(R.radial_encode_edge(g["r_vec"], 16, 2.5), g["edge_n16_rmax2p5"], **TOL)
+    assert torch.allclose(R.radial_encode_cos(g["r_len"], 8, 1.0), g["cos_n8"], **TOL)
+    assert torch.allclose(R.radial_encode_cos(g["r_len"], 12, 3.0), g["cos_n12"], **TOL)
+    assert torch.allclose(R.vec_linear(g["veclinear_state"]["W"], g["veclinear_in"]), g["veclinear_out"], **TOL)
+
+
+def test_reference_float32_rounding_of_the_polynomial_basis(golden):
+    """The reference evaluates radial_encode_8 as a float32 power sum with coefficients up to 2.7e4; its stored output
+    is therefore a few 1e-4 away from the exact value (basis functions are of size 1). The float64 oracle is the exact
+    value; this pins it to the golden vector within the reference's own rounding, and shows that the float32 oracle
+    (same formulation as the reference) carries an error of the same size."""
+    r = golden["radial"]
+    exact = R.radial_encode_8(r["r"].double(), 4.0)
+    ref_err = (r["jacobi8_r4"].double() - exact).abs().max().item()
+    f32_err = (R.radial_encode_8(r["r"], 4.0).double() - exact).abs().max().item()
+    assert 1e-6 < ref_err < 5e-4 and f32_err < 5e-4
