@@ -136,7 +136,6 @@ bee_scalar_tc_kernel(BtParams P) {
   __shared__ int s_src[BT_EDGES];
   __shared__ int s_rowwin[BT_EDGES + 1];
   __shared__ float s_jac[72];
-  __shared__ float s_head[4][128], s_tail[4][128];   // partial per-node sums of the four row quarters
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool mma_lane = warp == BT_MMA_WARP && lane == 0;
@@ -443,63 +442,20 @@ bee_scalar_tc_kernel(BtParams P) {
         tc::fence_before_sync();
         bt_sync_workers();
         lap(9);
-        // Per-node sums in two steps. (a) Thread (column, row quarter) adds up its 32 rows in edge order: the sum for
-        // the quarter's first node goes to s_head, for its last node (when different) to s_tail, nodes strictly inside
-        // the quarter are complete and written at once. (b) One thread per column joins the four quarters with the sum
-        // carried over from earlier tiles. Every addition happens in a fixed order.
-        {
-          const int col = tid & 127, rq = tid >> 7;
-          const int r_lo = rq * 32, r_hi = min(r_lo + 32, cnt);
-          if (col < A && r_lo < cnt) {
-            const int slot = col >> 2, sub = col & 3;
-            int c_node = s_src[r_lo];
-            float sum = 0.f, head = 0.f;
-            bool first = true;
-            // row e keeps this column at slot (slot & ~7) | ((slot ^ e) & 7); eb is a multiple of 8, so within a group
-            // of eight rows the offsets are loop-invariant
-            const float* sp = stage_f + (size_t)r_lo * A + (slot & ~7) * 4 + sub;
-            const int sx = slot & 7;
-            for (int eb = r_lo; eb < r_hi; eb += 8, sp += 8 * A) {
-              float v[8];
-#pragma unroll
-              for (int i = 0; i < 8; i++) v[i] = sp[i * A + ((sx ^ i) << 2)];   // rows beyond cnt hold zeros
-              const int last = min(eb + 7, r_hi - 1);
-              if (s_src[eb] == c_node && s_src[last] == c_node) {
-                sum += ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
-              } else {
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                  if (eb + i < r_hi) {
-                    const int s = s_src[eb + i];
-                    if (s != c_node) {
-                      if (first) { head = sum; first = false; }
-                      else P.out_a[(size_t)c_node * A + col] = sum * P.scale;
-                      for (int z = c_node + 1; z < s; z++) P.out_a[(size_t)z * A + col] = 0.f;   // nodes without edges
-                      sum = 0.f;
-                      c_node = s;
-                    }
-                    sum += v[i];
-                  }
-                }
-              }
-            }
-            s_head[rq][col] = first ? sum : head;
-            s_tail[rq][col] = first ? 0.f : sum;
-          }
-        }
-        bt_sync_workers();
+        // Per-node sums: one thread per output column adds the rows of the tile in edge order, carrying the sum of the
+        // node that continues from the previous tile. The order of the additions depends on the node's edge list
+        // alone, not on where the tiles of this block happen to start, so the result for a system is bit-identical
+        // whatever batch (or shard of a batch) it is processed in.
         if (tid < A) {
+          const int col = tid, slot = col >> 2, sub = col & 3;
           int c_node = tile_cur;
           float a_sum = acc;
-          for (int q = 0; q < 4 && q * 32 < cnt; q++) {
-            const int f = s_src[q * 32], l = s_src[min(q * 32 + 31, cnt - 1)];
-            if (f != c_node) { flush_until(c_node, f, a_sum); a_sum = 0.f; c_node = f; }
-            a_sum += s_head[q][tid];
-            if (l != f) {
-              P.out_a[(size_t)f * A + tid] = a_sum * P.scale;   // gaps after f were zero-filled by the quarter's thread
-              a_sum = s_tail[q][tid];
-              c_node = l;
-            }
+          const float* sp = stage_f + (slot & ~7) * 4 + sub;
+          const int sx = slot & 7;
+          for (int e = 0; e < cnt; e++) {
+            const int s = s_src[e];
+            if (s != c_node) { flush_until(c_node, s, a_sum); a_sum = 0.f; c_node = s; }
+            a_sum += sp[(size_t)e * A + ((sx ^ (e & 7)) << 2)];
           }
           acc = a_sum;
           cur = c_node;

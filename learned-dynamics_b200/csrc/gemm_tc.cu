@@ -32,6 +32,8 @@ struct GemmParams {
   int out_bf16;              // y is BF16 instead of FP32
   long long y_ld_row, y_ld_col; // BF16 output addressing: element (r, o, s) at r*y_ld_row + o*y_ld_col + s + y_off
   int y_off;
+  int y_s_split;             // BF16 output addressing: components s >= y_s_split are displaced by y_s_jump more elements
+  long long y_s_jump;
   int* status;
   uint32_t wait_limit;       // polls per bounded wait (tc::TC_WAIT_LIMIT in production)
   int selftest_no_weights;   // self-test only: the weight panels are never requested, so the first wait for them runs out
@@ -163,7 +165,8 @@ gemm_tc_kernel(GemmParams P) {
     if (!ok) break;
     tc::fence_after_sync();
     float* yrow = P.y + (ro * N) * S + rs;
-    __nv_bfloat16* yrow16 = reinterpret_cast<__nv_bfloat16*>(P.y) + ro * P.y_ld_row + rs + P.y_off;
+    __nv_bfloat16* yrow16 = reinterpret_cast<__nv_bfloat16*>(P.y) + ro * P.y_ld_row + rs + P.y_off +
+                            (rs >= P.y_s_split ? P.y_s_jump : 0);
     // S == 1 with the plain [rows][N] layout: a thread owns a row, so direct stores would put every 4-byte value
     // of a warp into a different sector; 32-column slices go through shared memory (the operand stages are idle
     // once the accumulators are complete) and leave as 128-byte rows
@@ -251,7 +254,8 @@ extern "C" int ld_pack_weights_bf16(const float* W, long long sw0, long long sw1
 // device int32 that receives LD_FLAG_TIMEOUT if a bounded wait ran out.
 static int linear_tc_launch(const float* x, int in_bf16, long long rows_outer, int K, int S, const void* wp, const float* bias, int N, int act,
                             void* y, int out_bf16, long long ld_row, long long ld_col, int off, int* status_dev, void* stream,
-                            uint32_t wait_limit = tc::TC_WAIT_LIMIT, int selftest_no_weights = 0) {
+                            uint32_t wait_limit = tc::TC_WAIT_LIMIT, int selftest_no_weights = 0, int s_split = 1 << 30,
+                            long long s_jump = 0) {
   if (rows_outer < 0 || K <= 0 || N <= 0 || (S != 1 && S != 3 && S != 9)) return LD_ERR_SHAPE;
   if (N % 32 != 0 || N > 512) { ld_set_last_message("tensor-core linear: N must be a multiple of 32, at most 512"); return LD_ERR_UNSUPPORTED; }
   if (((uintptr_t)wp) % 16 != 0) { ld_set_last_message("tensor-core linear: packed weights must be 16-byte aligned"); return LD_ERR_SHAPE; }
@@ -263,6 +267,7 @@ static int linear_tc_launch(const float* x, int in_bf16, long long rows_outer, i
   GemmParams P;
   P.x = x; P.in_bf16 = in_bf16; P.y = (float*)y; P.out_bf16 = out_bf16; P.y_ld_row = ld_row; P.y_ld_col = ld_col; P.y_off = off; P.wp = (const __nv_bfloat16*)wp; P.bias = bias; P.rows = rows_outer * S; P.K = K; P.N = N; P.S = S;
   P.act = act; P.status = status_dev; P.wait_limit = wait_limit; P.selftest_no_weights = selftest_no_weights;
+  P.y_s_split = s_split; P.y_s_jump = s_jump;
   const size_t smem = 2 * GT_A_STAGE + 2 * (size_t)N * GT_KC * 2 + 1024;
   const bool unit = !in_bf16 && S == 1 && (K & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
   auto kern = unit ? gemm_tc_kernel<true, false> : (in_bf16 ? gemm_tc_kernel<false, true> : gemm_tc_kernel<false, false>);
@@ -298,6 +303,17 @@ extern "C" int ld_linear_bf16_tc_out16(const float* x, long long rows_outer, int
                                        int N, int act, void* y_bf16, long long ld_row, long long ld_col, int off,
                                        int* status_dev, void* stream) {
   return linear_tc_launch(x, 0, rows_outer, K, S, wp, bias, N, act, y_bf16, 1, ld_row, ld_col, off, status_dev, stream);
+}
+
+// ld_linear_bf16_tc_out16 with a two-piece component axis: components s >= s_split land s_jump elements further on.
+// The fused l<=2 message kernel gathers its left operands as two 16-byte halves per (node, channel), laid out
+// [node][half][channel][8] (values l0, l1[3], l2[0..3] | l2[4..8], three zeros): rank 2 goes there with ld_row = 16*N,
+// ld_col = 8, off = 4, s_split = 4, s_jump = 8*N - 8.
+extern "C" int ld_linear_bf16_tc_out16_split(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias,
+                                             int N, int act, void* y_bf16, long long ld_row, long long ld_col, int off,
+                                             int s_split, long long s_jump, int* status_dev, void* stream) {
+  return linear_tc_launch(x, 0, rows_outer, K, S, wp, bias, N, act, y_bf16, 1, ld_row, ld_col, off, status_dev, stream,
+                          tc::TC_WAIT_LIMIT, 0, s_split, s_jump);
 }
 
 // ld_linear_bf16_tc with the activations already stored as BF16, component-major: x_bf16 [rows_outer][S][K] (K

@@ -107,8 +107,10 @@ extern "C" int ld_group_norm(const float* x, int B, int N, int C, int S, int gro
   cudaStream_t st = (cudaStream_t)stream;
   float* stats = (float*)workspace;
   float* part = stats + (size_t)2 * B * groups;
-  // enough blocks to fill the device even for a few large systems: split the nodes of a (system, group) into chunks
-  int nchunks = (148 * 4 + B * groups - 1) / (B * groups);
+  // the nodes of a (system, group) are split into chunks of about 64 so that a few large systems still fill the device.
+  // The split depends on the system size alone, never on the batch: the statistics of a system are then bit-identical
+  // whatever batch it is part of (a batch sharded over several GPUs gives the results of the whole batch on one).
+  int nchunks = (N + 63) / 64;
   if (nchunks > 32) nchunks = 32;
   if (nchunks > N) nchunks = N;
   if (nchunks < 1) nchunks = 1;

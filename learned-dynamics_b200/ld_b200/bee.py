@@ -58,6 +58,23 @@ class MLP(nn.Module):
         return self.lin_direct(x) + self.layers(x)
 
 
+_ROWS_CACHE = {}
+
+
+def _gather_rows_buffer(Nt, chan, device):
+    """[Nt][2][chan][8] BF16 buffer for the neighbour rows of the fused edge kernel, zero-initialised once: three of
+    the sixteen values per (node, channel) are never written and must stay finite (they meet zeros in the MMA).
+    One buffer per (size, device) serves all layers: they use it one after the other on the same stream."""
+    key = (Nt, chan, torch.device(device).index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _ROWS_CACHE.get(key)
+    if buf is None:
+        if len(_ROWS_CACHE) > 8:
+            _ROWS_CACHE.clear()
+        buf = torch.zeros(Nt, 2, chan, 8, dtype=torch.bfloat16, device=device)
+        _ROWS_CACHE[key] = buf
+    return buf
+
+
 class Messages(nn.Module):
     def __init__(self, r0, dim_a, dim_v, dim_d, chan):
         super().__init__()
@@ -76,6 +93,7 @@ class Messages(nn.Module):
         self._packed = None
         self._packed_key = None
         self.precision = "fp32"  # "bf16": scalar channel on the tensor cores (2e-2 relative)
+        self.fused_kernel = True  # bf16, chan = dim_a = 128: one edge kernel per layer (False: the two-kernel path)
 
     def load_state_dict(self, state, *a, **k):
         # the reference wraps mlp_a in torch.compile, which prefixes its keys
@@ -108,11 +126,40 @@ class Messages(nn.Module):
             self._packed_key = key
         return self._packed
 
+    def _forward_fused_tc(self, graph, r_ij, x_a, x_v, x_d):
+        """chan = 128, dim_a = 128 on the tensor cores: three channel mixings that write the neighbour rows in the
+        gather layout, ONE edge kernel (rows gathered once by bulk copies, products by tcgen05, per-edge MLP), and the
+        two hoisted Y maps per node."""
+        batch, nodes = x_a.shape[0], x_a.shape[1]
+        Nt, C, dev = batch * nodes, self.chan, x_a.device
+        w = self._pack()
+        pk = lambda m: m._packed_for(ops)
+        rows = _gather_rows_buffer(Nt, C, dev)
+        ops.linear_bf16_tc(x_a.reshape(Nt, -1), pk(self.L0), C, inds=0, out=rows, out_layout=(16 * C, 8, 0))
+        ops.linear_bf16_tc(x_v.reshape(Nt, -1, 3), pk(self.L1), C, inds=1, out=rows, out_layout=(16 * C, 8, 1))
+        ops.linear_bf16_tc(x_d.reshape(Nt, -1, 3, 3), pk(self.L2), C, inds=2, out=rows, out_layout=(16 * C, 8, 4),
+                           out_split=(4, 8 * C - 8))
+        S_v = torch.empty(Nt, 3, 5 * C, dtype=torch.bfloat16, device=dev)
+        S_d = torch.empty(Nt, 9, 5 * C, dtype=torch.bfloat16, device=dev)
+        B_a = torch.empty(Nt, self.dim_a, dtype=torch.float32, device=dev)
+        with KERNEL_TIMER.region("bee_messages_fused_tc"):
+            check(lib().ld_bee_messages_fused_bf16_tc(ptr(graph.row_ptr), ptr(graph.dst32), ptr(r_ij.contiguous()), Nt, C, self.dim_a,
+                                                      float(self.r0), ptr(rows), ptr(w["enc_w"]), ptr(w["enc_b"]), ptr(w["jac"]),
+                                                      ptr(w["Yp"]), ptr(w["W1p"]), ptr(w["b1"]), ptr(w["W2p"]), ptr(w["b2"]),
+                                                      ptr(w["W3p"]), ptr(w["b3"]), 0.1, ptr(B_a), ptr(S_v), ptr(S_d),
+                                                      ptr(ops.tc_status(dev)), stream_ptr(dev)))
+        B_v = ops.linear_bf16_tc_cm(S_v, w["Yvp"], self.dim_v, 1)
+        B_d = ops.linear_bf16_tc_cm(S_d, w["Ydp"], self.dim_d, 2)
+        return (B_a.reshape(batch, nodes, -1), B_v.reshape(batch, nodes, -1, 3), B_d.reshape(batch, nodes, -1, 3, 3))
+
     def forward(self, graph, r_ij, x_a, x_v, x_d):
         if torch.is_grad_enabled() or not x_a.is_cuda:
             return self._forward_unfused(graph, r_ij, x_a, x_v, x_d)
         batch, nodes = x_a.shape[0], x_a.shape[1]
         Nt, C, dev = batch * nodes, self.chan, x_a.device
+        if (self.precision == "bf16" and self.fused_kernel and C == 128 and self.dim_a == 128 and self.dim_v % 32 == 0
+                and self.dim_d % 32 == 0):
+            return self._forward_fused_tc(graph, r_ij, x_a, x_v, x_d)
         w = self._pack()
         feat16 = self.precision == "bf16" and C % 32 == 0 and C <= 512
         if feat16:

@@ -340,10 +340,11 @@ def pack_weights_bf16(W):
     return out
 
 
-def linear_bf16_tc(x, W_packed, N, bias=None, act=ACT_NONE, inds=0, out_bf16=False, out=None, out_layout=None):
+def linear_bf16_tc(x, W_packed, N, bias=None, act=ACT_NONE, inds=0, out_bf16=False, out=None, out_layout=None, out_split=None):
     """y[..., o, s] = act(sum_i W[o,i] x[..., i, s] + b[o]) on tcgen05 (BF16 operands, FP32 accumulate).
     out_bf16: round the result to BF16. out / out_layout=(ld_row, ld_col, off): write BF16 element (r, o, s)
-    to out.flatten()[r*ld_row + o*ld_col + s + off] instead of a new tensor."""
+    to out.flatten()[r*ld_row + o*ld_col + s + off] instead of a new tensor; out_split=(s_split, s_jump) moves the
+    components s >= s_split another s_jump elements on."""
     x = x.contiguous()
     require_cuda_f32(x, "x")
     S = 3 ** inds
@@ -356,6 +357,11 @@ def linear_bf16_tc(x, W_packed, N, bias=None, act=ACT_NONE, inds=0, out_bf16=Fal
     shape[bd] = N
     st, status = stream_ptr(x.device), ptr(tc_status(x.device))
     with KERNEL_TIMER.region("linear_bf16_tc"):
+        if out is not None and out_split is not None:
+            ld_row, ld_col, off = out_layout
+            check(lib().ld_linear_bf16_tc_out16_split(ptr(x), rows, K, S, ptr(W_packed), ptr(bias), N, act, ptr(out), ld_row,
+                                                      ld_col, off, out_split[0], out_split[1], status, st))
+            return out
         if out is not None:
             ld_row, ld_col, off = out_layout
             check(lib().ld_linear_bf16_tc_out16(ptr(x), rows, K, S, ptr(W_packed), ptr(bias), N, act, ptr(out), ld_row, ld_col,
