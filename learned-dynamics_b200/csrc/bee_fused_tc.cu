@@ -40,8 +40,9 @@ constexpr int BF_EDGES = 128;
 constexpr int BF_C = 128, BF_A = 128;
 constexpr int BF_WORK_WARPS = 16;
 constexpr int BF_WORK_THREADS = BF_WORK_WARPS * 32;
-constexpr int BF_MMA_WARP = 16, BF_WPROD_WARP = 17, BF_GATHER_WARP = 18, BF_BUILD_WARP0 = 19, BF_BUILD_WARPS = 2;
-constexpr int BF_THREADS = (BF_WORK_WARPS + 3 + BF_BUILD_WARPS) * 32;          // 672
+// 20 warps: five per scheduler partition, the most that fit at 96 registers per thread (16384 registers per partition)
+constexpr int BF_MMA_WARP = 16, BF_GATHER_WARP = 17, BF_BUILD_WARP0 = 18, BF_BUILD_WARPS = 2;
+constexpr int BF_THREADS = (BF_WORK_WARPS + 2 + BF_BUILD_WARPS) * 32;          // 640
 constexpr int BF_SYNC_THREADS = (BF_WORK_WARPS + 1) * 32;                      // working warps + MMA warp
 constexpr int BF_PANEL = BF_EDGES * 16 + 16;     // byte stride between 8-column panels of the MLP operand tile (padded)
 constexpr int BF_NG = 8;                         // ring groups (two edges each)
@@ -160,7 +161,7 @@ __device__ __forceinline__ void bf_store_node_g(int g, __nv_bfloat16* S_v, __nv_
   else bf_store_node<3>(S_v, S_d, node, c, acc, scale);
 }
 
-__global__ void __maxnreg__(96)
+__global__ void __launch_bounds__(BF_THREADS, 1)
 bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t bar_full[BF_NG], bar_slot_empty[BF_NG], bar_dfull[2], bar_dempty[2];
@@ -271,7 +272,10 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
     }
   } else if (warp >= BF_BUILD_WARP0) {
     // ===== builders: G_e of every edge (B operand, 64 x 16 BF16, K-major panels) =======================================
+    // The second builder warp also streams the weight slabs of the four layers: its lane 0 does so after the warp's
+    // last G of the tile (the ring belongs to the MLP from then until the last layer has been multiplied).
     const int b = warp - BF_BUILD_WARP0;
+    uint32_t wloads = 0;
     unsigned short tab[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) tab[i] = P.gamma_tab[lane * 4 + i];
@@ -319,38 +323,32 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
           if (lane == 0) tc::mbar_arrive(&bar_full[gs]);
         }
         Gbase += groups;
+        if (b == BF_BUILD_WARPS - 1) {
+          if (lane == 0 && !fail) {
+            // the ring is free for weights once every product MMA of the tile has read its rows
+            if (!tc::mbar_wait(&bar_weights_go, tiles & 1, wl)) fail = 1;
+            for (int l = 0; l < BF_LAYERS && !fail; l++) {
+              const BfLayer& L = P.layer[l];
+              for (int ks = 0; ks < L.ksteps; ks += L.slab_ksteps, wloads++) {
+                const uint32_t st = wloads % BF_WSTAGES, use = wloads / BF_WSTAGES;
+                const uint32_t bytes = (uint32_t)min(L.slab_ksteps, L.ksteps - ks) * L.N * 32;
+                // a slab slot is free when the MMAs that read its previous content are done
+                if (use >= 1 && !tc::mbar_wait(&bar_wempty[st], (use - 1) & 1, wl)) { fail = 1; break; }
+                if (s_fail) { fail = 1; break; }
+                tc::mbar_expect_tx(&bar_wfull[st], bytes);
+                tc::bulk_g2s(ring + (size_t)st * BF_SLAB_BYTES, L.w + (size_t)ks * L.N * 16, bytes, &bar_wfull[st]);
+              }
+            }
+            if (fail) {   // let slabs in flight land (bounded)
+              for (uint32_t i = wloads > BF_WSTAGES ? wloads - BF_WSTAGES : 0; i < wloads; i++)
+                tc::mbar_wait(&bar_wfull[i % BF_WSTAGES], (i / BF_WSTAGES) & 1, wl);
+            }
+          }
+          fail = __shfl_sync(0xffffffffu, fail, 0);
+        }
       }
     }
     if (fail) s_fail = 1;
-  } else if (warp == BF_WPROD_WARP) {
-    // ===== weight slabs of the four layers, once the products of the tile are done with the ring ===================
-    if (lane == 0) {
-      uint32_t loads = 0, tiles = 0;
-      for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
-        const long long ntiles = bf_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt)).ntiles;
-        for (long long t = 0; t < ntiles && !fail; t++, tiles++) {
-          if (!tc::mbar_wait(&bar_weights_go, tiles & 1, wl)) { fail = 1; break; }
-          for (int l = 0; l < BF_LAYERS && !fail; l++) {
-            const BfLayer& L = P.layer[l];
-            for (int ks = 0; ks < L.ksteps; ks += L.slab_ksteps, loads++) {
-              const uint32_t st = loads % BF_WSTAGES, use = loads / BF_WSTAGES;
-              const uint32_t bytes = (uint32_t)min(L.slab_ksteps, L.ksteps - ks) * L.N * 32;
-              // a slab slot is free when the MMAs that read its previous content are done; the first slabs of a tile
-              // are free by bar_weights_go (all weight MMAs of the previous tile were waited for by then)
-              if (use >= 1 && !tc::mbar_wait(&bar_wempty[st], (use - 1) & 1, wl)) { fail = 1; break; }
-              if (s_fail) { fail = 1; break; }
-              tc::mbar_expect_tx(&bar_wfull[st], bytes);
-              tc::bulk_g2s(ring + (size_t)st * BF_SLAB_BYTES, L.w + (size_t)ks * L.N * 16, bytes, &bar_wfull[st]);
-            }
-          }
-        }
-      }
-      if (fail) {
-        s_fail = 1;
-        for (uint32_t i = loads > BF_WSTAGES ? loads - BF_WSTAGES : 0; i < loads; i++)
-          tc::mbar_wait(&bar_wfull[i % BF_WSTAGES], (i / BF_WSTAGES) & 1, wl);
-      }
-    }
   } else if (warp == BF_MMA_WARP) {
     // ===== MMA issue ===========================================================================================
     const bool mma_lane = lane == 0;
