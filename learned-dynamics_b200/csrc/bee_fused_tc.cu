@@ -28,7 +28,7 @@
 //
 // Shared memory: operand tile 97 KB | 96 KB ring, used as eight two-edge groups (two rows + two G matrices, 12 KB) while
 // the products are formed and as three 32 KB weight slabs while the MLP runs | small operands. Tensor memory: columns
-// [0, 256) two D groups (two edges each), later the MLP accumulators; [256, 384) pa.
+// [0, 384) three D groups (two edges each), the first 256 later the MLP accumulators; [384, 512) pa.
 // Every wait is bounded; a wait that runs out sets LD_FLAG_TIMEOUT and all roles leave.
 #include "common.cuh"
 #include "tc05.cuh"
@@ -60,7 +60,8 @@ constexpr int BF_OFF_W9 = BF_OFF_RING + BF_RING_BYTES;                         /
 constexpr int BF_OFF_ENC = BF_OFF_W9 + 4 * BF_C * 16;                          // radial operand: 128 edges x 32
 constexpr int BF_OFF_BIAS = BF_OFF_ENC + 4 * BF_EDGES * 16;
 constexpr int BF_SMEM = BF_OFF_BIAS + 5 * BF_A * 4;
-constexpr uint32_t BF_TMEM_COLS = 512, BF_TMEM_PA = 256;
+constexpr int BF_ND = 3;                         // D groups in tensor memory (two edges x 64 columns each)
+constexpr uint32_t BF_TMEM_COLS = 512, BF_TMEM_PA = BF_ND * 128;
 constexpr int BF_GAMMA_ENTRIES = 128;            // 115 used
 
 struct BfLayer {
@@ -80,7 +81,26 @@ struct BfParams {
   float* out_a; __nv_bfloat16* S_v; __nv_bfloat16* S_d;
   int* status;
   uint32_t wait_limit;
+  int spin;                      // waits on the per-group barriers poll instead of suspending
+  long long* prof;               // diagnostics build only
   unsigned short gamma_tab[BF_GAMMA_ENTRIES];   // bits 0-10 byte offset inside G_e, 11-14 monomial, 15 sign; 0xffff unused
+};
+
+// Diagnostics build (-DLD_PHASE_COUNTERS): cycles per phase of one thread per role, added into prof[16]:
+// working thread 0: 0 geometry, 1 wait pa, 2 wait D, 3 products, 4 barrier after products, 5 wait layers, 6 epilogues,
+// 7 scalar sums, 8 end-of-tile barriers; MMA lane: 9 wait rows + G, 10 wait D free, 11 wait weights; builder 0:
+// 12 wait free group, 13 build; gather lane 0: 14 wait free group; builder 1 lane 0: 15 weight streaming.
+struct BfProf {
+#ifdef LD_PHASE_COUNTERS
+  long long t; long long* prof; bool on;
+  __device__ __forceinline__ void start(long long* p, bool enable) { prof = p; on = enable && p != nullptr; t = clock64(); }
+  __device__ __forceinline__ void lap(int slot) {   // slot >= 32: restart the clock without recording
+    if (on) { const long long n = clock64(); if (slot < 32) atomicAdd((unsigned long long*)&prof[slot], (unsigned long long)(n - t)); t = n; }
+  }
+#else
+  __device__ __forceinline__ void start(long long*, bool) {}
+  __device__ __forceinline__ void lap(int) {}
+#endif
 };
 
 struct BfRange { int n_begin, n_end; long long e_begin, e_end, ntiles; };
@@ -153,18 +173,35 @@ __device__ __forceinline__ void bf_store_node(__nv_bfloat16* __restrict__ S_v, _
   }
 }
 
-__device__ __forceinline__ void bf_store_node_g(int g, __nv_bfloat16* S_v, __nv_bfloat16* S_d, int node, int c, const float* acc,
-                                                float scale) {
-  if (g == 0) bf_store_node<0>(S_v, S_d, node, c, acc, scale);
-  else if (g == 1) bf_store_node<1>(S_v, S_d, node, c, acc, scale);
-  else if (g == 2) bf_store_node<2>(S_v, S_d, node, c, acc, scale);
-  else bf_store_node<3>(S_v, S_d, node, c, acc, scale);
+// End of a node's edge list for one thread (channel c, column group g): write its sixteen running sums for `node`, then
+// zeros for the nodes without edges up to `next` (exclusive). One copy of this code, called from the few places where
+// a node can end; the sums travel by value so that they stay in registers at the call sites.
+__device__ __noinline__ void bf_flush_node(int g, __nv_bfloat16* S_v, __nv_bfloat16* S_d, int node, int next, int c, float scale,
+                                           float a0, float a1, float a2, float a3, float a4, float a5, float a6, float a7,
+                                           float a8, float a9, float a10, float a11, float a12, float a13, float a14, float a15) {
+  float acc[16] = {a0, a1, a2, a3, a4, a5, a6, a7, a8, a9, a10, a11, a12, a13, a14, a15};
+  for (int v = node; v < next; v++) {
+    if (g == 0) bf_store_node<0>(S_v, S_d, v, c, acc, scale);
+    else if (g == 1) bf_store_node<1>(S_v, S_d, v, c, acc, scale);
+    else if (g == 2) bf_store_node<2>(S_v, S_d, v, c, acc, scale);
+    else bf_store_node<3>(S_v, S_d, v, c, acc, scale);
+    if (v == node) {
+#pragma unroll
+      for (int i = 0; i < 16; i++) acc[i] = 0.f;
+    }
+  }
 }
+#define BF_FLUSH(node, next)                                                                                              \
+  do {                                                                                                                    \
+    bf_flush_node(g, P.S_v, P.S_d, (node), (next), ch, P.scale, acc[0], acc[1], acc[2], acc[3], acc[4], acc[5], acc[6],  \
+                  acc[7], acc[8], acc[9], acc[10], acc[11], acc[12], acc[13], acc[14], acc[15]);                          \
+    _Pragma("unroll") for (int i_ = 0; i_ < 16; i_++) acc[i_] = 0.f;                                                      \
+  } while (0)
 
 __global__ void __launch_bounds__(BF_THREADS, 1)
 bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t bar_full[BF_NG], bar_slot_empty[BF_NG], bar_dfull[2], bar_dempty[2];
+  __shared__ __align__(8) uint64_t bar_full[BF_NG], bar_slot_empty[BF_NG], bar_dfull[BF_ND], bar_dempty[BF_ND];
   __shared__ __align__(8) uint64_t bar_pa, bar_geom, bar_gather_go, bar_weights_go;
   __shared__ __align__(8) uint64_t bar_wfull[BF_WSTAGES], bar_wempty[BF_WSTAGES], bar_accum;
   __shared__ uint32_t tmem_slot;
@@ -181,8 +218,14 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
   unsigned char* enc_smem = smem + BF_OFF_ENC;
   float* s_bias = reinterpret_cast<float*>(smem + BF_OFF_BIAS);   // [b1 (2A) | b2 (2A) | b3 (A)]
   const uint32_t wl = P.wait_limit;
+  // the per-group barriers (64 groups per tile) complete within a few hundred cycles
+  auto hot_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+    if (P.spin == 2) return tc::mbar_wait_tight(bar, parity, wl << 6);
+    return P.spin ? tc::mbar_wait_spin(bar, parity, wl << 4) : tc::mbar_wait(bar, parity, wl);
+  };
+  BfProf pf;
 
-  for (int i = tid; i < 72; i += BF_THREADS) s_jac[i] = P.jacobi[i];
+  if (tid < 8) ld_poly8_to_chebyshev(P.jacobi + tid * 9, s_jac + tid * 9);   // Chebyshev form of the radial polynomials
   for (int i = tid; i < 2 * BF_A; i += BF_THREADS) { s_bias[i] = P.b1[i]; s_bias[2 * BF_A + i] = P.b2[i]; }
   for (int i = tid; i < BF_A; i += BF_THREADS) s_bias[4 * BF_A + i] = P.b3[i];
   if (tid < BF_C) {
@@ -211,7 +254,7 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
   }
   if (tid == 0) {
     for (int s = 0; s < BF_NG; s++) { tc::mbar_init(&bar_full[s], 2); tc::mbar_init(&bar_slot_empty[s], 1); }
-    for (int s = 0; s < 2; s++) { tc::mbar_init(&bar_dfull[s], 1); tc::mbar_init(&bar_dempty[s], BF_WORK_WARPS); }
+    for (int s = 0; s < BF_ND; s++) { tc::mbar_init(&bar_dfull[s], 1); tc::mbar_init(&bar_dempty[s], BF_WORK_WARPS); }
     tc::mbar_init(&bar_pa, 1); tc::mbar_init(&bar_geom, 1); tc::mbar_init(&bar_gather_go, 1); tc::mbar_init(&bar_weights_go, 1);
     for (int s = 0; s < BF_WSTAGES; s++) { tc::mbar_init(&bar_wfull[s], 1); tc::mbar_init(&bar_wempty[s], 1); }
     tc::mbar_init(&bar_accum, 1);
@@ -237,6 +280,7 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
       uint32_t tiles = 0;
       bool issued = false;
       uint32_t last_use = 0;
+      pf.start(P.prof, lane == 0 && blockIdx.x == 0);
       for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
         const BfRange br = bf_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt));
         for (long long e0 = br.e_begin; e0 < br.e_end && !fail; e0 += BF_EDGES, tiles++) {
@@ -254,7 +298,9 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
             const int j = __ldg(P.dst + e0 + e);
             int ok = 1;
             if (u == 0) {
-              if (use >= 1 && !tc::mbar_wait(&bar_slot_empty[k], (use - 1) & 1, wl)) ok = 0;
+              pf.lap(100);
+              if (use >= 1 && !hot_wait(&bar_slot_empty[k], (use - 1) & 1)) ok = 0;
+              pf.lap(14);
               if (ok) tc::mbar_expect_tx(&bar_full[k], 2 * BF_ROW_BYTES);
             }
             ok = __all_sync(pair_mask, ok);
@@ -281,6 +327,7 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
     for (int i = 0; i < 4; i++) tab[i] = P.gamma_tab[lane * 4 + i];
     long long Gbase = 0;
     uint32_t tiles = 0;
+    pf.start(P.prof, lane == 0 && blockIdx.x == 0);
     for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
       const BfRange br = bf_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt));
       for (long long e0 = br.e_begin; e0 < br.e_end && !fail; e0 += BF_EDGES, tiles++) {
@@ -302,7 +349,9 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
           const long long Gg = Gbase + grp;
           const int gs = (int)(Gg % BF_NG);
           const uint32_t use = (uint32_t)(Gg / BF_NG);
-          if (use >= 1 && !tc::mbar_wait(&bar_slot_empty[gs], (use - 1) & 1, wl)) { fail = 1; break; }
+          if (b == 0) pf.lap(100);
+          if (use >= 1 && !hot_wait(&bar_slot_empty[gs], (use - 1) & 1)) { fail = 1; break; }
+          if (b == 0) pf.lap(12);
           if (s_fail) { fail = 1; break; }
 #pragma unroll
           for (int u = 0; u < 2; u++) {
@@ -321,9 +370,11 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
           tc::fence_async_smem();
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(&bar_full[gs]);
+          if (b == 0) pf.lap(13);
         }
         Gbase += groups;
         if (b == BF_BUILD_WARPS - 1) {
+          pf.lap(100);
           if (lane == 0 && !fail) {
             // the ring is free for weights once every product MMA of the tile has read its rows
             if (!tc::mbar_wait(&bar_weights_go, tiles & 1, wl)) fail = 1;
@@ -344,6 +395,7 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
                 tc::mbar_wait(&bar_wfull[i % BF_WSTAGES], (i / BF_WSTAGES) & 1, wl);
             }
           }
+          pf.lap(15);
           fail = __shfl_sync(0xffffffffu, fail, 0);
         }
       }
@@ -358,6 +410,7 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
     const uint64_t row_desc0 = tc::smem_desc(ring_base, BF_C * 16, 128);
     const uint64_t gam_desc0 = tc::smem_desc(ring_base + 2 * BF_ROW_BYTES, 64 * 16, 128);
     const uint32_t idesc_d = tc::idesc_bf16(BF_C, 64), idesc_pa = tc::idesc_bf16(BF_C, BF_EDGES);
+    pf.start(P.prof, lane == 0 && blockIdx.x == 0);
     for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
       const BfRange br = bf_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt));
       for (long long e0 = br.e_begin; e0 < br.e_end; e0 += BF_EDGES, tiles++) {
@@ -373,9 +426,12 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
           tc::mma_commit(&bar_pa);
           for (int grp = 0; grp < groups; grp++, G++) {
             const int gs = (int)(G % BF_NG);
-            const uint32_t use = (uint32_t)(G / BF_NG), d = (uint32_t)(G & 1), duse = (uint32_t)(G >> 1);
-            if (!tc::mbar_wait(&bar_full[gs], use & 1, wl)) { fail = 1; break; }
-            if (duse >= 1 && !tc::mbar_wait(&bar_dempty[d], (duse - 1) & 1, wl)) { fail = 1; break; }
+            const uint32_t use = (uint32_t)(G / BF_NG), d = (uint32_t)(G % BF_ND), duse = (uint32_t)(G / BF_ND);
+            pf.lap(100);
+            if (!hot_wait(&bar_full[gs], use & 1)) { fail = 1; break; }
+            pf.lap(9);
+            if (duse >= 1 && !hot_wait(&bar_dempty[d], (duse - 1) & 1)) { fail = 1; break; }
+            pf.lap(10);
             tc::fence_after_sync();
             const uint64_t goff = (uint64_t)((gs * BF_GROUP_BYTES) >> 4);
             tc::mma_bf16(tmem_base + d * 128, row_desc0 + goff, gam_desc0 + goff, idesc_d, 0u);
@@ -401,7 +457,9 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
             uint32_t accumulate = 0u;
             for (int ks0 = 0; ks0 < l_ksteps; ks0 += l_slab, wmmas++) {
               const uint32_t st = wmmas % BF_WSTAGES, use = wmmas / BF_WSTAGES;
+              pf.lap(100);
               if (!tc::mbar_wait(&bar_wfull[st], use & 1, wl)) { fail = 1; break; }
+              pf.lap(11);
               tc::fence_after_sync();
               uint64_t bd = tc::smem_desc(ring_base + st * BF_SLAB_BYTES, l_N * 16, 128);
               const int nk = min(l_slab, l_ksteps - ks0);
@@ -436,6 +494,7 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
     const uint32_t tmem_row = tmem_base + ((uint32_t)(q * 32) << 16);
     uint32_t accum_phase = 0, tiles = 0;
     long long G = 0;
+    pf.start(P.prof, tid == 0 && blockIdx.x == 0);
     for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
       const BfRange br = bf_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt));
       const int n_begin = br.n_begin, n_end = br.n_end;
@@ -473,7 +532,7 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
             const long long e = e0 + tid;
             const float d = sqrtf(gx * gx + gy * gy + gz * gz);
             const float zz = d / P.r0;
-            ld_radial_poly8(zz, fmaxf(1.f - zz, 0.f), s_jac, enc);
+            ld_radial_cheb8(zz, fmaxf(1.f - zz, 0.f), s_jac, enc);
             enc[8] = 1.f;   // multiplies lin_enc's bias
             const float sc = 7.f / P.r0;
             const float ux = gx * sc, uy = gy * sc, uz = gz * sc;
@@ -515,57 +574,55 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
         tc::fence_before_sync();
         if (bf_sync_or(fail)) { fail = 1; break; }                                        // [B1]
         if (tid == 0) tc::mbar_arrive(&bar_geom);       // builders may read the monomials of this tile
+        pf.lap(0);
         // ---- 2. products: D_e from tensor memory, times pa, into the running sums / the operand tile -------------
         if (!tc::mbar_wait(&bar_pa, tiles & 1, wl)) fail = 1;
         tc::fence_after_sync();
-        for (int oct = 0; oct * 4 < groups && !fail; oct++) {
-          float pa[8];
-          tc::tmem_ld8(tmem_row + BF_TMEM_PA + oct * 8, pa);
-#pragma unroll
-          for (int gi = 0; gi < 4; gi++) {
-            const int grp = oct * 4 + gi;
-            if (grp >= groups) break;
-            const uint32_t d = (uint32_t)(G & 1), duse = (uint32_t)(G >> 1);
-            G++;
-            if (!tc::mbar_wait(&bar_dfull[d], duse & 1, wl)) { fail = 1; break; }
-            tc::fence_after_sync();
-            float v[32];
-            tc::tmem_ld16x2(tmem_row + d * 128 + g * 16, tmem_row + d * 128 + 64 + g * 16, v);
-            tc::fence_before_sync();
-            __syncwarp();
-            if (lane == 0) tc::mbar_arrive(&bar_dempty[d]);   // this warp has its copy: the group may be overwritten
-#pragma unroll
-            for (int u = 0; u < 2; u++) {
-              const int e = 2 * grp + u;
-              if (e < cnt) {
-                const int s = s_src[e];
-                if (s != cur) {
-                  bf_store_node_g(g, P.S_v, P.S_d, cur, ch, acc, P.scale);
-#pragma unroll
-                  for (int i = 0; i < 16; i++) acc[i] = 0.f;
-                  for (int z = cur + 1; z < s; z++) bf_store_node_g(g, P.S_v, P.S_d, z, ch, acc, P.scale);   // nodes without edges
-                  cur = s;
-                }
-                const float p = pa[2 * gi + u];
-                if (g == 0) {
-                  // columns 0..2 are the scalar products y000, y110, y220 of this (edge, channel)
-                  unsigned short* arow = reinterpret_cast<unsigned short*>(a_smem + (size_t)e * 16) + (ch & 7);
-                  arow[(ch >> 3) * (BF_PANEL / 2)] = bf_bf16(p * v[u * 16]);
-                  arow[((BF_C + ch) >> 3) * (BF_PANEL / 2)] = bf_bf16(p * v[u * 16 + 1]);
-                  arow[((2 * BF_C + ch) >> 3) * (BF_PANEL / 2)] = bf_bf16(p * v[u * 16 + 2]);
-#pragma unroll
-                  for (int i = 3; i < 16; i++) acc[i] = fmaf(p, v[u * 16 + i], acc[i]);
-                } else {
-#pragma unroll
-                  for (int i = 0; i < 16; i++) acc[i] = fmaf(p, v[u * 16 + i], acc[i]);
-                }
-              }
+        pf.lap(1);
+#pragma unroll 1
+        for (int grp = 0; grp < groups && !fail; grp++) {
+          const uint32_t d = (uint32_t)(G % BF_ND), duse = (uint32_t)(G / BF_ND);
+          G++;
+          pf.lap(3);
+          if (!hot_wait(&bar_dfull[d], duse & 1)) { fail = 1; break; }
+          pf.lap(2);
+          tc::fence_after_sync();
+          float v[32], pa[2];
+          tc::tmem_ld16x2_2(tmem_row + d * 128 + g * 16, tmem_row + d * 128 + 64 + g * 16, tmem_row + BF_TMEM_PA + 2 * grp, v, pa);
+          pf.lap(16);
+          tc::fence_before_sync();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(&bar_dempty[d]);   // this warp has its copy: the group may be overwritten
+          pf.lap(17);
+          const int e = 2 * grp;
+          const bool two = e + 1 < cnt;
+          const int s0 = s_src[e], s1 = s_src[two ? e + 1 : e];
+          if (s0 != cur) { BF_FLUSH(cur, s0); cur = s0; }
+          if (g == 0) {
+            // columns 0..2 are the scalar products y000, y110, y220 of this (edge, channel)
+            unsigned short* arow = reinterpret_cast<unsigned short*>(a_smem + (size_t)e * 16) + (ch & 7);
+            arow[(ch >> 3) * (BF_PANEL / 2)] = bf_bf16(pa[0] * v[0]);
+            arow[((BF_C + ch) >> 3) * (BF_PANEL / 2)] = bf_bf16(pa[0] * v[1]);
+            arow[((2 * BF_C + ch) >> 3) * (BF_PANEL / 2)] = bf_bf16(pa[0] * v[2]);
+            if (two) {
+              arow[(ch >> 3) * (BF_PANEL / 2) + 8] = bf_bf16(pa[1] * v[16]);
+              arow[((BF_C + ch) >> 3) * (BF_PANEL / 2) + 8] = bf_bf16(pa[1] * v[17]);
+              arow[((2 * BF_C + ch) >> 3) * (BF_PANEL / 2) + 8] = bf_bf16(pa[1] * v[18]);
             }
           }
+#pragma unroll
+          for (int i = 0; i < 16; i++) acc[i] = fmaf(pa[0], v[i], acc[i]);   // (group 0: sums 0..2 are never stored)
+          if (two) {
+            if (s1 != cur) { BF_FLUSH(cur, s1); cur = s1; }
+#pragma unroll
+            for (int i = 0; i < 16; i++) acc[i] = fmaf(pa[1], v[16 + i], acc[i]);
+          }
         }
+        pf.lap(3);
         tc::fence_async_smem();
         tc::fence_before_sync();
         if (bf_sync_or(fail)) { fail = 1; break; }                                        // [B2]
+        pf.lap(4);
         // ---- 3. four layers ------------------------------------------------------------------------------------
         for (int l = 0; l < BF_LAYERS; l++) {
           {
@@ -576,6 +633,7 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
           }
           accum_phase++;
           tc::fence_after_sync();
+          pf.lap(5);
           const int N = P.layer[l].N;
           if (!fail && l < BF_LAYERS - 1) {
             // bias, activation -> BF16 into the operand tile at out_col (this thread: edge `row`, its quarter of the columns)
@@ -609,6 +667,7 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
           }
           tc::fence_before_sync();
           if (bf_sync_or(fail)) { fail = 1; break; }                                      // [B3..B6]
+          pf.lap(6);
         }
         if (fail) break;
         // ---- 4. per-node sums of the scalar output: tensor memory holds [channel][edge] after the transposed last
@@ -618,7 +677,9 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
           const float b3 = s_bias[4 * BF_A + ch];
           for (int cb = 0; cb < cnt; cb += 32) {
             float v[32];
+            pf.lap(7);
             tc::tmem_ld32(tmem_row + cb, v);
+            pf.lap(18);
 #pragma unroll
             for (int i = 0; i < 32; i++) {
               const int e = cb + i;
@@ -636,18 +697,17 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
           }
         }
         node_lo = s_src[cnt - 1];
+        pf.lap(7);
         tc::fence_before_sync();
         if (bf_sync_or(fail)) { fail = 1; break; }                                        // [B7]
         if (tid <= BF_EDGES) s_rowwin[tid] = P.row_ptr[min(node_lo + tid, n_end)];
         // (s_rowwin is read by the geometry of the next tile, after which [B1] orders it against the next refresh)
         asm volatile("barrier.cta.sync 2, %0;" ::"n"(BF_WORK_THREADS) : "memory");
+        pf.lap(8);
       }
       if (!fail && n_begin < n_end) {
         // last node of the slice, then nodes without edges up to its end
-        bf_store_node_g(g, P.S_v, P.S_d, cur, ch, acc, P.scale);
-#pragma unroll
-        for (int i = 0; i < 16; i++) acc[i] = 0.f;
-        for (int z = cur + 1; z < n_end; z++) bf_store_node_g(g, P.S_v, P.S_d, z, ch, acc, P.scale);
+        BF_FLUSH(cur, n_end);
         if (g == 0) {
           P.out_a[(size_t)cur_a * BF_A + ch] = acc_a * P.scale;
           for (int z = cur_a + 1; z < n_end; z++) P.out_a[(size_t)z * BF_A + ch] = 0.f;
@@ -713,6 +773,12 @@ extern "C" int ld_bee_gamma_table(int* out) {
   return n;
 }
 
+extern "C" int ld_bee_messages_fused_bf16_tc_opt(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, int dim_a,
+                                                 float r0, const void* rows, const float* enc_w, const float* enc_b,
+                                                 const float* jacobi, const void* Yp, const void* W1p, const float* b1,
+                                                 const void* W2p, const float* b2, const void* W3p, const float* b3, float scale,
+                                                 float* out_a, void* S_v, void* S_d, int* status_dev, void* stream, int spin);
+
 // Whole message layer for chan = 128, dim_a = 128 (BF16 tensor-core path, 2e-2 relative):
 //   rows    [Nt][2][128][8] BF16: per node and channel (l0, l1[3], l2[0..3] | l2[4..8], 0, 0, 0), written by
 //           ld_linear_bf16_tc_out16 / _out16_split; the three unused values must be zero (or any finite number)
@@ -724,6 +790,20 @@ extern "C" int ld_bee_messages_fused_bf16_tc(const int* row_ptr, const int* dst,
                                              const float* jacobi, const void* Yp, const void* W1p, const float* b1,
                                              const void* W2p, const float* b2, const void* W3p, const float* b3, float scale,
                                              float* out_a, void* S_v, void* S_d, int* status_dev, void* stream) {
+  return ld_bee_messages_fused_bf16_tc_opt(row_ptr, dst, rij, Nt, chan, dim_a, r0, rows, enc_w, enc_b, jacobi, Yp, W1p, b1, W2p, b2,
+                                           W3p, b3, scale, out_a, S_v, S_d, status_dev, stream, 0);
+}
+
+#ifdef LD_PHASE_COUNTERS
+long long* ld_internal_phase_counters();
+#endif
+
+// `spin`: 1 = the waits on the per-group barriers poll (default), 0 = they suspend with a time hint
+extern "C" int ld_bee_messages_fused_bf16_tc_opt(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, int dim_a,
+                                                 float r0, const void* rows, const float* enc_w, const float* enc_b,
+                                                 const float* jacobi, const void* Yp, const void* W1p, const float* b1,
+                                                 const void* W2p, const float* b2, const void* W3p, const float* b3, float scale,
+                                                 float* out_a, void* S_v, void* S_d, int* status_dev, void* stream, int spin) {
   if (Nt < 0 || !(r0 > 0.f)) return LD_ERR_SHAPE;
   if (chan != BF_C || dim_a != BF_A) {
     ld_set_last_message("fused l<=2 message kernel: built for chan = 128 and dim_a = 128 (other widths: the two-kernel path)");
@@ -748,6 +828,12 @@ extern "C" int ld_bee_messages_fused_bf16_tc(const int* row_ptr, const int* dst,
   }
   Q.out_a = out_a; Q.S_v = (__nv_bfloat16*)S_v; Q.S_d = (__nv_bfloat16*)S_d; Q.status = status_dev;
   Q.wait_limit = tc::TC_WAIT_LIMIT;
+  Q.spin = spin;
+#ifdef LD_PHASE_COUNTERS
+  Q.prof = ld_internal_phase_counters();
+#else
+  Q.prof = nullptr;
+#endif
   {
     GammaEntry ent[BF_GAMMA_ENTRIES];
     const int n = build_gamma_entries(ent);

@@ -68,7 +68,7 @@ __device__ __forceinline__ void edge_geometry(const float* __restrict__ rij, lon
   const float d = sqrtf(x * x + y * y + z * z);
   const float zz = d / r0;
   const float env = fmaxf(1.f - zz, 0.f);
-  ld_radial_poly8(zz, env, jac, g->enc);
+  ld_radial_cheb8(zz, env, jac, g->enc);
   const float s = 7.f / r0;
   const float ux = x * s, uy = y * s, uz = z * s;
   const float inv = 1.0f / sqrtf(1.f + ux * ux + uy * uy + uz * uz);
@@ -103,7 +103,7 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
   __shared__ EdgeGeom s_geom[BV_TILE];
   __shared__ int s_dst[BV_TILE];
   __shared__ float s_jac[72];
-  for (int i = threadIdx.x; i < 72; i += blockDim.x) s_jac[i] = P.jacobi[i];
+  if (threadIdx.x < 8) ld_poly8_to_chebyshev(P.jacobi + threadIdx.x * 9, s_jac + threadIdx.x * 9);   // Chebyshev form of the radial polynomials
   __syncthreads();
   const int C = P.chan;
   // all blocks walk the node range segment by segment, so that the neighbour rows a segment gathers (its nodes'
@@ -271,7 +271,7 @@ bee_scalar_kernel(BeeScalarParams P) {
   float* bufB = bufA + (size_t)2 * A * MT_ROWS;        // [2A][32]
   float* wstage = bufB + (size_t)2 * A * MT_ROWS;      // 2 x 16 x 2A
   const int ldo = A + 1;
-  for (int i = tid; i < 72; i += MT_THREADS) s_jac[i] = P.g.jacobi[i];
+  if (tid < 8) ld_poly8_to_chebyshev(P.g.jacobi + tid * 9, s_jac + tid * 9);   // Chebyshev form of the radial polynomials
   int n_begin, n_end;
   bm_block_range(P.g.row_ptr, 0, P.g.Nt, &n_begin, &n_end);
   if (n_begin >= n_end) return;

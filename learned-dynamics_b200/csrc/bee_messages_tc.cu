@@ -113,7 +113,7 @@ __device__ __forceinline__ void bt_geometry(float x, float y, float z, float r0,
   const float d = sqrtf(x * x + y * y + z * z);
   const float zz = d / r0;
   const float env = fmaxf(1.f - zz, 0.f);
-  ld_radial_poly8(zz, env, jac, g->enc);
+  ld_radial_cheb8(zz, env, jac, g->enc);
   const float s = 7.f / r0;
   const float ux = x * s, uy = y * s, uz = z * s;
   const float inv = rsqrtf(1.f + ux * ux + uy * uy + uz * uz);
@@ -149,7 +149,7 @@ bee_scalar_tc_kernel(BtParams P) {
   float* stage_f = reinterpret_cast<float*>(smem);                // [128][A] FP32
   const uint32_t slab = P.slab_bytes;
 
-  for (int i = tid; i < 72; i += BT_THREADS) s_jac[i] = P.jacobi[i];
+  if (tid < 8) ld_poly8_to_chebyshev(P.jacobi + tid * 9, s_jac + tid * 9);   // Chebyshev form of the radial polynomials
   for (int i = tid; i < 2 * A; i += BT_THREADS) { s_bias[i] = P.layer[1].bias[i]; s_bias[2 * A + i] = P.layer[2].bias[i]; }
   for (int i = tid; i < A; i += BT_THREADS) s_bias[4 * A + i] = P.layer[3].bias[i];
   if (tid == 0) {

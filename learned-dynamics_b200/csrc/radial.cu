@@ -14,6 +14,11 @@ namespace {
 
 __global__ void radial_encode_kernel(int kind, const float* __restrict__ r, long long rows, int n, float rmax,
                                      float pi_over_rmax, const float* __restrict__ coeff, float* __restrict__ out) {
+  __shared__ float s_cheb[72];
+  if (kind == 4) {
+    if (threadIdx.x < 8) ld_poly8_to_chebyshev(coeff + threadIdx.x * 9, s_cheb + threadIdx.x * 9);
+    __syncthreads();
+  }
   const long long total = rows * n;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long row = i / n;
@@ -31,9 +36,11 @@ __global__ void radial_encode_kernel(int kind, const float* __restrict__ r, long
         v = cosf(npi * sqrtf(xs)) * fmaxf(1.f - xs, 0.f);
       } else if (kind == 4) {
         const float zz = sqrtf(sq) / rmax;
-        double a = (double)coeff[m * 9 + 8];
-        for (int p = 7; p >= 0; p--) a = fma(a, (double)zz, (double)coeff[m * 9 + p]);
-        v = (float)(a * (double)fmaxf(1.f - zz, 0.f));
+        const float t = 2.f * zz - 1.f, t2 = 2.f * t;
+        const float* c = s_cheb + m * 9;
+        float b1 = 0.f, b2 = 0.f;
+        for (int k = 8; k >= 1; k--) { const float b0 = fmaf(t2, b1, c[k] - b2); b2 = b1; b1 = b0; }
+        v = (fmaf(t, b1, c[0]) - b2) * fmaxf(1.f - zz, 0.f);
       } else {
         v = radial_feature(kind, m, n, sqrtf(sq), rmax, pi_over_rmax);
       }

@@ -56,6 +56,35 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   return false;
 }
 
+// Bounded wait by polling (mbarrier.test_wait does not suspend the thread): for barriers that complete within a few
+// hundred cycles, where the wake-up of a suspended thread would cost more than the polling. A short pause between polls
+// leaves the issue slots to the warps that do the work. About 2^24 polls (more than a second) before giving up.
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, uint32_t limit = TC_SPIN_LIMIT) {
+  for (uint32_t i = 0; i < limit; i++) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if (i >= 8) __nanosleep(32);
+  }
+  return false;
+}
+// the same without any pause: the warp is never descheduled while it waits
+__device__ __forceinline__ bool mbar_wait_tight(uint64_t* bar, uint32_t parity, uint32_t limit = TC_SPIN_LIMIT) {
+  for (uint32_t i = 0; i < limit; i++)
+    if (mbar_test_wait(bar, parity)) return true;
+  return false;
+}
+
 // ---- async-proxy visibility of generic shared-memory stores ------------------------------------------
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -155,6 +184,25 @@ __device__ __forceinline__ void tmem_ld16x2(uint32_t a0, uint32_t a1, float* v) 
       : "memory");
 #pragma unroll
   for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// two 16-column groups plus two more columns (x2) at a third address, one wait for all: v[0..31], w[0..1]
+__device__ __forceinline__ void tmem_ld16x2_2(uint32_t a0, uint32_t a1, uint32_t a2, float* v, float* w) {
+  uint32_t r[34];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%34];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%35];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x2.b32 {%32, %33}, [%36];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+        "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
+        "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33])
+      : "r"(a0), "r"(a1), "r"(a2)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+  w[0] = __uint_as_float(r[32]); w[1] = __uint_as_float(r[33]);
 }
 
 // four 8-column groups at column offsets 0, stride, 2*stride, 3*stride, one wait for all

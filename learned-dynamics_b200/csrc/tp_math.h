@@ -137,15 +137,35 @@ LD_HD float radial_feature(int kind, int m, int n, float d, float rmax, float pi
 LD_HD float silu_f(float x) { return x / (1.0f + expf(-x)); }
 
 // Polynomial radial basis of managan/jacobi_radenc.py:27-33: enc[m] = env * sum_p coeff[m][p] z^p for an 8x9
-// coefficient matrix (the shifted Jacobi(1,0) polynomials there). The coefficients reach 2.7e4 with alternating
-// signs, so a float32 power sum loses four digits to cancellation (the reference's own float32 evaluation is
-// 2.4e-4 off the exact value of a basis function of size 1). Evaluated here by Horner's rule in double, once per
-// edge (72 double FMAs), which leaves only the final rounding to float32.
-LD_HD void ld_radial_poly8(float z, float env, const float* coeff, float* enc) {
-  const double zd = (double)z;
+// coefficient matrix (the shifted Jacobi(1,0) polynomials there), z in [0, 1]. The monomial coefficients reach 2.7e4
+// with alternating signs, so a float32 power sum loses four digits to cancellation (the reference's own float32
+// evaluation is 2.4e-4 off the exact value of a basis function of size 1). Here each polynomial is re-expressed once,
+// in double, in the Chebyshev basis of t = 2z - 1 (coefficients of order 1) and evaluated per edge by Clenshaw's
+// recurrence in float32: error about 2e-6 of a basis function of size 8, at 16 FMAs per function.
+LD_HD void ld_poly8_to_chebyshev(const float* a, float* c) {
+  double p[10], q[10];
+  for (int n = 0; n < 10; n++) p[n] = 0.0;
+  p[0] = (double)a[8];
+  for (int k = 7; k >= 0; k--) {
+    // q = p * z with z = (t + 1) / 2;  t T_0 = T_1,  t T_n = (T_{n+1} + T_{n-1}) / 2
+    for (int n = 0; n < 10; n++) q[n] = 0.0;
+    q[1] += p[0];
+    for (int n = 1; n < 9; n++) { q[n + 1] += 0.5 * p[n]; q[n - 1] += 0.5 * p[n]; }
+    for (int n = 0; n < 10; n++) p[n] = 0.5 * (q[n] + p[n]);
+    p[0] += (double)a[k];
+  }
+  for (int n = 0; n < 9; n++) c[n] = (float)p[n];
+}
+
+LD_HD void ld_radial_cheb8(float z, float env, const float* cheb, float* enc) {
+  const float t = 2.f * z - 1.f, t2 = 2.f * t;
   for (int m = 0; m < 8; m++) {
-    double a = (double)coeff[m * 9 + 8];
-    for (int p = 7; p >= 0; p--) a = fma(a, zd, (double)coeff[m * 9 + p]);
-    enc[m] = (float)(a * (double)env);
+    const float* c = cheb + m * 9;
+    float b1 = 0.f, b2 = 0.f;
+    for (int k = 8; k >= 1; k--) {
+      const float b0 = fmaf(t2, b1, c[k] - b2);
+      b2 = b1; b1 = b0;
+    }
+    enc[m] = (fmaf(t, b1, c[0]) - b2) * env;
   }
 }

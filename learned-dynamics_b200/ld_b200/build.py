@@ -18,9 +18,12 @@ NVCC_FLAGS = [
 ]
 
 
-# LD_PHASE_COUNTERS=1 in the environment builds the diagnostics variant (cycle counters inside the fused tensor-core kernels)
+# LD_PHASE_COUNTERS=1 in the environment selects the diagnostics variant (cycle counters inside the fused tensor-core
+# kernels): a library of its own, built and loaded only while the variable is set
 if os.environ.get("LD_PHASE_COUNTERS", "0") == "1":
     NVCC_FLAGS.append("-DLD_PHASE_COUNTERS")
+    OBJ_DIR = os.path.join(CSRC, "build_prof")
+    LIB_PATH = os.path.join(HERE, "libld_hotpath_prof.so")
 
 
 def sources():
