@@ -1,34 +1,32 @@
 // One edge kernel per l<=2 ("Bee") message layer on the Blackwell tensor cores: Messages.forward of the reference
 // (archs/diffuser_atoms15.py:227-253) for chan = 128 product channels and dim_a = 128, with every neighbour row
-// gathered exactly once and the 13 products formed by the tensor cores instead of the FP32 lanes.
+// gathered exactly once and both the 13 products and their per-node sums formed by the tensor cores.
 //
 //   pa[e,c]   = lin_enc(radial_encode_8(r_e))[c]                                  (managan/jacobi_radenc.py:27-33)
 //   rhat_e    = tens_sigmoid(1, r_e * 7/r0)                                       (managan/tensor_products.py:167-182)
 //   the right operands of the Bee products are pa, pa*rhat, pa*rhat rhat^T, so each of the 63 product components
-//   of an (edge, channel) is  pa[e,c] * sum_m l[dst_e, c, m] * G_e[m, o]  with l = (l0, l1[3], l2[9]) the thirteen
+//   of an (edge, channel) is  sum_m (pa[e,c] l[dst_e, c, m]) * G_e[m, o]  with l = (l0, l1[3], l2[9]) the thirteen
 //   left values of the neighbour and G_e a 13 x 63 matrix of monomials of rhat_e (degree <= 2, signs of the
 //   Levi-Civita symbol) that does not depend on the channel (managan/codegen_tensor_products.py:235-249).
 //
-// Per edge ONE tcgen05 MMA  D_e[c, o] = L_e[c, 0:16] * G_e[0:16, 0:64]  (M = 128 channels, N = 64, K = 16, BF16 operands,
-// FP32 accumulators in tensor memory):
-//   * L_e is the neighbour's row, stored per node as two 16-byte halves per channel, [node][2][chan][8] BF16: a single
-//     4 KB bulk copy puts it into shared memory in exactly the K-major operand layout, without passing through
-//     registers;
-//   * G_e is written by two builder warps (115 non-zero BF16 entries at fixed positions);
-//   * pa for the whole tile comes from one more MMA, [chan x 27] x [27 x edges] with lin_enc's weights and the radial
-//     functions split into BF16 high and low parts (error 2^-17);
-//   * the sixteen working warps read D_e from tensor memory (lane = channel), multiply by pa and add into 60 running
-//     sums per channel held in registers (sixteen columns per warp); the three scalar products are rounded to BF16 into
-//     the operand tile of the per-edge MLP. Sums are written once per node, in edge order.
+// Per edge the sixteen working warps (a warp = 32 channels of every fourth edge) load the neighbour's row
+// ([node][2][chan][8] BF16: two 16-byte halves per channel) three edges ahead, and for the current edge compute pa and
+// the three scalar products y000, y110, y220 in registers (FP32; the scalar products go as BF16 into the operand tile
+// of the per-edge MLP), scale the row by pa and store it into shared memory as a K-major operand L_e [128 channels x
+// 16]. The same warps write G_e (102 non-zero BF16 entries at fixed positions, one per thread). One thread then issues one tcgen05
+// MMA per edge,
+//   S_node[c, 0:64] += L_e * G_e        the 60 rank-1 / rank-2 components ACCUMULATE in tensor memory over the edges
+//                                       of a node: the per-node sum of edges_reduce_src costs no instruction at all,
+// and the working warps read S_node once per NODE (double-buffered), writing it as BF16 [node][component][5*chan].
 // After the 128 edges of a tile: psi = [y000|y110|y220] Y^T, two hidden layers, and the last layer with weights
-// [W3 | W_direct + I] as in bee_messages_tc.cu - the last one transposed (weights as the M operand), so that its
-// result lies in tensor memory as [channel][edge] and the per-node sum over edges is a plain sequential sum in one
-// thread per channel. All additions happen in an order fixed by the node's edge list alone, so a system's result does
-// not depend on the batch (or shard) it is processed in.
+// [W3 | W_direct + I] as in bee_messages_tc.cu - the last one transposed (weights as the M operand), so that its result
+// lies in tensor memory as [channel][edge] and the per-node sum over edges is a sequential sum in one thread per
+// channel. All additions happen in an order fixed by the node's edge list alone, so a system's result does not depend
+// on the batch (or shard) it is processed in.
 //
-// Shared memory: operand tile 97 KB | 96 KB ring, used as eight two-edge groups (two rows + two G matrices, 12 KB) while
-// the products are formed and as three 32 KB weight slabs while the MLP runs | small operands. Tensor memory: columns
-// [0, 384) three D groups (two edges each), the first 256 later the MLP accumulators; [384, 512) pa.
+// Shared memory: MLP operand tile 97 KB | 96 KB ring, used as seven two-edge groups (two rows + two G matrices, 13 KB)
+// while the products are formed and as three 32 KB weight slabs while the MLP runs | small operands.
+// Tensor memory: [0,128) two node accumulators | [256,512) the MLP accumulators.
 // Every wait is bounded; a wait that runs out sets LD_FLAG_TIMEOUT and all roles leave.
 #include "common.cuh"
 #include "tc05.cuh"
@@ -40,29 +38,28 @@ constexpr int BF_EDGES = 128;
 constexpr int BF_C = 128, BF_A = 128;
 constexpr int BF_WORK_WARPS = 16;
 constexpr int BF_WORK_THREADS = BF_WORK_WARPS * 32;
-// 20 warps: five per scheduler partition, the most that fit at 96 registers per thread (16384 registers per partition)
-constexpr int BF_MMA_WARP = 16, BF_GATHER_WARP = 17, BF_BUILD_WARP0 = 18, BF_BUILD_WARPS = 2;
-constexpr int BF_THREADS = (BF_WORK_WARPS + 2 + BF_BUILD_WARPS) * 32;          // 640
+// 18 warps, at most five per scheduler partition: 96 registers per thread fit (16384 registers per partition)
+constexpr int BF_MMA_WARP = 16, BF_WEIGHT_WARP = 17;
+constexpr int BF_THREADS = (BF_WORK_WARPS + 2) * 32;                           // 576
 constexpr int BF_SYNC_THREADS = (BF_WORK_WARPS + 1) * 32;                      // working warps + MMA warp
 constexpr int BF_PANEL = BF_EDGES * 16 + 16;     // byte stride between 8-column panels of the MLP operand tile (padded)
 constexpr int BF_NG = 8;                         // ring groups (two edges each)
 constexpr int BF_ROW_BYTES = 2 * BF_C * 16;      // 4096: one neighbour row = two K panels of 128 channels
-constexpr int BF_GAMMA_BYTES = 64 * 32;          // 2048: G_e as N = 64 rows x K = 16
+constexpr int BF_GAMMA_ROWS = 64;                // G_e as the N operand: 64 rows (60 used)
+constexpr int BF_GAMMA_BYTES = 2 * BF_GAMMA_ROWS * 16;                         // 2560: two K panels
 constexpr int BF_GROUP_BYTES = 2 * BF_ROW_BYTES + 2 * BF_GAMMA_BYTES;          // 12288
-constexpr int BF_RING_BYTES = BF_NG * BF_GROUP_BYTES;                          // 98304
 constexpr int BF_WSTAGES = 3, BF_SLAB_BYTES = 32 * 1024;
-static_assert(BF_RING_BYTES == BF_WSTAGES * BF_SLAB_BYTES, "the ring is shared by row groups and weight slabs");
+constexpr int BF_RING_BYTES = BF_WSTAGES * BF_SLAB_BYTES;                      // 98304
+static_assert(BF_NG * BF_GROUP_BYTES <= BF_RING_BYTES, "row groups and weight slabs share the ring");
 constexpr int BF_LAYERS = 4;
 constexpr int BF_OFF_A = 0;
 constexpr int BF_A_BYTES = (3 * BF_C / 8) * BF_PANEL;                          // 99072
 constexpr int BF_OFF_RING = BF_OFF_A + BF_A_BYTES;
-constexpr int BF_OFF_W9 = BF_OFF_RING + BF_RING_BYTES;                         // lin_enc operand: 128 rows x 32 (4 panels)
-constexpr int BF_OFF_ENC = BF_OFF_W9 + 4 * BF_C * 16;                          // radial operand: 128 edges x 32
-constexpr int BF_OFF_BIAS = BF_OFF_ENC + 4 * BF_EDGES * 16;
+constexpr int BF_OFF_BIAS = BF_OFF_RING + BF_RING_BYTES;
 constexpr int BF_SMEM = BF_OFF_BIAS + 5 * BF_A * 4;
-constexpr int BF_ND = 3;                         // D groups in tensor memory (two edges x 64 columns each)
-constexpr uint32_t BF_TMEM_COLS = 512, BF_TMEM_PA = BF_ND * 128;
-constexpr int BF_GAMMA_ENTRIES = 128;            // 115 used
+constexpr uint32_t BF_TMEM_COLS = 512, BF_TMEM_MLP = 256;
+constexpr int BF_YL = 1;                         // node boundaries are served BF_YL groups of a warp (8 edges) behind its stores
+constexpr int BF_GAMMA_ENTRIES = 128;            // 102 used
 
 struct BfLayer {
   const __nv_bfloat16* w;   // packed panels [K/8][N][8]
@@ -83,13 +80,14 @@ struct BfParams {
   uint32_t wait_limit;
   int spin;                      // waits on the per-group barriers poll instead of suspending
   long long* prof;               // diagnostics build only
-  unsigned short gamma_tab[BF_GAMMA_ENTRIES];   // bits 0-10 byte offset inside G_e, 11-14 monomial, 15 sign; 0xffff unused
+  unsigned short gamma_tab[BF_GAMMA_ENTRIES];   // bits 0-10 (byte offset inside G_e) / 2, 11-14 monomial, 15 sign; 0xffff unused
 };
 
-// Diagnostics build (-DLD_PHASE_COUNTERS): cycles per phase of one thread per role, added into prof[16]:
-// working thread 0: 0 geometry, 1 wait pa, 2 wait D, 3 products, 4 barrier after products, 5 wait layers, 6 epilogues,
-// 7 scalar sums, 8 end-of-tile barriers; MMA lane: 9 wait rows + G, 10 wait D free, 11 wait weights; builder 0:
-// 12 wait free group, 13 build; gather lane 0: 14 wait free group; builder 1 lane 0: 15 weight streaming.
+// Diagnostics build (-DLD_PHASE_COUNTERS): cycles per phase of one thread per role (block 0), added into prof[32]:
+// working thread 0: 0 geometry, 2 wait free ring group, 3 products + scale + store, 4 barrier after products,
+// 5 wait layers, 6 epilogues, 7 scalar sums, 8 end-of-tile barriers, 18 node drains;
+// MMA lane: 9 wait rows + G, 10 wait node buffer, 11 wait weights;
+// builder 0: 12 wait free group, 13 build; builder 1 lane 0: 15 weight streaming.
 struct BfProf {
 #ifdef LD_PHASE_COUNTERS
   long long t; long long* prof; bool on;
@@ -104,6 +102,7 @@ struct BfProf {
 };
 
 struct BfRange { int n_begin, n_end; long long e_begin, e_end, ntiles; };
+
 
 __device__ __forceinline__ int bf_work_lb(const int* __restrict__ row_ptr, int lo, int hi, long long target) {
   const long long base = (long long)row_ptr[lo] + lo;
@@ -152,8 +151,8 @@ __device__ __forceinline__ unsigned short bf_bf16(float v) {
   return *reinterpret_cast<unsigned short*>(&h);
 }
 
-// column o of D_e (0..63) -> where its per-node sum goes. o in [3,18): rank-1 product (o-3)/3, component (o-3)%3;
-// o in [18,63): rank-2 product (o-18)/9, component (o-18)%9. Writes (or zero-fills) the sixteen columns of group G.
+// column o of a node accumulator (0..63) -> where it goes. o in [0,15): rank-1 product o/3, component o%3;
+// o in [15,60): rank-2 product (o-15)/9, component (o-15)%9; 60..63 unused. Writes the sixteen columns of group G.
 template <int G>
 __device__ __forceinline__ void bf_store_node(__nv_bfloat16* __restrict__ S_v, __nv_bfloat16* __restrict__ S_d, int node, int c,
                                               const float* acc, float scale) {
@@ -161,104 +160,81 @@ __device__ __forceinline__ void bf_store_node(__nv_bfloat16* __restrict__ S_v, _
   for (int k = 0; k < 16; k++) {
     constexpr int base = 16 * G;
     const int o = base + k;
-    if (o < 3 || o == 63) continue;
+    if (o >= 60) continue;
     const __nv_bfloat16 v = __float2bfloat16_rn(acc[k] * scale);
-    if (o < 18) {
-      const int vi = o - 3;
-      S_v[((size_t)node * 3 + (vi % 3)) * (5 * BF_C) + (vi / 3) * BF_C + c] = v;
+    if (o < 15) {
+      S_v[((size_t)node * 3 + (o % 3)) * (5 * BF_C) + (o / 3) * BF_C + c] = v;
     } else {
-      const int di = o - 18;
+      const int di = o - 15;
       S_d[((size_t)node * 9 + (di % 9)) * (5 * BF_C) + (di / 9) * BF_C + c] = v;
     }
   }
 }
 
-// End of a node's edge list for one thread (channel c, column group g): write its sixteen running sums for `node`, then
-// zeros for the nodes without edges up to `next` (exclusive). One copy of this code, called from the few places where
-// a node can end; the sums travel by value so that they stay in registers at the call sites.
-__device__ __noinline__ void bf_flush_node(int g, __nv_bfloat16* S_v, __nv_bfloat16* S_d, int node, int next, int c, float scale,
-                                           float a0, float a1, float a2, float a3, float a4, float a5, float a6, float a7,
-                                           float a8, float a9, float a10, float a11, float a12, float a13, float a14, float a15) {
+// End of a node's edge list for one thread (channel c, column group g): write its sixteen sums for `node` (skipped when
+// node < 0), then zeros for the nodes without edges from `zero_from` up to `next` (exclusive). One copy of this code,
+// called from the few places where a node can end; the sums travel by value so that they stay in registers.
+__device__ __noinline__ void bf_flush_node(int g, __nv_bfloat16* S_v, __nv_bfloat16* S_d, int node, int zero_from, int next, int c,
+                                           float scale, float a0, float a1, float a2, float a3, float a4, float a5, float a6,
+                                           float a7, float a8, float a9, float a10, float a11, float a12, float a13, float a14,
+                                           float a15) {
   float acc[16] = {a0, a1, a2, a3, a4, a5, a6, a7, a8, a9, a10, a11, a12, a13, a14, a15};
-  for (int v = node; v < next; v++) {
+  for (int v = (node >= 0 ? node : zero_from); v < next; v++) {
+    if (v != node) {
+#pragma unroll
+      for (int i = 0; i < 16; i++) acc[i] = 0.f;
+    }
     if (g == 0) bf_store_node<0>(S_v, S_d, v, c, acc, scale);
     else if (g == 1) bf_store_node<1>(S_v, S_d, v, c, acc, scale);
     else if (g == 2) bf_store_node<2>(S_v, S_d, v, c, acc, scale);
     else bf_store_node<3>(S_v, S_d, v, c, acc, scale);
-    if (v == node) {
-#pragma unroll
-      for (int i = 0; i < 16; i++) acc[i] = 0.f;
-    }
+    if (v == node) v = zero_from - 1;   // continue with the nodes that have no edges
   }
 }
-#define BF_FLUSH(node, next)                                                                                              \
-  do {                                                                                                                    \
-    bf_flush_node(g, P.S_v, P.S_d, (node), (next), ch, P.scale, acc[0], acc[1], acc[2], acc[3], acc[4], acc[5], acc[6],  \
-                  acc[7], acc[8], acc[9], acc[10], acc[11], acc[12], acc[13], acc[14], acc[15]);                          \
-    _Pragma("unroll") for (int i_ = 0; i_ < 16; i_++) acc[i_] = 0.f;                                                      \
-  } while (0)
 
-__global__ void __launch_bounds__(BF_THREADS, 1)
+__global__ void __maxnreg__(96)
 bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t bar_full[BF_NG], bar_slot_empty[BF_NG], bar_dfull[BF_ND], bar_dempty[BF_ND];
-  __shared__ __align__(8) uint64_t bar_pa, bar_geom, bar_gather_go, bar_weights_go;
+  __shared__ __align__(8) uint64_t bar_full[BF_NG], bar_slot_empty[BF_NG];
+  __shared__ __align__(8) uint64_t bar_dfull[2], bar_dempty[2];
+  __shared__ __align__(8) uint64_t bar_weights_go;
   __shared__ __align__(8) uint64_t bar_wfull[BF_WSTAGES], bar_wempty[BF_WSTAGES], bar_accum;
   __shared__ uint32_t tmem_slot;
   __shared__ volatile int s_fail;
-  __shared__ __align__(16) float s_mono[BF_EDGES][12];   // 1, rx, ry, rz, rx rx, rx ry, rx rz, ry ry, ry rz, rz rz
-  __shared__ int s_src[BF_EDGES];
+  // per edge: eight radial functions | 1, rx, ry, rz | rx rx, rx ry, rx rz, ry ry | ry rz, rz rz, 0, 0
+  __shared__ __align__(16) float s_geo[BF_EDGES][20];
+  __shared__ __align__(16) int s_src[BF_EDGES];
+  __shared__ int s_dst[BF_EDGES];
+  __shared__ int s_bnd[BF_EDGES];      // edges of the tile at which a new source node starts, ascending
+  __shared__ int s_nbnd, s_prev_src;   // their number; source node of the last edge of the previous tile (-1: none)
+  __shared__ unsigned s_bmask[BF_EDGES / 32];   // the same as one bit per edge (for the MMA thread)
   __shared__ int s_rowwin[BF_EDGES + 1];
   __shared__ float s_jac[72];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   unsigned char* a_smem = smem + BF_OFF_A;
   unsigned char* ring = smem + BF_OFF_RING;
-  unsigned char* w9_smem = smem + BF_OFF_W9;
-  unsigned char* enc_smem = smem + BF_OFF_ENC;
   float* s_bias = reinterpret_cast<float*>(smem + BF_OFF_BIAS);   // [b1 (2A) | b2 (2A) | b3 (A)]
   const uint32_t wl = P.wait_limit;
   // the per-group barriers (64 groups per tile) complete within a few hundred cycles
   auto hot_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
-    if (P.spin == 2) return tc::mbar_wait_tight(bar, parity, wl << 6);
-    return P.spin ? tc::mbar_wait_spin(bar, parity, wl << 4) : tc::mbar_wait(bar, parity, wl);
+    return (P.spin & 1) ? tc::mbar_wait_spin(bar, parity, wl << 4) : tc::mbar_wait(bar, parity, wl);
   };
   BfProf pf;
 
   if (tid < 8) ld_poly8_to_chebyshev(P.jacobi + tid * 9, s_jac + tid * 9);   // Chebyshev form of the radial polynomials
   for (int i = tid; i < 2 * BF_A; i += BF_THREADS) { s_bias[i] = P.b1[i]; s_bias[2 * BF_A + i] = P.b2[i]; }
   for (int i = tid; i < BF_A; i += BF_THREADS) s_bias[4 * BF_A + i] = P.b3[i];
-  if (tid < BF_C) {
-    // lin_enc as the M operand of the pa product: [W_hi (8 weights, bias) | W_hi | W_lo | 0], 32 columns, K-major panels
-    float w[9];
-#pragma unroll
-    for (int m = 0; m < 8; m++) w[m] = P.enc_w[tid * 8 + m];
-    w[8] = P.enc_b[tid];
-    unsigned short row[32];
-#pragma unroll
-    for (int m = 0; m < 9; m++) {
-      const __nv_bfloat16 hi = __float2bfloat16_rn(w[m]);
-      const unsigned short h = *reinterpret_cast<const unsigned short*>(&hi);
-      row[m] = h; row[9 + m] = h;
-      row[18 + m] = bf_bf16(w[m] - __bfloat162float(hi));
-    }
-#pragma unroll
-    for (int m = 27; m < 32; m++) row[m] = 0;
-#pragma unroll
-    for (int p = 0; p < 4; p++) {
-      uint4 q;
-      q.x = row[p * 8] | ((uint32_t)row[p * 8 + 1] << 16); q.y = row[p * 8 + 2] | ((uint32_t)row[p * 8 + 3] << 16);
-      q.z = row[p * 8 + 4] | ((uint32_t)row[p * 8 + 5] << 16); q.w = row[p * 8 + 6] | ((uint32_t)row[p * 8 + 7] << 16);
-      *reinterpret_cast<uint4*>(w9_smem + p * (BF_C * 16) + tid * 16) = q;
-    }
-  }
   if (tid == 0) {
-    for (int s = 0; s < BF_NG; s++) { tc::mbar_init(&bar_full[s], 2); tc::mbar_init(&bar_slot_empty[s], 1); }
-    for (int s = 0; s < BF_ND; s++) { tc::mbar_init(&bar_dfull[s], 1); tc::mbar_init(&bar_dempty[s], BF_WORK_WARPS); }
-    tc::mbar_init(&bar_pa, 1); tc::mbar_init(&bar_geom, 1); tc::mbar_init(&bar_gather_go, 1); tc::mbar_init(&bar_weights_go, 1);
+    for (int s = 0; s < BF_NG; s++) { tc::mbar_init(&bar_full[s], 4); tc::mbar_init(&bar_slot_empty[s], 1); }   // 4 warps per group
+    for (int s = 0; s < 2; s++) { tc::mbar_init(&bar_dfull[s], 1); tc::mbar_init(&bar_dempty[s], BF_WORK_WARPS); }
+    tc::mbar_init(&bar_weights_go, 1);
     for (int s = 0; s < BF_WSTAGES; s++) { tc::mbar_init(&bar_wfull[s], 1); tc::mbar_init(&bar_wempty[s], 1); }
     tc::mbar_init(&bar_accum, 1);
     tc::mbar_init_fence();
+    // every ring group starts out free: complete the first phase of its "empty" barrier, so that the n-th use of a group
+    // always waits for phase n (no special case for the first use)
+    for (int s = 0; s < BF_NG; s++) tc::mbar_arrive(&bar_slot_empty[s]);
     s_fail = 0;
   }
   if (warp == 0) { tc::tmem_alloc(&tmem_slot, BF_TMEM_COLS); tc::tmem_relinquish(); }
@@ -270,181 +246,102 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
   const int seg_nodes = P.seg_nodes > 0 ? P.seg_nodes : P.Nt;
   int fail = 0;
 
-  if (warp == BF_GATHER_WARP) {
-    // ===== gather: lanes 2k, 2k+1 own ring group k; lane 2k waits for the group to be free and announces the bytes,
-    // then each of the two lanes requests one neighbour row (a 4 KB bulk copy straight into operand layout) ==========
-    if (lane < 2 * BF_NG) {
-      const int k = lane >> 1, u = lane & 1;
-      const unsigned pair_mask = 3u << (2 * k);
-      long long Gbase = 0;      // groups of all earlier tiles
-      uint32_t tiles = 0;
-      bool issued = false;
-      uint32_t last_use = 0;
-      pf.start(P.prof, lane == 0 && blockIdx.x == 0);
+  if (warp == BF_WEIGHT_WARP) {
+    // ===== weight slabs of the four layers, once the products of the tile are done with the ring ===================
+    if (lane == 0) {
+      uint32_t wloads = 0, tiles = 0;
+      pf.start(P.prof, blockIdx.x == 0);
       for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
-        const BfRange br = bf_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt));
-        for (long long e0 = br.e_begin; e0 < br.e_end && !fail; e0 += BF_EDGES, tiles++) {
-          const int cnt = (int)((br.e_end - e0) < BF_EDGES ? (br.e_end - e0) : BF_EDGES);
-          const int groups = (cnt + 1) >> 1;
-          // the ring holds weight slabs until the last layer of the previous tile has been multiplied
-          if (tiles >= 1 && !tc::mbar_wait(&bar_gather_go, (tiles - 1) & 1, wl)) { fail = 1; break; }
-          // first group of this tile that lands in ring group k
-          int grp = (int)(((long long)k - Gbase) % BF_NG);
-          if (grp < 0) grp += BF_NG;
-          for (; grp < groups; grp += BF_NG) {
-            const long long Gg = Gbase + grp;
-            const uint32_t use = (uint32_t)(Gg / BF_NG);
-            const int e = min(2 * grp + u, cnt - 1);
-            const int j = __ldg(P.dst + e0 + e);
-            int ok = 1;
-            if (u == 0) {
-              pf.lap(100);
-              if (use >= 1 && !hot_wait(&bar_slot_empty[k], (use - 1) & 1)) ok = 0;
-              pf.lap(14);
-              if (ok) tc::mbar_expect_tx(&bar_full[k], 2 * BF_ROW_BYTES);
-            }
-            ok = __all_sync(pair_mask, ok);
-            if (!ok || s_fail) { fail = 1; break; }
-            tc::bulk_g2s(ring + k * BF_GROUP_BYTES + u * BF_ROW_BYTES, P.rows + (size_t)j * (2 * BF_C * 8), BF_ROW_BYTES, &bar_full[k]);
-            issued = true; last_use = use;
-          }
-          Gbase += groups;
-        }
-      }
-      if (fail) {
-        s_fail = 1;
-        if (issued && u == 0) tc::mbar_wait(&bar_full[k], last_use & 1, wl);   // let copies in flight land (bounded)
-      }
-    }
-  } else if (warp >= BF_BUILD_WARP0) {
-    // ===== builders: G_e of every edge (B operand, 64 x 16 BF16, K-major panels) =======================================
-    // The second builder warp also streams the weight slabs of the four layers: its lane 0 does so after the warp's
-    // last G of the tile (the ring belongs to the MLP from then until the last layer has been multiplied).
-    const int b = warp - BF_BUILD_WARP0;
-    uint32_t wloads = 0;
-    unsigned short tab[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) tab[i] = P.gamma_tab[lane * 4 + i];
-    long long Gbase = 0;
-    uint32_t tiles = 0;
-    pf.start(P.prof, lane == 0 && blockIdx.x == 0);
-    for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
-      const BfRange br = bf_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt));
-      for (long long e0 = br.e_begin; e0 < br.e_end && !fail; e0 += BF_EDGES, tiles++) {
-        const int cnt = (int)((br.e_end - e0) < BF_EDGES ? (br.e_end - e0) : BF_EDGES);
-        const int groups = (cnt + 1) >> 1;
-        if (tiles >= 1 && !tc::mbar_wait(&bar_gather_go, (tiles - 1) & 1, wl)) { fail = 1; break; }
-        // the weight slabs of the previous tile overwrote the G areas: clear the ones this warp fills in this tile
-        // (ring groups of one parity), the entries written below sit at fixed positions among zeros
-        {
-          const int par = (int)((Gbase + b) & 1);
-          for (int gs = par; gs < BF_NG; gs += 2) {
-            uint4* gz = reinterpret_cast<uint4*>(ring + gs * BF_GROUP_BYTES + 2 * BF_ROW_BYTES);
-            for (int i = lane; i < 2 * BF_GAMMA_BYTES / 16; i += 32) gz[i] = make_uint4(0u, 0u, 0u, 0u);
-          }
-          __syncwarp();   // the entries written below belong to chunks other lanes have just cleared
-        }
-        if (!tc::mbar_wait(&bar_geom, tiles & 1, wl)) { fail = 1; break; }    // monomials of this tile are in s_mono
-        for (int grp = b; grp < groups; grp += BF_BUILD_WARPS) {
-          const long long Gg = Gbase + grp;
-          const int gs = (int)(Gg % BF_NG);
-          const uint32_t use = (uint32_t)(Gg / BF_NG);
-          if (b == 0) pf.lap(100);
-          if (use >= 1 && !hot_wait(&bar_slot_empty[gs], (use - 1) & 1)) { fail = 1; break; }
-          if (b == 0) pf.lap(12);
-          if (s_fail) { fail = 1; break; }
-#pragma unroll
-          for (int u = 0; u < 2; u++) {
-            const int e = min(2 * grp + u, cnt - 1);
-            unsigned char* gdst = ring + gs * BF_GROUP_BYTES + 2 * BF_ROW_BYTES + u * BF_GAMMA_BYTES;
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-              const unsigned t = tab[i];
-              if (t != 0xffffu) {
-                float v = s_mono[e][(t >> 11) & 15];
-                if (t & 0x8000u) v = -v;
-                *reinterpret_cast<unsigned short*>(gdst + (t & 0x7ffu)) = bf_bf16(v);
-              }
-            }
-          }
-          tc::fence_async_smem();
-          __syncwarp();
-          if (lane == 0) tc::mbar_arrive(&bar_full[gs]);
-          if (b == 0) pf.lap(13);
-        }
-        Gbase += groups;
-        if (b == BF_BUILD_WARPS - 1) {
+        const long long ntiles = bf_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt)).ntiles;
+        for (long long t = 0; t < ntiles && !fail; t++, tiles++) {
           pf.lap(100);
-          if (lane == 0 && !fail) {
-            // the ring is free for weights once every product MMA of the tile has read its rows
-            if (!tc::mbar_wait(&bar_weights_go, tiles & 1, wl)) fail = 1;
-            for (int l = 0; l < BF_LAYERS && !fail; l++) {
-              const BfLayer& L = P.layer[l];
-              for (int ks = 0; ks < L.ksteps; ks += L.slab_ksteps, wloads++) {
-                const uint32_t st = wloads % BF_WSTAGES, use = wloads / BF_WSTAGES;
-                const uint32_t bytes = (uint32_t)min(L.slab_ksteps, L.ksteps - ks) * L.N * 32;
-                // a slab slot is free when the MMAs that read its previous content are done
-                if (use >= 1 && !tc::mbar_wait(&bar_wempty[st], (use - 1) & 1, wl)) { fail = 1; break; }
-                if (s_fail) { fail = 1; break; }
-                tc::mbar_expect_tx(&bar_wfull[st], bytes);
-                tc::bulk_g2s(ring + (size_t)st * BF_SLAB_BYTES, L.w + (size_t)ks * L.N * 16, bytes, &bar_wfull[st]);
-              }
-            }
-            if (fail) {   // let slabs in flight land (bounded)
-              for (uint32_t i = wloads > BF_WSTAGES ? wloads - BF_WSTAGES : 0; i < wloads; i++)
-                tc::mbar_wait(&bar_wfull[i % BF_WSTAGES], (i / BF_WSTAGES) & 1, wl);
+          // the ring is free for weights once every product MMA of the tile has read its rows
+          if (!tc::mbar_wait(&bar_weights_go, tiles & 1, wl)) { fail = 1; break; }
+          for (int l = 0; l < BF_LAYERS && !fail; l++) {
+            const BfLayer& L = P.layer[l];
+            for (int ks = 0; ks < L.ksteps; ks += L.slab_ksteps, wloads++) {
+              const uint32_t st = wloads % BF_WSTAGES, use = wloads / BF_WSTAGES;
+              const uint32_t bytes = (uint32_t)min(L.slab_ksteps, L.ksteps - ks) * L.N * 32;
+              // a slab slot is free when the MMAs that read its previous content are done
+              if (use >= 1 && !tc::mbar_wait(&bar_wempty[st], (use - 1) & 1, wl)) { fail = 1; break; }
+              if (s_fail) { fail = 1; break; }
+              tc::mbar_expect_tx(&bar_wfull[st], bytes);
+              tc::bulk_g2s(ring + (size_t)st * BF_SLAB_BYTES, L.w + (size_t)ks * L.N * 16, bytes, &bar_wfull[st]);
             }
           }
           pf.lap(15);
-          fail = __shfl_sync(0xffffffffu, fail, 0);
         }
       }
+      if (fail) {   // let slabs in flight land (bounded)
+        s_fail = 1;
+        for (uint32_t i = wloads > BF_WSTAGES ? wloads - BF_WSTAGES : 0; i < wloads; i++)
+          tc::mbar_wait(&bar_wfull[i % BF_WSTAGES], (i / BF_WSTAGES) & 1, wl);
+      }
     }
-    if (fail) s_fail = 1;
   } else if (warp == BF_MMA_WARP) {
     // ===== MMA issue ===========================================================================================
     const bool mma_lane = lane == 0;
     uint32_t wmmas = 0, tiles = 0;
-    long long G = 0;
+    uint32_t full_ph = 0;       // bit gs: parity of the next phase to wait for on bar_full[gs]
+    uint32_t nc = 0;            // nodes (with edges) completed so far: the running node uses accumulator nc & 1
     const uint32_t a_base = tc::smem_u32(a_smem), ring_base = tc::smem_u32(ring);
     const uint64_t row_desc0 = tc::smem_desc(ring_base, BF_C * 16, 128);
-    const uint64_t gam_desc0 = tc::smem_desc(ring_base + 2 * BF_ROW_BYTES, 64 * 16, 128);
-    const uint32_t idesc_d = tc::idesc_bf16(BF_C, 64), idesc_pa = tc::idesc_bf16(BF_C, BF_EDGES);
+    const uint64_t gam_desc0 = tc::smem_desc(ring_base + 2 * BF_ROW_BYTES, BF_GAMMA_ROWS * 16, 128);
+    // the byte offset of a ring group (in 16-byte units) only ever changes the low word of a descriptor
+    const uint32_t row_lo = (uint32_t)row_desc0, row_hi = (uint32_t)(row_desc0 >> 32);
+    const uint32_t gam_lo = (uint32_t)gam_desc0, gam_hi = (uint32_t)(gam_desc0 >> 32);
+    const uint32_t idesc_s = tc::idesc_bf16(BF_C, 64);
     pf.start(P.prof, lane == 0 && blockIdx.x == 0);
     for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
       const BfRange br = bf_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt));
+      bool have = false;        // a node is accumulating (none yet in this slice)
       for (long long e0 = br.e_begin; e0 < br.e_end; e0 += BF_EDGES, tiles++) {
         const int cnt = (int)((br.e_end - e0) < BF_EDGES ? (br.e_end - e0) : BF_EDGES);
         const int groups = (cnt + 1) >> 1;
-        if (bf_sync_or(fail)) { fail = 1; break; }      // [B1] geometry staged (radial operand, monomials)
+        const bool last_tile = e0 + BF_EDGES >= br.e_end;
+        if (bf_sync_or(fail)) { fail = 1; break; }      // [B1] geometry staged (radial functions, monomials, src, dst, boundaries)
         if (mma_lane && !fail) {
           tc::fence_after_sync();
-          const uint64_t wd = tc::smem_desc(tc::smem_u32(w9_smem), BF_C * 16, 128);
-          const uint64_t ed = tc::smem_desc(tc::smem_u32(enc_smem), BF_EDGES * 16, 128);
-          tc::mma_bf16(tmem_base + BF_TMEM_PA, wd, ed, idesc_pa, 0u);
-          tc::mma_bf16(tmem_base + BF_TMEM_PA, wd + ((2 * BF_C * 16) >> 4), ed + ((2 * BF_EDGES * 16) >> 4), idesc_pa, 1u);
-          tc::mma_commit(&bar_pa);
-          for (int grp = 0; grp < groups; grp++, G++) {
-            const int gs = (int)(G % BF_NG);
-            const uint32_t use = (uint32_t)(G / BF_NG), d = (uint32_t)(G % BF_ND), duse = (uint32_t)(G / BF_ND);
+          unsigned bm = 0;
+#pragma unroll 1
+          for (int grp = 0; grp < groups; grp++) {
+            const int gs = grp & (BF_NG - 1);
+            if ((grp & 15) == 0) bm = s_bmask[grp >> 4];   // node-boundary flags of the next 32 edges
             pf.lap(100);
-            if (!hot_wait(&bar_full[gs], use & 1)) { fail = 1; break; }
+            if (!hot_wait(&bar_full[gs], (full_ph >> gs) & 1)) { fail = 1; break; }
+            full_ph ^= 1u << gs;
             pf.lap(9);
-            if (duse >= 1 && !hot_wait(&bar_dempty[d], (duse - 1) & 1)) { fail = 1; break; }
-            pf.lap(10);
             tc::fence_after_sync();
-            const uint64_t goff = (uint64_t)((gs * BF_GROUP_BYTES) >> 4);
-            tc::mma_bf16(tmem_base + d * 128, row_desc0 + goff, gam_desc0 + goff, idesc_d, 0u);
-            tc::mma_bf16(tmem_base + d * 128 + 64, row_desc0 + goff + (BF_ROW_BYTES >> 4), gam_desc0 + goff + (BF_GAMMA_BYTES >> 4),
-                         idesc_d, 0u);
-            tc::mma_commit(&bar_dfull[d]);
+            const uint32_t goff = (uint32_t)gs * (BF_GROUP_BYTES >> 4);
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+              const int e = 2 * grp + u;
+              if (e >= cnt) break;
+              uint32_t accumulate = 1u;
+              if ((bm >> (e & 31)) & 1u) {
+                // a new node starts at this edge: hand the accumulator of the finished one to the working warps and
+                // take the other one, which must have been read out (it held the node before the previous one)
+                if (have) { tc::mma_commit(&bar_dfull[nc & 1]); nc++; }
+                have = true;
+                if (nc >= 2 && !hot_wait(&bar_dempty[nc & 1], ((nc >> 1) - 1) & 1)) { fail = 1; break; }
+                pf.lap(10);
+                tc::fence_after_sync();
+                accumulate = 0u;
+              }
+              const uint64_t rd = ((uint64_t)row_hi << 32) | (row_lo + goff + u * (BF_ROW_BYTES >> 4));
+              const uint64_t gd = ((uint64_t)gam_hi << 32) | (gam_lo + goff + u * (BF_GAMMA_BYTES >> 4));
+              tc::mma_bf16(tmem_base + (nc & 1) * 64, rd, gd, idesc_s, accumulate);
+            }
+            if (fail) break;
             tc::mma_commit(&bar_slot_empty[gs]);
           }
-          if (!fail) tc::mma_commit(&bar_weights_go);   // every product MMA of the tile has read its rows: the ring may take weights
+          if (!fail) {
+            if (last_tile && have) { tc::mma_commit(&bar_dfull[nc & 1]); nc++; have = false; }   // last node of the slice
+            tc::mma_commit(&bar_weights_go);   // every product MMA of the tile has read its rows: the ring may take weights
+          }
         }
-        if (!mma_lane) G += groups;
+        nc = __shfl_sync(0xffffffffu, nc, 0);
         fail = __shfl_sync(0xffffffffu, fail, 0);
-        G = __shfl_sync(0xffffffffu, G, 0);
         if (bf_sync_or(fail)) { fail = 1; break; }      // [B2] scalar products of the tile are in the operand tile
         for (int l = 0; l < BF_LAYERS; l++) {
           if (mma_lane && !fail) {
@@ -465,8 +362,8 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
               const int nk = min(l_slab, l_ksteps - ks0);
 #pragma unroll 4
               for (int kk = 0; kk < nk; kk++) {
-                if (transposed) tc::mma_bf16(tmem_base, bd, ad, idesc, accumulate);
-                else tc::mma_bf16(tmem_base, ad, bd, idesc, accumulate);
+                if (transposed) tc::mma_bf16(tmem_base + BF_TMEM_MLP, bd, ad, idesc, accumulate);
+                else tc::mma_bf16(tmem_base + BF_TMEM_MLP, ad, bd, idesc, accumulate);
                 accumulate = 1u;
                 ad += a_step;
                 bd += b_step;
@@ -475,7 +372,6 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
             }
             if (!fail) {
               tc::mma_commit(&bar_accum);
-              if (l == BF_LAYERS - 1) tc::mma_commit(&bar_gather_go);   // the ring may take rows of the next tile
             }
           }
           fail = __shfl_sync(0xffffffffu, fail, 0);
@@ -488,52 +384,81 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
     if (fail) s_fail = 1;
   } else {
     // ===== working warps =========================================================================================
-    const int q = warp & 3, g = warp >> 2;              // tensor-memory lane quarter (fixed by the warp id), column group
+    const int q = warp & 3, j = warp >> 2;              // tensor-memory lane quarter (fixed by the warp id); edges j mod 4
+    const int g = j;                                    // column group of the node accumulators this warp reads out
     const int ch = q * 32 + lane;                       // product channel = tensor-memory lane in the product phase
     const int row = q * 32 + lane;                      // edge row = tensor-memory lane in the MLP phase
     const uint32_t tmem_row = tmem_base + ((uint32_t)(q * 32) << 16);
-    uint32_t accum_phase = 0, tiles = 0;
-    long long G = 0;
+    uint32_t accum_phase = 0, tiles = 0, nc = 0;
+    float w8[8];
+#pragma unroll
+    for (int m = 0; m < 8; m++) w8[m] = P.enc_w[ch * 8 + m];   // lin_enc of this thread's product channel
+    const float wb = P.enc_b[ch];
+    // this thread's entry of G_e (the four warps of a ring group write all 102 between them)
+    const unsigned gtab = P.gamma_tab[q * 32 + lane];
+    const int g_mono = 8 + ((gtab >> 11) & 15), g_off = 2 * (gtab & 0x7ffu);
+    const bool g_neg = (gtab & 0x8000u) != 0, g_has = gtab != 0xffffu;
+    uint32_t empty_ph = 0;      // bit gs: parity of the next phase to wait for on bar_slot_empty[gs]
     pf.start(P.prof, tid == 0 && blockIdx.x == 0);
     for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
       const BfRange br = bf_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt));
       const int n_begin = br.n_begin, n_end = br.n_end;
-      float acc[16];
-#pragma unroll
-      for (int i = 0; i < 16; i++) acc[i] = 0.f;
       float acc_a = 0.f;
-      int cur = n_begin;          // node whose product sums are running (all working threads agree)
-      int cur_a = n_begin;        // node whose scalar sum is running (threads of column group 0)
+      int cur = -1;               // node whose product sums are accumulating in tensor memory (all working threads agree)
+      int zero_from = n_begin;    // first node whose sums have not been written yet
+      int cur_a = n_begin;        // node whose scalar sum is running (threads of the warps j == 0)
       int node_lo = n_begin;
       asm volatile("barrier.cta.sync 2, %0;" ::"n"(BF_WORK_THREADS) : "memory");
       if (tid <= BF_EDGES) s_rowwin[tid] = P.row_ptr[min(node_lo + tid, n_end > n_begin ? n_end : n_begin)];
+      if (tid == 0) s_prev_src = -1;
       float pre_x = 0.f, pre_y = 0.f, pre_z = 0.f;
+      int pre_j = 0;
       if (tid < BF_EDGES && br.e_begin + tid < br.e_end) {
         const long long en = br.e_begin + tid;
-        pre_x = P.rij[en * 3]; pre_y = P.rij[en * 3 + 1]; pre_z = P.rij[en * 3 + 2];
+        pre_x = P.rij[en * 3]; pre_y = P.rij[en * 3 + 1]; pre_z = P.rij[en * 3 + 2]; pre_j = P.dst[en];
       }
       asm volatile("barrier.cta.sync 2, %0;" ::"n"(BF_WORK_THREADS) : "memory");
+
+      // one node boundary: the node `cur` is complete in its accumulator (the MMA thread has committed it) - read this
+      // thread's sixteen columns, release the buffer, write them; then zeros for the nodes without edges before `next`
+      auto end_node = [&](int next) {
+        float a[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) a[i] = 0.f;
+        if (cur >= 0) {
+          if (!hot_wait(&bar_dfull[nc & 1], (nc >> 1) & 1)) { fail = 1; return; }
+          tc::fence_after_sync();
+          tc::tmem_ld16(tmem_row + (nc & 1) * 64 + g * 16, a);
+          tc::fence_before_sync();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(&bar_dempty[nc & 1]);
+          nc++;
+        }
+        bf_flush_node(g, P.S_v, P.S_d, cur, zero_from, next, ch, P.scale, a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], a[8], a[9],
+                      a[10], a[11], a[12], a[13], a[14], a[15]);
+      };
+
       for (long long e0 = br.e_begin; e0 < br.e_end; e0 += BF_EDGES, tiles++) {
         const int cnt = (int)((br.e_end - e0) < BF_EDGES ? (br.e_end - e0) : BF_EDGES);
         const int groups = (cnt + 1) >> 1;
         // ---- 1. edge geometry: radial functions -> operand of the pa product, monomials of rhat, source node ---------
         if (tid < BF_EDGES) {
           const float gx = pre_x, gy = pre_y, gz = pre_z;
+          const int gj = pre_j;
           {
             const long long en = e0 + BF_EDGES + tid;   // next tile's edge of this thread
-            if (en < br.e_end) { pre_x = P.rij[en * 3]; pre_y = P.rij[en * 3 + 1]; pre_z = P.rij[en * 3 + 2]; }
+            if (en < br.e_end) { pre_x = P.rij[en * 3]; pre_y = P.rij[en * 3 + 1]; pre_z = P.rij[en * 3 + 2]; pre_j = P.dst[en]; }
           }
           int s = -1;
-          float enc[9];
+          float enc[8];
 #pragma unroll
-          for (int m = 0; m < 9; m++) enc[m] = 0.f;
+          for (int m = 0; m < 8; m++) enc[m] = 0.f;
           float rx = 0.f, ry = 0.f, rz = 0.f;
           if (tid < cnt) {
             const long long e = e0 + tid;
             const float d = sqrtf(gx * gx + gy * gy + gz * gz);
             const float zz = d / P.r0;
             ld_radial_cheb8(zz, fmaxf(1.f - zz, 0.f), s_jac, enc);
-            enc[8] = 1.f;   // multiplies lin_enc's bias
             const float sc = 7.f / P.r0;
             const float ux = gx * sc, uy = gy * sc, uz = gz * sc;
             const float inv = rsqrtf(1.f + ux * ux + uy * uy + uz * uz);
@@ -547,78 +472,139 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
             }
           }
           s_src[tid] = s;
-          float4* mp = reinterpret_cast<float4*>(&s_mono[tid][0]);
-          mp[0] = make_float4(1.f, rx, ry, rz);
-          mp[1] = make_float4(rx * rx, rx * ry, rx * rz, ry * ry);
-          mp[2] = make_float4(ry * rz, rz * rz, 0.f, 0.f);
-          // N operand of the pa product, row = edge: [enc_hi (8 functions, 1) | enc_lo | enc_hi | 0]
-          unsigned short rw[32];
-#pragma unroll
-          for (int m = 0; m < 9; m++) {
-            const __nv_bfloat16 hi = __float2bfloat16_rn(enc[m]);
-            const unsigned short h = *reinterpret_cast<const unsigned short*>(&hi);
-            rw[m] = h; rw[18 + m] = h;
-            rw[9 + m] = bf_bf16(enc[m] - __bfloat162float(hi));
-          }
-#pragma unroll
-          for (int m = 27; m < 32; m++) rw[m] = 0;
-#pragma unroll
-          for (int p = 0; p < 4; p++) {
-            uint4 qv;
-            qv.x = rw[p * 8] | ((uint32_t)rw[p * 8 + 1] << 16); qv.y = rw[p * 8 + 2] | ((uint32_t)rw[p * 8 + 3] << 16);
-            qv.z = rw[p * 8 + 4] | ((uint32_t)rw[p * 8 + 5] << 16); qv.w = rw[p * 8 + 6] | ((uint32_t)rw[p * 8 + 7] << 16);
-            *reinterpret_cast<uint4*>(enc_smem + p * (BF_EDGES * 16) + tid * 16) = qv;
-          }
+          s_dst[tid] = tid < cnt ? gj : 0;
+          float4* gp = reinterpret_cast<float4*>(&s_geo[tid][0]);
+          gp[0] = make_float4(enc[0], enc[1], enc[2], enc[3]);
+          gp[1] = make_float4(enc[4], enc[5], enc[6], enc[7]);
+          gp[2] = make_float4(1.f, rx, ry, rz);
+          gp[3] = make_float4(rx * rx, rx * ry, rx * rz, ry * ry);
+          gp[4] = make_float4(ry * rz, rz * rz, 0.f, 0.f);
         }
-        tc::fence_async_smem();
+        // the weight slabs of the previous tile overwrote the G areas of the ring: clear them (32 KB); the entries written
+        // later sit at fixed positions among zeros
+#pragma unroll
+        for (int i = 0; i < (BF_NG * 2 * BF_GAMMA_BYTES / 16) / BF_WORK_THREADS; i++) {
+          const int idx = tid + i * BF_WORK_THREADS;
+          *reinterpret_cast<uint4*>(ring + (idx >> 8) * BF_GROUP_BYTES + 2 * BF_ROW_BYTES + (idx & 255) * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        asm volatile("barrier.cta.sync 2, %0;" ::"n"(BF_WORK_THREADS) : "memory");
+        if (warp == 0) {
+          // boundary list: edges whose source differs from the edge before (the first edge compares with the last edge
+          // of the previous tile of this slice), compacted in order by ballots
+          int n = 0;
+          for (int base = 0; base < cnt; base += 32) {
+            const int e = base + lane;
+            bool isb = false;
+            if (e < cnt) isb = s_src[e] != (e == 0 ? s_prev_src : s_src[e - 1]);
+            const unsigned m = __ballot_sync(0xffffffffu, isb);
+            if (lane == 0) s_bmask[base >> 5] = m;
+            if (isb) s_bnd[n + __popc(m & ((1u << lane) - 1))] = e;
+            n += __popc(m);
+          }
+          __syncwarp();
+          if (lane == 0) { s_nbnd = n; s_prev_src = s_src[cnt - 1]; }
+        }
         tc::fence_before_sync();
         if (bf_sync_or(fail)) { fail = 1; break; }                                        // [B1]
-        if (tid == 0) tc::mbar_arrive(&bar_geom);       // builders may read the monomials of this tile
         pf.lap(0);
-        // ---- 2. products: D_e from tensor memory, times pa, into the running sums / the operand tile -------------
-        if (!tc::mbar_wait(&bar_pa, tiles & 1, wl)) fail = 1;
-        tc::fence_after_sync();
-        pf.lap(1);
+        // ---- 2. products ------------------------------------------------------------------------------------------
+        // This warp: channels 32q..32q+31 of the ring groups (edge pairs) j, j+4, j+8, ...  Per group: the rows of its
+        // next group are requested; for the two edges of this group pa and the three scalar products are formed (FP32),
+        // the scalar products go into the MLP's operand tile, the rows scaled by pa go into the ring as MMA operands.
+        // Node boundaries (listed by the geometry pass) are served BF_YL groups of this warp behind: all sixteen warps
+        // read out their columns of the finished node.
+        {
+          const __nv_bfloat16* rows_c = P.rows + (size_t)ch * 8;
+          uint4 cur_r[4], nxt_r[4];   // two edges x (low, high half) of the group in work and of the next group
+          auto request = [&](int grp, uint4* r) {
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+              const int e = 2 * grp + u;
+              r[2 * u] = make_uint4(0u, 0u, 0u, 0u); r[2 * u + 1] = r[2 * u];
+              if (e < cnt) {
+                const __nv_bfloat16* rp = rows_c + (size_t)s_dst[e] * (2 * BF_C * 8);
+                r[2 * u] = __ldg(reinterpret_cast<const uint4*>(rp));
+                r[2 * u + 1] = __ldg(reinterpret_cast<const uint4*>(rp + BF_C * 8));
+              }
+            }
+          };
+          request(j, cur_r);
+          int bi = 0;                                   // next entry of the tile's boundary list
+          const int nb = s_nbnd;
 #pragma unroll 1
-        for (int grp = 0; grp < groups && !fail; grp++) {
-          const uint32_t d = (uint32_t)(G % BF_ND), duse = (uint32_t)(G / BF_ND);
-          G++;
-          pf.lap(3);
-          if (!hot_wait(&bar_dfull[d], duse & 1)) { fail = 1; break; }
-          pf.lap(2);
-          tc::fence_after_sync();
-          float v[32], pa[2];
-          tc::tmem_ld16x2_2(tmem_row + d * 128 + g * 16, tmem_row + d * 128 + 64 + g * 16, tmem_row + BF_TMEM_PA + 2 * grp, v, pa);
-          pf.lap(16);
-          tc::fence_before_sync();
-          __syncwarp();
-          if (lane == 0) tc::mbar_arrive(&bar_dempty[d]);   // this warp has its copy: the group may be overwritten
-          pf.lap(17);
-          const int e = 2 * grp;
-          const bool two = e + 1 < cnt;
-          const int s0 = s_src[e], s1 = s_src[two ? e + 1 : e];
-          if (s0 != cur) { BF_FLUSH(cur, s0); cur = s0; }
-          if (g == 0) {
-            // columns 0..2 are the scalar products y000, y110, y220 of this (edge, channel)
-            unsigned short* arow = reinterpret_cast<unsigned short*>(a_smem + (size_t)e * 16) + (ch & 7);
-            arow[(ch >> 3) * (BF_PANEL / 2)] = bf_bf16(pa[0] * v[0]);
-            arow[((BF_C + ch) >> 3) * (BF_PANEL / 2)] = bf_bf16(pa[0] * v[1]);
-            arow[((2 * BF_C + ch) >> 3) * (BF_PANEL / 2)] = bf_bf16(pa[0] * v[2]);
-            if (two) {
-              arow[(ch >> 3) * (BF_PANEL / 2) + 8] = bf_bf16(pa[1] * v[16]);
-              arow[((BF_C + ch) >> 3) * (BF_PANEL / 2) + 8] = bf_bf16(pa[1] * v[17]);
-              arow[((2 * BF_C + ch) >> 3) * (BF_PANEL / 2) + 8] = bf_bf16(pa[1] * v[18]);
+          for (int grp = j; grp < groups + 4 * BF_YL && !fail; grp += 4) {
+            if (grp < groups) {
+              request(grp + 4, nxt_r);
+              const int gs = grp & (BF_NG - 1);
+              uint32_t o[2][8];
+#pragma unroll
+              for (int u = 0; u < 2; u++) {
+                const int e = 2 * grp + u;
+                if (e < cnt) {
+                  const float4* gp = reinterpret_cast<const float4*>(&s_geo[e][0]);
+                  const float4 e0v = gp[0], e1v = gp[1], r1 = gp[2], r2 = gp[3], r3 = gp[4];
+                  float pa = wb;
+                  pa = fmaf(e0v.x, w8[0], pa); pa = fmaf(e0v.y, w8[1], pa); pa = fmaf(e0v.z, w8[2], pa); pa = fmaf(e0v.w, w8[3], pa);
+                  pa = fmaf(e1v.x, w8[4], pa); pa = fmaf(e1v.y, w8[5], pa); pa = fmaf(e1v.z, w8[6], pa); pa = fmaf(e1v.w, w8[7], pa);
+                  const uint32_t w[8] = {cur_r[2 * u].x, cur_r[2 * u].y, cur_r[2 * u].z, cur_r[2 * u].w,
+                                         cur_r[2 * u + 1].x, cur_r[2 * u + 1].y, cur_r[2 * u + 1].z, cur_r[2 * u + 1].w};
+                  float l[16];
+#pragma unroll
+                  for (int i = 0; i < 8; i++) { l[2 * i] = __uint_as_float(w[i] << 16); l[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+                  // y000 = l0 pa, y110 = (l1 . r) pa, y220 = (r^T l2 r) pa with the six distinct products of r
+                  const float y1 = l[1] * r1.y + l[2] * r1.z + l[3] * r1.w;
+                  const float y2 = l[4] * r2.x + (l[5] + l[7]) * r2.y + (l[6] + l[10]) * r2.z + l[8] * r2.w + (l[9] + l[11]) * r3.x +
+                                   l[12] * r3.y;
+                  unsigned short* arow = reinterpret_cast<unsigned short*>(a_smem + (size_t)e * 16) + (ch & 7);
+                  arow[(ch >> 3) * (BF_PANEL / 2)] = bf_bf16(pa * l[0]);
+                  arow[((BF_C + ch) >> 3) * (BF_PANEL / 2)] = bf_bf16(pa * y1);
+                  arow[((2 * BF_C + ch) >> 3) * (BF_PANEL / 2)] = bf_bf16(pa * y2);
+#pragma unroll
+                  for (int i = 0; i < 8; i++) o[u][i] = tc::pack_bf16x2(pa * l[2 * i], pa * l[2 * i + 1]);
+                }
+              }
+              pf.lap(3);
+              if (!hot_wait(&bar_slot_empty[gs], (empty_ph >> gs) & 1)) { fail = 1; break; }
+              empty_ph ^= 1u << gs;
+              pf.lap(2);
+#pragma unroll
+              for (int u = 0; u < 2; u++) {
+                if (2 * grp + u < cnt) {
+                  unsigned char* dstp = ring + gs * BF_GROUP_BYTES + u * BF_ROW_BYTES + ch * 16;
+                  *reinterpret_cast<uint4*>(dstp) = make_uint4(o[u][0], o[u][1], o[u][2], o[u][3]);
+                  *reinterpret_cast<uint4*>(dstp + BF_C * 16) = make_uint4(o[u][4], o[u][5], o[u][6], o[u][7]);
+                  if (g_has) {
+                    const float gv = s_geo[2 * grp + u][g_mono];
+                    *reinterpret_cast<unsigned short*>(ring + gs * BF_GROUP_BYTES + 2 * BF_ROW_BYTES + u * BF_GAMMA_BYTES + g_off) =
+                        bf_bf16(g_neg ? -gv : gv);
+                  }
+                }
+              }
+              tc::fence_async_smem();
+              __syncwarp();
+              if (lane == 0) tc::mbar_arrive(&bar_full[gs]);
+#pragma unroll
+              for (int i = 0; i < 4; i++) cur_r[i] = nxt_r[i];
+              pf.lap(3);
+            }
+            // node boundaries up to the last edge of the group stored BF_YL steps ago
+            const int upto = 2 * (grp - 4 * BF_YL) + 1;
+            while (bi < nb && s_bnd[bi] <= upto && !fail) {
+              const int s = s_src[s_bnd[bi]];
+              pf.lap(100); end_node(s); cur = s; zero_from = s + 1; bi++; pf.lap(18);
             }
           }
-#pragma unroll
-          for (int i = 0; i < 16; i++) acc[i] = fmaf(pa[0], v[i], acc[i]);   // (group 0: sums 0..2 are never stored)
-          if (two) {
-            if (s1 != cur) { BF_FLUSH(cur, s1); cur = s1; }
-#pragma unroll
-            for (int i = 0; i < 16; i++) acc[i] = fmaf(pa[1], v[16 + i], acc[i]);
+          // node boundaries among the last edges of the tile
+          while (bi < nb && !fail) {
+            const int s = s_src[s_bnd[bi]];
+            pf.lap(100); end_node(s); cur = s; zero_from = s + 1; bi++; pf.lap(18);
           }
         }
-        pf.lap(3);
+        if (!fail && e0 + BF_EDGES >= br.e_end) {
+          // end of this block's slice: its last node, then the nodes without edges up to the end of the slice
+          end_node(n_end);
+          cur = -1; zero_from = n_end;
+        }
         tc::fence_async_smem();
         tc::fence_before_sync();
         if (bf_sync_or(fail)) { fail = 1; break; }                                        // [B2]
@@ -642,7 +628,7 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
             const int cpp = max(N / 4, 32);
             for (int cb = g * cpp; cb < min((g + 1) * cpp, N); cb += 32) {
               float v[32];
-              tc::tmem_ld32(tmem_row + cb, v);
+              tc::tmem_ld32(tmem_row + BF_TMEM_MLP + cb, v);
 #pragma unroll
               for (int g8 = 0; g8 < 4; g8++) {
                 float t8[8];
@@ -653,9 +639,9 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
                   b8[0] = ba.x; b8[1] = ba.y; b8[2] = ba.z; b8[3] = ba.w; b8[4] = bb.x; b8[5] = bb.y; b8[6] = bb.z; b8[7] = bb.w;
                 }
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                  const float uu = v[g8 * 8 + j] + b8[j];
-                  t8[j] = (act == 2) ? fmaxf(uu, 0.1f * uu) : uu;   // LeakyReLU(0.1)
+                for (int jj = 0; jj < 8; jj++) {
+                  const float uu = v[g8 * 8 + jj] + b8[jj];
+                  t8[jj] = (act == 2) ? fmaxf(uu, 0.1f * uu) : uu;   // LeakyReLU(0.1)
                 }
                 uint4 qv;
                 qv.x = tc::pack_bf16x2(t8[0], t8[1]); qv.y = tc::pack_bf16x2(t8[2], t8[3]);
@@ -673,25 +659,34 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
         // ---- 4. per-node sums of the scalar output: tensor memory holds [channel][edge] after the transposed last
         // layer; one thread per channel adds its row in edge order --------------------------------------------------
         tc::fence_after_sync();
-        if (g == 0) {
+        if (j == 0) {
           const float b3 = s_bias[4 * BF_A + ch];
-          for (int cb = 0; cb < cnt; cb += 32) {
-            float v[32];
-            pf.lap(7);
-            tc::tmem_ld32(tmem_row + cb, v);
-            pf.lap(18);
+#pragma unroll 1
+          for (int cb = 0; cb < cnt; cb += 16) {
+            float v[16];
+            tc::tmem_ld16(tmem_row + BF_TMEM_MLP + cb, v);
+            int sn[16];
 #pragma unroll
-            for (int i = 0; i < 32; i++) {
-              const int e = cb + i;
-              if (e < cnt) {
-                const int s = s_src[e];
-                if (s != cur_a) {
-                  P.out_a[(size_t)cur_a * BF_A + ch] = acc_a * P.scale;
-                  for (int z = cur_a + 1; z < s; z++) P.out_a[(size_t)z * BF_A + ch] = 0.f;
-                  acc_a = 0.f;
-                  cur_a = s;
+            for (int i = 0; i < 4; i++) {
+              const int4 t = *reinterpret_cast<const int4*>(&s_src[cb + 4 * i]);
+              sn[4 * i] = t.x; sn[4 * i + 1] = t.y; sn[4 * i + 2] = t.z; sn[4 * i + 3] = t.w;
+            }
+            if (cb + 16 <= cnt && sn[0] == cur_a && sn[15] == cur_a) {
+              // sixteen edges of the running node (sources are sorted): the same additions in the same order, no tests
+#pragma unroll
+              for (int i = 0; i < 16; i++) acc_a += v[i] + b3;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; i++) {
+                if (cb + i < cnt) {
+                  if (sn[i] != cur_a) {
+                    P.out_a[(size_t)cur_a * BF_A + ch] = acc_a * P.scale;
+                    for (int z = cur_a + 1; z < sn[i]; z++) P.out_a[(size_t)z * BF_A + ch] = 0.f;
+                    acc_a = 0.f;
+                    cur_a = sn[i];
+                  }
+                  acc_a += v[i] + b3;
                 }
-                acc_a += v[i] + b3;
               }
             }
           }
@@ -706,9 +701,12 @@ bee_fused_tc_kernel(const __grid_constant__ BfParams P) {
         pf.lap(8);
       }
       if (!fail && n_begin < n_end) {
-        // last node of the slice, then nodes without edges up to its end
-        BF_FLUSH(cur, n_end);
-        if (g == 0) {
+        if (br.e_begin >= br.e_end) {
+          // a slice without any edge: zeros for all its nodes
+          bf_flush_node(g, P.S_v, P.S_d, -1, n_begin, n_end, ch, P.scale, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f,
+                        0.f, 0.f, 0.f, 0.f);
+        }
+        if (j == 0) {
           P.out_a[(size_t)cur_a * BF_A + ch] = acc_a * P.scale;
           for (int z = cur_a + 1; z < n_end; z++) P.out_a[(size_t)z * BF_A + ch] = 0.f;
         }
@@ -839,8 +837,11 @@ extern "C" int ld_bee_messages_fused_bf16_tc_opt(const int* row_ptr, const int* 
     const int n = build_gamma_entries(ent);
     for (int i = 0; i < BF_GAMMA_ENTRIES; i++) {
       if (i < n) {
-        const int off = (ent[i].m / 8) * (64 * 16) + ent[i].o * 16 + (ent[i].m % 8) * 2;
-        Q.gamma_tab[i] = (unsigned short)(off | (ent[i].mono << 11) | (ent[i].neg << 15));
+        // operand row = sum index (the three scalar products are formed in registers and have no row)
+        const int row = ent[i].o - 3;
+        const int off = (ent[i].m / 8) * (BF_GAMMA_ROWS * 16) + row * 16 + (ent[i].m % 8) * 2;
+        Q.gamma_tab[i] = ent[i].o < 3 ? (unsigned short)0xffffu
+                                      : (unsigned short)((off >> 1) | (ent[i].mono << 11) | (ent[i].neg << 15));
       } else {
         Q.gamma_tab[i] = 0xffffu;
       }

@@ -205,6 +205,53 @@ __device__ __forceinline__ void tmem_ld16x2_2(uint32_t a0, uint32_t a1, uint32_t
   w[0] = __uint_as_float(r[32]); w[1] = __uint_as_float(r[33]);
 }
 
+// four columns at a0 plus one column at a1, one wait for both
+__device__ __forceinline__ void tmem_ld4_1(uint32_t a0, uint32_t a1, float* v, float* w) {
+  uint32_t r[5];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%5];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x1.b32 {%4}, [%6];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4])
+      : "r"(a0), "r"(a1)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 4; i++) v[i] = __uint_as_float(r[i]);
+  w[0] = __uint_as_float(r[4]);
+}
+// four consecutive columns
+__device__ __forceinline__ void tmem_ld4(uint32_t a0, float* v) {
+  uint32_t r[4];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a0) : "memory");
+#pragma unroll
+  for (int i = 0; i < 4; i++) v[i] = __uint_as_float(r[i]);
+}
+// one column
+__device__ __forceinline__ float tmem_ld1(uint32_t a0) {
+  uint32_t r;
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r) : "r"(a0) : "memory");
+  return __uint_as_float(r);
+}
+// sixteen consecutive columns
+__device__ __forceinline__ void tmem_ld16(uint32_t a0, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(a0)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+
 // four 8-column groups at column offsets 0, stride, 2*stride, 3*stride, one wait for all
 __device__ __forceinline__ void tmem_ld8x4(uint32_t taddr, uint32_t stride, float* v) {
   uint32_t r[32];

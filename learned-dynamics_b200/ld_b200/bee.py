@@ -93,7 +93,10 @@ class Messages(nn.Module):
         self._packed = None
         self._packed_key = None
         self.precision = "fp32"  # "bf16": scalar channel on the tensor cores (2e-2 relative)
-        self.fused_kernel = True  # bf16, chan = dim_a = 128: one edge kernel per layer (False: the two-kernel path)
+        # bf16, chan = dim_a = 128: True runs the layer as ONE edge kernel (rows gathered once, per-node sums accumulated
+        # by the tensor cores). Correct and deterministic, but measured slower than the two-kernel path on B200 (its
+        # per-edge synchronisation leaves the warps latency-bound), so it is opt-in.
+        self.fused_kernel = False
 
     def load_state_dict(self, state, *a, **k):
         # the reference wraps mlp_a in torch.compile, which prefixes its keys

@@ -192,6 +192,7 @@ def test_messages_single_edge_kernel_vs_oracle_and_two_kernel_path(B, N, r0, box
     with torch.no_grad():
         graph = GL.Graph.radius_graph(r0, box, pos.cuda())
         args = (graph, graph.rij, x_a.cuda(), x_v.cuda(), x_d.cuda())
+        mes.fused_kernel = True
         got = mes(*args)
         again = mes(*args)
         mes.fused_kernel = False
