@@ -133,7 +133,7 @@ bee_scalar_tc_kernel(BtParams P) {
   __shared__ uint32_t tmem_slot;
   __shared__ BtGeom s_geom[BT_EDGES];
   __shared__ int s_dst[BT_EDGES];
-  __shared__ int s_src[BT_EDGES];
+  __shared__ __align__(16) int s_src[BT_EDGES];
   __shared__ int s_rowwin[BT_EDGES + 1];
   __shared__ float s_jac[72];
 
@@ -207,7 +207,10 @@ bee_scalar_tc_kernel(BtParams P) {
             // everything that is constant over the layer is computed once: the issuing thread runs alone in its warp,
             // so every instruction between two MMAs is exposed latency
             const int l_ksteps = P.layer[l].ksteps, l_slab = P.layer[l].slab_ksteps, l_N = P.layer[l].N;
-            const uint32_t idesc = tc::idesc_bf16(BT_EDGES, l_N);
+            // dim_a = 128: the last layer is issued transposed (weights as the M operand, the tile as the N operand), so its
+            // result lies in tensor memory as [channel][edge] and the per-node sum is a walk along columns in one thread
+            const bool transposed = l == BT_LAYERS - 1 && A == 128;
+            const uint32_t idesc = transposed ? tc::idesc_bf16(l_N, BT_EDGES) : tc::idesc_bf16(BT_EDGES, l_N);
             uint64_t ad = tc::smem_desc(a_base + P.layer[l].a_panel * BT_PANEL, BT_PANEL, 128);
             const uint64_t a_step = (uint64_t)((2 * BT_PANEL) >> 4), b_step = (uint64_t)((2 * l_N * 16) >> 4);
             uint32_t accumulate = 0u;
@@ -219,7 +222,8 @@ bee_scalar_tc_kernel(BtParams P) {
               const int nk = min(l_slab, l_ksteps - ks0);
 #pragma unroll 4
               for (int kk = 0; kk < nk; kk++) {
-                tc::mma_bf16(tmem_base, ad, bd, idesc, accumulate);
+                if (transposed) tc::mma_bf16(tmem_base, bd, ad, idesc, accumulate);
+                else tc::mma_bf16(tmem_base, ad, bd, idesc, accumulate);
                 accumulate = 1u;
                 ad += a_step;   // the address field of a descriptor counts 16-byte units: next K-step = two panels on
                 bd += b_step;
@@ -417,10 +421,47 @@ bee_scalar_tc_kernel(BtParams P) {
           if (l < BT_LAYERS - 1) lap(3 + 2 * l);
         }
         if (fail) break;
-        // ---- 4. last layer's accumulators -> staging -> per-node sums -----------------------------------------
+        // ---- 4. last layer's accumulators -> per-node sums ---------------------------------------------------------
         const int tile_cur = cur;
         node_lo = s_src[cnt - 1];
         if (tid <= BT_EDGES) s_rowwin[tid] = P.row_ptr[min(node_lo + tid, n_end)];
+        if (A == 128) {
+          // transposed last layer: thread tid < 128 owns channel tid (its tensor-memory lane) and adds the tile's edges
+          // (columns) in order, carrying the sum of the node that continues from the previous tile. The order of the
+          // additions depends on the node's edge list alone, so a system's result does not depend on its batch.
+          if (tid < A) {
+            const float b3 = s_bias[4 * A + tid];
+            int c_node = tile_cur;
+            float a_sum = acc;
+#pragma unroll 1
+            for (int cb = 0; cb < cnt; cb += 16) {
+              float v[16];
+              tc::tmem_ld16(tmem_row + cb, v);
+              int sn[16];
+#pragma unroll
+              for (int i = 0; i < 4; i++) {
+                const int4 t = *reinterpret_cast<const int4*>(&s_src[cb + 4 * i]);
+                sn[4 * i] = t.x; sn[4 * i + 1] = t.y; sn[4 * i + 2] = t.z; sn[4 * i + 3] = t.w;
+              }
+              if (cb + 16 <= cnt && sn[0] == c_node && sn[15] == c_node) {
+#pragma unroll
+                for (int i = 0; i < 16; i++) a_sum += v[i] + b3;   // sixteen edges of the running node (sources are sorted)
+              } else {
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                  if (cb + i < cnt) {
+                    if (sn[i] != c_node) { flush_until(c_node, sn[i], a_sum); a_sum = 0.f; c_node = sn[i]; }
+                    a_sum += v[i] + b3;
+                  }
+                }
+              }
+            }
+            acc = a_sum;
+            cur = c_node;
+          }
+          tc::fence_before_sync();
+          lap(9);
+        } else {
         {
           const float* bias = s_bias + 4 * A;
           const int cpp = max(A / 4, 32);
@@ -459,6 +500,7 @@ bee_scalar_tc_kernel(BtParams P) {
           }
           acc = a_sum;
           cur = c_node;
+        }
         }
         if (bt_sync_or(fail)) { fail = 1; break; }                                        // [B7]
         lap(10);
