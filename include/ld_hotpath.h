@@ -144,6 +144,13 @@ int ld_linear_bf16_tc_in16(const void* x_bf16, long long rows_outer, int K, int 
 int ld_linear_bf16_tc_out16(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias, int N,
                             int act, void* y_bf16, long long ld_row, long long ld_col, int off, int* status_dev, void* stream);
 
+/* ld_linear_bf16_tc_out16 with a two-piece component axis (components s >= s_split land s_jump elements further on) and,
+ * with in_cm != 0, component-major FP32 activations x [rows_outer][S][K]. Writes the gather layouts of the fused l<=2
+ * edge kernels; same reference operator as ld_linear_bf16_tc. */
+int ld_linear_bf16_tc_out16_split(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias, int N,
+                                  int act, void* y_bf16, long long ld_row, long long ld_col, int off, int s_split,
+                                  long long s_jump, int in_cm, int* status_dev, void* stream);
+
 /* Self-test of the bounded waits (no counterpart in the reference): ld_linear_bf16_tc (S = 1, no bias) on a launch
  * whose weight panels are never requested and whose waits give up after 64 polls. Every block leaves through the
  * failure path: *status_dev receives LD_FLAG_TIMEOUT, tensor memory is released, y stays unwritten, the device stays
@@ -260,6 +267,33 @@ int ld_ant16_contract_out(int product, const float* U, const float* dy, long lon
                           void* stream);
 int ld_tensor_prod_bare(int mode, int inds_l, int inds_r, int inds_o, const float* a, const float* b, long long n, float* out,
                         void* stream);
+
+/* ---- the l<=2 message layer as ONE edge kernel (chan = 128, dim_a = 128; BF16 tensor-core path, 2e-2 relative) ------
+ * Messages.forward (archs/diffuser_atoms15.py:227-253) with every neighbour row gathered once: rows [Nt][2][128][8] BF16
+ * (per node and channel l0, l1[3], l2[0..3] | l2[4..8], three zeros; written by ld_linear_bf16_tc_out16 / _split), the
+ * per-node sums of the rank-1 / rank-2 products accumulated by tcgen05 MMAs in tensor memory. out_a [Nt][128] FP32;
+ * S_v [Nt][3][640], S_d [Nt][9][640] BF16 as from ld_bee_messages_vd_f32 (out_bf16). Other arguments as
+ * ld_bee_messages_scalar_bf16_tc. Measured slower than the two-kernel path on B200; kept as an option.
+ * ld_bee_gamma_table: the (column, left component, monomial, sign) table of the products as a matrix product, for host
+ * checks against the reference's einsum definitions (managan/codegen_tensor_products.py:235-249); returns the count. */
+int ld_bee_messages_fused_bf16_tc(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, int dim_a, float r0,
+                                  const void* rows, const float* enc_w, const float* enc_b, const float* jacobi, const void* Yp,
+                                  const void* W1p, const float* b1, const void* W2p, const float* b2, const void* W3p,
+                                  const float* b3, float scale, float* out_a, void* S_v, void* S_d, int* status_dev,
+                                  void* stream);
+int ld_bee_gamma_table(int* out);
+
+/* ---- component-major activations (no counterpart in the reference, whose tensors are [.., chan, 3^l]) -------------
+ * Between fused stages the vector / rank-2 node features can be kept as [node][component][chan]: every (node,
+ * component) pair is then a plain GEMM row, and the channel mixings above take them without strided access:
+ * ld_linear_bf16_tc_out16_split (in_cm = 1) reads them, ld_linear_bf16_tc / _in16 with S = 1 over rows*3^l rows write
+ * them. The two operators below are the node-local ones in that layout: TensGroupNorm (managan/tensor_products.py:215-232)
+ * and the Bee products of SelfTensProds (archs/diffuser_atoms15.py:59-95), results identical to their
+ * [.., chan, 3^l] forms element for element. */
+int ld_group_norm_cm(const float* x, int B, int N, int C, int S, int groups, int center, float eps, const float* gamma,
+                     const float* beta, float* y, void* workspace, void* stream);
+int ld_bee_self_products_cm(const float* lr0, const float* lr1, const float* lr2, long long rows, int chan, float* P_a,
+                            void* P_v, void* P_d, void* stream);
 
 #ifdef __cplusplus
 }

@@ -25,6 +25,7 @@ constexpr int GT_A_STAGE = GT_ROWS * GT_KC * 2;  // bytes
 struct GemmParams {
   const float* x; float* y;
   int in_bf16;               // x holds BF16 values laid out [rows_outer][S][K] (K contiguous per GEMM row, K % 8 == 0)
+  int in_cm;                 // x holds FP32 values laid out [rows_outer][S][K] (component-major: K contiguous per GEMM row)
   const __nv_bfloat16* wp;   // packed weights [nchunks][8 panels][N][8]
   const float* bias;
   long long rows;            // logical rows = rows_outer * S
@@ -87,7 +88,7 @@ gemm_tc_kernel(GemmParams P) {
     const bool row_ok = row < P.rows;
     const long long ro = row_ok ? row / S : 0;
     const int rs = row_ok ? (int)(row - ro * S) : 0;
-    const float* xrow = P.x + (ro * K) * S + rs;
+    const float* xrow = P.in_cm ? P.x + row * K : P.x + (ro * K) * S + rs;
     const __nv_bfloat16* xrow16 = reinterpret_cast<const __nv_bfloat16*>(P.x) + row * K;
     for (int c = 0; c < nchunks; c++, g++) {
       const int st = g & 1;
@@ -170,7 +171,7 @@ gemm_tc_kernel(GemmParams P) {
     // S == 1 with the plain [rows][N] layout: a thread owns a row, so direct stores would put every 4-byte value
     // of a warp into a different sector; 32-column slices go through shared memory (the operand stages are idle
     // once the accumulators are complete) and leave as 128-byte rows
-    const bool staged = UNIT && (!P.out_bf16 || (P.y_ld_col == 1 && P.y_ld_row == N && P.y_off == 0));
+    const bool staged = UNIT && S == 1 && (!P.out_bf16 || (P.y_ld_col == 1 && P.y_ld_row == N && P.y_off == 0));
     float* stage_f = reinterpret_cast<float*>(smem);   // [128 rows][33]
     for (int cb = 0; cb < N; cb += 32) {
       float v[32];
@@ -255,7 +256,7 @@ extern "C" int ld_pack_weights_bf16(const float* W, long long sw0, long long sw1
 static int linear_tc_launch(const float* x, int in_bf16, long long rows_outer, int K, int S, const void* wp, const float* bias, int N, int act,
                             void* y, int out_bf16, long long ld_row, long long ld_col, int off, int* status_dev, void* stream,
                             uint32_t wait_limit = tc::TC_WAIT_LIMIT, int selftest_no_weights = 0, int s_split = 1 << 30,
-                            long long s_jump = 0) {
+                            long long s_jump = 0, int in_cm = 0) {
   if (rows_outer < 0 || K <= 0 || N <= 0 || (S != 1 && S != 3 && S != 9)) return LD_ERR_SHAPE;
   if (N % 32 != 0 || N > 512) { ld_set_last_message("tensor-core linear: N must be a multiple of 32, at most 512"); return LD_ERR_UNSUPPORTED; }
   if (((uintptr_t)wp) % 16 != 0) { ld_set_last_message("tensor-core linear: packed weights must be 16-byte aligned"); return LD_ERR_SHAPE; }
@@ -267,9 +268,11 @@ static int linear_tc_launch(const float* x, int in_bf16, long long rows_outer, i
   GemmParams P;
   P.x = x; P.in_bf16 = in_bf16; P.y = (float*)y; P.out_bf16 = out_bf16; P.y_ld_row = ld_row; P.y_ld_col = ld_col; P.y_off = off; P.wp = (const __nv_bfloat16*)wp; P.bias = bias; P.rows = rows_outer * S; P.K = K; P.N = N; P.S = S;
   P.act = act; P.status = status_dev; P.wait_limit = wait_limit; P.selftest_no_weights = selftest_no_weights;
-  P.y_s_split = s_split; P.y_s_jump = s_jump;
+  P.y_s_split = s_split; P.y_s_jump = s_jump; P.in_cm = in_cm;
   const size_t smem = 2 * GT_A_STAGE + 2 * (size_t)N * GT_KC * 2 + 1024;
-  const bool unit = !in_bf16 && S == 1 && (K & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  // rows of K contiguous floats (plain rows, or component-major activations): 16-byte loads along the row
+  const bool unit = !in_bf16 && (S == 1 || in_cm) && (K & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  if (in_cm && !unit) { ld_set_last_message("tensor-core linear: component-major input needs K a multiple of 4 and a 16-byte aligned base"); return LD_ERR_UNSUPPORTED; }
   auto kern = unit ? gemm_tc_kernel<true, false> : (in_bf16 ? gemm_tc_kernel<false, true> : gemm_tc_kernel<false, false>);
   LD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const long long ntiles = (P.rows + GT_ROWS - 1) / GT_ROWS;
@@ -309,11 +312,13 @@ extern "C" int ld_linear_bf16_tc_out16(const float* x, long long rows_outer, int
 // The fused l<=2 message kernel gathers its left operands as two 16-byte halves per (node, channel), laid out
 // [node][half][channel][8] (values l0, l1[3], l2[0..3] | l2[4..8], three zeros): rank 2 goes there with ld_row = 16*N,
 // ld_col = 8, off = 4, s_split = 4, s_jump = 8*N - 8.
+// in_cm != 0: the activations are component-major FP32, x [rows_outer][S][K] (a (row, component) pair is K contiguous
+// floats: 16-byte loads instead of element-strided ones); the output addressing is unchanged.
 extern "C" int ld_linear_bf16_tc_out16_split(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias,
                                              int N, int act, void* y_bf16, long long ld_row, long long ld_col, int off,
-                                             int s_split, long long s_jump, int* status_dev, void* stream) {
+                                             int s_split, long long s_jump, int in_cm, int* status_dev, void* stream) {
   return linear_tc_launch(x, 0, rows_outer, K, S, wp, bias, N, act, y_bf16, 1, ld_row, ld_col, off, status_dev, stream,
-                          tc::TC_WAIT_LIMIT, 0, s_split, s_jump);
+                          tc::TC_WAIT_LIMIT, 0, s_split, s_jump, in_cm);
 }
 
 // ld_linear_bf16_tc with the activations already stored as BF16, component-major: x_bf16 [rows_outer][S][K] (K

@@ -27,28 +27,31 @@ __device__ __forceinline__ float gn_block_sum(float v, float* red) {
 
 // One block per (system, group, chunk of nodes): count, mean and sum of squared deviations from that mean of the chunk
 // (two passes over the chunk; not centred: mean = 0). part[((b*G + g)*nchunks + k)*3 + {0,1,2}].
+// cm != 0: x is component-major, [B][N][S][C]: a node holds S runs of cpg contiguous floats of the group, C apart
 __global__ void __launch_bounds__(GN_THREADS) gn_partial_kernel(const float* __restrict__ x, int N, int C, int S, int G, int center,
-                                                               int nchunks, float* __restrict__ part) {
+                                                               int nchunks, int cm, float* __restrict__ part) {
   __shared__ float red[GN_THREADS / 32];
   const int bg = blockIdx.x, b = bg / G, g = bg % G, kc = blockIdx.y;
-  const int cpg = C / G, slab = cpg * S;            // contiguous floats per node
+  const int cpg = C / G, slab = cpg * S;            // floats of the group per node
+  const int run = cm ? cpg : slab, run_stride = cm ? C : 0;   // contiguous run, distance between the runs of a node
   const int per = (N + nchunks - 1) / nchunks;
   const int n0 = kc * per, n1 = min(N, n0 + per);
   const long long total = (long long)max(n1 - n0, 0) * slab;
-  const float* base = x + (((size_t)b * N + n0) * C + (size_t)g * cpg) * S;
+  const float* base = cm ? x + ((size_t)b * N + n0) * C * S + (size_t)g * cpg : x + (((size_t)b * N + n0) * C + (size_t)g * cpg) * S;
+  auto at = [&](long long i) -> float {
+    const long long n = i / slab;
+    const int rem = (int)(i - n * slab), r = rem / run;
+    return base[(size_t)n * C * S + (size_t)r * run_stride + (rem - r * run)];
+  };
   float mean = 0.f;
   if (center && total > 0) {
     float s = 0.f;
-    for (long long i = threadIdx.x; i < total; i += GN_THREADS) {
-      const long long n = i / slab;
-      s += base[(size_t)n * C * S + (i - n * slab)];
-    }
+    for (long long i = threadIdx.x; i < total; i += GN_THREADS) s += at(i);
     mean = gn_block_sum(s, red) / (float)total;
   }
   float q = 0.f;
   for (long long i = threadIdx.x; i < total; i += GN_THREADS) {
-    const long long n = i / slab;
-    const float d = base[(size_t)n * C * S + (i - n * slab)] - mean;
+    const float d = at(i) - mean;
     q = fmaf(d, d, q);
   }
   q = gn_block_sum(q, red);
@@ -80,14 +83,13 @@ __global__ void gn_finalize_kernel(const float* __restrict__ part, int BG, int n
   stats[(size_t)bg * 2 + 1] = 1.0f / sqrtf(eps + second);
 }
 
-__global__ void __launch_bounds__(256) gn_apply_kernel(const float* __restrict__ x, long long total, int N, int C, int S, int G,
+__global__ void __launch_bounds__(256) gn_apply_kernel(const float* __restrict__ x, long long total, int N, int C, int S, int G, int cm,
                                                        const float* __restrict__ stats, const float* __restrict__ gamma,
                                                        const float* __restrict__ beta, float* __restrict__ y) {
   const int cpg = C / G;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long cs = i / S;              // (b, n, c)
-    const int c = (int)(cs % C);
-    const long long b = cs / ((long long)N * C);
+    const int c = cm ? (int)(i % C) : (int)((i / S) % C);
+    const long long b = i / ((long long)N * C * S);
     const float* st = stats + ((size_t)b * G + c / cpg) * 2;
     const float v = (x[i] - st[0]) * st[1] * gamma[c];
     y[i] = beta != nullptr ? v + beta[c] : v;
@@ -98,8 +100,9 @@ __global__ void __launch_bounds__(256) gn_apply_kernel(const float* __restrict__
 
 // x, y: [B][N][C][S]; gamma [C]; beta [C] or NULL; center != 0 subtracts the group mean (ScalGroupNorm, S = 1).
 // workspace: 98 * B * groups floats of device memory (statistics per system and group + up to 32 chunk partials).
-extern "C" int ld_group_norm(const float* x, int B, int N, int C, int S, int groups, int center, float eps, const float* gamma,
-                             const float* beta, float* y, void* workspace, void* stream) {
+// ld_group_norm_cm: the same for component-major activations, x and y [B][N][S][C].
+static int group_norm_launch(const float* x, int B, int N, int C, int S, int groups, int center, float eps, const float* gamma,
+                             const float* beta, float* y, void* workspace, void* stream, int cm) {
   if (B < 0 || N <= 0 || C <= 0 || S <= 0 || groups <= 0 || C % groups != 0) return LD_ERR_SHAPE;
   if (center && S != 1) { ld_set_last_message("group norm: the centred form is defined for scalars (S = 1)"); return LD_ERR_SHAPE; }
   if (B == 0) return LD_OK;
@@ -114,14 +117,24 @@ extern "C" int ld_group_norm(const float* x, int B, int N, int C, int S, int gro
   if (nchunks > 32) nchunks = 32;
   if (nchunks > N) nchunks = N;
   if (nchunks < 1) nchunks = 1;
-  gn_partial_kernel<<<dim3(B * groups, nchunks), GN_THREADS, 0, st>>>(x, N, C, S, groups, center, nchunks, part);
+  gn_partial_kernel<<<dim3(B * groups, nchunks), GN_THREADS, 0, st>>>(x, N, C, S, groups, center, nchunks, cm, part);
   LD_LAUNCH_CHECK();
   gn_finalize_kernel<<<(B * groups + 127) / 128, 128, 0, st>>>(part, B * groups, nchunks, center, (long long)N * (C / groups), eps, stats);
   LD_LAUNCH_CHECK();
   const long long total = (long long)B * N * C * S;
   long long blocks = (total + 255) / 256;
   if (blocks > 148LL * 32) blocks = 148LL * 32;
-  gn_apply_kernel<<<(unsigned)blocks, 256, 0, st>>>(x, total, N, C, S, groups, stats, gamma, beta, y);
+  gn_apply_kernel<<<(unsigned)blocks, 256, 0, st>>>(x, total, N, C, S, groups, cm, stats, gamma, beta, y);
   LD_LAUNCH_CHECK();
   return LD_OK;
+}
+
+extern "C" int ld_group_norm(const float* x, int B, int N, int C, int S, int groups, int center, float eps, const float* gamma,
+                             const float* beta, float* y, void* workspace, void* stream) {
+  return group_norm_launch(x, B, N, C, S, groups, center, eps, gamma, beta, y, workspace, stream, 0);
+}
+
+extern "C" int ld_group_norm_cm(const float* x, int B, int N, int C, int S, int groups, int center, float eps, const float* gamma,
+                                const float* beta, float* y, void* workspace, void* stream) {
+  return group_norm_launch(x, B, N, C, S, groups, center, eps, gamma, beta, y, workspace, stream, 1);
 }

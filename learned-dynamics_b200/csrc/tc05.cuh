@@ -219,6 +219,24 @@ __device__ __forceinline__ void tmem_ld4_1(uint32_t a0, uint32_t a1, float* v, f
   for (int i = 0; i < 4; i++) v[i] = __uint_as_float(r[i]);
   w[0] = __uint_as_float(r[4]);
 }
+// sixteen consecutive columns, split into request and wait, so that work on an earlier block of columns can run while
+// the request is in flight. The wait names the registers as read-write operands: nothing that uses them may be moved
+// in front of it.
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t a0, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(a0)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16_wait(uint32_t* r) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
 // four consecutive columns
 __device__ __forceinline__ void tmem_ld4(uint32_t a0, float* v) {
   uint32_t r[4];

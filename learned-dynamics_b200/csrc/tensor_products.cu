@@ -161,7 +161,8 @@ __device__ __forceinline__ void sp_store(OT* __restrict__ g, float* wbuf, int la
   __syncwarp();
 }
 
-template <typename OT>
+// CM: lr1 / lr2 are component-major, [rows][3][2*chan] and [rows][9][2*chan] (lanes read consecutive addresses)
+template <typename OT, bool CM>
 __global__ void __launch_bounds__(SP_WARPS * 32)
 bee_self_products_kernel(const float* __restrict__ lr0, const float* __restrict__ lr1, const float* __restrict__ lr2,
                          long long rows, int C, float* __restrict__ P_a, OT* __restrict__ P_v, OT* __restrict__ P_d) {
@@ -176,10 +177,19 @@ bee_self_products_kernel(const float* __restrict__ lr0, const float* __restrict_
     const size_t in = (size_t)row * 2 * C + c0;     // left operand of channel c0 (right: + C)
     float l1[3], l2[9], r1[3], r2[9];
     const float l0 = __ldg(lr0 + in + lane), r0 = __ldg(lr0 + in + C + lane);
-    sp_load<3>(lr1 + in * 3, wbuf, lane, l1);
-    sp_load<3>(lr1 + (in + C) * 3, wbuf, lane, r1);
-    sp_load<9>(lr2 + in * 9, wbuf, lane, l2);
-    sp_load<9>(lr2 + (in + C) * 9, wbuf, lane, r2);
+    if (CM) {
+      const float* p1 = lr1 + (size_t)row * 3 * 2 * C + c0 + lane;
+      const float* p2 = lr2 + (size_t)row * 9 * 2 * C + c0 + lane;
+#pragma unroll
+      for (int x = 0; x < 3; x++) { l1[x] = __ldg(p1 + (size_t)x * 2 * C); r1[x] = __ldg(p1 + (size_t)x * 2 * C + C); }
+#pragma unroll
+      for (int x = 0; x < 9; x++) { l2[x] = __ldg(p2 + (size_t)x * 2 * C); r2[x] = __ldg(p2 + (size_t)x * 2 * C + C); }
+    } else {
+      sp_load<3>(lr1 + in * 3, wbuf, lane, l1);
+      sp_load<3>(lr1 + (in + C) * 3, wbuf, lane, r1);
+      sp_load<9>(lr2 + in * 9, wbuf, lane, l2);
+      sp_load<9>(lr2 + (in + C) * 9, wbuf, lane, r2);
+    }
     BeeOut o;
     bee_fwd_point(l0, l1, l2, r0, r1, r2, &o);
     float* pa = P_a + (size_t)row * 3 * C + c0 + lane;
@@ -220,22 +230,37 @@ bee_self_products_kernel(const float* __restrict__ lr0, const float* __restrict_
 // [chan, 2*chan). Outputs as described at bee_self_products_kernel. chan a multiple of 32.
 // out_bf16: P_v and P_d are BF16 and component-major, [rows][3][5*chan] and [rows][9][5*chan] (the input form of
 // ld_linear_bf16_tc_in16); P_a stays FP32.
-extern "C" int ld_bee_self_products(const float* lr0, const float* lr1, const float* lr2, long long rows, int chan, float* P_a,
-                                    void* P_v, void* P_d, int out_bf16, void* stream) {
+// ld_bee_self_products_cm: lr1 / lr2 component-major, [rows][3][2*chan] and [rows][9][2*chan]; BF16 outputs only.
+static int self_products_launch(const float* lr0, const float* lr1, const float* lr2, long long rows, int chan, float* P_a,
+                                void* P_v, void* P_d, int out_bf16, int in_cm, void* stream) {
   if (rows < 0 || chan <= 0) return LD_ERR_SHAPE;
   if (chan % 32 != 0) { ld_set_last_message("bee self products: chan must be a multiple of 32"); return LD_ERR_UNSUPPORTED; }
   if (rows == 0) return LD_OK;
   const long long items = rows * (chan / 32);
   long long blocks = (items + SP_WARPS - 1) / SP_WARPS;
   if (blocks > 148LL * 16) blocks = 148LL * 16;
-  if (out_bf16)
-    bee_self_products_kernel<__nv_bfloat16><<<(unsigned)blocks, SP_WARPS * 32, 0, (cudaStream_t)stream>>>(
+  if (in_cm && !out_bf16) { ld_set_last_message("bee self products: component-major inputs come with BF16 outputs"); return LD_ERR_UNSUPPORTED; }
+  if (in_cm)
+    bee_self_products_kernel<__nv_bfloat16, true><<<(unsigned)blocks, SP_WARPS * 32, 0, (cudaStream_t)stream>>>(
+        lr0, lr1, lr2, rows, chan, P_a, (__nv_bfloat16*)P_v, (__nv_bfloat16*)P_d);
+  else if (out_bf16)
+    bee_self_products_kernel<__nv_bfloat16, false><<<(unsigned)blocks, SP_WARPS * 32, 0, (cudaStream_t)stream>>>(
         lr0, lr1, lr2, rows, chan, P_a, (__nv_bfloat16*)P_v, (__nv_bfloat16*)P_d);
   else
-    bee_self_products_kernel<float><<<(unsigned)blocks, SP_WARPS * 32, 0, (cudaStream_t)stream>>>(lr0, lr1, lr2, rows, chan, P_a,
-                                                                                                  (float*)P_v, (float*)P_d);
+    bee_self_products_kernel<float, false><<<(unsigned)blocks, SP_WARPS * 32, 0, (cudaStream_t)stream>>>(lr0, lr1, lr2, rows, chan, P_a,
+                                                                                                         (float*)P_v, (float*)P_d);
   LD_LAUNCH_CHECK();
   return LD_OK;
+}
+
+extern "C" int ld_bee_self_products(const float* lr0, const float* lr1, const float* lr2, long long rows, int chan, float* P_a,
+                                    void* P_v, void* P_d, int out_bf16, void* stream) {
+  return self_products_launch(lr0, lr1, lr2, rows, chan, P_a, P_v, P_d, out_bf16, 0, stream);
+}
+
+extern "C" int ld_bee_self_products_cm(const float* lr0, const float* lr1, const float* lr2, long long rows, int chan, float* P_a,
+                                       void* P_v, void* P_d, void* stream) {
+  return self_products_launch(lr0, lr1, lr2, rows, chan, P_a, P_v, P_d, 1, 1, stream);
 }
 
 // rows*chan elements per rank-0 operand; operands are contiguous [rows, chan, (3,)^l] float32.

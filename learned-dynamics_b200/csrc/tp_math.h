@@ -157,6 +157,16 @@ LD_HD void ld_poly8_to_chebyshev(const float* a, float* c) {
   for (int n = 0; n < 9; n++) c[n] = (float)p[n];
 }
 
+// one polynomial of the Chebyshev form: t = 2z - 1, t2 = 2t, c its nine coefficients
+LD_HD float ld_cheb9(float t, float t2, const float* c) {
+  float b1 = 0.f, b2 = 0.f;
+  for (int k = 8; k >= 1; k--) {
+    const float b0 = fmaf(t2, b1, c[k] - b2);
+    b2 = b1; b1 = b0;
+  }
+  return fmaf(t, b1, c[0]) - b2;
+}
+
 LD_HD void ld_radial_cheb8(float z, float env, const float* cheb, float* enc) {
   const float t = 2.f * z - 1.f, t2 = 2.f * t;
   for (int m = 0; m < 8; m++) {

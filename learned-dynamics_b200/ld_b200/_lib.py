@@ -38,7 +38,9 @@ SIGNATURES = {
     "ld_pack_weights_bf16": [P, LL, LL, I, I, P, P],
     "ld_linear_bf16_tc": [P, LL, I, I, P, P, I, I, P, P, P],
     "ld_linear_bf16_tc_out16": [P, LL, I, I, P, P, I, I, P, LL, LL, I, P, P],
-    "ld_linear_bf16_tc_out16_split": [P, LL, I, I, P, P, I, I, P, LL, LL, I, I, LL, P, P],
+    "ld_linear_bf16_tc_out16_split": [P, LL, I, I, P, P, I, I, P, LL, LL, I, I, LL, I, P, P],
+    "ld_group_norm_cm": [P, I, I, I, I, I, I, F, P, P, P, P, P],
+    "ld_bee_self_products_cm": [P, P, P, LL, I, P, P, P, P],
     "ld_bee_messages_fused_bf16_tc": [P, P, P, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P, F, P, P, P, P, P],
     "ld_bee_gamma_table": [P],
     "ld_painn_message_bf16_tc": [P, P, P, I, I, I, I, F, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, P],

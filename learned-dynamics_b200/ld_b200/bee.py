@@ -155,6 +155,41 @@ class Messages(nn.Module):
         B_d = ops.linear_bf16_tc_cm(S_d, w["Ydp"], self.dim_d, 2)
         return (B_a.reshape(batch, nodes, -1), B_v.reshape(batch, nodes, -1, 3), B_d.reshape(batch, nodes, -1, 3, 3))
 
+    def cm_ready(self):
+        """the tensor-core path that takes component-major activations applies (widths in whole tensor-core tiles)"""
+        return (self.precision == "bf16" and self.chan % 32 == 0 and self.chan <= 512 and self.dim_a in (64, 128)
+                and self.dim_v % 32 == 0 and self.dim_d % 32 == 0 and self.dim_v % 4 == 0 and self.dim_d % 4 == 0)
+
+    def forward_cm(self, graph, r_ij, x_a, x_v, x_d):
+        """forward for component-major activations, x_v [B, N, 3, dim_v], x_d [B, N, 9, dim_d] (results in the same
+        form): every channel mixing then works on plain rows (16-byte loads, coalesced stores)."""
+        batch, nodes = x_a.shape[0], x_a.shape[1]
+        Nt, C, dev = batch * nodes, self.chan, x_a.device
+        w = self._pack()
+        pk = lambda m: m._packed_for(ops)
+        lp = torch.empty(Nt, C, 16, dtype=torch.bfloat16, device=dev)
+        ops.linear_bf16_tc(x_a.reshape(Nt, -1), pk(self.L0), C, inds=0, out=lp, out_layout=(16 * C, 16, 0))
+        ops.linear_bf16_tc(x_v.reshape(Nt, 3, -1), pk(self.L1), C, inds=1, out=lp, out_layout=(16 * C, 16, 1), in_cm=True)
+        ops.linear_bf16_tc(x_d.reshape(Nt, 9, -1), pk(self.L2), C, inds=2, out=lp, out_layout=(16 * C, 16, 4), in_cm=True)
+        rij = r_ij.contiguous()
+        S_v = torch.empty(Nt, 3, 5 * C, dtype=torch.bfloat16, device=dev)
+        S_d = torch.empty(Nt, 9, 5 * C, dtype=torch.bfloat16, device=dev)
+        B_a = torch.empty(Nt, self.dim_a, dtype=torch.float32, device=dev)
+        st = stream_ptr(dev)
+        with KERNEL_TIMER.region("bee_messages_vd"):
+            check(lib().ld_bee_messages_vd_f32(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, float(self.r0), ptr(lp),
+                                               ptr(lp), ptr(lp), ptr(w["enc_w"]), ptr(w["enc_b"]), ptr(w["jac"]), 0.1,
+                                               ptr(S_v), ptr(S_d), 2, 1, st))
+        with KERNEL_TIMER.region("bee_messages_scalar_tc"):
+            check(lib().ld_bee_messages_scalar_bf16_tc(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, self.dim_a,
+                                                       float(self.r0), ptr(lp), ptr(lp), ptr(lp), ptr(w["enc_w"]),
+                                                       ptr(w["enc_b"]), ptr(w["jac"]), ptr(w["Yp"]), ptr(w["W1p"]), ptr(w["b1"]),
+                                                       ptr(w["W2p"]), ptr(w["b2"]), ptr(w["W3p"]), ptr(w["b3"]), 0.1, ptr(B_a),
+                                                       2, ptr(ops.tc_status(dev)), st))
+        B_v = ops.linear_bf16_tc_rows16(S_v, w["Yvp"], self.dim_v)
+        B_d = ops.linear_bf16_tc_rows16(S_d, w["Ydp"], self.dim_d)
+        return (B_a.reshape(batch, nodes, -1), B_v.reshape(batch, nodes, 3, -1), B_d.reshape(batch, nodes, 9, -1))
+
     def forward(self, graph, r_ij, x_a, x_v, x_d):
         if torch.is_grad_enabled() or not x_a.is_cuda:
             return self._forward_unfused(graph, r_ij, x_a, x_v, x_d)
@@ -293,6 +328,29 @@ class SelfTensProds(nn.Module):
             return ops.linear_bf16_tc(x, c[name + "p"], W.shape[0], None, ops.ACT_NONE, inds=inds)
         return ops.tensor_linear_fwd(inds, W, x.contiguous())
 
+    def cm_ready(self):
+        c = self._cat_weights() if self.L0.precision == "bf16" else {}
+        return (self.L0.precision == "bf16" and self.chan % 32 == 0 and 2 * self.chan <= 512
+                and all(n + "p" in c and c[n].shape[0] % 32 == 0 and c[n].shape[1] % 4 == 0 for n in ("LR0", "LR1", "LR2", "Ya", "Yv", "Yd")))
+
+    def forward_cm(self, x_a, x_v, x_d):
+        """forward for component-major activations x_v [B, N, 3, dim_v], x_d [B, N, 9, dim_d] (results in the same form):
+        all six channel mixings run on plain rows."""
+        batch, nodes = x_a.shape[0], x_a.shape[1]
+        n = batch * nodes
+        c = self._cat_weights()
+        lin = lambda name, x: ops.linear_bf16_tc(x, c[name + "p"], c[name].shape[0], None, ops.ACT_NONE, inds=0)
+        lr0 = lin("LR0", x_a.reshape(n, -1))
+        lr1 = lin("LR1", x_v.reshape(n * 3, -1)).reshape(n, 3, -1)
+        lr2 = lin("LR2", x_d.reshape(n * 9, -1)).reshape(n, 9, -1)
+        P_a, P_v, P_d = ops.bee_self_products_cm(lr0, lr1, lr2)
+        y_a = lin("Ya", P_a)
+        y_v = ops.linear_bf16_tc_rows16(P_v, c["Yvp"], c["Yv"].shape[0])
+        y_d = ops.linear_bf16_tc_rows16(P_d, c["Ydp"], c["Yd"].shape[0])
+        return (self.gn_a(y_a.reshape(batch, nodes, -1)),
+                ops.group_norm_cm(y_v.reshape(batch, nodes, 3, -1), self.gn_v.groups, self.gn_v.epsilon, self.gn_v.gamma),
+                ops.group_norm_cm(y_d.reshape(batch, nodes, 9, -1), self.gn_d.groups, self.gn_d.epsilon, self.gn_d.gamma))
+
     def forward(self, x_a, x_v, x_d):
         rest = x_a.shape[:-1]
         n = 1
@@ -335,6 +393,16 @@ class BeeBlock(nn.Module):
         d_a, d_v, d_d = self.prods(x_a, x_v, x_d)
         return x_a + d_a, x_v + d_v, x_d + d_d
 
+    def cm_ready(self):
+        return self.messages.cm_ready() and not self.messages.fused_kernel and self.prods.cm_ready()
+
+    def forward_cm(self, graph, r_ij, x_a, x_v, x_d):
+        """the same layer on component-major activations (x_v [B, N, 3, dim_v], x_d [B, N, 9, dim_d])"""
+        d_a, d_v, d_d = self.messages.forward_cm(graph, r_ij, x_a, x_v, x_d)
+        x_a, x_v, x_d = x_a + d_a, x_v + d_v, x_d + d_d
+        d_a, d_v, d_d = self.prods.forward_cm(x_a, x_v, x_d)
+        return x_a + d_a, x_v + d_v, x_d + d_d
+
 
 class BeeDenoiser(nn.Module):
     """Meanflow-style denoiser with scalar, vector and rank-2 channels: the model the benchmark
@@ -350,6 +418,10 @@ class BeeDenoiser(nn.Module):
         self.blocks = nn.ModuleList([BeeBlock(r0, dim_a, dim_v, dim_d, chan) for _ in range(depth)])
         self.readout = TensLinear(1, dim_v, 1)
         self.graph_cache = None   # set by painn.enable_rollout_graphs: fixed-capacity graph buffers for rollouts
+        # True: between the layers the vector / rank-2 features are kept as [B, N, 3 | 9, chan] (every channel mixing reads
+        # and writes plain rows). Same results; measured 2 % slower than the [.., chan, 3^l] form with the present
+        # tensor-core linear (its epilogue for plain rows goes through shared memory), so it is off by default.
+        self.component_major = False
 
     def forward(self, x0, x1, box, types, counter=None):
         from .graph_layers import Graph
@@ -357,6 +429,16 @@ class BeeDenoiser(nn.Module):
         graph = Graph.radius_graph(self.r0, box, x1.contiguous(), cache=self.graph_cache)
         x_a = self.type_embed(types)[None].expand(batch, -1, -1).contiguous()
         x_v = self.v_readin((x1 - x0)[..., None, :].contiguous())
+        if self.component_major and not torch.is_grad_enabled() and x0.is_cuda and all(blk.cm_ready() for blk in self.blocks):
+            # between the layers the vector / rank-2 features stay component-major ([B, N, 3 | 9, chan]): every channel
+            # mixing then reads and writes plain rows; converted only here and at the read-out
+            x_v = x_v.transpose(-1, -2).contiguous()
+            x_d = torch.zeros(batch, nodes, 9, self.dim_d, device=x0.device)
+            for blk in self.blocks:
+                x_a, x_v, x_d = blk.forward_cm(graph, graph.rij, x_a, x_v, x_d)
+            if counter is not None:
+                graph.count_edges(counter, len(self.blocks))
+            return torch.matmul(x_v, self.readout.W.t()).squeeze(-1)
         x_d = torch.zeros(batch, nodes, self.dim_d, 3, 3, device=x0.device)
         for blk in self.blocks:
             x_a, x_v, x_d = blk(graph, graph.rij, x_a, x_v, x_d)

@@ -147,6 +147,23 @@ def bee_fwd(l_0, l_1, l_2, r_0, r_1, r_2):
     return outs
 
 
+def bee_self_products_cm(lr_0, lr_1, lr_2):
+    """bee_self_products for component-major operands lr_1 [rows, 3, 2*chan], lr_2 [rows, 9, 2*chan]; P_v / P_d BF16
+    component-major."""
+    for name, t in (("lr_0", lr_0), ("lr_1", lr_1), ("lr_2", lr_2)):
+        require_cuda_f32(t, name)
+    rows, chan = lr_0.shape[0], lr_0.shape[1] // 2
+    if lr_0.shape != (rows, 2 * chan) or lr_1.shape != (rows, 3, 2 * chan) or lr_2.shape != (rows, 9, 2 * chan):
+        raise RuntimeError("bee_self_products_cm: expected [rows, 2*chan], [rows, 3, 2*chan], [rows, 9, 2*chan]")
+    dev = lr_0.device
+    P_a = torch.empty(rows, 3 * chan, dtype=torch.float32, device=dev)
+    P_v = torch.empty(rows, 3, 5 * chan, dtype=torch.bfloat16, device=dev)
+    P_d = torch.empty(rows, 9, 5 * chan, dtype=torch.bfloat16, device=dev)
+    with KERNEL_TIMER.region("bee_self_products"):
+        check(lib().ld_bee_self_products_cm(ptr(lr_0), ptr(lr_1), ptr(lr_2), rows, chan, ptr(P_a), ptr(P_v), ptr(P_d), stream_ptr(dev)))
+    return P_a, P_v, P_d
+
+
 def bee_self_products(lr_0, lr_1, lr_2, out_bf16=False):
     """13 Bee products of left = lr[:, :chan], right = lr[:, chan:], concatenated per rank:
     P_a [rows, 3*chan], P_v [rows, 5*chan, 3], P_d [rows, 5*chan, 3, 3] (the inputs of concatenated Y maps).
@@ -340,15 +357,20 @@ def pack_weights_bf16(W):
     return out
 
 
-def linear_bf16_tc(x, W_packed, N, bias=None, act=ACT_NONE, inds=0, out_bf16=False, out=None, out_layout=None, out_split=None):
+def linear_bf16_tc(x, W_packed, N, bias=None, act=ACT_NONE, inds=0, out_bf16=False, out=None, out_layout=None, out_split=None,
+                   in_cm=False):
     """y[..., o, s] = act(sum_i W[o,i] x[..., i, s] + b[o]) on tcgen05 (BF16 operands, FP32 accumulate).
     out_bf16: round the result to BF16. out / out_layout=(ld_row, ld_col, off): write BF16 element (r, o, s)
     to out.flatten()[r*ld_row + o*ld_col + s + off] instead of a new tensor; out_split=(s_split, s_jump) moves the
-    components s >= s_split another s_jump elements on."""
+    components s >= s_split another s_jump elements on. in_cm (with out): x is component-major, [..., 3**inds, K]."""
     x = x.contiguous()
     require_cuda_f32(x, "x")
     S = 3 ** inds
     shape = list(x.shape)
+    if in_cm:
+        if out is None or x.dim() < 2 or (inds > 0 and shape[-2] != S):
+            raise RuntimeError("linear_bf16_tc: component-major input is [..., 3**inds, K] and needs an output buffer")
+        shape = shape[:-2] + [shape[-1]] + [3] * inds if inds > 0 else shape
     bd = len(shape) - (1 + inds)
     K = shape[bd]
     rows = 1
@@ -357,10 +379,11 @@ def linear_bf16_tc(x, W_packed, N, bias=None, act=ACT_NONE, inds=0, out_bf16=Fal
     shape[bd] = N
     st, status = stream_ptr(x.device), ptr(tc_status(x.device))
     with KERNEL_TIMER.region("linear_bf16_tc"):
-        if out is not None and out_split is not None:
+        if out is not None and (out_split is not None or in_cm):
             ld_row, ld_col, off = out_layout
+            sp = out_split if out_split is not None else (1 << 30, 0)
             check(lib().ld_linear_bf16_tc_out16_split(ptr(x), rows, K, S, ptr(W_packed), ptr(bias), N, act, ptr(out), ld_row,
-                                                      ld_col, off, out_split[0], out_split[1], status, st))
+                                                      ld_col, off, sp[0], sp[1], 1 if in_cm else 0, status, st))
             return out
         if out is not None:
             ld_row, ld_col, off = out_layout
@@ -374,6 +397,20 @@ def linear_bf16_tc(x, W_packed, N, bias=None, act=ACT_NONE, inds=0, out_bf16=Fal
             return y
         y = torch.empty(shape, dtype=torch.float32, device=x.device)
         check(lib().ld_linear_bf16_tc(ptr(x), rows, K, S, ptr(W_packed), ptr(bias), N, act, ptr(y), status, st))
+    return y
+
+
+def linear_bf16_tc_rows16(x16, W_packed, N, bias=None, act=ACT_NONE):
+    """y [..., N] FP32 = act(x16 [..., K] W^T + b) for BF16 rows (K contiguous, a multiple of 8). With component-major
+    activations [rows, 3**inds, K] the result is component-major as well, [rows, 3**inds, N]: plain rows in and out."""
+    if not x16.is_cuda or x16.dtype != torch.bfloat16 or not x16.is_contiguous():
+        raise RuntimeError("linear_bf16_tc_rows16: expected a contiguous CUDA BF16 tensor")
+    K = x16.shape[-1]
+    rows = x16.numel() // K
+    y = torch.empty(tuple(x16.shape[:-1]) + (N,), dtype=torch.float32, device=x16.device)
+    with KERNEL_TIMER.region("linear_bf16_tc"):
+        check(lib().ld_linear_bf16_tc_in16(ptr(x16), rows, K, 1, ptr(W_packed), ptr(bias), N, act, ptr(y),
+                                           ptr(tc_status(x16.device)), stream_ptr(x16.device)))
     return y
 
 
@@ -417,6 +454,22 @@ def painn_message_bf16_tc(row_ptr, dst, rij, mlp_dist, actv, x_v, rmax, eps=0.1,
                                              ptr(w[2]), ptr(mlp_dist.b[2]), ptr(actv), ptr(x_v), ptr(g16), ptr(res_a), ptr(res_v),
                                              ptr(out_a), ptr(out_v), ptr(edge_counter), ptr(tc_status(x_v.device)), st))
     return out_a, out_v
+
+
+def group_norm_cm(x, groups, eps, gamma):
+    """TensGroupNorm of component-major activations x [B, N, S, C] (S = 3**inds): same statistics and result as
+    group_norm on the [B, N, C, (3,)*inds] form, element for element."""
+    require_cuda_f32(x, "x")
+    x = x.contiguous()
+    B, N, S, C = x.shape
+    if C % groups != 0:
+        raise RuntimeError("group_norm: channels must divide into the groups")
+    y = torch.empty_like(x)
+    ws = torch.empty(max(98 * B * groups, 1), dtype=torch.float32, device=x.device)
+    g = gamma.detach().reshape(-1).float().contiguous()
+    with KERNEL_TIMER.region("group_norm"):
+        check(lib().ld_group_norm_cm(ptr(x), B, N, C, S, groups, 0, float(eps), ptr(g), None, ptr(y), ptr(ws), stream_ptr(x.device)))
+    return y
 
 
 def group_norm(x, groups, eps, gamma, beta=None, center=False):

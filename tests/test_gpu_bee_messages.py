@@ -172,6 +172,27 @@ def test_messages_tensor_core_vs_fp32(dims, B, N, r0, box):
         assert torch.equal(a, b)  # fixed summation order: run-to-run identical
 
 
+def test_component_major_path_matches_channel_major_path():
+    """the l<=2 denoiser with its vector / rank-2 features kept component-major between the layers ([B, N, 3 | 9, chan],
+    plain rows for every channel mixing) against the same network in the reference's [.., chan, 3^l] layout: the
+    node-local operators give identical values, the channel mixings the same BF16 products in another order"""
+    from ld_b200 import bee, ops
+    torch.manual_seed(5)
+    dn = bee.set_precision(bee.BeeDenoiser(4.0, 128, 64, 32, 128, ntypes=5, depth=3).cuda(), "bf16")
+    g = torch.Generator().manual_seed(6)
+    x0 = torch.cumsum(torch.randn(3, 100, 3, generator=g) / 3 ** 0.5, dim=1).cuda()
+    x1 = x0 + 0.1 * torch.randn(3, 100, 3, generator=g).cuda()
+    types = torch.randint(0, 5, (100,), generator=g).cuda()
+    with torch.no_grad():
+        ref = dn(x0, x1, None, types)
+        dn.component_major = True
+        assert all(blk.cm_ready() for blk in dn.blocks)
+        got = dn(x0, x1, None, types)
+    torch.cuda.synchronize()
+    ops.check_tc_status("cuda")
+    close(got, ref, 1e-5)
+
+
 @pytest.mark.parametrize("B,N,r0,box", [(2, 300, 3.0, (9.0, 9.0, 9.5)), (8, 256, 5.0, None), (1, 6, 1.0, None), (3, 40, 0.9, None),
                                         (2, 20, 0.01, None), (1, 700, 2.5, (9.0, 8.0, 8.5))])
 def test_messages_single_edge_kernel_vs_oracle_and_two_kernel_path(B, N, r0, box):
