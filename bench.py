@@ -373,6 +373,11 @@ def main():
                     help="nodes of the bounded CPU-baseline sample (10-30 s of host work)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-fp32-leg", action="store_true", help="skip the two float32 steps reported under 'fp32'")
+    ap.add_argument("--l2-layer", default="pair", choices=["pair", "single"],
+                    help="l<=2 message layer: 'pair' = two edge kernels (default), 'single' = one edge kernel per layer "
+                         "(chan = dim_a = 128; per-node sums accumulated in tensor memory; measured slower)")
+    ap.add_argument("--component-major", action="store_true",
+                    help="keep the vector / rank-2 node features as [.., 3|9, chan] between the layers (plain-row channel mixings)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -401,6 +406,10 @@ def main():
     if is_bee:
         from ld_b200 import bee
         dn = bee.set_precision(build_model(w, dev), args.precision)
+        dn.component_major = args.component_major
+        for m in dn.modules():
+            if isinstance(m, bee.Messages):
+                m.fused_kernel = args.l2_layer == "single"
     else:
         dn = painn.set_precision(build_model(w, dev), args.precision)
     painn.enable_rollout_graphs(dn)   # fixed-capacity graph buffers: no step waits for its edge count
@@ -518,7 +527,7 @@ def main():
             "metric": "edge_messages_per_sec", "value": value, "unit": "edge-messages/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16" if tc_path else "f32", "data": "synthetic",
-            "config": workload_config(args.workload, w), "precision": args.precision,
+            "config": workload_config(args.workload, w), "precision": args.precision, "l2_layer": args.l2_layer if is_bee else None,
             "edges_per_step": total_edges // args.steps,
             "dt_steps_per_sec": args.steps / (total_ms * 1e-3),
             "system_steps_per_sec": args.steps * w["systems"] / (total_ms * 1e-3),

@@ -76,6 +76,20 @@ int ld_row_ptr_from_sorted(const void* src, int index_bytes, long long E, int Nt
 int ld_segment_sum(const float* x_edge, const int* row_ptr, int Nt, int F, float* out, void* stream);
 int ld_gather_rows(const float* x_node, const void* idx, int index_bytes, long long E, int F, float* out, void* stream);
 
+/* Legacy padded tables of the reference extension: get_neighbours, edges_read, edges_reduce
+ * (extensions/neighbour_grid/neighbour_grid.cpp:69-168, neighbour_grid_kern.cu:62-133, 226-306).
+ * lists / neighbours int32 [batch, nodes, nmax] hold in-system node indices, counts int32 [batch, nodes].
+ * ld_neighbour_lists_from_csr pads the CSR edge list (entries past a node's count are 0; a node with more than nmax
+ * neighbours raises LD_FLAG_CAPACITY in *status_dev). ld_edges_read_padded: out [batch, nodes, nmax, chan] = x of the
+ * neighbour, 0 past the count. ld_edges_reduce_padded: out [batch, nodes, chan] = sum over the first count slots,
+ * added in ascending slot order. */
+int ld_neighbour_lists_from_csr(const int* row_ptr, const int* dst, int batch, int nodes, int nmax, int* lists, int* counts,
+                                int* status_dev, void* stream);
+int ld_edges_read_padded(const int* neighbours, const int* counts, const float* x, int batch, int nodes, int nmax, int chan,
+                         float* out, void* stream);
+int ld_edges_reduce_padded(const int* counts, const float* x, int batch, int nodes, int nmax, int chan, float* out,
+                           void* stream);
+
 /* ---- channel mixing -------------------------------------------------------------------------
  * Replaces tensor_ops_cuda.tensor_linear forward and backward
  * (extensions/tensor_ops/tensor_ops.cpp:31-170, tensor_ops_kern.cu:6-71).

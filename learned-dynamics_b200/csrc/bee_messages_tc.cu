@@ -31,6 +31,15 @@ constexpr int BT_SYNC_THREADS = (BT_WORK_WARPS + 1) * 32;
 constexpr int BT_STAGES = 3;        // weight ring: 32 KB slabs (a bulk copy costs about the same issue time whatever its size)
 constexpr int BT_SLAB_BYTES = 32 * 1024;
 constexpr int BT_LAYERS = 4;
+#ifndef BT_PIPE_SUMS
+#define BT_PIPE_SUMS 0
+#endif
+#ifndef BT_RELAY
+#define BT_RELAY 1
+#endif
+#ifndef BT_PIPE_EPI
+#define BT_PIPE_EPI 1
+#endif
 // Byte stride between the 8-column panels of the operand tile: 128 rows x 16 bytes plus one 16-byte pad, so that the
 // panels a warp of the product phase writes to (32 channels = 4 panels, same row) fall into different banks
 constexpr int BT_PANEL = BT_EDGES * 16 + 16;
@@ -58,7 +67,7 @@ struct BtParams {
   int feat_bf16;            // 0: L0/L1/L2 FP32; 1: BF16; 2: L0 = interleaved BF16 [node][chan][16]
   float* out_a;
   int* status;
-  long long* prof;          // optional cycle counters: 0 geometry, 1 products, 2/4/6/8 waiting for layers, 3/5/7 epilogues, 9 staging, 10 sums
+  long long* prof;          // optional cycle counters, 3 x 12: 0 geometry, 11 products, 1 barrier after them, 2/4/6/8 waiting for layers, 3/5/7 epilogues, 9 staging, 10 sums
 };
 
 struct __align__(16) BtGeom { float enc[8]; float rhat[3]; float pad; };   // 48 bytes: three 16-byte shared-memory loads
@@ -125,15 +134,16 @@ __device__ __forceinline__ unsigned short bt_bf16(float v) {
   return *reinterpret_cast<unsigned short*>(&h);
 }
 
-template <bool PROF>
+// FAST: the instance for chan = dim_a = 128 with interleaved BF16 rows (widths and row format are compile-time constants)
+template <bool PROF, bool FAST>
 __global__ void __launch_bounds__(BT_THREADS, 1)
 bee_scalar_tc_kernel(BtParams P) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t bar_full[BT_STAGES], bar_empty[BT_STAGES], bar_accum;
   __shared__ uint32_t tmem_slot;
-  __shared__ BtGeom s_geom[BT_EDGES];
-  __shared__ int s_dst[BT_EDGES];
-  __shared__ __align__(16) int s_src[BT_EDGES];
+  __shared__ BtGeom s_geom[2][BT_EDGES];          // two tiles: the overlapped schedule fills one while the other is read
+  __shared__ int s_dst[2][BT_EDGES];
+  __shared__ __align__(16) int s_src[2][BT_EDGES];
   __shared__ int s_rowwin[BT_EDGES + 1];
   __shared__ float s_jac[72];
 
@@ -142,7 +152,8 @@ bee_scalar_tc_kernel(BtParams P) {
   const bool prod_lane = warp == BT_PROD_WARP && lane == 0;
   const int quarter = warp & 3, part = (warp >> 2) & 3;  // TMEM lane quarter (fixed by the warp id), column part
   const int row = quarter * 32 + lane;
-  const int C = P.chan, A = P.dim_a;
+  const int C = FAST ? 128 : P.chan, A = FAST ? 128 : P.dim_a;
+  const int feat = FAST ? 2 : P.feat_bf16;
   unsigned char* a_smem = smem;                                   // 128 x max(3C, 3A) BF16, overlaid by the staging tile
   unsigned char* b_smem = smem + P.stage_off;                     // BT_STAGES x slab
   float* s_bias = reinterpret_cast<float*>(smem + P.bias_off);    // biases of layers 1..3: [2A | 2A | A]
@@ -158,7 +169,7 @@ bee_scalar_tc_kernel(BtParams P) {
     tc::mbar_init_fence();
   }
   uint32_t ncols = 32;
-  while (ncols < (uint32_t)(2 * A)) ncols <<= 1;
+  while (ncols < (uint32_t)(A == 128 ? 512 : 2 * A)) ncols <<= 1;   // dim_a = 128 keeps the last layer's result in columns [256, 384)
   if (warp == 0) { tc::tmem_alloc(&tmem_slot, ncols); tc::tmem_relinquish(); }
   tc::fence_before_sync();
   __syncthreads();
@@ -194,13 +205,15 @@ bee_scalar_tc_kernel(BtParams P) {
     }
   } else if (warp == BT_MMA_WARP) {
     // ===== MMA issue =========================================================================================
-    uint32_t mmas = 0;
+    uint32_t mmas = 0, accum_phase = 0;
     const uint32_t a_base = tc::smem_u32(a_smem);
+    const bool OV = FAST || A == 128;   // overlapped schedule of the working warps: barriers B1, B6 and B7 fall away
     for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
       const long long ntiles = bt_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt)).ntiles;
+      bool stop = false;   // a barrier reported a failure: every warp leaves at that barrier
       for (long long t = 0; t < ntiles; t++) {
-        if (bt_sync_or(fail)) { fail = 1; break; }      // [B1] geometry staged
-        if (bt_sync_or(fail)) { fail = 1; break; }      // [B2] product tile ready
+        if (!OV && bt_sync_or(fail)) { fail = 1; stop = true; break; }      // [B1] geometry staged
+        if (bt_sync_or(fail)) { fail = 1; stop = true; break; }             // [B2] product tile ready
         for (int l = 0; l < BT_LAYERS; l++) {
           if (mma_lane && !fail) {
             tc::fence_after_sync();
@@ -208,8 +221,10 @@ bee_scalar_tc_kernel(BtParams P) {
             // so every instruction between two MMAs is exposed latency
             const int l_ksteps = P.layer[l].ksteps, l_slab = P.layer[l].slab_ksteps, l_N = P.layer[l].N;
             // dim_a = 128: the last layer is issued transposed (weights as the M operand, the tile as the N operand), so its
-            // result lies in tensor memory as [channel][edge] and the per-node sum is a walk along columns in one thread
-            const bool transposed = l == BT_LAYERS - 1 && A == 128;
+            // result lies in tensor memory as [channel][edge] and the per-node sum is a walk along columns in one thread.
+            // It goes to columns [256, 384), which stay untouched while the next tile's first layers run.
+            const bool transposed = l == BT_LAYERS - 1 && OV;
+            const uint32_t d_tmem = tmem_base + (transposed ? 256u : 0u);
             const uint32_t idesc = transposed ? tc::idesc_bf16(l_N, BT_EDGES) : tc::idesc_bf16(BT_EDGES, l_N);
             uint64_t ad = tc::smem_desc(a_base + P.layer[l].a_panel * BT_PANEL, BT_PANEL, 128);
             const uint64_t a_step = (uint64_t)((2 * BT_PANEL) >> 4), b_step = (uint64_t)((2 * l_N * 16) >> 4);
@@ -222,8 +237,8 @@ bee_scalar_tc_kernel(BtParams P) {
               const int nk = min(l_slab, l_ksteps - ks0);
 #pragma unroll 4
               for (int kk = 0; kk < nk; kk++) {
-                if (transposed) tc::mma_bf16(tmem_base, bd, ad, idesc, accumulate);
-                else tc::mma_bf16(tmem_base, ad, bd, idesc, accumulate);
+                if (transposed) tc::mma_bf16(d_tmem, bd, ad, idesc, accumulate);
+                else tc::mma_bf16(d_tmem, ad, bd, idesc, accumulate);
                 accumulate = 1u;
                 ad += a_step;   // the address field of a descriptor counts 16-byte units: next K-step = two panels on
                 bd += b_step;
@@ -231,17 +246,35 @@ bee_scalar_tc_kernel(BtParams P) {
               tc::mma_commit(&bar_empty[st]);
             }
             if (!fail) tc::mma_commit(&bar_accum);
+#if BT_RELAY
+            // the issuing lane polls for the completion itself and passes it on through the block barrier below: a
+            // hardware barrier wakes the sixteen working warps faster than sixteen suspended mbarrier waits
+            if (!fail && !tc::mbar_wait_tight(&bar_accum, accum_phase & 1)) fail = 1;
+            tc::fence_before_sync();
+#endif
           }
+          accum_phase++;
           fail = __shfl_sync(0xffffffffu, fail, 0);
-          if (bt_sync_or(fail)) { fail = 1; break; }    // [B3..B6] accumulators consumed / next operand ready
+#if BT_RELAY
+          if (bt_sync_or(fail)) { fail = 1; stop = true; break; }    // [A0..A3] accumulators of layer l complete
+#endif
+          if (OV && l == BT_LAYERS - 1) break;          // the next barrier is B2 of the following tile (or the segment's end)
+          if (bt_sync_or(fail)) { fail = 1; stop = true; break; }    // [B3..B6] accumulators consumed / next operand ready
         }
-        if (fail) break;
-        if (bt_sync_or(fail)) { fail = 1; break; }      // [B7] tile finished
+        if (stop) break;
+        if (!OV && bt_sync_or(fail)) { fail = 1; stop = true; break; }      // [B7] tile finished
       }
+      if (!stop && bt_sync_or(fail)) fail = 1;                              // [B8] segment finished
     }
   } else {
     // ===== working warps =========================================================================================
+    // dim_a = 128 runs the overlapped schedule: the geometry of the next tile is computed by warps 4..7 while the
+    // first GEMM of this tile runs, and the per-node sums of a tile (warps 0..3, reading tensor-memory columns
+    // [256, 384)) run while the other warps already form the products of the next tile.
+    const bool OV = FAST || A == 128;
+#if !BT_RELAY
     uint32_t accum_phase = 0;
+#endif
     long long pc[PROF ? 12 : 1];
 #pragma unroll
     for (int i = 0; i < (PROF ? 12 : 1); i++) pc[i] = 0;
@@ -253,8 +286,18 @@ bee_scalar_tc_kernel(BtParams P) {
       if (tid < A)
         for (int v = from; v < next; v++) P.out_a[(size_t)v * A + tid] = (v == from ? value : 0.f) * P.scale;
     };
-    // product role: channel c, every pc_stride-th edge (the lanes of a warp share the edge, so loads stay coalesced)
+    // product role: channel c; the lanes of a warp share the edge, so loads stay coalesced. The edges of a tile are
+    // taken in batches of UNR: edge(b, u) = pb_base + b * pb_step + u * pu_step for b in [pb_lo, pb_hi)
+    constexpr int UNR = 4;  // neighbour rows in flight per thread (the loop is bound by L2 latency otherwise)
     const int pc_c = tid % C, pc_h = tid / C, pc_stride = BT_WORK_THREADS / C;
+    int pb_base = pc_h, pb_step = pc_stride * UNR, pu_step = pc_stride, pb_lo = 0,
+        pb_hi = pc_h < pc_stride ? (BT_EDGES - pc_h + pc_stride * UNR - 1) / (pc_stride * UNR) : 0;
+    if (OV && C == 128) {
+      // the warps that add up the previous tile first (pc_h = 0) take 5 of the 32 batches, the others 9 each
+      pb_base = 0; pb_step = UNR; pu_step = 1;
+      pb_lo = pc_h == 0 ? 0 : 5 + 9 * (pc_h - 1);
+      pb_hi = 5 + 9 * pc_h;
+    }
     // this thread's three columns of the operand tile (element offsets within a row's panels)
     const int a_off0 = (pc_c >> 3) * (BT_PANEL / 2) + (pc_c & 7), a_off1 = ((C + pc_c) >> 3) * (BT_PANEL / 2) + (pc_c & 7),
               a_off2 = ((2 * C + pc_c) >> 3) * (BT_PANEL / 2) + (pc_c & 7);
@@ -264,104 +307,192 @@ bee_scalar_tc_kernel(BtParams P) {
       for (int m = 0; m < 8; m++) w8[m] = P.enc_w[pc_c * 8 + m];
       wb = P.enc_b[pc_c];
     }
+    const int gt = OV ? tid - BT_EDGES : tid;   // geometry role: thread gt in [0, 128) owns edge gt of a tile
+    const uint32_t sum_col = OV ? 256u : 0u;
     for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
       const BtRange br = bt_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt));
       const int n_begin = br.n_begin, n_end = br.n_end;
       float acc = 0.f;
       int cur = n_begin, node_lo = n_begin;
-      bt_sync_workers();
-      if (tid <= BT_EDGES) s_rowwin[tid] = P.row_ptr[min(node_lo + tid, n_end > n_begin ? n_end : n_begin)];
       float pre_x = 0.f, pre_y = 0.f, pre_z = 0.f;
       int pre_j = 0;
-      if (tid < BT_EDGES && br.e_begin + tid < br.e_end) {
-        const long long en = br.e_begin + tid;
+      // edge geometry of the tile that starts at edge e0 into buffer b (the displacement and neighbour index were
+      // fetched one tile ahead); nlo: a node at or before the tile's first source node, s_rowwin starts there
+      auto geometry = [&](long long e0, int cnt, int b, int nlo) {
+        int j = 0, s = -1;
+        const float gx = pre_x, gy = pre_y, gz = pre_z;
+        const int gj = pre_j;
+        {
+          const long long en = e0 + BT_EDGES + gt;   // next tile's edge for this thread
+          if (en < br.e_end) { pre_x = P.rij[en * 3]; pre_y = P.rij[en * 3 + 1]; pre_z = P.rij[en * 3 + 2]; pre_j = P.dst[en]; }
+        }
+        if (gt < cnt) {
+          const long long e = e0 + gt;
+          bt_geometry(gx, gy, gz, P.r0, s_jac, &s_geom[b][gt]);
+          j = gj;
+          if ((long long)s_rowwin[BT_EDGES] > e) {
+            int lo = 0, hi = BT_EDGES;
+            while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if ((long long)s_rowwin[mid] > e) hi = mid; else lo = mid; }
+            s = nlo + lo;
+          } else {
+            s = bt_lb_row(P.row_ptr, nlo + BT_EDGES, n_end, e + 1) - 1;
+          }
+        }
+        s_dst[b][gt] = j;
+        s_src[b][gt] = s;
+      };
+      // transposed last layer: thread tid < 128 owns channel tid (its tensor-memory lane) and adds the tile's edges
+      // (columns) in order, carrying the sum of the node that continues from the previous tile. The order of the
+      // additions depends on the node's edge list alone, so a system's result does not depend on its batch.
+      auto sums_transposed = [&](int b, int cnt) {
+        const float b3 = s_bias[4 * A + tid];
+        int c_node = cur;
+        float a_sum = acc;
+        // sixteen edges (columns cb .. cb + 15) of this thread's channel
+        auto add16 = [&](const uint32_t* r, int cb) {
+          if (cb + 16 <= cnt && s_src[b][cb] == c_node && s_src[b][cb + 15] == c_node) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) a_sum += __uint_as_float(r[i]) + b3;   // sixteen edges of the running node (sources are sorted)
+          } else {
+#pragma unroll
+            for (int i4 = 0; i4 < 4; i4++) {
+              const int4 t = *reinterpret_cast<const int4*>(&s_src[b][cb + 4 * i4]);
+              const int sn[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+              for (int k = 0; k < 4; k++) {
+                const int i = 4 * i4 + k;
+                if (cb + i < cnt) {
+                  if (sn[k] != c_node) { flush_until(c_node, sn[k], a_sum); a_sum = 0.f; c_node = sn[k]; }
+                  a_sum += __uint_as_float(r[i]) + b3;
+                }
+              }
+            }
+          }
+        };
+        // two register blocks: the next sixteen columns are on their way from tensor memory while these are added
+        uint32_t ra[16], rb[16];
+        const uint32_t t0 = tmem_row + sum_col;
+        if (!(FAST && BT_PIPE_SUMS)) {
+#pragma unroll 1
+          for (int cb = 0; cb < cnt; cb += 16) {
+            tc::tmem_ld16_issue(t0 + cb, ra);
+            tc::tmem_ld16_wait(ra);
+            add16(ra, cb);
+          }
+          acc = a_sum;
+          cur = c_node;
+          return;
+        }
+        tc::tmem_ld16_issue(t0, ra);
+        tc::tmem_ld16_wait(ra);
+#pragma unroll 1
+        for (int cb = 0; cb < cnt; cb += 32) {
+          const bool more = cb + 16 < cnt, more2 = cb + 32 < cnt;
+          if (more) tc::tmem_ld16_issue(t0 + cb + 16, rb);
+          add16(ra, cb);
+          if (more) {
+            tc::tmem_ld16_wait(rb);
+            if (more2) tc::tmem_ld16_issue(t0 + cb + 32, ra);
+            add16(rb, cb + 16);
+            if (more2) tc::tmem_ld16_wait(ra);
+          }
+        }
+        acc = a_sum;
+        cur = c_node;
+      };
+      bt_sync_workers();
+      if (gt >= 0 && gt <= BT_EDGES) s_rowwin[gt] = P.row_ptr[min(node_lo + gt, n_end > n_begin ? n_end : n_begin)];
+      if (gt >= 0 && gt < BT_EDGES && br.e_begin + gt < br.e_end) {
+        const long long en = br.e_begin + gt;
         pre_x = P.rij[en * 3]; pre_y = P.rij[en * 3 + 1]; pre_z = P.rij[en * 3 + 2]; pre_j = P.dst[en];
       }
       bt_sync_workers();
-      for (long long e0 = br.e_begin; e0 < br.e_end; e0 += BT_EDGES) {
+      if (OV) {
+        if (gt >= 0 && gt < BT_EDGES && br.e_begin < br.e_end)
+          geometry(br.e_begin, (int)min((long long)BT_EDGES, br.e_end - br.e_begin), 0, node_lo);
+        bt_sync_workers();
+      }
+      int prev_cnt = 0, tile_no = 0, win = 0;
+      bool stop = false;   // a barrier reported a failure: every warp leaves at that barrier
+      for (long long e0 = br.e_begin; e0 < br.e_end; e0 += BT_EDGES, tile_no++) {
         const int cnt = (int)((br.e_end - e0) < BT_EDGES ? (br.e_end - e0) : BT_EDGES);
-        // ---- 1. edge geometry (the displacement and neighbour index of this tile were fetched one tile ahead) ------
-        if (tid < BT_EDGES) {
-          int j = 0, s = -1;
-          const float gx = pre_x, gy = pre_y, gz = pre_z;
-          const int gj = pre_j;
-          {
-            const long long en = e0 + BT_EDGES + tid;   // next tile's edge for this thread
-            if (en < br.e_end) { pre_x = P.rij[en * 3]; pre_y = P.rij[en * 3 + 1]; pre_z = P.rij[en * 3 + 2]; pre_j = P.dst[en]; }
-          }
-          if (tid < cnt) {
-            const long long e = e0 + tid;
-            bt_geometry(gx, gy, gz, P.r0, s_jac, &s_geom[tid]);
-            j = gj;
-            if ((long long)s_rowwin[BT_EDGES] > e) {
-              int lo = 0, hi = BT_EDGES;
-              while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if ((long long)s_rowwin[mid] > e) hi = mid; else lo = mid; }
-              s = node_lo + lo;
-            } else {
-              s = bt_lb_row(P.row_ptr, node_lo + BT_EDGES, n_end, e + 1) - 1;
-            }
-          }
-          s_dst[tid] = j;
-          s_src[tid] = s;
+        const int gb = OV ? (tile_no & 1) : 0;   // buffer of this tile's geometry
+        if (!OV) {
+          // ---- 1. edge geometry ---------------------------------------------------------------------------------
+          if (tid < BT_EDGES) geometry(e0, cnt, 0, node_lo);
+          if (bt_sync_or(fail)) { fail = 1; stop = true; break; }                         // [B1]
+          lap(0);
+        } else {
+          // ---- 1. per-node sums of the previous tile; source-node window of the next tile ----------------------
+          if (tid < A && tile_no > 0 && !fail) { sums_transposed(gb ^ 1, prev_cnt); tc::fence_before_sync(); }
+          node_lo = s_src[gb][cnt - 1];
+          if (gt >= 0 && gt <= BT_EDGES) win = P.row_ptr[min(node_lo + gt, n_end)];   // stored after the products
+          lap(10);
         }
-        if (bt_sync_or(fail)) { fail = 1; break; }                                        // [B1]
-        lap(0);
         // ---- 2. scalar products -> operand tile (columns c, C+c, 2C+c of row t) ------------------------------
-        if (pc_h < pc_stride) {
+        if (pb_lo < pb_hi) {
           const __nv_bfloat16* Lp = reinterpret_cast<const __nv_bfloat16*>(P.L0);
-          constexpr int UNR = 4;  // neighbour rows in flight per thread (the loop is bound by L2 latency otherwise)
-          for (int tb = pc_h; tb < BT_EDGES; tb += pc_stride * UNR) {
+          const int* tdst = s_dst[gb];
+          const int last = max(cnt - 1, 0);
+#pragma unroll 1
+          for (int pb = pb_lo; pb < pb_hi; pb++) {
+            // the batch's rows are requested together and waited for together: the loads of a warp share a scoreboard,
+            // so a rotating prefetch (reload a slot as soon as it is unpacked) would wait for the newest load every time
             uint32_t raw[UNR][8];
-            if (P.feat_bf16 == 2) {
+            if (feat == 2) {
 #pragma unroll
               for (int u = 0; u < UNR; u++) {
-                const int t = min(tb + u * pc_stride, max(cnt - 1, 0));   // clamped: the load is unconditional
-                tc::ldg_raw8(Lp + ((size_t)s_dst[t] * C + pc_c) * 16, raw[u]);
+                const int t = min(pb_base + pb * pb_step + u * pu_step, last);   // clamped: the load is unconditional
+                tc::ldg_raw8(Lp + ((size_t)tdst[t] * C + pc_c) * 16, raw[u]);
               }
             }
 #pragma unroll
             for (int u = 0; u < UNR; u++) {
-              const int t = tb + u * pc_stride;
+              const int t = pb_base + pb * pb_step + u * pu_step;
               if (t >= BT_EDGES) break;
+              float l0 = 0.f, l1[3] = {0.f, 0.f, 0.f}, l2[9] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+              if (feat == 2) {
+                l0 = tc::bf16_at(raw[u], 0);
+#pragma unroll
+                for (int k = 0; k < 3; k++) l1[k] = tc::bf16_at(raw[u], 1 + k);
+#pragma unroll
+                for (int k = 0; k < 9; k++) l2[k] = tc::bf16_at(raw[u], 4 + k);
+              }
               float y0 = 0.f, y1 = 0.f, y2 = 0.f;
               if (t < cnt) {
-                const float4* gp = reinterpret_cast<const float4*>(&s_geom[t]);
+                const float4* gp = reinterpret_cast<const float4*>(&s_geom[gb][t]);
                 const float4 e0 = gp[0], e1 = gp[1], rr = gp[2];
                 float pa = wb;
                 pa = fmaf(e0.x, w8[0], pa); pa = fmaf(e0.y, w8[1], pa); pa = fmaf(e0.z, w8[2], pa); pa = fmaf(e0.w, w8[3], pa);
                 pa = fmaf(e1.x, w8[4], pa); pa = fmaf(e1.y, w8[5], pa); pa = fmaf(e1.z, w8[6], pa); pa = fmaf(e1.w, w8[7], pa);
                 const float rh[3] = {rr.x, rr.y, rr.z};
-                const size_t j = (size_t)s_dst[t] * C + pc_c;
-                float l0, l1[3], l2[9];
-                if (P.feat_bf16 == 2) {
-                  l0 = tc::bf16_at(raw[u], 0);
+                if (feat != 2) {
+                  const size_t j = (size_t)tdst[t] * C + pc_c;
+                  if (feat) {
+                    const __nv_bfloat16* F0 = reinterpret_cast<const __nv_bfloat16*>(P.L0);
+                    const __nv_bfloat16* F1 = reinterpret_cast<const __nv_bfloat16*>(P.L1);
+                    const __nv_bfloat16* F2 = reinterpret_cast<const __nv_bfloat16*>(P.L2);
+                    l0 = __bfloat162float(F0[j]);
 #pragma unroll
-                  for (int k = 0; k < 3; k++) l1[k] = tc::bf16_at(raw[u], 1 + k);
+                    for (int k = 0; k < 3; k++) l1[k] = __bfloat162float(F1[j * 3 + k]);
 #pragma unroll
-                  for (int k = 0; k < 9; k++) l2[k] = tc::bf16_at(raw[u], 4 + k);
-                } else if (P.feat_bf16) {
-                  const __nv_bfloat16* F0 = reinterpret_cast<const __nv_bfloat16*>(P.L0);
-                  const __nv_bfloat16* F1 = reinterpret_cast<const __nv_bfloat16*>(P.L1);
-                  const __nv_bfloat16* F2 = reinterpret_cast<const __nv_bfloat16*>(P.L2);
-                  l0 = __bfloat162float(F0[j]);
+                    for (int k = 0; k < 9; k++) l2[k] = __bfloat162float(F2[j * 9 + k]);
+                  } else {
+                    l0 = __ldg(P.L0 + j);
 #pragma unroll
-                  for (int k = 0; k < 3; k++) l1[k] = __bfloat162float(F1[j * 3 + k]);
+                    for (int k = 0; k < 3; k++) l1[k] = __ldg(P.L1 + j * 3 + k);
 #pragma unroll
-                  for (int k = 0; k < 9; k++) l2[k] = __bfloat162float(F2[j * 9 + k]);
-                } else {
-                  l0 = __ldg(P.L0 + j);
-#pragma unroll
-                  for (int k = 0; k < 3; k++) l1[k] = __ldg(P.L1 + j * 3 + k);
-#pragma unroll
-                  for (int k = 0; k < 9; k++) l2[k] = __ldg(P.L2 + j * 9 + k);
+                    for (int k = 0; k < 9; k++) l2[k] = __ldg(P.L2 + j * 9 + k);
+                  }
                 }
+                // every rounding is spelled out, so that all instances of the kernel (and any later build) give the same bits
                 y0 = l0 * pa;
-                y1 = (l1[0] * rh[0] + l1[1] * rh[1] + l1[2] * rh[2]) * pa;
+                y1 = fmaf(l1[2], rh[2], fmaf(l1[1], rh[1], l1[0] * rh[0])) * pa;
                 // r^T l2 r, row by row
-                const float m0 = l2[0] * rh[0] + l2[1] * rh[1] + l2[2] * rh[2];
-                const float m1 = l2[3] * rh[0] + l2[4] * rh[1] + l2[5] * rh[2];
-                const float m2 = l2[6] * rh[0] + l2[7] * rh[1] + l2[8] * rh[2];
-                y2 = (m0 * rh[0] + m1 * rh[1] + m2 * rh[2]) * pa;
+                const float m0 = fmaf(l2[2], rh[2], fmaf(l2[1], rh[1], l2[0] * rh[0]));
+                const float m1 = fmaf(l2[5], rh[2], fmaf(l2[4], rh[1], l2[3] * rh[0]));
+                const float m2 = fmaf(l2[8], rh[2], fmaf(l2[7], rh[1], l2[6] * rh[0]));
+                y2 = fmaf(m2, rh[2], fmaf(m1, rh[1], m0 * rh[0])) * pa;
               }
               unsigned short* arow = reinterpret_cast<unsigned short*>(a_smem + (size_t)t * 16);
               arow[a_off0] = bt_bf16(y0);
@@ -370,12 +501,23 @@ bee_scalar_tc_kernel(BtParams P) {
             }
           }
         }
+        if (OV && gt >= 0 && gt <= BT_EDGES) s_rowwin[gt] = win;
         tc::fence_async_smem();
         tc::fence_before_sync();
-        if (bt_sync_or(fail)) { fail = 1; break; }                                        // [B2]
+        lap(11);
+        if (bt_sync_or(fail)) { fail = 1; stop = true; break; }                           // [B2]
         lap(1);
+        // overlapped schedule: the geometry of the next tile, while the first GEMM of this one runs
+        if (OV && gt >= 0 && gt < BT_EDGES && e0 + BT_EDGES < br.e_end) {
+          const long long en0 = e0 + BT_EDGES;
+          geometry(en0, (int)min((long long)BT_EDGES, br.e_end - en0), gb ^ 1, node_lo);
+          lap(0);
+        }
         // ---- 3. four layers ------------------------------------------------------------------------------------
         for (int l = 0; l < BT_LAYERS; l++) {
+#if BT_RELAY
+          if (bt_sync_or(fail)) { fail = 1; stop = true; break; }                         // [A0..A3]
+#else
           {
             int done = 1;
             if (lane == 0) done = tc::mbar_wait(&bar_accum, accum_phase & 1) ? 1 : 0;
@@ -383,6 +525,7 @@ bee_scalar_tc_kernel(BtParams P) {
             if (!done) fail = 1;
           }
           accum_phase++;
+#endif
           tc::fence_after_sync();
           lap(2 + 2 * l);
           const int N = P.layer[l].N;
@@ -391,77 +534,71 @@ bee_scalar_tc_kernel(BtParams P) {
             const float* bias = l == 0 ? nullptr : s_bias + (l - 1) * 2 * A;
             const int act = P.layer[l].act, oc = P.layer[l].out_col;
             const int cpp = max(N / 4, 32);  // columns per part
-            for (int cb = part * cpp; cb < min((part + 1) * cpp, N); cb += 32) {
-              float v[32];
-              tc::tmem_ld32(tmem_row + cb, v);
+            // eight columns from `cb` on: bias, activation, BF16, one 16-byte store into the operand tile
+            auto put8 = [&](const float* v8, int cb) {
+              float t8[8];
+              float b8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+              if (bias != nullptr) {   // two 16-byte shared-memory loads for eight biases
+                const float4 ba = *reinterpret_cast<const float4*>(bias + cb);
+                const float4 bb = *reinterpret_cast<const float4*>(bias + cb + 4);
+                b8[0] = ba.x; b8[1] = ba.y; b8[2] = ba.z; b8[3] = ba.w; b8[4] = bb.x; b8[5] = bb.y; b8[6] = bb.z; b8[7] = bb.w;
+              }
 #pragma unroll
-              for (int g8 = 0; g8 < 4; g8++) {
-                float t8[8];
-                float b8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                if (bias != nullptr) {   // two 16-byte shared-memory loads for eight biases
-                  const float4 ba = *reinterpret_cast<const float4*>(bias + cb + g8 * 8);
-                  const float4 bb = *reinterpret_cast<const float4*>(bias + cb + g8 * 8 + 4);
-                  b8[0] = ba.x; b8[1] = ba.y; b8[2] = ba.z; b8[3] = ba.w; b8[4] = bb.x; b8[5] = bb.y; b8[6] = bb.z; b8[7] = bb.w;
-                }
+              for (int j = 0; j < 8; j++) {
+                const float u = v8[j] + b8[j];
+                t8[j] = (act == 2) ? fmaxf(u, 0.1f * u) : u;   // LeakyReLU(0.1) = max(u, 0.1 u)
+              }
+              uint4 q;
+              q.x = tc::pack_bf16x2(t8[0], t8[1]); q.y = tc::pack_bf16x2(t8[2], t8[3]);
+              q.z = tc::pack_bf16x2(t8[4], t8[5]); q.w = tc::pack_bf16x2(t8[6], t8[7]);
+              *reinterpret_cast<uint4*>(a_smem + (size_t)((oc + cb) >> 3) * BT_PANEL + row * 16) = q;
+            };
+            if (FAST && BT_PIPE_EPI) {
+              // sixteen columns at a time through two register blocks: the next block is on its way from tensor memory
+              // while this one is converted and stored
+              auto put16 = [&](const uint32_t* r, int cb) {
+                float v[16];
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                  const float u = v[g8 * 8 + j] + b8[j];
-                  t8[j] = (act == 2) ? fmaxf(u, 0.1f * u) : u;   // LeakyReLU(0.1) = max(u, 0.1 u)
-                }
-                uint4 q;
-                q.x = tc::pack_bf16x2(t8[0], t8[1]); q.y = tc::pack_bf16x2(t8[2], t8[3]);
-                q.z = tc::pack_bf16x2(t8[4], t8[5]); q.w = tc::pack_bf16x2(t8[6], t8[7]);
-                *reinterpret_cast<uint4*>(a_smem + (size_t)(((oc + cb) >> 3) + g8) * BT_PANEL + row * 16) = q;
+                for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+                put8(v, cb);
+                put8(v + 8, cb + 8);
+              };
+              uint32_t ra[16], rb[16];
+              const int c_lo = part * cpp, c_hi = min((part + 1) * cpp, N);
+              tc::tmem_ld16_issue(tmem_row + c_lo, ra);
+              tc::tmem_ld16_wait(ra);
+#pragma unroll 1
+              for (int cb = c_lo; cb < c_hi; cb += 32) {
+                const bool more2 = cb + 32 < c_hi;
+                tc::tmem_ld16_issue(tmem_row + cb + 16, rb);
+                put16(ra, cb);
+                tc::tmem_ld16_wait(rb);
+                if (more2) tc::tmem_ld16_issue(tmem_row + cb + 32, ra);
+                put16(rb, cb + 16);
+                if (more2) tc::tmem_ld16_wait(ra);
+              }
+            } else {
+              for (int cb = part * cpp; cb < min((part + 1) * cpp, N); cb += 32) {
+                float v[32];
+                tc::tmem_ld32(tmem_row + cb, v);
+#pragma unroll
+                for (int g8 = 0; g8 < 4; g8++) put8(v + g8 * 8, cb + g8 * 8);
               }
             }
             tc::fence_async_smem();
             tc::fence_before_sync();
           }
-          if (bt_sync_or(fail)) { fail = 1; break; }                                      // [B3..B6]
+          if (OV && l == BT_LAYERS - 1) break;   // the sums of this tile follow at the top of the next one
+          if (bt_sync_or(fail)) { fail = 1; stop = true; break; }                         // [B3..B6]
           if (l < BT_LAYERS - 1) lap(3 + 2 * l);
         }
-        if (fail) break;
-        // ---- 4. last layer's accumulators -> per-node sums ---------------------------------------------------------
+        if (stop) break;
+        prev_cnt = cnt;
+        if (OV) continue;
+        // ---- 4. last layer's accumulators -> per-node sums (dim_a = 64) -----------------------------------------
         const int tile_cur = cur;
-        node_lo = s_src[cnt - 1];
+        node_lo = s_src[0][cnt - 1];
         if (tid <= BT_EDGES) s_rowwin[tid] = P.row_ptr[min(node_lo + tid, n_end)];
-        if (A == 128) {
-          // transposed last layer: thread tid < 128 owns channel tid (its tensor-memory lane) and adds the tile's edges
-          // (columns) in order, carrying the sum of the node that continues from the previous tile. The order of the
-          // additions depends on the node's edge list alone, so a system's result does not depend on its batch.
-          if (tid < A) {
-            const float b3 = s_bias[4 * A + tid];
-            int c_node = tile_cur;
-            float a_sum = acc;
-#pragma unroll 1
-            for (int cb = 0; cb < cnt; cb += 16) {
-              float v[16];
-              tc::tmem_ld16(tmem_row + cb, v);
-              int sn[16];
-#pragma unroll
-              for (int i = 0; i < 4; i++) {
-                const int4 t = *reinterpret_cast<const int4*>(&s_src[cb + 4 * i]);
-                sn[4 * i] = t.x; sn[4 * i + 1] = t.y; sn[4 * i + 2] = t.z; sn[4 * i + 3] = t.w;
-              }
-              if (cb + 16 <= cnt && sn[0] == c_node && sn[15] == c_node) {
-#pragma unroll
-                for (int i = 0; i < 16; i++) a_sum += v[i] + b3;   // sixteen edges of the running node (sources are sorted)
-              } else {
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                  if (cb + i < cnt) {
-                    if (sn[i] != c_node) { flush_until(c_node, sn[i], a_sum); a_sum = 0.f; c_node = sn[i]; }
-                    a_sum += v[i] + b3;
-                  }
-                }
-              }
-            }
-            acc = a_sum;
-            cur = c_node;
-          }
-          tc::fence_before_sync();
-          lap(9);
-        } else {
         {
           const float* bias = s_bias + 4 * A;
           const int cpp = max(A / 4, 32);
@@ -494,21 +631,23 @@ bee_scalar_tc_kernel(BtParams P) {
           const float* sp = stage_f + (slot & ~7) * 4 + sub;
           const int sx = slot & 7;
           for (int e = 0; e < cnt; e++) {
-            const int s = s_src[e];
+            const int s = s_src[0][e];
             if (s != c_node) { flush_until(c_node, s, a_sum); a_sum = 0.f; c_node = s; }
             a_sum += sp[(size_t)e * A + ((sx ^ (e & 7)) << 2)];
           }
           acc = a_sum;
           cur = c_node;
         }
-        }
-        if (bt_sync_or(fail)) { fail = 1; break; }                                        // [B7]
+        if (bt_sync_or(fail)) { fail = 1; stop = true; break; }                           // [B7]
         lap(10);
       }
+      if (OV && !fail && tid < A && tile_no > 0) { sums_transposed((tile_no - 1) & 1, prev_cnt); tc::fence_before_sync(); lap(9); }
+      if (!stop && bt_sync_or(fail)) fail = 1;                                            // [B8] segment finished
       if (!fail && n_begin < n_end) flush_until(cur, n_end, acc);
     }
-    if (PROF && P.prof != nullptr && tid == 0)
-      for (int i = 0; i < 12; i++) atomicAdd((unsigned long long*)&P.prof[i], (unsigned long long)pc[i]);
+    // one thread of each role: tid 0 (adds up the previous tile), 128 (geometry of the next tile), 256 (neither)
+    if (PROF && P.prof != nullptr && (tid == 0 || tid == 128 || tid == 256))
+      for (int i = 0; i < 12; i++) atomicAdd((unsigned long long*)&P.prof[(tid >> 7) * 12 + i], (unsigned long long)pc[i]);
   }
   if (fail && lane == 0 && P.status != nullptr) atomicOr(P.status, LD_FLAG_TIMEOUT);
   __syncthreads();
@@ -559,10 +698,12 @@ extern "C" int ld_bee_messages_scalar_bf16_tc(const int* row_ptr, const int* dst
   P.out_a = out_a; P.status = status_dev; P.feat_bf16 = feat_bf16;
 #ifdef LD_PHASE_COUNTERS
   P.prof = ld_internal_phase_counters();
-  auto kern = P.prof != nullptr ? bee_scalar_tc_kernel<true> : bee_scalar_tc_kernel<false>;
+  const bool fast = C == 128 && A == 128 && feat_bf16 == 2;
+  auto kern = P.prof != nullptr ? (fast ? bee_scalar_tc_kernel<true, true> : bee_scalar_tc_kernel<true, false>)
+                                : (fast ? bee_scalar_tc_kernel<false, true> : bee_scalar_tc_kernel<false, false>);
 #else
   P.prof = nullptr;
-  auto kern = bee_scalar_tc_kernel<false>;
+  auto kern = (C == 128 && A == 128 && feat_bf16 == 2) ? bee_scalar_tc_kernel<false, true> : bee_scalar_tc_kernel<false, false>;
 #endif
   LD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int dev = 0, sms = 148;

@@ -90,6 +90,57 @@ gather_rows_scalar(const float* __restrict__ x, const IndexT* __restrict__ idx, 
   }
 }
 
+// ---- legacy padded neighbour lists (extensions/neighbour_grid/neighbour_grid_kern.cu:226-306) ----------------
+// One warp per (node, slot) row of the padded table; lanes run over the channels, so reads and writes are coalesced.
+__global__ void __launch_bounds__(SEG_WARPS * 32)
+padded_read_kernel(const int* __restrict__ neighbours, const int* __restrict__ counts, const float* __restrict__ x,
+                   float* __restrict__ out, long long slots, int nodes, int nmax, int chan) {
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (long long s = (long long)blockIdx.x * SEG_WARPS + w; s < slots; s += (long long)gridDim.x * SEG_WARPS) {
+    const long long i = s / nmax;
+    const int j = (int)(s - i * nmax);
+    float* o = out + (size_t)s * chan;
+    if (j < counts[i]) {
+      const float* r = x + ((size_t)(i / nodes) * nodes + (size_t)neighbours[s]) * chan;
+      for (int c = lane; c < chan; c += 32) o[c] = __ldg(&r[c]);
+    } else {
+      for (int c = lane; c < chan; c += 32) o[c] = 0.f;
+    }
+  }
+}
+
+// One warp per node; each lane owns channels and adds the slots in ascending order, as the reference's loop does.
+__global__ void __launch_bounds__(SEG_WARPS * 32)
+padded_reduce_kernel(const int* __restrict__ counts, const float* __restrict__ x, float* __restrict__ out,
+                     long long Nt, int nmax, int chan) {
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (long long i = (long long)blockIdx.x * SEG_WARPS + w; i < Nt; i += (long long)gridDim.x * SEG_WARPS) {
+    const int n = min(counts[i], nmax);
+    const float* r = x + (size_t)i * nmax * chan;
+    for (int c = lane; c < chan; c += 32) {
+      float a = 0.f;
+      for (int j = 0; j < n; j++) a += __ldg(&r[(size_t)j * chan + c]);
+      out[(size_t)i * chan + c] = a;
+    }
+  }
+}
+
+// CSR edge list -> padded per-node lists of in-system neighbour indices (what getNeighbours returns,
+// neighbour_grid_kern.cu:62-133). A node with more than nmax neighbours raises LD_FLAG_CAPACITY.
+__global__ void padded_lists_kernel(const int* __restrict__ row_ptr, const int* __restrict__ dst, long long Nt, int nodes,
+                                    int nmax, int* __restrict__ lists, int* __restrict__ counts, int* __restrict__ status) {
+  const long long s = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= Nt * nmax) return;
+  const long long i = s / nmax;
+  const int j = (int)(s - i * nmax);
+  const int e0 = row_ptr[i], n = row_ptr[i + 1] - e0;
+  if (j == 0) {
+    counts[i] = n;
+    if (n > nmax) atomicOr(status, LD_FLAG_CAPACITY);
+  }
+  lists[s] = j < n ? dst[e0 + j] - (int)(i / nodes) * nodes : 0;
+}
+
 inline int rows_grid(long long rows) {
   long long b = (rows + SEG_WARPS - 1) / SEG_WARPS;
   const long long cap = 148LL * 16;
@@ -133,6 +184,39 @@ extern "C" int ld_gather_rows(const float* x_node, const void* idx, int index_by
     if (index_bytes == 4) gather_rows_scalar<int><<<g, SEG_WARPS * 32, 0, st>>>(x_node, (const int*)idx, E, F, out);
     else gather_rows_scalar<long long><<<g, SEG_WARPS * 32, 0, st>>>(x_node, (const long long*)idx, E, F, out);
   }
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}
+
+// Legacy dense interface of the reference extension (neighbour_grid.cpp:105-168): padded tables
+// [batch, nodes, neighboursmax(, chan)]. neighbours holds in-system node indices.
+extern "C" int ld_edges_read_padded(const int* neighbours, const int* counts, const float* x, int batch, int nodes, int nmax,
+                                    int chan, float* out, void* stream) {
+  if (batch < 0 || nodes < 0 || nmax < 0 || chan < 0) return LD_ERR_SHAPE;
+  const long long slots = (long long)batch * nodes * nmax;
+  if (slots == 0 || chan == 0) return LD_OK;
+  padded_read_kernel<<<rows_grid(slots), SEG_WARPS * 32, 0, (cudaStream_t)stream>>>(neighbours, counts, x, out, slots, nodes, nmax, chan);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}
+
+extern "C" int ld_edges_reduce_padded(const int* counts, const float* x, int batch, int nodes, int nmax, int chan, float* out,
+                                      void* stream) {
+  if (batch < 0 || nodes < 0 || nmax < 0 || chan < 0) return LD_ERR_SHAPE;
+  const long long Nt = (long long)batch * nodes;
+  if (Nt == 0 || chan == 0) return LD_OK;
+  padded_reduce_kernel<<<rows_grid(Nt), SEG_WARPS * 32, 0, (cudaStream_t)stream>>>(counts, x, out, Nt, nmax, chan);
+  LD_LAUNCH_CHECK();
+  return LD_OK;
+}
+
+extern "C" int ld_neighbour_lists_from_csr(const int* row_ptr, const int* dst, int batch, int nodes, int nmax, int* lists,
+                                           int* counts, int* status_dev, void* stream) {
+  if (batch < 0 || nodes < 0 || nmax <= 0) return LD_ERR_SHAPE;
+  const long long total = (long long)batch * nodes * nmax;
+  if (total == 0) return LD_OK;
+  padded_lists_kernel<<<(unsigned)ld_cdiv(total, 256), 256, 0, (cudaStream_t)stream>>>(row_ptr, dst, (long long)batch * nodes, nodes,
+                                                                                nmax, lists, counts, status_dev);
   LD_LAUNCH_CHECK();
   return LD_OK;
 }

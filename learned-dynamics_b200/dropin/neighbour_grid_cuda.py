@@ -12,6 +12,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from ld_b200 import graph as _graph  # noqa: E402
+from ld_b200._lib import lib as _lib, check as _check, ptr as _ptr, stream_ptr as _stream_ptr, LD_FLAG_CAPACITY  # noqa: E402
 
 MODE = int(os.environ.get("LD_NEIGHBOUR_MODE", "0"))
 
@@ -50,39 +51,56 @@ def get_neighbours(listmax, neighboursmax, cutoff, box_x, box_y, box_z, x):
     """-> (neighbourLists int32 [batch, nodes, neighboursmax], neighbourCounts int32 [batch, nodes]).
     Entries past a node's count are unspecified in the reference; here they are 0."""
     _check_listmax(listmax)
-    _, g = _build(cutoff, (box_x, box_y, box_z), x)
+    b, g = _build(cutoff, (box_x, box_y, box_z), x)
     batch, nodes, _ = x.shape
-    row_ptr = g["row_ptr"].long()
-    counts = (row_ptr[1:] - row_ptr[:-1]).to(torch.int32)
-    if counts.numel() > 0 and int(counts.max().item()) > neighboursmax:
+    lists = torch.empty(batch, nodes, neighboursmax, dtype=torch.int32, device=x.device)
+    counts = torch.empty(batch, nodes, dtype=torch.int32, device=x.device)
+    b.status.zero_()
+    _check(_lib().ld_neighbour_lists_from_csr(_ptr(g["row_ptr"]), _ptr(g["dst"]), batch, nodes, int(neighboursmax), _ptr(lists),
+                                             _ptr(counts), _ptr(b.status), _stream_ptr(x.device)))
+    if int(b.status.item()) & LD_FLAG_CAPACITY:
         raise RuntimeError("Neighbour list overflow occurred. Try increasing neighboursmax.")
-    lists = torch.zeros(batch * nodes, neighboursmax, dtype=torch.int32, device=x.device)
-    if g["E"] > 0:
-        src = g["src"].long()
-        slot = torch.arange(g["E"], device=x.device) - row_ptr[src]
-        lists[src, slot] = (g["dst"].long() - (src // nodes) * nodes).to(torch.int32)
-    return lists.reshape(batch, nodes, neighboursmax), counts.reshape(batch, nodes)
+    return lists, counts
+
+
+def _check_padded(neighbourCounts, neighbours, x, xdim):
+    for t, n in ((neighbourCounts, "neighbourCounts"), (neighbours, "neighbours"), (x, "x")):
+        _check_input(t, n)
+    if neighbourCounts.dim() != 2:
+        raise RuntimeError("neighbourCounts must have shape (batch, nodes)")
+    if neighbours.dim() != 3:
+        raise RuntimeError("neighbours must have shape (batch, nodes, neighboursmax)")
+    if x.dim() != xdim:
+        raise RuntimeError("x must have shape (batch, nodes, chan)" if xdim == 3 else
+                           "x must have shape (batch, nodes, neighboursmax, chan)")
+    batch, nodes = neighbourCounts.shape
+    if not (batch == neighbours.shape[0] == x.shape[0]):
+        raise RuntimeError("batch dimension of all tensors must match")
+    if not (nodes == neighbours.shape[1] == x.shape[1]):
+        raise RuntimeError("node dimension of all tensors must match")
+    if neighbourCounts.dtype != torch.int32 or neighbours.dtype != torch.int32 or x.dtype != torch.float32:
+        raise RuntimeError("expected int32 neighbourCounts and neighbours, float32 x")
+    return batch, nodes, neighbours.shape[2]
 
 
 def edges_read(neighbourCounts, neighbours, x):
-    """Legacy dense padded gather [batch, nodes, neighboursmax, chan] (zero past the count)."""
-    for t, n in ((neighbourCounts, "neighbourCounts"), (neighbours, "neighbours"), (x, "x")):
-        _check_input(t, n)
-    if neighbourCounts.dim() != 2 or neighbours.dim() != 3 or x.dim() != 3:
-        raise RuntimeError("expected neighbourCounts (batch, nodes), neighbours (batch, nodes, neighboursmax), x (batch, nodes, chan)")
-    batch, nodes, nmax = neighbours.shape
-    idx = neighbours.long() + (torch.arange(batch, device=x.device) * nodes)[:, None, None]
-    out = x.reshape(batch * nodes, -1)[idx.reshape(-1)].reshape(batch, nodes, nmax, -1)
-    mask = torch.arange(nmax, device=x.device)[None, None, :] < neighbourCounts[:, :, None]
-    return out * mask[..., None]
+    """Legacy dense padded gather -> [batch, nodes, neighboursmax, chan], zero past the count
+    (neighbour_grid.cpp:105-134)."""
+    batch, nodes, nmax = _check_padded(neighbourCounts, neighbours, x, 3)
+    chan = x.shape[2]
+    out = torch.empty(batch, nodes, nmax, chan, dtype=torch.float32, device=x.device)
+    _check(_lib().ld_edges_read_padded(_ptr(neighbours), _ptr(neighbourCounts), _ptr(x), batch, nodes, nmax, chan, _ptr(out),
+                                      _stream_ptr(x.device)))
+    return out
 
 
 def edges_reduce(neighbourCounts, neighbours, x):
-    """Legacy dense padded sum over the neighbour axis -> [batch, nodes, chan]."""
-    for t, n in ((neighbourCounts, "neighbourCounts"), (neighbours, "neighbours"), (x, "x")):
-        _check_input(t, n)
-    if x.dim() != 4:
-        raise RuntimeError("x must have shape (batch, nodes, neighboursmax, chan)")
-    nmax = x.shape[2]
-    mask = torch.arange(nmax, device=x.device)[None, None, :] < neighbourCounts[:, :, None]
-    return (x * mask[..., None]).sum(2)
+    """Legacy dense padded sum over the neighbour axis -> [batch, nodes, chan] (neighbour_grid.cpp:136-168)."""
+    batch, nodes, nmax = _check_padded(neighbourCounts, neighbours, x, 4)
+    if nmax != x.shape[2]:
+        raise RuntimeError("neighboursmax dimension must match between neighbours and x")
+    chan = x.shape[3]
+    out = torch.empty(batch, nodes, chan, dtype=torch.float32, device=x.device)
+    _check(_lib().ld_edges_reduce_padded(_ptr(neighbourCounts), _ptr(x), batch, nodes, nmax, chan, _ptr(out),
+                                        _stream_ptr(x.device)))
+    return out

@@ -23,6 +23,9 @@ SIGNATURES = {
     "ld_row_ptr_from_sorted": [P, I, LL, I, P, P],
     "ld_segment_sum": [P, P, I, I, P, P],
     "ld_gather_rows": [P, P, I, LL, I, P, P],
+    "ld_neighbour_lists_from_csr": [P, P, I, I, I, P, P, P, P],
+    "ld_edges_read_padded": [P, P, P, I, I, I, I, P, P],
+    "ld_edges_reduce_padded": [P, P, I, I, I, I, P, P],
     "ld_tensor_linear": [I, P, LL, LL, P, P, LL, I, I, P],
     "ld_tensor_linear_dw_workspace": [I, LL, I, I, P],
     "ld_tensor_linear_dw": [I, P, P, P, LL, I, I, P, SZ, P],

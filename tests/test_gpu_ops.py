@@ -185,6 +185,19 @@ def test_drop_in_neighbour_grid_module():
     ones = torch.ones(20, 60, 7, device="cuda")
     red = ng.edges_reduce(counts, neighbours, ng.edges_read(counts, neighbours, ones))
     assert (red[:, :, 0] - counts).abs().sum() < 1e-4
+    # bit-exact against the loops of neighbour_grid_kern.cu:226-306 (zero past the count; slots added in ascending order)
+    feat = torch.randn(20, 60, 37, generator=gen).cuda()
+    read = ng.edges_read(counts, neighbours, feat)
+    want = torch.gather(feat[:, None].expand(-1, 60, -1, -1), 2, neighbours.long()[..., None].expand(-1, -1, -1, 37)) * mask[..., None]
+    assert torch.equal(read, want)
+    table = torch.randn(20, 60, 32, 37, generator=gen).cuda()
+    acc = torch.zeros(20, 60, 37, device="cuda")
+    for j in range(32):
+        acc = torch.where(mask[:, :, j, None], acc + table[:, :, j], acc)
+    assert torch.equal(ng.edges_reduce(counts, neighbours, table), acc)
+    with pytest.raises(RuntimeError, match="neighboursmax dimension"):
+        ng.edges_reduce(counts, neighbours, table[:, :, :16].contiguous())
+    assert ng.edges_read(counts[:0], neighbours[:0], feat[:0]).shape == (0, 60, 32, 37)
     src, dst, ec = ng.get_edges(32, 64, 7., *box, x)
     assert src.dtype == torch.int32 and ec.shape == (20,) and int(ec[-1]) == src.numel() == int(counts.sum())
     with pytest.raises(RuntimeError, match="listmax"):
