@@ -50,7 +50,8 @@ DEFAULT_WORKLOAD = "polymers_l2_1024x256"
 DRAM_BYTES_PER_EDGE = {"bee_scalar_tc_kernel": 64.1, "bee_vd_kernel": 62.0, "painn_message_tc_kernel": 33.8}
 # timer regions of the edge kernels of an l<=2 message layer -> kernel names
 BEE_EDGE_REGIONS = {"bee_messages_fused_tc": "bee_fused_tc_kernel", "bee_messages_scalar_tc": "bee_scalar_tc_kernel",
-                    "bee_messages_scalar": "bee_scalar_kernel", "bee_messages_vd": "bee_vd_kernel"}
+                    "bee_messages_scalar": "bee_scalar_kernel", "bee_messages_vd": "bee_vd_kernel",
+                    "bee_messages_vd_tc": "bee_vd_tc_kernel"}
 
 
 def make_positions(w, systems, seed):
@@ -376,6 +377,8 @@ def main():
     ap.add_argument("--l2-layer", default="pair", choices=["pair", "single"],
                     help="l<=2 message layer: 'pair' = two edge kernels (default), 'single' = one edge kernel per layer "
                          "(chan = dim_a = 128; per-node sums accumulated in tensor memory; measured slower)")
+    ap.add_argument("--product-sums", default="fma", choices=["fma", "tensor"],
+                    help="l<=2 network: rank-1 / rank-2 product sums by FP32 FMAs (default) or by one tcgen05 MMA per edge")
     ap.add_argument("--component-major", action="store_true",
                     help="keep the vector / rank-2 node features as [.., 3|9, chan] between the layers (plain-row channel mixings)")
     args = ap.parse_args()
@@ -410,6 +413,7 @@ def main():
         for m in dn.modules():
             if isinstance(m, bee.Messages):
                 m.fused_kernel = args.l2_layer == "single"
+                m.vd_tensor_core = args.product_sums == "tensor"
     else:
         dn = painn.set_precision(build_model(w, dev), args.precision)
     painn.enable_rollout_graphs(dn)   # fixed-capacity graph buffers: no step waits for its edge count
@@ -527,7 +531,7 @@ def main():
             "metric": "edge_messages_per_sec", "value": value, "unit": "edge-messages/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16" if tc_path else "f32", "data": "synthetic",
-            "config": workload_config(args.workload, w), "precision": args.precision, "l2_layer": args.l2_layer if is_bee else None,
+            "config": workload_config(args.workload, w), "precision": args.precision, "l2_layer": args.l2_layer if is_bee else None, "product_sums": args.product_sums if is_bee else None,
             "edges_per_step": total_edges // args.steps,
             "dt_steps_per_sec": args.steps / (total_ms * 1e-3),
             "system_steps_per_sec": args.steps * w["systems"] / (total_ms * 1e-3),

@@ -214,6 +214,14 @@ int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, const float* ri
 int ld_bee_messages_vd_f32(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, float r0, const float* L0,
                            const float* L1, const float* L2, const float* enc_w, const float* enc_b, const float* jacobi,
                            float scale, void* S_v, void* S_d, int feat_bf16, int out_bf16, void* stream);
+/* The same sums for chan = 128 on the tensor cores: one tcgen05 MMA per edge (the neighbour's row scaled by the radial
+ * weight, times a 16 x 64 matrix of monomials of the unit vector), accumulated over a node's edges in tensor memory.
+ * rows [Nt][128][16] BF16 interleaved per channel (l0, l1[3], l2[9], 3 unused; written by ld_linear_bf16_tc_out16);
+ * S_v [Nt][3][640], S_d [Nt][9][640] BF16 component-major, times scale. BF16 operands, FP32 accumulation: 2e-2.
+ * A wait that runs out raises LD_FLAG_TIMEOUT in *status_dev. */
+int ld_bee_messages_vd_bf16_tc(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, float r0, const void* rows,
+                               const float* enc_w, const float* enc_b, const float* jacobi, float scale, void* S_v, void* S_d,
+                               int* status_dev, void* stream);
 int ld_bee_messages_scalar_f32(const int* row_ptr, const int* dst, const float* rij, int Nt, int chan, int dim_a, float r0,
                                const float* L0, const float* L1, const float* L2, const float* enc_w, const float* enc_b,
                                const float* jacobi, const float* Yt, const float* W1t, const float* b1, const float* W2t,

@@ -97,6 +97,11 @@ class Messages(nn.Module):
         # by the tensor cores). Correct and deterministic, but measured slower than the two-kernel path on B200 (its
         # per-edge synchronisation leaves the warps latency-bound), so it is opt-in.
         self.fused_kernel = False
+        # bf16, chan = 128: True forms the rank-1 / rank-2 product sums on the tensor cores (one MMA per edge with the
+        # scaled row as a tensor-memory operand, sums accumulated in tensor memory) instead of FP32 FMAs. Correct and
+        # deterministic, four times fewer instructions per edge, but measured slower on B200 (about 24 ms against 17 ms
+        # per 19.4 M edges): its warps wait on one another once per four edges, the FMA kernel's never do. Opt-in.
+        self.vd_tensor_core = False
 
     def load_state_dict(self, state, *a, **k):
         # the reference wraps mlp_a in torch.compile, which prefixes its keys
@@ -222,10 +227,16 @@ class Messages(nn.Module):
         S_d = torch.empty((Nt, 9, 5 * C) if sums16 else (Nt, 5 * C, 3, 3), dtype=sdt, device=dev)
         B_a = torch.empty(Nt, self.dim_a, dtype=torch.float32, device=dev)
         st = stream_ptr(dev)
-        with KERNEL_TIMER.region("bee_messages_vd"):
-            check(lib().ld_bee_messages_vd_f32(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, float(self.r0), ptr(l0),
-                                               ptr(l1), ptr(l2), ptr(w["enc_w"]), ptr(w["enc_b"]), ptr(w["jac"]), 0.1,
-                                               ptr(S_v), ptr(S_d), 2 if feat16 else 0, 1 if sums16 else 0, st))
+        if feat16 and sums16 and C == 128 and self.vd_tensor_core:
+            with KERNEL_TIMER.region("bee_messages_vd_tc"):
+                check(lib().ld_bee_messages_vd_bf16_tc(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, float(self.r0), ptr(lp),
+                                                       ptr(w["enc_w"]), ptr(w["enc_b"]), ptr(w["jac"]), 0.1, ptr(S_v), ptr(S_d),
+                                                       ptr(ops.tc_status(dev)), st))
+        else:
+            with KERNEL_TIMER.region("bee_messages_vd"):
+                check(lib().ld_bee_messages_vd_f32(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, float(self.r0), ptr(l0),
+                                                   ptr(l1), ptr(l2), ptr(w["enc_w"]), ptr(w["enc_b"]), ptr(w["jac"]), 0.1,
+                                                   ptr(S_v), ptr(S_d), 2 if feat16 else 0, 1 if sums16 else 0, st))
         if self.precision == "bf16":
             with KERNEL_TIMER.region("bee_messages_scalar_tc"):
                 check(lib().ld_bee_messages_scalar_bf16_tc(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, self.dim_a,

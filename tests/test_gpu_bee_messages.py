@@ -239,6 +239,49 @@ def test_messages_single_edge_kernel_vs_oracle_and_two_kernel_path(B, N, r0, box
             assert a.abs().max() == 0
 
 
+@pytest.mark.parametrize("B,N,r0,box", [(2, 300, 3.0, (9.0, 9.0, 9.5)), (8, 256, 5.0, None), (1, 6, 1.0, None), (3, 40, 0.9, None),
+                                        (2, 20, 0.01, None), (1, 700, 2.5, (9.0, 8.0, 8.5)), (24, 512, 5.0, None)])
+def test_product_sums_on_tensor_cores_vs_oracle_and_fma_kernel(B, N, r0, box):
+    """chan = 128: the rank-1 / rank-2 product sums by one tcgen05 MMA per edge, accumulated per node in tensor memory,
+    against the float64 oracle at 2e-2 and against the FP32 FMA kernel on the same BF16 rows; bit-identical reruns, no
+    wait ran out. Cases: many tiles and node segments, nodes with more than a tile of edges, sparse graphs with isolated
+    nodes, a graph without any edge."""
+    from ld_b200 import bee, graph_layers as GL, ops
+    from oracle import reference_math as R
+    dims = (128, 64, 32, 128)
+    torch.manual_seed(N + 1)
+    mes = bee.set_precision(bee.Messages(r0, *dims).cuda(), "bf16")
+    g = torch.Generator().manual_seed(18 + N)
+    if box is None:
+        pos = torch.cumsum(torch.randn(B, N, 3, generator=g) / 3 ** 0.5, dim=1)
+    else:
+        pos = torch.rand(B, N, 3, generator=g) * torch.tensor(box)
+    x_a, x_v, x_d = torch.randn(B, N, 128, generator=g), torch.randn(B, N, 64, 3, generator=g), torch.randn(B, N, 32, 3, 3, generator=g)
+    with torch.no_grad():
+        graph = GL.Graph.radius_graph(r0, box, pos.cuda())
+        args = (graph, graph.rij, x_a.cuda(), x_v.cuda(), x_d.cuda())
+        mes.vd_tensor_core = True
+        got = mes(*args)
+        again = mes(*args)
+        mes.vd_tensor_core = False
+        fma = mes(*args)
+    torch.cuda.synchronize()
+    ops.check_tc_status("cuda")
+    ref = R.OMessages(r0, *dims)
+    ref.load_state_dict({k: v.cpu() for k, v in mes.state_dict().items()})
+    ref.double()
+    with torch.no_grad():
+        want = ref(graph.src.cpu(), graph.dst.cpu(), graph.rij.cpu().double(), x_a.double(), x_v.double(), x_d.double())
+    for a, b, c, w in zip(got, again, fma, want):
+        assert torch.equal(a, b)
+        if w.abs().max() > 0:
+            close(a, w, BF16_BAR)
+            close(a, c, BF16_BAR)
+        else:
+            assert a.abs().max() == 0
+    assert torch.equal(got[0], fma[0])   # the scalar channel does not depend on the choice
+
+
 @pytest.mark.parametrize("dims,rows", [((128, 64, 32, 128), (3, 50)), ((16, 8, 8, 32), (1, 7)), ((64, 32, 16, 96), (2, 33))])
 def test_self_tens_prods_fused_vs_reference_sequence(dims, rows):
     """node-local products: three stacked channel mixings + one product kernel + three concatenated Y maps against
