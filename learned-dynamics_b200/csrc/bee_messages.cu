@@ -28,7 +28,7 @@ __device__ __forceinline__ float bm_ld(const __nv_bfloat16* p, size_t i) { retur
 
 
 constexpr int BM_TILE = 32;  // edges staged per step (scalar kernel: the rows of its MLP tile)
-constexpr int BV_TILE = 64;  // edges staged per step in the product-sum kernel (two block barriers per step)
+constexpr int BV_TILE = 128;  // edges staged per step in the product-sum kernel (two block barriers per step)
 
 struct BeeEdgeParams {
   const int* row_ptr; const int* dst; const float* rij;
@@ -94,9 +94,11 @@ __device__ __forceinline__ void edge_phi(const EdgeGeom& g, const float* w8, flo
 // S_v[node][k][c][3], k over (011,101,121,211,111); S_d[node][k][c][9], k over (022,202,112,222,212):
 // the layouts a channel mixing with 5*chan inputs expects. Thread = channel; a block walks its nodes
 // and stages the geometry of up to 32 edges at a time in shared memory.
-template <typename FT, bool PACKED>
+// CC: the channel count as a compile-time constant (0: taken from the parameters)
+template <typename FT, bool PACKED, int CC>
 __global__ void __launch_bounds__(128, 4)   // four blocks per SM: at most 128 registers
-bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d, float scale, int out_bf16) {
+bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d, float scale, int out_bf16_) {
+  const int out_bf16 = CC > 0 ? 1 : out_bf16_;   // the instance with a constant width is the tensor-core path's: BF16 sums
   const FT* __restrict__ F0 = reinterpret_cast<const FT*>(P.L0);
   const FT* __restrict__ F1 = reinterpret_cast<const FT*>(P.L1);
   const FT* __restrict__ F2 = reinterpret_cast<const FT*>(P.L2);
@@ -105,7 +107,7 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
   __shared__ float s_jac[72];
   if (threadIdx.x < 8) ld_poly8_to_chebyshev(P.jacobi + threadIdx.x * 9, s_jac + threadIdx.x * 9);   // Chebyshev form of the radial polynomials
   __syncthreads();
-  const int C = P.chan;
+  const int C = CC > 0 ? CC : P.chan;
   // all blocks walk the node range segment by segment, so that the neighbour rows a segment gathers (its nodes'
   // neighbours are nearby nodes) stay resident in L2 while its edges are processed
   const int seg_nodes = P.seg_nodes > 0 ? P.seg_nodes : P.Nt;
@@ -378,9 +380,10 @@ extern "C" int ld_bee_messages_vd_f32(const int* row_ptr, const int* dst, const 
   BeeEdgeParams P{row_ptr, dst, rij, Nt, chan, r0, L0, L1, L2, enc_w, enc_b, jacobi, (int)(seg < 1024 ? 1024 : seg)};
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (feat_bf16 == 2) bee_vd_kernel<__nv_bfloat16, true><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale, out_bf16);
-  else if (feat_bf16) bee_vd_kernel<__nv_bfloat16, false><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale, out_bf16);
-  else bee_vd_kernel<float, false><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale, out_bf16);
+  if (feat_bf16 == 2 && chan == 128 && out_bf16) bee_vd_kernel<__nv_bfloat16, true, 128><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale, 1);
+  else if (feat_bf16 == 2) bee_vd_kernel<__nv_bfloat16, true, 0><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale, out_bf16);
+  else if (feat_bf16) bee_vd_kernel<__nv_bfloat16, false, 0><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale, out_bf16);
+  else bee_vd_kernel<float, false, 0><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale, out_bf16);
   LD_LAUNCH_CHECK();
   return LD_OK;
 }
