@@ -250,6 +250,11 @@ extern "C" int ld_pack_weights_bf16(const float* W, long long sw0, long long sw1
   return LD_OK;
 }
 
+// the streaming kernel for BF16 rows (gemm_rows16.cu)
+bool ld_gemm_rows16_applies(int K, int N);
+int ld_gemm_rows16_launch(const void* x16, long long rows, int K, int S, const void* wp, const float* bias, int N, int act, float* y,
+                          int* status_dev, void* stream, unsigned wait_limit);
+
 // y = act(x W^T + b) on the tensor cores. x: FP32 [rows_outer, K, S] contiguous, y: [rows_outer, N, S].
 // S in {1,3,9}; N a multiple of 32, N <= 512. wp from ld_pack_weights_bf16. status_dev: optional
 // device int32 that receives LD_FLAG_TIMEOUT if a bounded wait ran out.
@@ -265,6 +270,8 @@ static int linear_tc_launch(const float* x, int in_bf16, long long rows_outer, i
     return LD_ERR_UNSUPPORTED;
   }
   if (rows_outer == 0) return LD_OK;
+  if (in_bf16 && !out_bf16 && !selftest_no_weights && ld_gemm_rows16_applies(K, N))
+    return ld_gemm_rows16_launch(x, rows_outer * S, K, S, wp, bias, N, act, (float*)y, status_dev, stream, wait_limit);
   GemmParams P;
   P.x = x; P.in_bf16 = in_bf16; P.y = (float*)y; P.out_bf16 = out_bf16; P.y_ld_row = ld_row; P.y_ld_col = ld_col; P.y_off = off; P.wp = (const __nv_bfloat16*)wp; P.bias = bias; P.rows = rows_outer * S; P.K = K; P.N = N; P.S = S;
   P.act = act; P.status = status_dev; P.wait_limit = wait_limit; P.selftest_no_weights = selftest_no_weights;

@@ -192,6 +192,35 @@ def test_linear_component_major_bf16_input_matches_fp32_input(inds, rows, K, N):
     assert int(ops.tc_status("cuda").item()) == 0
 
 
+@pytest.mark.parametrize("rows,S,K,N,bias,act", [(148 * 128 * 3 + 77, 1, 640, 64, False, 0), (40000, 9, 640, 32, False, 0),
+                                                 (30011, 3, 256, 128, True, 2), (1000, 1, 64, 96, True, 1), (1, 1, 640, 64, False, 0)])
+def test_streaming_rows_gemm_against_float_reference(rows, S, K, N, bias, act):
+    """the streaming kernel for BF16 rows (weights resident in shared memory, six chunks of asynchronous copies in
+    flight, accumulators of two tiles alternating): many tiles per block, a ragged last tile, bias and activation,
+    against the FP32 product of the same BF16-rounded operands (1e-5 of the output scale; the sums differ only in order)"""
+    from ld_b200 import ops
+    g = torch.Generator().manual_seed(rows % 1000 + K + N)
+    x16 = torch.randn(rows, S, K, generator=g).to(torch.bfloat16).cuda()
+    W = (torch.randn(N, K, generator=g) * K ** -0.5).cuda()
+    b = torch.randn(N, generator=g).cuda() if bias else None
+    Wp = ops.pack_weights_bf16(W)
+    inds = {1: 0, 3: 1, 9: 2}[S]
+    got = ops.linear_bf16_tc_cm(x16, Wp, N, inds, bias=b, act=act)
+    again = ops.linear_bf16_tc_cm(x16, Wp, N, inds, bias=b, act=act)
+    torch.cuda.synchronize()
+    assert int(ops.tc_status("cuda").item()) == 0
+    assert torch.equal(got, again)
+    want = x16.float() @ W.to(torch.bfloat16).float().t()
+    if bias:
+        want = want + b
+    if act == 1:
+        want = torch.nn.functional.silu(want)
+    elif act == 2:
+        want = torch.nn.functional.leaky_relu(want, 0.1)
+    want = want.permute(0, 2, 1).reshape(got.shape)
+    close(got, want, 1e-5)
+
+
 def test_bounded_wait_runs_out_and_returns():
     """A launch of the tensor-core linear whose weight panels are never requested: every wait gives up after 64 polls,
     all blocks leave through the failure path (status flag set, tensor memory released, no trap), the host check
