@@ -31,15 +31,6 @@ constexpr int BT_SYNC_THREADS = (BT_WORK_WARPS + 1) * 32;
 constexpr int BT_STAGES = 3;        // weight ring: 32 KB slabs (a bulk copy costs about the same issue time whatever its size)
 constexpr int BT_SLAB_BYTES = 32 * 1024;
 constexpr int BT_LAYERS = 4;
-#ifndef BT_PIPE_SUMS
-#define BT_PIPE_SUMS 0
-#endif
-#ifndef BT_RELAY
-#define BT_RELAY 1
-#endif
-#ifndef BT_PIPE_EPI
-#define BT_PIPE_EPI 1
-#endif
 // Byte stride between the 8-column panels of the operand tile: 128 rows x 16 bytes plus one 16-byte pad, so that the
 // panels a warp of the product phase writes to (32 channels = 4 panels, same row) fall into different banks
 constexpr int BT_PANEL = BT_EDGES * 16 + 16;
@@ -246,18 +237,14 @@ bee_scalar_tc_kernel(BtParams P) {
               tc::mma_commit(&bar_empty[st]);
             }
             if (!fail) tc::mma_commit(&bar_accum);
-#if BT_RELAY
             // the issuing lane polls for the completion itself and passes it on through the block barrier below: a
             // hardware barrier wakes the sixteen working warps faster than sixteen suspended mbarrier waits
             if (!fail && !tc::mbar_wait_tight(&bar_accum, accum_phase & 1)) fail = 1;
             tc::fence_before_sync();
-#endif
           }
           accum_phase++;
           fail = __shfl_sync(0xffffffffu, fail, 0);
-#if BT_RELAY
           if (bt_sync_or(fail)) { fail = 1; stop = true; break; }    // [A0..A3] accumulators of layer l complete
-#endif
           if (OV && l == BT_LAYERS - 1) break;          // the next barrier is B2 of the following tile (or the segment's end)
           if (bt_sync_or(fail)) { fail = 1; stop = true; break; }    // [B3..B6] accumulators consumed / next operand ready
         }
@@ -272,9 +259,6 @@ bee_scalar_tc_kernel(BtParams P) {
     // first GEMM of this tile runs, and the per-node sums of a tile (warps 0..3, reading tensor-memory columns
     // [256, 384)) run while the other warps already form the products of the next tile.
     const bool OV = FAST || A == 128;
-#if !BT_RELAY
-    uint32_t accum_phase = 0;
-#endif
     long long pc[PROF ? 12 : 1];
 #pragma unroll
     for (int i = 0; i < (PROF ? 12 : 1); i++) pc[i] = 0;
@@ -369,33 +353,13 @@ bee_scalar_tc_kernel(BtParams P) {
             }
           }
         };
-        // two register blocks: the next sixteen columns are on their way from tensor memory while these are added
-        uint32_t ra[16], rb[16];
+        uint32_t ra[16];
         const uint32_t t0 = tmem_row + sum_col;
-        if (!(FAST && BT_PIPE_SUMS)) {
 #pragma unroll 1
-          for (int cb = 0; cb < cnt; cb += 16) {
-            tc::tmem_ld16_issue(t0 + cb, ra);
-            tc::tmem_ld16_wait(ra);
-            add16(ra, cb);
-          }
-          acc = a_sum;
-          cur = c_node;
-          return;
-        }
-        tc::tmem_ld16_issue(t0, ra);
-        tc::tmem_ld16_wait(ra);
-#pragma unroll 1
-        for (int cb = 0; cb < cnt; cb += 32) {
-          const bool more = cb + 16 < cnt, more2 = cb + 32 < cnt;
-          if (more) tc::tmem_ld16_issue(t0 + cb + 16, rb);
+        for (int cb = 0; cb < cnt; cb += 16) {
+          tc::tmem_ld16_issue(t0 + cb, ra);
+          tc::tmem_ld16_wait(ra);
           add16(ra, cb);
-          if (more) {
-            tc::tmem_ld16_wait(rb);
-            if (more2) tc::tmem_ld16_issue(t0 + cb + 32, ra);
-            add16(rb, cb + 16);
-            if (more2) tc::tmem_ld16_wait(ra);
-          }
         }
         acc = a_sum;
         cur = c_node;
@@ -515,17 +479,7 @@ bee_scalar_tc_kernel(BtParams P) {
         }
         // ---- 3. four layers ------------------------------------------------------------------------------------
         for (int l = 0; l < BT_LAYERS; l++) {
-#if BT_RELAY
-          if (bt_sync_or(fail)) { fail = 1; stop = true; break; }                         // [A0..A3]
-#else
-          {
-            int done = 1;
-            if (lane == 0) done = tc::mbar_wait(&bar_accum, accum_phase & 1) ? 1 : 0;
-            done = __shfl_sync(0xffffffffu, done, 0);
-            if (!done) fail = 1;
-          }
-          accum_phase++;
-#endif
+          if (bt_sync_or(fail)) { fail = 1; stop = true; break; }                         // [A0..A3] layer l complete
           tc::fence_after_sync();
           lap(2 + 2 * l);
           const int N = P.layer[l].N;
@@ -553,7 +507,7 @@ bee_scalar_tc_kernel(BtParams P) {
               q.z = tc::pack_bf16x2(t8[4], t8[5]); q.w = tc::pack_bf16x2(t8[6], t8[7]);
               *reinterpret_cast<uint4*>(a_smem + (size_t)((oc + cb) >> 3) * BT_PANEL + row * 16) = q;
             };
-            if (FAST && BT_PIPE_EPI) {
+            if (FAST) {
               // sixteen columns at a time through two register blocks: the next block is on its way from tensor memory
               // while this one is converted and stored
               auto put16 = [&](const uint32_t* r, int cb) {
