@@ -164,6 +164,13 @@ int ld_linear_bf16_tc_out16(const float* x, long long rows_outer, int K, int S, 
 int ld_linear_bf16_tc_out16_split(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias, int N,
                                   int act, void* y_bf16, long long ld_row, long long ld_col, int off, int s_split,
                                   long long s_jump, int in_cm, int* status_dev, void* stream);
+/* The three channel mixings L0, L1, L2 of an l<=2 message layer (archs/diffuser_atoms15.py:244-246) in one launch that
+ * writes whole neighbour rows: rows [Nt][128][16] BF16 = (L0 x_a, L1 x_v [3], L2 x_d [9], 0, 0, 0) per (node, channel),
+ * the same values as three ld_linear_bf16_tc_out16 launches into that buffer, without their partially written sectors.
+ * x_a [Nt][da], x_v [Nt][dv][3], x_d [Nt][dd][3][3] FP32; W*p from ld_pack_weights_bf16 ([128][da|dv|dd]); chan = 128,
+ * widths multiples of 16 with da + 3 dv + 9 dd <= 640. LD_FLAG_TIMEOUT in *status_dev if a wait runs out. */
+int ld_bee_left_rows_bf16_tc(const float* x_a, const float* x_v, const float* x_d, long long Nt, int da, int dv, int dd, int chan,
+                             const void* W0p, const void* W1p, const void* W2p, void* rows, int* status_dev, void* stream);
 
 /* Self-test of the bounded waits (no counterpart in the reference): ld_linear_bf16_tc (S = 1, no bias) on a launch
  * whose weight panels are never requested and whose waits give up after 64 polls. Every block leaves through the

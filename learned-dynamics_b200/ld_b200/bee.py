@@ -102,6 +102,8 @@ class Messages(nn.Module):
         # deterministic, four times fewer instructions per edge, but measured slower on B200 (about 24 ms against 17 ms
         # per 19.4 M edges): its warps wait on one another once per four edges, the FMA kernel's never do. Opt-in.
         self.vd_tensor_core = False
+        # bf16, chan = 128: L0, L1, L2 as one launch that writes whole neighbour rows
+        self.rows_one_launch = True
 
     def load_state_dict(self, state, *a, **k):
         # the reference wraps mlp_a in torch.compile, which prefixes its keys
@@ -210,9 +212,18 @@ class Messages(nn.Module):
             # the edge kernels fetch all thirteen values of a (neighbour, channel) with one 32-byte load
             pk = lambda m: m._packed_for(ops)
             lp = torch.empty(Nt, C, 16, dtype=torch.bfloat16, device=dev)
-            ops.linear_bf16_tc(x_a.reshape(Nt, -1), pk(self.L0), C, inds=0, out=lp, out_layout=(16 * C, 16, 0))
-            ops.linear_bf16_tc(x_v.reshape(Nt, -1, 3), pk(self.L1), C, inds=1, out=lp, out_layout=(16 * C, 16, 1))
-            ops.linear_bf16_tc(x_d.reshape(Nt, -1, 3, 3), pk(self.L2), C, inds=2, out=lp, out_layout=(16 * C, 16, 4))
+            da, dv, dd = x_a.shape[-1], x_v.shape[-2], x_d.shape[-3]
+            if (self.rows_one_launch and C == 128 and da % 16 == 0 and dv % 16 == 0 and dd % 16 == 0 and da + 3 * dv + 9 * dd <= 640
+                    and all(t.dtype == torch.float32 for t in (x_a, x_v, x_d))):
+                # one launch that writes whole 32-byte rows (three launches write 2, 6 and 18 bytes of each)
+                with KERNEL_TIMER.region("linear_bf16_tc"):
+                    check(lib().ld_bee_left_rows_bf16_tc(ptr(x_a.contiguous()), ptr(x_v.contiguous()), ptr(x_d.contiguous()), Nt, da, dv,
+                                                         dd, C, ptr(pk(self.L0)), ptr(pk(self.L1)), ptr(pk(self.L2)), ptr(lp),
+                                                         ptr(ops.tc_status(dev)), stream_ptr(dev)))
+            else:
+                ops.linear_bf16_tc(x_a.reshape(Nt, -1), pk(self.L0), C, inds=0, out=lp, out_layout=(16 * C, 16, 0))
+                ops.linear_bf16_tc(x_v.reshape(Nt, -1, 3), pk(self.L1), C, inds=1, out=lp, out_layout=(16 * C, 16, 1))
+                ops.linear_bf16_tc(x_d.reshape(Nt, -1, 3, 3), pk(self.L2), C, inds=2, out=lp, out_layout=(16 * C, 16, 4))
             l0 = l1 = l2 = lp
         else:
             l0 = self.L0(x_a.reshape(Nt, -1))

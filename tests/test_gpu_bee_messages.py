@@ -239,6 +239,40 @@ def test_messages_single_edge_kernel_vs_oracle_and_two_kernel_path(B, N, r0, box
             assert a.abs().max() == 0
 
 
+@pytest.mark.parametrize("Nt,dims", [(1000, (128, 64, 32)), (128 * 150 + 5, (128, 64, 32)), (7, (64, 16, 16)), (300, (16, 48, 32))])
+def test_left_rows_in_one_launch_equal_three_launches(Nt, dims):
+    """L0 | L1 | L2 of a message layer as one launch that writes whole [node][chan][16] BF16 rows against the three
+    tensor-core linears writing into the same buffer: same BF16 operands and FP32 sums (bit for bit, or one BF16 step
+    where the sums round differently), pads zero; also against the FP32 product of the rounded operands."""
+    from ld_b200 import ops
+    from ld_b200._lib import lib, check, ptr, stream_ptr
+    da, dv, dd = dims
+    C = 128
+    g = torch.Generator().manual_seed(Nt + da)
+    x_a, x_v, x_d = (torch.randn(Nt, da, generator=g).cuda(), torch.randn(Nt, dv, 3, generator=g).cuda(),
+                     torch.randn(Nt, dd, 3, 3, generator=g).cuda())
+    W = [(torch.randn(C, k, generator=g) * k ** -0.5).cuda() for k in dims]
+    Wp = [ops.pack_weights_bf16(w) for w in W]
+    want = torch.full((Nt, C, 16), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.linear_bf16_tc(x_a, Wp[0], C, inds=0, out=want, out_layout=(16 * C, 16, 0))
+    ops.linear_bf16_tc(x_v, Wp[1], C, inds=1, out=want, out_layout=(16 * C, 16, 1))
+    ops.linear_bf16_tc(x_d, Wp[2], C, inds=2, out=want, out_layout=(16 * C, 16, 4))
+    got = torch.full((Nt, C, 16), float("nan"), dtype=torch.bfloat16, device="cuda")
+    check(lib().ld_bee_left_rows_bf16_tc(ptr(x_a), ptr(x_v), ptr(x_d), Nt, da, dv, dd, C, ptr(Wp[0]), ptr(Wp[1]), ptr(Wp[2]), ptr(got),
+                                         ptr(ops.tc_status("cuda")), stream_ptr(torch.device("cuda"))))
+    torch.cuda.synchronize()
+    ops.check_tc_status("cuda")
+    assert (got[:, :, 13:] == 0).all()
+    g13, w13 = got[:, :, :13].float(), want[:, :, :13].float()
+    assert torch.isfinite(g13).all()
+    close(g13, w13, 2.0 ** -7)                       # at most one BF16 step of the largest entry
+    assert (g13 != w13).float().mean() < 1e-3       # and almost all entries bit-identical
+    r = lambda t: t.to(torch.bfloat16).float()
+    ref = torch.cat([(r(x_a) @ r(W[0]).t())[:, :, None], torch.einsum("nks,ck->ncs", r(x_v), r(W[1])),
+                     torch.einsum("nks,ck->ncs", r(x_d).reshape(Nt, dd, 9), r(W[2]))], dim=2)
+    close(g13, ref, 2.0 ** -7)
+
+
 @pytest.mark.parametrize("B,N,r0,box", [(2, 300, 3.0, (9.0, 9.0, 9.5)), (8, 256, 5.0, None), (1, 6, 1.0, None), (3, 40, 0.9, None),
                                         (2, 20, 0.01, None), (1, 700, 2.5, (9.0, 8.0, 8.5)), (24, 512, 5.0, None)])
 def test_product_sums_on_tensor_cores_vs_oracle_and_fma_kernel(B, N, r0, box):
