@@ -323,6 +323,14 @@ int ld_group_norm_cm(const float* x, int B, int N, int C, int S, int groups, int
                      const float* beta, float* y, void* workspace, void* stream);
 int ld_bee_self_products_cm(const float* lr0, const float* lr1, const float* lr2, long long rows, int chan, float* P_a,
                             void* P_v, void* P_d, void* stream);
+/* The six channel mixings in front of the node-local products and the products themselves in one launch (chan = 128;
+ * archs/diffuser_atoms15.py:59-95): x_a [Nt][da], x_v [Nt][dv][3], x_d [Nt][dd][3][3] FP32; LR*p = ld_pack_weights_bf16 of
+ * the stacked (left | right) weight matrices [256][da|dv|dd]; outputs as ld_bee_self_products with out_bf16 = 1. Widths
+ * multiples of 16 with da + 3 dv + 9 dd <= 640. BF16 operands, FP32 accumulation and products. LD_FLAG_TIMEOUT in
+ * *status_dev if a wait runs out. */
+int ld_bee_self_front_bf16_tc(const float* x_a, const float* x_v, const float* x_d, long long Nt, int da, int dv, int dd, int chan,
+                              const void* LR0p, const void* LR1p, const void* LR2p, float* P_a, void* P_v, void* P_d,
+                              int* status_dev, void* stream);
 
 #ifdef __cplusplus
 }

@@ -61,6 +61,7 @@ SIGNATURES = {
     "ld_tensor_prod_bare": [I, I, I, I, P, P, LL, P, P],
     "ld_bee_messages_scalar_bf16_tc": [P, P, P, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P, P, P, F, P, I, P, P],
     "ld_bee_messages_vd_f32": [P, P, P, I, I, F, P, P, P, P, P, P, F, P, P, I, I, P],
+    "ld_bee_self_front_bf16_tc": [P, P, P, LL, I, I, I, I, P, P, P, P, P, P, P, P],
     "ld_bee_left_rows_bf16_tc": [P, P, P, LL, I, I, I, I, P, P, P, P, P, P],
     "ld_bee_messages_vd_bf16_tc": [P, P, P, I, I, F, P, P, P, P, F, P, P, P, P],
     "ld_bee_messages_scalar_f32": [P, P, P, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P, P, P, P, F, P, P],

@@ -327,6 +327,8 @@ class SelfTensProds(nn.Module):
         self.gn_d = TensGroupNorm(2, dim_d, groups)
         self.chan = chan
         self._cat, self._cat_key = None, None
+        # bf16, chan = 128: the six channel mixings in front of the products and the products as one launch
+        self.front_one_launch = True
 
     def _cat_weights(self):
         """left|right weights stacked per rank and the Y maps concatenated along their inputs (cached)"""
@@ -383,8 +385,21 @@ class SelfTensProds(nn.Module):
             # three channel mixings in (left|right stacked), one product kernel, three channel mixings out
             c = self._cat_weights()
             tc_out = all(n + "p" in c and c[n].shape[0] % 32 == 0 for n in ("Yv", "Yd"))  # BF16 products for tcgen05 Y maps
-            P_a, P_v, P_d = ops.bee_self_products(self._mix(c, "LR0", 0, xa), self._mix(c, "LR1", 1, xv), self._mix(c, "LR2", 2, xd),
-                                                  out_bf16=tc_out)
+            da, dv, dd = xa.shape[1], xv.shape[1], xd.shape[1]
+            if (tc_out and self.front_one_launch and "LR0p" in c and self.chan == 128 and da % 16 == 0 and dv % 16 == 0
+                    and dd % 16 == 0 and da + 3 * dv + 9 * dd <= 640 and all(t.dtype == torch.float32 for t in (xa, xv, xd))):
+                # the six channel mixings and the products in one launch: the mixed features never leave the SM
+                dev, C = xa.device, self.chan
+                P_a = torch.empty(n, 3 * C, dtype=torch.float32, device=dev)
+                P_v = torch.empty(n, 3, 5 * C, dtype=torch.bfloat16, device=dev)
+                P_d = torch.empty(n, 9, 5 * C, dtype=torch.bfloat16, device=dev)
+                with KERNEL_TIMER.region("bee_self_products"):
+                    check(lib().ld_bee_self_front_bf16_tc(ptr(xa.contiguous()), ptr(xv.contiguous()), ptr(xd.contiguous()), n, da, dv, dd,
+                                                          C, ptr(c["LR0p"]), ptr(c["LR1p"]), ptr(c["LR2p"]), ptr(P_a), ptr(P_v), ptr(P_d),
+                                                          ptr(ops.tc_status(dev)), stream_ptr(dev)))
+            else:
+                P_a, P_v, P_d = ops.bee_self_products(self._mix(c, "LR0", 0, xa), self._mix(c, "LR1", 1, xv), self._mix(c, "LR2", 2, xd),
+                                                      out_bf16=tc_out)
             y_a = self._mix(c, "Ya", 0, P_a)
             if tc_out:
                 y_v = ops.linear_bf16_tc_cm(P_v, c["Yvp"], c["Yv"].shape[0], 1)

@@ -239,6 +239,39 @@ def test_messages_single_edge_kernel_vs_oracle_and_two_kernel_path(B, N, r0, box
             assert a.abs().max() == 0
 
 
+@pytest.mark.parametrize("rows,dims", [((3, 50), (128, 64, 32, 128)), ((1, 64 * 150 + 9), (128, 64, 32, 128)), ((2, 5), (64, 16, 16, 128)),
+                                       ((1, 77), (16, 48, 32, 128))])
+def test_self_products_front_in_one_launch(rows, dims):
+    """the six channel mixings in front of the node-local products and the products as one launch (the mixed features stay
+    in tensor memory) against the separate launches (three stacked tensor-core linears + the product kernel): same BF16
+    operands, FP32 sums and FP32 products, so the module outputs agree to FP32 rounding; and against the float64
+    oracle at the BF16 bar; bit-identical reruns"""
+    from ld_b200 import bee, ops
+    from oracle import reference_math as R
+    torch.manual_seed(sum(dims) + rows[1])
+    mod = bee.set_precision(bee.SelfTensProds(*dims).cuda(), "bf16")
+    g = torch.Generator().manual_seed(5)
+    da, dv, dd, _ = dims
+    x_a, x_v, x_d = (torch.randn(*rows, da, generator=g), torch.randn(*rows, dv, 3, generator=g),
+                     torch.randn(*rows, dd, 3, 3, generator=g))
+    ref_mod = R.OSelfTensProds(*dims)
+    ref_mod.load_state_dict({k: v.cpu() for k, v in mod.state_dict().items()})
+    ref_mod.double()
+    with torch.no_grad():
+        want = ref_mod(x_a.double(), x_v.double(), x_d.double())
+        assert mod.front_one_launch
+        got = mod(x_a.cuda(), x_v.cuda(), x_d.cuda())
+        again = mod(x_a.cuda(), x_v.cuda(), x_d.cuda())
+        mod.front_one_launch = False
+        sep = mod(x_a.cuda(), x_v.cuda(), x_d.cuda())
+    torch.cuda.synchronize()
+    ops.check_tc_status("cuda")
+    for a, b, c, w in zip(got, again, sep, want):
+        assert torch.equal(a, b)
+        close(a, c, 1e-5)
+        close(a, w, BF16_BAR)
+
+
 @pytest.mark.parametrize("Nt,dims", [(1000, (128, 64, 32)), (128 * 150 + 5, (128, 64, 32)), (7, (64, 16, 16)), (300, (16, 48, 32))])
 def test_left_rows_in_one_launch_equal_three_launches(Nt, dims):
     """L0 | L1 | L2 of a message layer as one launch that writes whole [node][chan][16] BF16 rows against the three
