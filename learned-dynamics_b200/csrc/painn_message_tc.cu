@@ -194,7 +194,7 @@ painn_message_tc_kernel(TcMessageParams P) {
     }
   } else if (warp == MT_MMA_WARP) {
     // ===== MMA issue ========================================================================================
-    uint32_t mmas = 0;
+    uint32_t mmas = 0, accum_phase = 0;
     const uint32_t a_base = tc::smem_u32(a_smem);
     for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
     const long long ntiles = block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt), MT_EDGES).ntiles;
@@ -231,8 +231,14 @@ painn_message_tc_kernel(TcMessageParams P) {
             tc::mma_commit(&bar_empty[st]);
           }
           if (!fail) tc::mma_commit(&bar_accum);
+          // the issuing lane polls for the completion itself and passes it on through the block barrier below: a
+          // hardware barrier wakes the sixteen working warps faster than sixteen suspended mbarrier waits
+          if (!fail && !tc::mbar_wait_tight(&bar_accum, accum_phase & 1)) fail = 1;
+          tc::fence_before_sync();
         }
+        accum_phase++;
         fail = __shfl_sync(0xffffffffu, fail, 0);
+        if (sync_or(fail)) { fail = 1; break; }    // [A0..A2] accumulators of this layer complete
         if (sync_or(fail)) { fail = 1; break; }    // [B3..B5] accumulators consumed / next operand tile ready
       }
       if (fail) break;
@@ -247,7 +253,6 @@ painn_message_tc_kernel(TcMessageParams P) {
     auto lap = [&](int i) {
       if (PROF) { const long long t = clock64(); pc[i] += t - tprev; tprev = t; }
     };
-    uint32_t accum_phase = 0;
     const bool reducer = tid < MT_CG * 4;  // the staging tile has MT_CG * 4 columns, one per reducing thread
 
     auto flush_until = [&](int pass, int from, int next, float value) {
@@ -347,13 +352,7 @@ painn_message_tc_kernel(TcMessageParams P) {
 
       // ---- 3. three layers -------------------------------------------------------------------------------------
       for (int layer = 0; layer < 3; layer++) {
-        {  // one lane per warp polls, the others wait for it
-          int done = 1;
-          if (lane == 0) done = tc::mbar_wait(&bar_accum, accum_phase & 1) ? 1 : 0;
-          done = __shfl_sync(0xffffffffu, done, 0);
-          if (!done) fail = 1;
-        }
-        accum_phase++;
+        if (sync_or(fail)) { fail = 1; break; }                                          // [A0..A2] this layer's accumulators are complete
         tc::fence_after_sync();
         lap(2 + 2 * layer);
         if (!fail && layer < 2) {
