@@ -112,7 +112,8 @@ __device__ __forceinline__ int sync_or(int flag) {
 // barrier 2: working warps only
 __device__ __forceinline__ void sync_workers() { asm volatile("barrier.cta.sync 2, %0;" ::"n"(MT_WORK_THREADS) : "memory"); }
 
-template <bool PROF, bool G16>
+// NN: the width n as a compile-time constant (0: taken from the parameters)
+template <bool PROF, bool G16, int NN>
 __global__ void __launch_bounds__(MT_THREADS_TC, 1)
 painn_message_tc_kernel(TcMessageParams P) {
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -130,7 +131,7 @@ painn_message_tc_kernel(TcMessageParams P) {
   const bool prod_lane = warp == MT_PROD_WARP && lane == 0;
   const int quarter = warp & 3, part = (warp >> 2) & 3;
   const int row = quarter * 32 + lane;  // edge slot / TMEM lane owned in the epilogues
-  const int n = P.n, N = 4 * n;
+  const int n = NN > 0 ? NN : P.n, N = 4 * n;
   // dynamic shared memory: [ A operand tile, overlaid by the reduction staging | weight ring | biases ]
   unsigned char* a_smem = smem;                                   // 128 x N BF16
   unsigned char* b_smem = smem + P.stage_off;                     // nstages x slab
@@ -652,10 +653,11 @@ extern "C" int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, cons
   P.bias_off = (unsigned)(front + ring);
   const size_t smem = front + ring + (size_t)3 * N * 4 + 1024;
 #ifdef LD_PHASE_COUNTERS
-  auto kern = gather16 != nullptr ? (P.prof != nullptr ? painn_message_tc_kernel<true, true> : painn_message_tc_kernel<false, true>)
-                                  : (P.prof != nullptr ? painn_message_tc_kernel<true, false> : painn_message_tc_kernel<false, false>);
+  auto kern = gather16 != nullptr ? (P.prof != nullptr ? painn_message_tc_kernel<true, true, 0> : (n == 128 ? painn_message_tc_kernel<false, true, 128> : painn_message_tc_kernel<false, true, 0>))
+                                  : (P.prof != nullptr ? painn_message_tc_kernel<true, false, 0> : painn_message_tc_kernel<false, false, 0>);
 #else
-  auto kern = gather16 != nullptr ? painn_message_tc_kernel<false, true> : painn_message_tc_kernel<false, false>;
+  auto kern = gather16 != nullptr ? (n == 128 ? painn_message_tc_kernel<false, true, 128> : painn_message_tc_kernel<false, true, 0>)
+                                  : painn_message_tc_kernel<false, false, 0>;
 #endif
   LD_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int dev = 0, sms = 148;
