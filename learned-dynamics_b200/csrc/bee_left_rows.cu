@@ -7,18 +7,19 @@
 // than the arithmetic and the inputs together. Here a block owns 128 nodes: each thread reads its node's three
 // feature rows with 16-byte loads (they are contiguous per node: [K][3^l] floats), rounds them to BF16 and stores
 // them component by component as K-major operand tiles (eight channels of one component are one 16-byte piece: the
-// transposition happens in registers); thirteen small GEMMs follow, one per Cartesian component, issued TRANSPOSED
-// (weights as the M operand, the node tile as the N operand), so that a tensor-memory lane is an output channel and a
-// column a node: four components (512 columns) per pass, and after each pass thread c packs the four values of
-// (node, c) into 8 bytes of the row. The four passes of a block complete every 32-byte sector of its 512 KB of rows
-// within microseconds, so the sectors leave L2 whole.
+// transposition happens in registers); for every 32 nodes thirteen small GEMMs follow, one per Cartesian component,
+// issued TRANSPOSED (weights as the M operand, 32 nodes as the N operand), so that a tensor-memory lane is an output
+// channel and a column a node: 13 accumulators of 32 columns. Thread c then holds all thirteen values of (node, c),
+// packs them into the 32-byte row, and the warp's 32 rows of a node (1 KB of consecutive addresses) leave as two
+// fully coalesced stores after a transposition through a per-warp staging buffer: every sector is written once, whole.
 // Every wait is bounded; a wait that runs out sets LD_FLAG_TIMEOUT and the block leaves.
 #include "common.cuh"
 #include "tc05.cuh"
 
 namespace {
 
-constexpr int LR_NODES = 128;     // nodes per tile (N of the MMAs)
+constexpr int LR_NODES = 128;     // nodes per tile
+constexpr int LR_SUB = 32;        // nodes per group of GEMMs (N of the MMAs)
 constexpr int LR_C = 128;         // output channels (M of the MMAs)
 constexpr int LR_THREADS = 128;
 constexpr int LR_PANEL = LR_NODES * 16;   // bytes of one 8-wide K panel of a 128-row operand
@@ -65,6 +66,7 @@ bee_left_rows_kernel(const __grid_constant__ LeftRowsParams P) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t bar_w, bar_acc;
   __shared__ uint32_t tmem_slot;
+  __shared__ __align__(16) unsigned char s_stage[LR_THREADS / 32][1024];   // per warp: 32 rows of 32 bytes on their way out
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int da = P.da, dv = P.dv, dd = P.dd;
@@ -96,7 +98,7 @@ bee_left_rows_kernel(const __grid_constant__ LeftRowsParams P) {
     tc::bulk_g2s(w_d, P.w2, b2, &bar_w);
   }
   const long long ntiles = (P.Nt + LR_NODES - 1) / LR_NODES;
-  const uint32_t idesc = tc::idesc_bf16(LR_C, LR_NODES);
+  const uint32_t idesc = tc::idesc_bf16(LR_C, LR_SUB);
   uint32_t acc_phase = 0;
   bool ok = true, have_w = false;
 
@@ -116,22 +118,23 @@ bee_left_rows_kernel(const __grid_constant__ LeftRowsParams P) {
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
-    // ---- 2. four passes of four components: GEMMs into 4 x 128 tensor-memory columns, then 8 bytes per (node, channel)
-    for (int pass = 0; pass < 4 && ok; pass++) {
+    // ---- 2. per 32 nodes: thirteen GEMMs into 13 x 32 tensor-memory columns, then whole 32-byte rows ---------------
+    const int nvalid = (int)min((long long)LR_NODES, P.Nt - tile * LR_NODES);
+    for (int sub = 0; sub < LR_NODES / LR_SUB && ok; sub++) {
+      if (sub * LR_SUB >= nvalid) break;
       if (tid == 0) {
         if (!have_w) { have_w = tc::mbar_wait(&bar_w, 0, wl); }
         if (have_w) {
           tc::fence_after_sync();
-          const int ncomp = pass == 3 ? 1 : 4;
-          for (int j = 0; j < ncomp; j++) {
-            const int m = pass * 4 + j;                       // slot of the row: 0 = l0, 1..3 = l1, 4..12 = l2
+#pragma unroll 1
+          for (int m = 0; m < 13; m++) {                      // slot of the row: 0 = l0, 1..3 = l1, 4..12 = l2
             const unsigned char* a_tile = m == 0 ? t_a : (m < 4 ? t_v + (size_t)(m - 1) * v_bytes : t_d + (size_t)(m - 4) * d_bytes);
             const unsigned char* w_tile = m == 0 ? w_a : (m < 4 ? w_v : w_d);
             const int K = m == 0 ? da : (m < 4 ? dv : dd);
             uint64_t wd = tc::smem_desc(tc::smem_u32(w_tile), LR_C * 16, 128);
-            uint64_t xd = tc::smem_desc(tc::smem_u32(a_tile), LR_PANEL, 128);
+            uint64_t xd = tc::smem_desc(tc::smem_u32(a_tile) + sub * LR_SUB * 16, LR_PANEL, 128);
             for (int ks = 0; ks < K / 16; ks++) {
-              tc::mma_bf16(tmem_base + j * LR_NODES, wd, xd, idesc, ks > 0 ? 1u : 0u);
+              tc::mma_bf16(tmem_base + m * LR_SUB, wd, xd, idesc, ks > 0 ? 1u : 0u);
               wd += (uint64_t)((2 * LR_C * 16) >> 4);         // the address field of a descriptor counts 16-byte units
               xd += (uint64_t)((2 * LR_PANEL) >> 4);
             }
@@ -144,35 +147,41 @@ bee_left_rows_kernel(const __grid_constant__ LeftRowsParams P) {
       ok = __syncthreads_and(ok);
       if (!ok) break;
       tc::fence_after_sync();
-      // thread = channel (its tensor-memory lane); columns = the tile's nodes
+      // thread = channel (its tensor-memory lane); columns = nodes. Eight nodes at a time: the thirteen values of
+      // (node, channel) become one 32-byte row; a warp's 32 rows of a node are 1 KB of consecutive addresses, written
+      // as two fully coalesced 512-byte stores after a transposition through the warp's staging buffer.
       const uint32_t t_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
-      __nv_bfloat16* out = P.rows + ((size_t)tile * LR_NODES * LR_C + tid) * 16 + pass * 4;
-      const int nvalid = (int)min((long long)LR_NODES, P.Nt - tile * LR_NODES);
+      const int lane = tid & 31;
+      unsigned char* stage = s_stage[warp];
 #pragma unroll 1
-      for (int nb = 0; nb < LR_NODES; nb += 16) {
-        if (nb >= nvalid) break;
-        float v[4][16];
-        tc::tmem_ld16(t_lane + nb, v[0]);
-        if (pass < 3) {
-          tc::tmem_ld16(t_lane + LR_NODES + nb, v[1]);
-          tc::tmem_ld16(t_lane + 2 * LR_NODES + nb, v[2]);
-          tc::tmem_ld16(t_lane + 3 * LR_NODES + nb, v[3]);
-        } else {
+      for (int q = 0; q < LR_SUB / 8; q++) {
+        const int n0 = sub * LR_SUB + q * 8;
+        if (n0 >= nvalid) break;
+        float v[13][8];
 #pragma unroll
-          for (int i = 0; i < 16; i++) v[1][i] = v[2][i] = v[3][i] = 0.f;   // the three unused values of a row
-        }
+        for (int m = 0; m < 13; m++) tc::tmem_ld8_issue(t_lane + m * LR_SUB + q * 8, v[m]);
+        tc::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; i++) {
-          if (nb + i < nvalid) {
-            uint2 q;
-            q.x = tc::pack_bf16x2(v[0][i], v[1][i]);
-            q.y = tc::pack_bf16x2(v[2][i], v[3][i]);
-            *reinterpret_cast<uint2*>(out + (size_t)(nb + i) * LR_C * 16) = q;
-          }
+        for (int i = 0; i < 8; i++) {
+          if (n0 + i >= nvalid) break;
+          uint4 lo, hi;
+          lo.x = tc::pack_bf16x2(v[0][i], v[1][i]);   lo.y = tc::pack_bf16x2(v[2][i], v[3][i]);
+          lo.z = tc::pack_bf16x2(v[4][i], v[5][i]);   lo.w = tc::pack_bf16x2(v[6][i], v[7][i]);
+          hi.x = tc::pack_bf16x2(v[8][i], v[9][i]);   hi.y = tc::pack_bf16x2(v[10][i], v[11][i]);
+          hi.z = tc::pack_bf16x2(v[12][i], 0.f);      hi.w = 0u;                       // the three unused values of a row
+          *reinterpret_cast<uint4*>(stage + lane * 32) = lo;
+          *reinterpret_cast<uint4*>(stage + lane * 32 + 16) = hi;
+          __syncwarp();
+          const uint4 p0 = *reinterpret_cast<const uint4*>(stage + lane * 16);
+          const uint4 p1 = *reinterpret_cast<const uint4*>(stage + 512 + lane * 16);
+          unsigned char* out = reinterpret_cast<unsigned char*>(P.rows) + ((size_t)(tile * LR_NODES + n0 + i) * LR_C + warp * 32) * 32;
+          *reinterpret_cast<uint4*>(out + lane * 16) = p0;
+          *reinterpret_cast<uint4*>(out + 512 + lane * 16) = p1;
+          __syncwarp();
         }
       }
       tc::fence_before_sync();
-      __syncthreads();   // the accumulators are free for the next pass, and (after the last pass) the tiles for the next nodes
+      __syncthreads();   // the accumulators are free for the next 32 nodes (after the last: the tiles for the next nodes)
     }
   }
   if (!ok && tid == 0 && P.status != nullptr) atomicOr(P.status, LD_FLAG_TIMEOUT);

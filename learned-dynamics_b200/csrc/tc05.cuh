@@ -266,6 +266,14 @@ __device__ __forceinline__ void tmem_ld4(uint32_t a0, float* v) {
 #pragma unroll
   for (int i = 0; i < 4; i++) v[i] = __uint_as_float(r[i]);
 }
+// eight consecutive columns, request only (tmem_ld_wait before the values are used)
+__device__ __forceinline__ void tmem_ld8_issue(uint32_t a0, float* v) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
+               : "r"(a0)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // one column
 __device__ __forceinline__ float tmem_ld1(uint32_t a0) {
   uint32_t r;
