@@ -8,7 +8,7 @@
 // (loaded once by a bulk copy) and streams 128-row tiles through a ring of 128-wide K chunks:
 //   warps 4..7   one thread per row issues sixteen 16-byte cp.async copies per chunk straight into the K-major operand
 //                layout (a row's eight K values are exactly one 16-byte piece of it) and lets the chunk's mbarrier
-//                count their completion: four chunks (128 KB per SM) are in flight without a register holding data;
+//                count their completion: three or four chunks (96 or 128 KB per SM) are in flight without a register holding data;
 //   warp 8       one thread waits for a chunk, issues its eight MMAs (128 x N x 16) and commits the chunk back to the
 //                loaders; the accumulators of two tiles alternate in tensor memory;
 //   warps 0..3   read a finished tile's accumulators (a thread = a row = a tensor-memory lane), add the bias, apply the
@@ -36,6 +36,7 @@ struct RowsParams {
   const float* bias;
   long long rows;            // GEMM rows = rows_outer * S
   int K, N, S, act;
+  int stages;                // chunks of the ring in use (<= GR_STAGES)
   int* status;
   uint32_t wait_limit;
 };
@@ -46,9 +47,11 @@ __device__ __forceinline__ float gr_act(float v, int act) {
   return v;
 }
 
-// 16 bytes global -> shared without a register in between; src_bytes = 0 writes zeros
+// 16 bytes global -> shared without a register in between; src_bytes = 0 writes zeros. A thread's consecutive copies
+// take the two halves of every 32-byte sector: through L1 (.ca) the second half is a hit, which halves the L2 -> SM
+// traffic, as long as the block's shared memory leaves L1 room for the lines in flight (the launch sizes the ring for it).
 __device__ __forceinline__ void gr_cp_async16(void* dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(tc::smem_u32(dst)), "l"(src), "r"(src_bytes) : "memory");
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(tc::smem_u32(dst)), "l"(src), "r"(src_bytes) : "memory");
 }
 // the mbarrier receives one arrival from this thread once all its cp.async copies issued so far have landed
 __device__ __forceinline__ void gr_cp_async_arrive(uint64_t* bar) {
@@ -68,7 +71,7 @@ gemm_rows16_kernel(const __grid_constant__ RowsParams P) {
   const uint32_t w_bytes = (uint32_t)K * N * 2;
   unsigned char* w_smem = smem;
   unsigned char* ring = smem + ((w_bytes + 1023u) & ~1023u);
-  const uint32_t wl = P.wait_limit;
+  const uint32_t wl = P.wait_limit, nst = (uint32_t)P.stages;
   uint32_t acc_cols = 32;
   while (acc_cols < (uint32_t)N) acc_cols <<= 1;
   const uint32_t ncols = 2 * acc_cols;
@@ -112,7 +115,7 @@ gemm_rows16_kernel(const __grid_constant__ RowsParams P) {
         if (s_fail || !tc::mbar_wait(&bar_acc_empty[b], (tile_it >> 1) & 1, wl)) { fail = 1; break; }
         tc::fence_after_sync();
         for (int c = 0; c < nchunks; c++, g++) {
-          const uint32_t st = g % GR_STAGES, use = g / GR_STAGES;
+          const uint32_t st = g % nst, use = g / nst;
           if (!tc::mbar_wait(&bar_full[st], use & 1, wl)) { fail = 1; break; }
           tc::fence_async_smem();      // the copies went through the generic proxy, the tensor cores read through the async one
           tc::fence_after_sync();
@@ -145,7 +148,7 @@ gemm_rows16_kernel(const __grid_constant__ RowsParams P) {
       const __nv_bfloat16* xrow = P.x + (row_ok ? row : 0) * K;
       const uint32_t nbytes = row_ok ? 16u : 0u;
       for (int c = 0; c < nchunks; c++, g++) {
-        const uint32_t st = g % GR_STAGES, use = g / GR_STAGES;
+        const uint32_t st = g % nst, use = g / nst;
         // the MMAs that read this stage's previous content are done (every thread polls: no warp-wide handshake)
         if (s_fail || !tc::mbar_wait(&bar_empty[st], use & 1, wl)) { fail = 1; break; }
         unsigned char* dst = ring + (size_t)st * GR_STAGE_BYTES + r * 16;
@@ -209,7 +212,9 @@ int ld_gemm_rows16_launch(const void* x16, long long rows, int K, int S, const v
   P.x = (const __nv_bfloat16*)x16; P.y = y; P.wp = (const __nv_bfloat16*)wp; P.bias = bias; P.rows = rows; P.K = K; P.N = N; P.S = S;
   P.act = act; P.status = status_dev; P.wait_limit = wait_limit;
   const size_t w_bytes = (size_t)K * N * 2;
-  const size_t smem = ((w_bytes + 1023) & ~(size_t)1023) + (size_t)GR_STAGES * GR_STAGE_BYTES + 1024;
+  const size_t smem = ((w_bytes + 1023) & ~(size_t)1023) + (size_t)(w_bytes <= 48 * 1024 ? GR_STAGES : GR_STAGES - 1) * GR_STAGE_BYTES + 1024;
+  // L1 needs room for the lines in flight: with large weights the ring gives up a chunk for it
+  P.stages = w_bytes <= 48 * 1024 ? GR_STAGES : GR_STAGES - 1;
   LD_CUDA_TRY(cudaFuncSetAttribute(gemm_rows16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
