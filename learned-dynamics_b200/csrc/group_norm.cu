@@ -6,6 +6,7 @@
 // x: [B][N][C][S] float32 (S = 3^inds; S = 1 for scalars). Blocks per (system, group, chunk of nodes) compute partial
 // statistics (two passes over the chunk for the squared deviations), a small kernel joins them, a third applies them.
 #include <cuda_runtime.h>
+#include <cstdint>
 #include "common.cuh"
 
 namespace {
@@ -96,6 +97,92 @@ __global__ void __launch_bounds__(256) gn_apply_kernel(const float* __restrict__
   }
 }
 
+// ---- row-wise variants: a block owns (system, chunk of nodes) and all channel groups ------------------------------
+// A node's features are one contiguous row of L = C * S floats. The block has k * L/4 threads: thread t always reads
+// the same four consecutive floats (column t % (L/4)) of every k-th node, so its channel group, gamma and beta are
+// fixed, loads are 16 bytes and coalesced over whole rows, and no index arithmetic is left in the loops. Four
+// consecutive floats never straddle a group (cpg * S and cpg are multiples of 4 on this path). The partial sums of the
+// threads of a group are added by one thread in thread order: deterministic, and dependent on N alone.
+constexpr int GN_ROW_MAX_THREADS = 256;
+
+// group of the four floats at row position e
+__device__ __forceinline__ int gn_group_of(int e, int C, int S, int cpg, int cm) { return cm ? (e % C) / cpg : e / (cpg * S); }
+
+__global__ void __launch_bounds__(GN_ROW_MAX_THREADS)
+gn_partial_rows_kernel(const float* __restrict__ x, int N, int C, int S, int G, int center, int nchunks, int cm, int k,
+                       float* __restrict__ part) {
+  __shared__ float s_part[GN_ROW_MAX_THREADS];
+  __shared__ int s_gid[GN_ROW_MAX_THREADS];
+  __shared__ float s_mean[64];
+  const int L = C * S, L4 = L / 4, cpg = C / G;
+  const int b = blockIdx.x, kc = blockIdx.y, tid = threadIdx.x;
+  const int col = tid % L4, off = tid / L4;
+  const int per = (N + nchunks - 1) / nchunks;
+  const int n0 = kc * per, n1 = min(N, n0 + per);
+  const int g = gn_group_of(col * 4, C, S, cpg, cm);
+  s_gid[tid] = g;
+  const float4* base = reinterpret_cast<const float4*>(x + ((size_t)b * N) * L) + col;
+  const float total = (float)((long long)max(n1 - n0, 0) * cpg * S);
+  // the threads of group `grp` in thread order
+  auto group_sum = [&](int grp) {
+    float t = 0.f;
+    for (int i = 0; i < (int)blockDim.x; i++) if (s_gid[i] == grp) t += s_part[i];
+    return t;
+  };
+  float mean = 0.f;
+  if (center) {
+    float sm = 0.f;
+    for (int n = n0 + off; n < n1; n += k) { const float4 v = __ldg(base + (size_t)n * L4); sm += (v.x + v.y) + (v.z + v.w); }
+    s_part[tid] = sm;
+    __syncthreads();
+    if (tid < G) s_mean[tid] = total > 0.f ? group_sum(tid) / total : 0.f;
+    __syncthreads();
+    mean = s_mean[g];
+  }
+  float q = 0.f;
+  for (int n = n0 + off; n < n1; n += k) {
+    const float4 v = __ldg(base + (size_t)n * L4);
+    const float d0 = v.x - mean, d1 = v.y - mean, d2 = v.z - mean, d3 = v.w - mean;
+    q = fmaf(d0, d0, q); q = fmaf(d1, d1, q); q = fmaf(d2, d2, q); q = fmaf(d3, d3, q);
+  }
+  __syncthreads();
+  s_part[tid] = q;
+  __syncthreads();
+  if (tid < G) {
+    float* o = part + (((size_t)b * G + tid) * nchunks + kc) * 3;
+    o[0] = total; o[1] = center ? s_mean[tid] : 0.f; o[2] = group_sum(tid);
+  }
+}
+
+__global__ void __launch_bounds__(GN_ROW_MAX_THREADS)
+gn_apply_rows_kernel(const float* __restrict__ x, int N, int C, int S, int G, int nchunks, int cm, int k, const float* __restrict__ stats,
+                     const float* __restrict__ gamma, const float* __restrict__ beta, float* __restrict__ y) {
+  const int L = C * S, L4 = L / 4, cpg = C / G;
+  const int b = blockIdx.x, kc = blockIdx.y, tid = threadIdx.x;
+  const int col = tid % L4, off = tid / L4;
+  const int per = (N + nchunks - 1) / nchunks;
+  const int n0 = kc * per, n1 = min(N, n0 + per);
+  const int e = col * 4;
+  const float* st = stats + ((size_t)b * G + gn_group_of(e, C, S, cpg, cm)) * 2;
+  const float mean = st[0], rstd = st[1];
+  float ga[4], be[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const int c = cm ? (e + j) % C : (e + j) / S;
+    ga[j] = gamma[c] * rstd;
+    be[j] = beta != nullptr ? beta[c] : 0.f;
+  }
+  const float4* xin = reinterpret_cast<const float4*>(x + ((size_t)b * N) * L) + col;
+  float4* yout = reinterpret_cast<float4*>(y + ((size_t)b * N) * L) + col;
+  for (int n = n0 + off; n < n1; n += k) {
+    const float4 v = __ldg(xin + (size_t)n * L4);
+    float4 r;
+    r.x = fmaf(v.x - mean, ga[0], be[0]); r.y = fmaf(v.y - mean, ga[1], be[1]);
+    r.z = fmaf(v.z - mean, ga[2], be[2]); r.w = fmaf(v.w - mean, ga[3], be[3]);
+    yout[(size_t)n * L4] = r;
+  }
+}
+
 }  // namespace
 
 // x, y: [B][N][C][S]; gamma [C]; beta [C] or NULL; center != 0 subtracts the group mean (ScalGroupNorm, S = 1).
@@ -117,14 +204,24 @@ static int group_norm_launch(const float* x, int B, int N, int C, int S, int gro
   if (nchunks > 32) nchunks = 32;
   if (nchunks > N) nchunks = N;
   if (nchunks < 1) nchunks = 1;
-  gn_partial_kernel<<<dim3(B * groups, nchunks), GN_THREADS, 0, st>>>(x, N, C, S, groups, center, nchunks, cm, part);
+  // rows of whole 16-byte pieces that never straddle a channel group, short enough for one block: the row-wise kernels
+  const int L = C * S, cpg = C / groups;
+  const bool rows = L % 4 == 0 && cpg % 4 == 0 && L / 4 <= GN_ROW_MAX_THREADS && groups <= 64 && B <= 65535 &&
+                    ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0);
+  const int k = rows ? (GN_ROW_MAX_THREADS / (L / 4) > 0 ? GN_ROW_MAX_THREADS / (L / 4) : 1) : 0;
+  if (rows) gn_partial_rows_kernel<<<dim3(B, nchunks), k * (L / 4), 0, st>>>(x, N, C, S, groups, center, nchunks, cm, k, part);
+  else gn_partial_kernel<<<dim3(B * groups, nchunks), GN_THREADS, 0, st>>>(x, N, C, S, groups, center, nchunks, cm, part);
   LD_LAUNCH_CHECK();
   gn_finalize_kernel<<<(B * groups + 127) / 128, 128, 0, st>>>(part, B * groups, nchunks, center, (long long)N * (C / groups), eps, stats);
   LD_LAUNCH_CHECK();
-  const long long total = (long long)B * N * C * S;
-  long long blocks = (total + 255) / 256;
-  if (blocks > 148LL * 32) blocks = 148LL * 32;
-  gn_apply_kernel<<<(unsigned)blocks, 256, 0, st>>>(x, total, N, C, S, groups, cm, stats, gamma, beta, y);
+  if (rows) {
+    gn_apply_rows_kernel<<<dim3(B, nchunks), k * (L / 4), 0, st>>>(x, N, C, S, groups, nchunks, cm, k, stats, gamma, beta, y);
+  } else {
+    const long long total = (long long)B * N * C * S;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148LL * 32) blocks = 148LL * 32;
+    gn_apply_kernel<<<(unsigned)blocks, 256, 0, st>>>(x, total, N, C, S, groups, cm, stats, gamma, beta, y);
+  }
   LD_LAUNCH_CHECK();
   return LD_OK;
 }
