@@ -131,26 +131,34 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
       for (int eb = e_lo; eb < e_hi; eb += BV_TILE) {
         const int cnt = min(BV_TILE, e_hi - eb);
         __syncthreads();  // previous tile's readers are done
+        constexpr int UNR = 4;  // neighbour rows in flight per thread
+        // the edge list of the step is padded to whole batches with edges of weight zero (they read the row of the
+        // step's first neighbour), so that the batches below need neither bounds checks nor clamped indices
+        const int cnt_pad = (cnt + UNR - 1) & ~(UNR - 1);
         if (threadIdx.x < cnt) {
           edge_geometry(P.rij, (long long)eb + threadIdx.x, P.r0, s_jac, &s_geom[threadIdx.x]);
+          s_geom[threadIdx.x].pad = 1.f;
           s_dst[threadIdx.x] = P.dst[eb + threadIdx.x];
+        } else if (threadIdx.x < cnt_pad) {
+          EdgeGeom z;
+#pragma unroll
+          for (int m = 0; m < 8; m++) z.enc[m] = 0.f;
+          z.rhat[0] = z.rhat[1] = z.rhat[2] = 0.f; z.pad = 0.f;
+          s_geom[threadIdx.x] = z;
+          s_dst[threadIdx.x] = P.dst[eb];
         }
         __syncthreads();
         if (cok) {
-          constexpr int UNR = 4;  // neighbour rows in flight per thread
-          for (int tb = 0; tb < cnt; tb += UNR) {
+          for (int tb = 0; tb < cnt_pad; tb += UNR) {
             uint32_t raw[UNR][8];
             if (PACKED) {
 #pragma unroll
-              for (int u = 0; u < UNR; u++) {
-                const int t = min(tb + u, cnt - 1);
-                tc::ldg_raw8(reinterpret_cast<const __nv_bfloat16*>(P.L0) + ((size_t)s_dst[t] * C + c) * 16, raw[u]);
-              }
+              for (int u = 0; u < UNR; u++)
+                tc::ldg_raw8(reinterpret_cast<const __nv_bfloat16*>(P.L0) + ((size_t)s_dst[tb + u] * C + c) * 16, raw[u]);
             }
 #pragma unroll
             for (int u = 0; u < UNR; u++) {
               const int t = tb + u;
-              if (t >= cnt) break;
               const size_t j = (size_t)s_dst[t] * C + c;
               float l1[3], l2[9], pa;
               float l0;
@@ -175,6 +183,7 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
               pa = wb;
               pa = fmaf(e0.x, w8[0], pa); pa = fmaf(e0.y, w8[1], pa); pa = fmaf(e0.z, w8[2], pa); pa = fmaf(e0.w, w8[3], pa);
               pa = fmaf(e1.x, w8[4], pa); pa = fmaf(e1.y, w8[5], pa); pa = fmaf(e1.z, w8[6], pa); pa = fmaf(e1.w, w8[7], pa);
+              pa *= rr.w;   // 1 for an edge, 0 for the padding of the last batch: every product below carries pa as a factor
               const float rh[3] = {rr.x, rr.y, rr.z};
               // with rp = pa * rhat no separately scaled copy of l is needed: most products are single FMAs of an
               // element of l with rhat, rp or pa straight into the running sums
