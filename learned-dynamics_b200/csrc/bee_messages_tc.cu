@@ -118,6 +118,7 @@ __device__ __forceinline__ void bt_geometry(float x, float y, float z, float r0,
   const float ux = x * s, uy = y * s, uz = z * s;
   const float inv = rsqrtf(1.f + ux * ux + uy * uy + uz * uz);
   g->rhat[0] = ux * inv; g->rhat[1] = uy * inv; g->rhat[2] = uz * inv;
+  g->pad = 1.f;   // weight of the edge; the unused slots of a ragged last tile carry 0
 }
 
 __device__ __forceinline__ unsigned short bt_bf16(float v) {
@@ -321,6 +322,10 @@ bee_scalar_tc_kernel(BtParams P) {
           } else {
             s = bt_lb_row(P.row_ptr, nlo + BT_EDGES, n_end, e + 1) - 1;
           }
+        } else {
+          // a slot past the end of the block's edges: weight 0 and neighbour 0, so that the product phase needs no bounds check
+          float4* gp = reinterpret_cast<float4*>(&s_geom[b][gt]);
+          gp[0] = gp[1] = gp[2] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
         s_dst[b][gt] = j;
         s_src[b][gt] = s;
@@ -397,7 +402,6 @@ bee_scalar_tc_kernel(BtParams P) {
         if (pb_lo < pb_hi) {
           const __nv_bfloat16* Lp = reinterpret_cast<const __nv_bfloat16*>(P.L0);
           const int* tdst = s_dst[gb];
-          const int last = max(cnt - 1, 0);
 #pragma unroll 1
           for (int pb = pb_lo; pb < pb_hi; pb++) {
             // the batch's rows are requested together and waited for together: the loads of a warp share a scoreboard,
@@ -406,14 +410,15 @@ bee_scalar_tc_kernel(BtParams P) {
             if (feat == 2) {
 #pragma unroll
               for (int u = 0; u < UNR; u++) {
-                const int t = min(pb_base + pb * pb_step + u * pu_step, last);   // clamped: the load is unconditional
+                const int tu = pb_base + pb * pb_step + u * pu_step;       // slots past the edges name neighbour 0
+                const int t = FAST ? tu : min(tu, BT_EDGES - 1);
                 tc::ldg_raw8(Lp + ((size_t)tdst[t] * C + pc_c) * 16, raw[u]);
               }
             }
 #pragma unroll
             for (int u = 0; u < UNR; u++) {
               const int t = pb_base + pb * pb_step + u * pu_step;
-              if (t >= BT_EDGES) break;
+              if (!FAST && t >= BT_EDGES) break;
               float l0 = 0.f, l1[3] = {0.f, 0.f, 0.f}, l2[9] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
               if (feat == 2) {
                 l0 = tc::bf16_at(raw[u], 0);
@@ -423,12 +428,13 @@ bee_scalar_tc_kernel(BtParams P) {
                 for (int k = 0; k < 9; k++) l2[k] = tc::bf16_at(raw[u], 4 + k);
               }
               float y0 = 0.f, y1 = 0.f, y2 = 0.f;
-              if (t < cnt) {
+              {
                 const float4* gp = reinterpret_cast<const float4*>(&s_geom[gb][t]);
                 const float4 e0 = gp[0], e1 = gp[1], rr = gp[2];
                 float pa = wb;
                 pa = fmaf(e0.x, w8[0], pa); pa = fmaf(e0.y, w8[1], pa); pa = fmaf(e0.z, w8[2], pa); pa = fmaf(e0.w, w8[3], pa);
                 pa = fmaf(e1.x, w8[4], pa); pa = fmaf(e1.y, w8[5], pa); pa = fmaf(e1.z, w8[6], pa); pa = fmaf(e1.w, w8[7], pa);
+                pa *= rr.w;   // 1 for an edge, 0 for a slot past the block's edges: the three products carry pa as a factor
                 const float rh[3] = {rr.x, rr.y, rr.z};
                 if (feat != 2) {
                   const size_t j = (size_t)tdst[t] * C + pc_c;
