@@ -822,7 +822,7 @@ extern "C" int ld_bee_messages_fused_bf16_tc_opt(const int* row_ptr, const int* 
   Q.b1 = b1; Q.b2 = b2; Q.b3 = b3;
   {
     const long long seg = (40LL << 20) / BF_ROW_BYTES;   // about 40 MB of gathered rows per segment: they stay in L2
-    Q.seg_nodes = (int)(seg < 1024 ? 1024 : seg);
+    Q.seg_nodes = ld_even_segments(Nt, seg);
   }
   Q.out_a = out_a; Q.S_v = (__nv_bfloat16*)S_v; Q.S_d = (__nv_bfloat16*)S_d; Q.status = status_dev;
   Q.wait_limit = tc::TC_WAIT_LIMIT;

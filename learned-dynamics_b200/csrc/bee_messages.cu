@@ -386,7 +386,7 @@ extern "C" int ld_bee_messages_vd_f32(const int* row_ptr, const int* dst, const 
   if (Nt == 0) return LD_OK;
   // segment = about 40 MB of gathered rows (13 * chan values per node, 32 bytes per channel when interleaved)
   const long long seg = (40LL << 20) / ((feat_bf16 == 2 ? 32LL : feat_bf16 ? 26LL : 52LL) * chan);
-  BeeEdgeParams P{row_ptr, dst, rij, Nt, chan, r0, L0, L1, L2, enc_w, enc_b, jacobi, (int)(seg < 1024 ? 1024 : seg)};
+  BeeEdgeParams P{row_ptr, dst, rij, Nt, chan, r0, L0, L1, L2, enc_w, enc_b, jacobi, ld_even_segments(Nt, seg)};
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (feat_bf16 == 2 && chan == 128 && out_bf16) bee_vd_kernel<__nv_bfloat16, true, 128><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale, 1);

@@ -653,7 +653,7 @@ extern "C" int ld_bee_messages_scalar_bf16_tc(const int* row_ptr, const int* dst
   if (smem > 215 * 1024) { ld_set_last_message("bee messages (tensor-core path): shared-memory plan exceeds the limit"); return LD_ERR_UNSUPPORTED; }
   {
     const long long seg = (40LL << 20) / ((feat_bf16 == 2 ? 32LL : feat_bf16 ? 26LL : 52LL) * C);  // 13*chan values gathered per neighbour
-    P.seg_nodes = (int)(seg < 1024 ? 1024 : seg);
+    P.seg_nodes = ld_even_segments(Nt, seg);
   }
   P.out_a = out_a; P.status = status_dev; P.feat_bf16 = feat_bf16;
 #ifdef LD_PHASE_COUNTERS

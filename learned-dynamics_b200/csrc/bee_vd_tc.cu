@@ -554,7 +554,7 @@ extern "C" int ld_bee_messages_vd_bf16_tc(const int* row_ptr, const int* dst, co
   Q.rows = (const __nv_bfloat16*)rows; Q.enc_w = enc_w; Q.enc_b = enc_b; Q.jacobi = jacobi;
   {
     const long long seg = (40LL << 20) / (VT_C * 32);   // about 40 MB of gathered rows per segment: they stay in L2
-    Q.seg_nodes = (int)(seg < 1024 ? 1024 : seg);
+    Q.seg_nodes = ld_even_segments(Nt, seg);
   }
   Q.S_v = (__nv_bfloat16*)S_v; Q.S_d = (__nv_bfloat16*)S_d; Q.status = status_dev;
   Q.wait_limit = tc::TC_WAIT_LIMIT;

@@ -34,6 +34,14 @@ void ld_set_last_message(const char* msg);
 
 static inline size_t ld_align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 static inline int ld_cdiv(long long a, long long b) { return (int)((a + b - 1) / b); }
+// Nodes per segment when the edge kernels walk the node range in segments of about `want` nodes (so that the rows a
+// segment gathers stay in L2): the segments are made equal, since a short last segment gives every block a sliver of work
+static inline int ld_even_segments(long long Nt, long long want) {
+  if (want < 1024) want = 1024;
+  if (Nt <= want) return (int)(Nt > 0 ? Nt : 1);
+  const long long nseg = (Nt + want - 1) / want;
+  return (int)((Nt + nseg - 1) / nseg);
+}
 
 // exclusive prefix sum of n int32 values; out[n] receives the total (out has n+1 entries).
 // scratch must hold ld_scan_scratch_ints(n) ints.

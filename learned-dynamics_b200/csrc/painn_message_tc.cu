@@ -647,7 +647,7 @@ extern "C" int ld_painn_message_bf16_tc(const int* row_ptr, const int* dst, cons
   // (28n bytes per node) stay resident in L2 while its edges are processed
   {
     const long long seg = (40LL << 20) / (28LL * n);
-    P.seg_nodes = (int)(seg < 1024 ? 1024 : seg);
+    P.seg_nodes = ld_even_segments(Nt, seg);
   }
   P.stage_off = (unsigned)front;
   P.bias_off = (unsigned)(front + ring);
