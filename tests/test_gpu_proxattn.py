@@ -106,3 +106,36 @@ def test_tf32_tensor_core_forward(dim, Z, N, heads, periodic):
     ref_grads = torch.autograd.grad((R.proxattn(*ref_in, r0sq, box) * cot).sum(), ref_in)
     for mine, ref in zip(grads, ref_grads):
         close(mine, ref, rel=5e-5)
+
+
+def test_attention_modules_against_reference_golden():
+    """ProbePoints2, ProximityFlashAttention and ProximityFlashAttentionPeriodic with the reference's state dicts
+    against outputs of the reference's own classes (golden: its torch definition of the operator underneath), FP32
+    kernels at 2e-5; the TF32 tensor-core forward at 3e-3; gradients flow to inputs and weights"""
+    import os
+    from ld_b200 import attention_layers as AL
+    gold = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_golden_attention.pt"))
+    adim, vdim, chan = gold["dims"]
+    ax, vx, pos, pos2 = (gold[k].cuda() for k in ("ax", "vx", "pos", "pos2"))
+    probe = AL.ProbePoints2(2, len(gold["r0_list"]), adim, vdim).cuda()
+    probe.load_state_dict(gold["probe_state"])
+    att = AL.ProximityFlashAttention(gold["r0_list"], adim, vdim, chan).cuda()
+    att.load_state_dict(gold["att_state"])
+    attp = AL.ProximityFlashAttentionPeriodic(gold["r0_list"], adim, vdim, chan).cuda()
+    attp.load_state_dict(gold["attp_state"])
+    with torch.no_grad():
+        pts = probe(ax, vx, [pos, pos2])
+        close(pts, gold["probe_out"], 2e-6)
+        for got, want in zip(att(ax, vx, pts, pts + 0.1), gold["att_out"]):
+            close(got, want, 2e-5)
+        for got, want in zip(attp(ax, vx, pts, pts + 0.1, gold["box"]), gold["attp_out"]):
+            close(got, want, 2e-5)
+        att.precision = "tf32"
+        for got, want in zip(att(ax, vx, pts, pts + 0.1), gold["att_out"]):
+            close(got, want, 3e-3)
+        att.precision = "fp32"
+    axg = ax.clone().requires_grad_(True)
+    ay, vy = att(axg, vx, pts, pts + 0.1)
+    (ay.square().sum() + vy.square().sum()).backward()
+    assert axg.grad is not None and torch.isfinite(axg.grad).all() and axg.grad.abs().max() > 0
+    assert att.W_aq.grad is not None and torch.isfinite(att.W_aq.grad).all()
