@@ -153,6 +153,10 @@ int ld_linear_bf16_tc(const float* x, long long rows_outer, int K, int S, const 
  * any case, so the result equals that of the same values passed as FP32 */
 int ld_linear_bf16_tc_in16(const void* x_bf16, long long rows_outer, int K, int S, const void* wp, const float* bias, int N,
                            int act, float* y, int* status_dev, void* stream);
+/* The same with a residual, y = residual + act(x W^T + b), residual laid out like y. Only for the shapes of the streaming
+ * kernel (K a multiple of 128, N <= 128, packed weights up to 94 KB); LD_ERR_UNSUPPORTED otherwise. */
+int ld_linear_bf16_tc_in16_res(const void* x_bf16, const float* residual, long long rows_outer, int K, int S, const void* wp,
+                               const float* bias, int N, int act, float* y, int* status_dev, void* stream);
 /* same with a BF16 result written to y_bf16[r*ld_row + o*ld_col + s + off] (plain layout: ld_row = N*S,
  * ld_col = S, off = 0); used to interleave the left operands of the l<=2 message layer per channel */
 int ld_linear_bf16_tc_out16(const float* x, long long rows_outer, int K, int S, const void* wp, const float* bias, int N,
@@ -321,6 +325,9 @@ int ld_bee_gamma_table(int* out);
  * [.., chan, 3^l] forms element for element. */
 int ld_group_norm_cm(const float* x, int B, int N, int C, int S, int groups, int center, float eps, const float* gamma,
                      const float* beta, float* y, void* workspace, void* stream);
+/* ld_group_norm with a residual: y = residual + norm(x), residual laid out like x (may be NULL). */
+int ld_group_norm_res(const float* x, const float* residual, int B, int N, int C, int S, int groups, int center, float eps,
+                      const float* gamma, const float* beta, float* y, void* workspace, void* stream);
 int ld_bee_self_products_cm(const float* lr0, const float* lr1, const float* lr2, long long rows, int chan, float* P_a,
                             void* P_v, void* P_d, void* stream);
 /* The six channel mixings in front of the node-local products and the products themselves in one launch (chan = 128;

@@ -34,6 +34,7 @@ struct RowsParams {
   const __nv_bfloat16* x; float* y;
   const __nv_bfloat16* wp;   // packed weights [nchunks][8 panels][N][8]
   const float* bias;
+  const float* res;          // optional residual, laid out like y: y = res + act(...)
   long long rows;            // GEMM rows = rows_outer * S
   int K, N, S, act;
   int stages;                // chunks of the ring in use (<= GR_STAGES)
@@ -165,6 +166,22 @@ gemm_rows16_kernel(const __grid_constant__ RowsParams P) {
     uint32_t tile_it = 0;
     for (long long tile = blockIdx.x; tile < ntiles && !fail; tile += gridDim.x, tile_it++) {
       const uint32_t b = tile_it & 1;
+      const long long row = tile * GR_ROWS + tid;
+      const bool row_ok = row < P.rows;
+      const long long ro = row_ok ? row / S : 0;
+      const int rs = row_ok ? (int)(row - ro * S) : 0;
+      float* yrow = P.y + (ro * N) * S + rs;
+      const float* rrow = P.res != nullptr && row_ok ? P.res + (ro * N) * S + rs : nullptr;
+      // the residuals of the first 32 columns are fetched before the accumulator is waited for, those of the next 32
+      // beside the tensor-memory load: 32 independent loads in flight instead of a load in front of every store
+      float r[32];
+      auto fetch_res = [&](int cb) {
+        if (rrow != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) r[j] = __ldg(rrow + (size_t)(cb + j) * S);
+        }
+      };
+      fetch_res(0);
       {
         int ok = 1;
         if (lane == 0) ok = (!s_fail && tc::mbar_wait(&bar_acc_full[b], (tile_it >> 1) & 1, wl)) ? 1 : 0;
@@ -172,18 +189,16 @@ gemm_rows16_kernel(const __grid_constant__ RowsParams P) {
         if (!ok) { fail = 1; break; }
       }
       tc::fence_after_sync();
-      const long long row = tile * GR_ROWS + tid;
-      const bool row_ok = row < P.rows;
-      const long long ro = row_ok ? row / S : 0;
-      const int rs = row_ok ? (int)(row - ro * S) : 0;
-      float* yrow = P.y + (ro * N) * S + rs;
       for (int cb = 0; cb < N; cb += 32) {
         float v[32];
+        if (cb > 0) fetch_res(cb);
         tc::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + b * acc_cols + cb, v);
         if (row_ok) {
 #pragma unroll
-          for (int j = 0; j < 32; j++)
-            yrow[(size_t)(cb + j) * S] = gr_act(v[j] + (P.bias != nullptr ? __ldg(P.bias + cb + j) : 0.f), P.act);
+          for (int j = 0; j < 32; j++) {
+            const float t = gr_act(v[j] + (P.bias != nullptr ? __ldg(P.bias + cb + j) : 0.f), P.act);
+            yrow[(size_t)(cb + j) * S] = rrow != nullptr ? r[j] + t : t;
+          }
         }
       }
       tc::fence_before_sync();
@@ -207,8 +222,9 @@ bool ld_gemm_rows16_applies(int K, int N) {
 }
 
 int ld_gemm_rows16_launch(const void* x16, long long rows, int K, int S, const void* wp, const float* bias, int N, int act, float* y,
-                          int* status_dev, void* stream, unsigned wait_limit) {
+                          int* status_dev, void* stream, unsigned wait_limit, const float* res) {
   RowsParams P;
+  P.res = res;
   P.x = (const __nv_bfloat16*)x16; P.y = y; P.wp = (const __nv_bfloat16*)wp; P.bias = bias; P.rows = rows; P.K = K; P.N = N; P.S = S;
   P.act = act; P.status = status_dev; P.wait_limit = wait_limit;
   const size_t w_bytes = (size_t)K * N * 2;

@@ -253,7 +253,7 @@ extern "C" int ld_pack_weights_bf16(const float* W, long long sw0, long long sw1
 // the streaming kernel for BF16 rows (gemm_rows16.cu)
 bool ld_gemm_rows16_applies(int K, int N);
 int ld_gemm_rows16_launch(const void* x16, long long rows, int K, int S, const void* wp, const float* bias, int N, int act, float* y,
-                          int* status_dev, void* stream, unsigned wait_limit);
+                          int* status_dev, void* stream, unsigned wait_limit, const float* res);
 
 // y = act(x W^T + b) on the tensor cores. x: FP32 [rows_outer, K, S] contiguous, y: [rows_outer, N, S].
 // S in {1,3,9}; N a multiple of 32, N <= 512. wp from ld_pack_weights_bf16. status_dev: optional
@@ -271,7 +271,7 @@ static int linear_tc_launch(const float* x, int in_bf16, long long rows_outer, i
   }
   if (rows_outer == 0) return LD_OK;
   if (in_bf16 && !out_bf16 && !selftest_no_weights && ld_gemm_rows16_applies(K, N))
-    return ld_gemm_rows16_launch(x, rows_outer * S, K, S, wp, bias, N, act, (float*)y, status_dev, stream, wait_limit);
+    return ld_gemm_rows16_launch(x, rows_outer * S, K, S, wp, bias, N, act, (float*)y, status_dev, stream, wait_limit, nullptr);
   GemmParams P;
   P.x = x; P.in_bf16 = in_bf16; P.y = (float*)y; P.out_bf16 = out_bf16; P.y_ld_row = ld_row; P.y_ld_col = ld_col; P.y_off = off; P.wp = (const __nv_bfloat16*)wp; P.bias = bias; P.rows = rows_outer * S; P.K = K; P.N = N; P.S = S;
   P.act = act; P.status = status_dev; P.wait_limit = wait_limit; P.selftest_no_weights = selftest_no_weights;
@@ -345,4 +345,18 @@ extern "C" int ld_linear_bf16_tc_selftest_timeout(const float* x, long long rows
                                                   int* status_dev, void* stream) {
   if (rows_outer > 1024) return LD_ERR_SHAPE;
   return linear_tc_launch(x, 0, rows_outer, K, 1, wp, nullptr, N, 0, y, 0, (long long)N, 1, 0, status_dev, stream, 64u, 1);
+}
+
+// ld_linear_bf16_tc_in16 with a residual: y = residual + act(x W^T + b), residual laid out like y ([rows_outer][N][S]
+// FP32). Served by the streaming kernel only (K a multiple of 128, N <= 128, weights that fit in shared memory); other
+// shapes return LD_ERR_UNSUPPORTED and the caller adds the residual itself.
+extern "C" int ld_linear_bf16_tc_in16_res(const void* x_bf16, const float* residual, long long rows_outer, int K, int S, const void* wp,
+                                          const float* bias, int N, int act, float* y, int* status_dev, void* stream) {
+  if (rows_outer < 0 || K <= 0 || N <= 0 || (S != 1 && S != 3 && S != 9)) return LD_ERR_SHAPE;
+  if (!ld_gemm_rows16_applies(K, N) || (K & 7) != 0 || (reinterpret_cast<uintptr_t>(x_bf16) & 15) != 0) {
+    ld_set_last_message("tensor-core linear with residual: only the shapes of the streaming kernel");
+    return LD_ERR_UNSUPPORTED;
+  }
+  if (rows_outer == 0) return LD_OK;
+  return ld_gemm_rows16_launch(x_bf16, rows_outer * S, K, S, wp, bias, N, act, y, status_dev, stream, tc::TC_WAIT_LIMIT, residual);
 }

@@ -86,14 +86,16 @@ __global__ void gn_finalize_kernel(const float* __restrict__ part, int BG, int n
 
 __global__ void __launch_bounds__(256) gn_apply_kernel(const float* __restrict__ x, long long total, int N, int C, int S, int G, int cm,
                                                        const float* __restrict__ stats, const float* __restrict__ gamma,
-                                                       const float* __restrict__ beta, float* __restrict__ y) {
+                                                       const float* __restrict__ beta, const float* __restrict__ res,
+                                                       float* __restrict__ y) {
   const int cpg = C / G;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int c = cm ? (int)(i % C) : (int)((i / S) % C);
     const long long b = i / ((long long)N * C * S);
     const float* st = stats + ((size_t)b * G + c / cpg) * 2;
-    const float v = (x[i] - st[0]) * st[1] * gamma[c];
-    y[i] = beta != nullptr ? v + beta[c] : v;
+    float v = (x[i] - st[0]) * st[1] * gamma[c];
+    if (beta != nullptr) v += beta[c];
+    y[i] = res != nullptr ? res[i] + v : v;
   }
 }
 
@@ -156,7 +158,8 @@ gn_partial_rows_kernel(const float* __restrict__ x, int N, int C, int S, int G, 
 
 __global__ void __launch_bounds__(GN_ROW_MAX_THREADS)
 gn_apply_rows_kernel(const float* __restrict__ x, int N, int C, int S, int G, int nchunks, int cm, int k, const float* __restrict__ stats,
-                     const float* __restrict__ gamma, const float* __restrict__ beta, float* __restrict__ y) {
+                     const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ res,
+                     float* __restrict__ y) {
   const int L = C * S, L4 = L / 4, cpg = C / G;
   const int b = blockIdx.x, kc = blockIdx.y, tid = threadIdx.x;
   const int col = tid % L4, off = tid / L4;
@@ -174,11 +177,16 @@ gn_apply_rows_kernel(const float* __restrict__ x, int N, int C, int S, int G, in
   }
   const float4* xin = reinterpret_cast<const float4*>(x + ((size_t)b * N) * L) + col;
   float4* yout = reinterpret_cast<float4*>(y + ((size_t)b * N) * L) + col;
+  const float4* rin = res != nullptr ? reinterpret_cast<const float4*>(res + ((size_t)b * N) * L) + col : nullptr;
   for (int n = n0 + off; n < n1; n += k) {
     const float4 v = __ldg(xin + (size_t)n * L4);
     float4 r;
     r.x = fmaf(v.x - mean, ga[0], be[0]); r.y = fmaf(v.y - mean, ga[1], be[1]);
     r.z = fmaf(v.z - mean, ga[2], be[2]); r.w = fmaf(v.w - mean, ga[3], be[3]);
+    if (rin != nullptr) {   // the residual the caller would add next: res + norm, the same sum a separate add forms
+      const float4 q = __ldg(rin + (size_t)n * L4);
+      r.x = q.x + r.x; r.y = q.y + r.y; r.z = q.z + r.z; r.w = q.w + r.w;
+    }
     yout[(size_t)n * L4] = r;
   }
 }
@@ -189,7 +197,7 @@ gn_apply_rows_kernel(const float* __restrict__ x, int N, int C, int S, int G, in
 // workspace: 98 * B * groups floats of device memory (statistics per system and group + up to 32 chunk partials).
 // ld_group_norm_cm: the same for component-major activations, x and y [B][N][S][C].
 static int group_norm_launch(const float* x, int B, int N, int C, int S, int groups, int center, float eps, const float* gamma,
-                             const float* beta, float* y, void* workspace, void* stream, int cm) {
+                             const float* beta, float* y, void* workspace, void* stream, int cm, const float* res = nullptr) {
   if (B < 0 || N <= 0 || C <= 0 || S <= 0 || groups <= 0 || C % groups != 0) return LD_ERR_SHAPE;
   if (center && S != 1) { ld_set_last_message("group norm: the centred form is defined for scalars (S = 1)"); return LD_ERR_SHAPE; }
   if (B == 0) return LD_OK;
@@ -207,7 +215,7 @@ static int group_norm_launch(const float* x, int B, int N, int C, int S, int gro
   // rows of whole 16-byte pieces that never straddle a channel group, short enough for one block: the row-wise kernels
   const int L = C * S, cpg = C / groups;
   const bool rows = L % 4 == 0 && cpg % 4 == 0 && L / 4 <= GN_ROW_MAX_THREADS && groups <= 64 && B <= 65535 &&
-                    ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0);
+                    ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) && ((uintptr_t)res % 16 == 0);
   const int k = rows ? (GN_ROW_MAX_THREADS / (L / 4) > 0 ? GN_ROW_MAX_THREADS / (L / 4) : 1) : 0;
   if (rows) gn_partial_rows_kernel<<<dim3(B, nchunks), k * (L / 4), 0, st>>>(x, N, C, S, groups, center, nchunks, cm, k, part);
   else gn_partial_kernel<<<dim3(B * groups, nchunks), GN_THREADS, 0, st>>>(x, N, C, S, groups, center, nchunks, cm, part);
@@ -215,12 +223,12 @@ static int group_norm_launch(const float* x, int B, int N, int C, int S, int gro
   gn_finalize_kernel<<<(B * groups + 127) / 128, 128, 0, st>>>(part, B * groups, nchunks, center, (long long)N * (C / groups), eps, stats);
   LD_LAUNCH_CHECK();
   if (rows) {
-    gn_apply_rows_kernel<<<dim3(B, nchunks), k * (L / 4), 0, st>>>(x, N, C, S, groups, nchunks, cm, k, stats, gamma, beta, y);
+    gn_apply_rows_kernel<<<dim3(B, nchunks), k * (L / 4), 0, st>>>(x, N, C, S, groups, nchunks, cm, k, stats, gamma, beta, res, y);
   } else {
     const long long total = (long long)B * N * C * S;
     long long blocks = (total + 255) / 256;
     if (blocks > 148LL * 32) blocks = 148LL * 32;
-    gn_apply_kernel<<<(unsigned)blocks, 256, 0, st>>>(x, total, N, C, S, groups, cm, stats, gamma, beta, y);
+    gn_apply_kernel<<<(unsigned)blocks, 256, 0, st>>>(x, total, N, C, S, groups, cm, stats, gamma, beta, res, y);
   }
   LD_LAUNCH_CHECK();
   return LD_OK;
@@ -234,4 +242,11 @@ extern "C" int ld_group_norm(const float* x, int B, int N, int C, int S, int gro
 extern "C" int ld_group_norm_cm(const float* x, int B, int N, int C, int S, int groups, int center, float eps, const float* gamma,
                                 const float* beta, float* y, void* workspace, void* stream) {
   return group_norm_launch(x, B, N, C, S, groups, center, eps, gamma, beta, y, workspace, stream, 1);
+}
+
+// ld_group_norm with a residual: y = residual + norm(x), residual laid out like x (the sum a caller's separate add would
+// form, without the extra pass over the tensor). residual may be NULL.
+extern "C" int ld_group_norm_res(const float* x, const float* residual, int B, int N, int C, int S, int groups, int center, float eps,
+                                 const float* gamma, const float* beta, float* y, void* workspace, void* stream) {
+  return group_norm_launch(x, B, N, C, S, groups, center, eps, gamma, beta, y, workspace, stream, 0, residual);
 }

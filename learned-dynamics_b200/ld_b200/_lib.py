@@ -32,6 +32,7 @@ SIGNATURES = {
     "ld_bee_fwd": [P, P, P, P, P, P, LL, I, P, P],
     "ld_bee_self_products": [P, P, P, LL, I, P, P, P, I, P],
     "ld_linear_bf16_tc_in16": [P, LL, I, I, P, P, I, I, P, P, P],
+    "ld_linear_bf16_tc_in16_res": [P, P, LL, I, I, P, P, I, I, P, P, P],
     "ld_bee_bw": [I, P, P, P, P, LL, I, P, P, P, P],
     "ld_cow_o0_fwd": [P, P, P, P, LL, I, P, P, P],
     "ld_cow_o0_bw": [P, P, P, P, LL, I, P, P, P],
@@ -52,6 +53,7 @@ SIGNATURES = {
     "ld_linear_bf16_tc_selftest_timeout": [P, LL, I, P, I, P, P, P],
     "ld_counter_noise": [P, P, F, LL, LL, ctypes.c_ulonglong, ctypes.c_ulonglong, P],
     "ld_group_norm": [P, I, I, I, I, I, I, F, P, P, P, P, P],
+    "ld_group_norm_res": [P, P, I, I, I, I, I, I, F, P, P, P, P, P],
     "ld_proxattn_fwd": [P, P, P, P, P, P, I, I, I, I, I, F, F, F, P, P],
     "ld_proxattn_fwd_tf32_tc": [P, P, P, P, P, P, I, I, I, I, I, F, F, F, P, P, P],
     "ld_proxattn_bwd": [P, P, P, P, P, P, I, I, I, I, I, F, F, F, P, P, P, P, P, P, P],

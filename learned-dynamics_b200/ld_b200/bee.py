@@ -197,7 +197,16 @@ class Messages(nn.Module):
         B_d = ops.linear_bf16_tc_rows16(S_d, w["Ydp"], self.dim_d)
         return (B_a.reshape(batch, nodes, -1), B_v.reshape(batch, nodes, 3, -1), B_d.reshape(batch, nodes, 9, -1))
 
-    def forward(self, graph, r_ij, x_a, x_v, x_d):
+    def forward(self, graph, r_ij, x_a, x_v, x_d, add_input=False):
+        """add_input: returns the inputs plus the messages (the residual form the layers use), added inside the kernels'
+        epilogues on the tensor-core path"""
+        out = self._forward(graph, r_ij, x_a, x_v, x_d, add_input)
+        if add_input and not self._added:
+            out = (x_a + out[0], x_v + out[1], x_d + out[2])
+        return out
+
+    def _forward(self, graph, r_ij, x_a, x_v, x_d, add_input=False):
+        self._added = False
         if torch.is_grad_enabled() or not x_a.is_cuda:
             return self._forward_unfused(graph, r_ij, x_a, x_v, x_d)
         batch, nodes = x_a.shape[0], x_a.shape[1]
@@ -248,6 +257,9 @@ class Messages(nn.Module):
                 check(lib().ld_bee_messages_vd_f32(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, float(self.r0), ptr(l0),
                                                    ptr(l1), ptr(l2), ptr(w["enc_w"]), ptr(w["enc_b"]), ptr(w["jac"]), 0.1,
                                                    ptr(S_v), ptr(S_d), 2 if feat16 else 0, 1 if sums16 else 0, st))
+        # the residual form: the rank-1 and rank-2 adds happen in the epilogues of the two Y maps (the scalar edge kernel
+        # writes a node's row on its critical path, where a load of the residual cost more than the separate add)
+        fuse_add = (add_input and self.precision == "bf16" and sums16 and all(t.dtype == torch.float32 for t in (x_a, x_v, x_d)))
         if self.precision == "bf16":
             with KERNEL_TIMER.region("bee_messages_scalar_tc"):
                 check(lib().ld_bee_messages_scalar_bf16_tc(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, self.dim_a,
@@ -255,6 +267,8 @@ class Messages(nn.Module):
                                                            ptr(w["enc_b"]), ptr(w["jac"]), ptr(w["Yp"]), ptr(w["W1p"]), ptr(w["b1"]),
                                                            ptr(w["W2p"]), ptr(w["b2"]), ptr(w["W3p"]), ptr(w["b3"]), 0.1, ptr(B_a),
                                                            2 if feat16 else 0, ptr(ops.tc_status(dev)), st))
+            if fuse_add:
+                B_a += x_a.reshape(Nt, -1)
         else:
             with KERNEL_TIMER.region("bee_messages_scalar"):
                 check(lib().ld_bee_messages_scalar_f32(ptr(graph.row_ptr), ptr(graph.dst32), ptr(rij), Nt, C, self.dim_a,
@@ -263,11 +277,12 @@ class Messages(nn.Module):
                                                        ptr(w["W2t"]), ptr(w["b2"]), ptr(w["W3t"]), ptr(w["b3"]), ptr(w["Wdt"]),
                                                        0.1, ptr(B_a), st))
         if sums16:
-            B_v = ops.linear_bf16_tc_cm(S_v, w["Yvp"], self.dim_v, 1)
-            B_d = ops.linear_bf16_tc_cm(S_d, w["Ydp"], self.dim_d, 2)
+            B_v = ops.linear_bf16_tc_cm(S_v, w["Yvp"], self.dim_v, 1, residual=x_v.reshape(Nt, -1, 3) if fuse_add else None)
+            B_d = ops.linear_bf16_tc_cm(S_d, w["Ydp"], self.dim_d, 2, residual=x_d.reshape(Nt, -1, 3, 3) if fuse_add else None)
         else:
             B_v = ops.tensor_linear(1, w["Yv"], S_v)
             B_d = ops.tensor_linear(2, w["Yd"], S_d)
+        self._added = fuse_add
         return (B_a.reshape(batch, nodes, -1), B_v.reshape(batch, nodes, -1, 3), B_d.reshape(batch, nodes, -1, 3, 3))
 
     def _forward_unfused(self, graph, r_ij, x_a, x_v, x_d):
@@ -375,7 +390,9 @@ class SelfTensProds(nn.Module):
                 ops.group_norm_cm(y_v.reshape(batch, nodes, 3, -1), self.gn_v.groups, self.gn_v.epsilon, self.gn_v.gamma),
                 ops.group_norm_cm(y_d.reshape(batch, nodes, 9, -1), self.gn_d.groups, self.gn_d.epsilon, self.gn_d.gamma))
 
-    def forward(self, x_a, x_v, x_d):
+    def forward(self, x_a, x_v, x_d, add_input=False):
+        """add_input: returns the inputs plus the normalised products (the residual form the layers use), added inside the
+        group norms' second pass on the fused path"""
         rest = x_a.shape[:-1]
         n = 1
         for d in rest:
@@ -406,14 +423,18 @@ class SelfTensProds(nn.Module):
                 y_d = ops.linear_bf16_tc_cm(P_d, c["Ydp"], c["Yd"].shape[0], 2)
             else:
                 y_v, y_d = self._mix(c, "Yv", 1, P_v), self._mix(c, "Yd", 2, P_d)
-            return (self.gn_a(y_a.reshape(*rest, -1)), self.gn_v(y_v.reshape(*rest, -1, 3)),
-                    self.gn_d(y_d.reshape(*rest, -1, 3, 3)))
+            if add_input and len(rest) == 2:
+                return (self.gn_a(y_a.reshape(*rest, -1), residual=x_a), self.gn_v(y_v.reshape(*rest, -1, 3), residual=x_v),
+                        self.gn_d(y_d.reshape(*rest, -1, 3, 3), residual=x_d))
+            out = (self.gn_a(y_a.reshape(*rest, -1)), self.gn_v(y_v.reshape(*rest, -1, 3)), self.gn_d(y_d.reshape(*rest, -1, 3, 3)))
+            return (x_a + out[0], x_v + out[1], x_d + out[2]) if add_input else out
         y = Bee.apply(self.L0(xa), self.L1(xv), self.L2(xd), self.R0(xa), self.R1(xv), self.R2(xd))
         (y_000, y_110, y_220, y_011, y_101, y_121, y_211, y_022, y_202, y_112, y_222, y_111, y_212) = y
         y_a = self.Y_000(y_000) + self.Y_110(y_110) + self.Y_220(y_220)
         y_v = self.Y_011(y_011) + self.Y_101(y_101) + self.Y_121(y_121) + self.Y_211(y_211) + self.Y_111(y_111)
         y_d = self.Y_022(y_022) + self.Y_202(y_202) + self.Y_112(y_112) + self.Y_222(y_222) + self.Y_212(y_212)
-        return (self.gn_a(y_a.reshape(*rest, -1)), self.gn_v(y_v.reshape(*rest, -1, 3)), self.gn_d(y_d.reshape(*rest, -1, 3, 3)))
+        out = (self.gn_a(y_a.reshape(*rest, -1)), self.gn_v(y_v.reshape(*rest, -1, 3)), self.gn_d(y_d.reshape(*rest, -1, 3, 3)))
+        return (x_a + out[0], x_v + out[1], x_d + out[2]) if add_input else out
 
 
 class BeeBlock(nn.Module):
@@ -425,10 +446,8 @@ class BeeBlock(nn.Module):
         self.prods = SelfTensProds(dim_a, dim_v, dim_d, chan)
 
     def forward(self, graph, r_ij, x_a, x_v, x_d):
-        d_a, d_v, d_d = self.messages(graph, r_ij, x_a, x_v, x_d)
-        x_a, x_v, x_d = x_a + d_a, x_v + d_v, x_d + d_d
-        d_a, d_v, d_d = self.prods(x_a, x_v, x_d)
-        return x_a + d_a, x_v + d_v, x_d + d_d
+        x_a, x_v, x_d = self.messages(graph, r_ij, x_a, x_v, x_d, add_input=True)
+        return self.prods(x_a, x_v, x_d, add_input=True)
 
     def cm_ready(self):
         return self.messages.cm_ready() and not self.messages.fused_kernel and self.prods.cm_ready()

@@ -414,18 +414,26 @@ def linear_bf16_tc_rows16(x16, W_packed, N, bias=None, act=ACT_NONE):
     return y
 
 
-def linear_bf16_tc_cm(x16, W_packed, N, inds, bias=None, act=ACT_NONE):
+def linear_bf16_tc_cm(x16, W_packed, N, inds, bias=None, act=ACT_NONE, residual=None):
     """linear_bf16_tc for activations stored as BF16 in component-major form, x16 [rows, 3**inds, K] (K contiguous,
     a multiple of 8): returns y [rows, N, (3,)*inds] FP32. Same result as the FP32 [rows, K, (3,)*inds] form of the
-    same values (the MMA operands are BF16 either way)."""
+    same values (the MMA operands are BF16 either way). residual (FP32, shape of y): returns residual + y, added in the
+    kernel's epilogue where the streaming kernel serves the shape, by a separate add otherwise."""
     if not x16.is_cuda or x16.dtype != torch.bfloat16 or not x16.is_contiguous() or x16.dim() != 3 or x16.shape[1] != 3 ** inds:
         raise RuntimeError("linear_bf16_tc_cm: expected a contiguous CUDA BF16 tensor [rows, 3**inds, K]")
     rows, S, K = x16.shape
     y = torch.empty((rows, N) + (3,) * inds, dtype=torch.float32, device=x16.device)
+    if residual is not None:
+        residual = residual.reshape(y.shape).contiguous()
+        if residual.dtype == torch.float32 and K % 128 == 0 and N <= 128 and K * N * 2 <= 94 * 1024:
+            with KERNEL_TIMER.region("linear_bf16_tc"):
+                check(lib().ld_linear_bf16_tc_in16_res(ptr(x16), ptr(residual), rows, K, S, ptr(W_packed), ptr(bias), N, act, ptr(y),
+                                                       ptr(tc_status(x16.device)), stream_ptr(x16.device)))
+            return y
     with KERNEL_TIMER.region("linear_bf16_tc"):
         check(lib().ld_linear_bf16_tc_in16(ptr(x16), rows, K, S, ptr(W_packed), ptr(bias), N, act, ptr(y),
                                            ptr(tc_status(x16.device)), stream_ptr(x16.device)))
-    return y
+    return y if residual is None else residual + y
 
 
 def painn_message_bf16_tc(row_ptr, dst, rij, mlp_dist, actv, x_v, rmax, eps=0.1, radial_kind=RADIAL_PAINN, res_a=None,
@@ -472,10 +480,10 @@ def group_norm_cm(x, groups, eps, gamma):
     return y
 
 
-def group_norm(x, groups, eps, gamma, beta=None, center=False):
+def group_norm(x, groups, eps, gamma, beta=None, center=False, residual=None):
     """Per-system group norm of x [B, N, C, (3,)*inds] (fused statistics + apply kernels).
     center=True: ScalGroupNorm (mean subtracted, beta added; scalars only); center=False: TensGroupNorm (x is divided
-    by the root of the group's mean squared norm, gamma applied, no beta)."""
+    by the root of the group's mean squared norm, gamma applied, no beta). residual (shape of x): returns residual + norm."""
     require_cuda_f32(x, "x")
     x = x.contiguous()
     B, N, C = x.shape[0], x.shape[1], x.shape[2]
@@ -488,7 +496,12 @@ def group_norm(x, groups, eps, gamma, beta=None, center=False):
     ws = torch.empty(max(98 * B * groups, 1), dtype=torch.float32, device=x.device)
     g = gamma.detach().reshape(-1).float().contiguous()
     b = None if beta is None else beta.detach().reshape(-1).float().contiguous()
+    if residual is not None:
+        require_cuda_f32(residual, "residual")
+        residual = residual.contiguous()
+        if residual.shape != x.shape:
+            raise RuntimeError("group_norm: the residual must have the shape of x")
     with KERNEL_TIMER.region("group_norm"):
-        check(lib().ld_group_norm(ptr(x), B, N, C, S, groups, 1 if center else 0, float(eps), ptr(g), ptr(b), ptr(y), ptr(ws),
-                                  stream_ptr(x.device)))
+        check(lib().ld_group_norm_res(ptr(x), ptr(residual), B, N, C, S, groups, 1 if center else 0, float(eps), ptr(g), ptr(b), ptr(y),
+                                      ptr(ws), stream_ptr(x.device)))
     return y

@@ -68,16 +68,18 @@ class ScalGroupNorm(nn.Module):
         self.gamma = nn.Parameter(torch.ones(chan))
         self.beta = nn.Parameter(torch.zeros(chan))
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
+        """residual (shape of x): returns residual + norm(x) (one pass on the fused path)"""
         if not torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.float32:
-            return ops.group_norm(x, self.groups, self.epsilon, self.gamma, self.beta, center=True)
+            return ops.group_norm(x, self.groups, self.epsilon, self.gamma, self.beta, center=True, residual=residual)
         batch, nodes, _ = x.shape
         xg = x.reshape(batch, nodes, self.groups, -1)
         mean = xg.mean([1, 3], keepdim=True)
         x_shift = xg - mean
         var = (x_shift ** 2).mean([1, 3], keepdim=True)
         ans = x_shift / torch.sqrt(self.epsilon + var)
-        return self.beta + self.gamma * ans.reshape(batch, nodes, self.chan)
+        ans = self.beta + self.gamma * ans.reshape(batch, nodes, self.chan)
+        return ans if residual is None else residual + ans
 
 
 class Update(nn.Module):

@@ -51,14 +51,16 @@ class TensGroupNorm(nn.Module):
         self.inds, self.chan, self.groups, self.epsilon = inds, chan, groups, epsilon
         self.gamma = nn.Parameter(torch.ones(chan, *[1] * inds))
 
-    def forward(self, x):
+    def forward(self, x, residual=None):
+        """residual (shape of x): returns residual + norm(x) (one pass on the fused path)"""
         if not torch.is_grad_enabled() and x.is_cuda and x.dim() == 3 + self.inds and x.dtype == torch.float32:
-            return ops.group_norm(x, self.groups, self.epsilon, self.gamma, None, center=False)
+            return ops.group_norm(x, self.groups, self.epsilon, self.gamma, None, center=False, residual=residual)
         batch, nodes = x.shape[0], x.shape[1]
         xg = x.reshape(batch, nodes, self.groups, -1, 3 ** self.inds)
         moment2 = (xg ** 2).sum(-1, keepdim=True).mean([1, 3], keepdim=True)
         ans = xg / torch.sqrt(self.epsilon + moment2)
-        return self.gamma * ans.reshape(batch, nodes, self.chan, *[3] * self.inds)
+        ans = self.gamma * ans.reshape(batch, nodes, self.chan, *[3] * self.inds)
+        return ans if residual is None else residual + ans
 
 
 class _BareProdFn(torch.autograd.Function):

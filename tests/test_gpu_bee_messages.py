@@ -272,6 +272,39 @@ def test_self_products_front_in_one_launch(rows, dims):
         close(a, w, BF16_BAR)
 
 
+@pytest.mark.parametrize("dims,B,N,r0", [((128, 64, 32, 128), 8, 256, 5.0), ((128, 64, 32, 128), 2, 37, 3.0), ((64, 32, 32, 96), 3, 50, 5.0),
+                                         ((128, 8, 8, 32), 1, 6, 1.0), ((64, 32, 32, 128), 2, 20, 0.01)])
+@pytest.mark.parametrize("precision", ["bf16", "fp32"])
+def test_layer_residual_adds_inside_the_kernels(dims, B, N, r0, precision):
+    """add_input=True (the inputs added in the epilogues of the two Y maps and in the group norms' second pass) against the same modules followed by separate adds: FP32 adds of the same two numbers, so bit
+    for bit; shapes the fused epilogues do not serve take the separate adds and must agree all the same."""
+    from ld_b200 import bee, graph_layers as GL, ops
+    torch.manual_seed(sum(dims) + 3)
+    block = bee.set_precision(bee.BeeBlock(r0, *dims).cuda(), precision)
+    g = torch.Generator().manual_seed(21)
+    pos = torch.cumsum(torch.randn(B, N, 3, generator=g) / 3 ** 0.5, dim=1)
+    da, dv, dd, _ = dims
+    x = [t.cuda() for t in (torch.randn(B, N, da, generator=g), torch.randn(B, N, dv, 3, generator=g),
+                            torch.randn(B, N, dd, 3, 3, generator=g))]
+    with torch.no_grad():
+        graph = GL.Graph.radius_graph(r0, None, pos.cuda())
+        m = block.messages(graph, graph.rij, *x)
+        m_add = block.messages(graph, graph.rij, *x, add_input=True)
+        p = block.prods(*x)
+        p_add = block.prods(*x, add_input=True)
+        whole = block(graph, graph.rij, *x)
+    torch.cuda.synchronize()
+    ops.check_tc_status("cuda")
+    for xi, mi, mai, pi, pai in zip(x, m, m_add, p, p_add):
+        assert torch.equal(xi + mi, mai)
+        assert torch.equal(xi + pi, pai)
+    with torch.no_grad():
+        step = [xi + mi for xi, mi in zip(x, m)]
+        want = [si + pi for si, pi in zip(step, block.prods(*step))]
+    for a, b in zip(whole, want):
+        assert torch.equal(a, b)
+
+
 @pytest.mark.parametrize("Nt,dims", [(1000, (128, 64, 32)), (128 * 150 + 5, (128, 64, 32)), (7, (64, 16, 16)), (300, (16, 48, 32))])
 def test_left_rows_in_one_launch_equal_three_launches(Nt, dims):
     """L0 | L1 | L2 of a message layer as one launch that writes whole [node][chan][16] BF16 rows against the three
