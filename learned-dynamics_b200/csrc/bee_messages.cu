@@ -38,6 +38,7 @@ struct BeeEdgeParams {
   const float* enc_w; const float* enc_b;               // lin_enc: [chan,8], [chan]
   const float* jacobi;                                  // [8][9] polynomial coefficients
   int seg_nodes;                                        // nodes per scheduling segment (0: the whole range at once)
+  int* next_node;                                       // product-sum kernel: zeroed counter its blocks draw nodes from
 };
 
 // first node v in [lo, hi] whose preceding work (edges + nodes) reaches target
@@ -108,20 +109,36 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
   if (threadIdx.x < 8) ld_poly8_to_chebyshev(P.jacobi + threadIdx.x * 9, s_jac + threadIdx.x * 9);   // Chebyshev form of the radial polynomials
   __syncthreads();
   const int C = CC > 0 ? CC : P.chan;
-  // all blocks walk the node range segment by segment, so that the neighbour rows a segment gathers (its nodes'
-  // neighbours are nearby nodes) stay resident in L2 while its edges are processed
-  const int seg_nodes = P.seg_nodes > 0 ? P.seg_nodes : P.Nt;
-  for (int seg_lo = 0; seg_lo < P.Nt; seg_lo += seg_nodes) {
-  int n_begin, n_end;
-  bm_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt), &n_begin, &n_end);
+  // The blocks draw nodes one at a time from a counter: a node's sums are formed by one block in the order of its edge
+  // list, so the result does not depend on which block took it. All blocks work at the front of the node range,
+  // so the neighbour rows they gather (a node's neighbours are nearby nodes) stay resident in L2, and no block is left
+  // with more than one node while others are idle. The next node is asked for while the present one is processed.
+  __shared__ int s_node[2];
+  int drawn = 0;
+  if (threadIdx.x == 0) drawn = atomicAdd(P.next_node, 1);
+  const bool one_group = C <= (int)blockDim.x;
+  float w8[8], wb = 0.f;
+  {
+    const bool cok0 = (int)threadIdx.x < C;
+#pragma unroll
+    for (int m = 0; m < 8; m++) w8[m] = cok0 ? P.enc_w[threadIdx.x * 8 + m] : 0.f;
+    if (cok0) wb = P.enc_b[threadIdx.x];
+  }
+  for (int it = 0;; it++) {
+  if (threadIdx.x == 0) s_node[it & 1] = drawn;
+  __syncthreads();   // (a slot is rewritten two nodes later, behind the barrier of the node in between)
+  const int v = s_node[it & 1];
+  if (v >= P.Nt) break;
+  if (threadIdx.x == 0) drawn = atomicAdd(P.next_node, 1);
   for (int c0 = 0; c0 < C; c0 += blockDim.x) {   // channel groups (one pass when chan <= 128)
     const int c = c0 + threadIdx.x;
     const bool cok = c < C;
-    float w8[8], wb = 0.f;
+    if (!one_group) {
 #pragma unroll
-    for (int m = 0; m < 8; m++) w8[m] = cok ? P.enc_w[c * 8 + m] : 0.f;
-    if (cok) wb = P.enc_b[c];
-    for (int v = n_begin; v < n_end; v++) {
+      for (int m = 0; m < 8; m++) w8[m] = cok ? P.enc_w[c * 8 + m] : 0.f;
+      wb = cok ? P.enc_b[c] : 0.f;
+    }
+    {
       float av[15], ad[45];
 #pragma unroll
       for (int i = 0; i < 15; i++) av[i] = 0.f;
@@ -384,9 +401,12 @@ extern "C" int ld_bee_messages_vd_f32(const int* row_ptr, const int* dst, const 
   float* S_d = (float*)S_d_;
   if (Nt < 0 || chan <= 0 || !(r0 > 0.f)) return LD_ERR_SHAPE;
   if (Nt == 0) return LD_OK;
-  // segment = about 40 MB of gathered rows (13 * chan values per node, 32 bytes per channel when interleaved)
-  const long long seg = (40LL << 20) / ((feat_bf16 == 2 ? 32LL : feat_bf16 ? 26LL : 52LL) * chan);
-  BeeEdgeParams P{row_ptr, dst, rij, Nt, chan, r0, L0, L1, L2, enc_w, enc_b, jacobi, ld_even_segments(Nt, seg)};
+  int* next_node = nullptr;
+  {
+    const int rc = ld_work_counter((cudaStream_t)stream, &next_node);
+    if (rc != LD_OK) return rc;
+  }
+  BeeEdgeParams P{row_ptr, dst, rij, Nt, chan, r0, L0, L1, L2, enc_w, enc_b, jacobi, 0, next_node};
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (feat_bf16 == 2 && chan == 128 && out_bf16) bee_vd_kernel<__nv_bfloat16, true, 128><<<sms * 4, 128, 0, (cudaStream_t)stream>>>(P, S_v, S_d, scale, 1);

@@ -264,6 +264,8 @@ bee_scalar_tc_kernel(BtParams P) {
 #pragma unroll
     for (int i = 0; i < (PROF ? 12 : 1); i++) pc[i] = 0;
     long long tprev = PROF ? clock64() : 0;
+    unsigned long long t_block0 = 0, tiles_done = 0;
+    if (PROF) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_block0));
     auto lap = [&](int i) {
       if (PROF) { const long long t = clock64(); pc[i] += t - tprev; tprev = t; }
     };
@@ -297,6 +299,7 @@ bee_scalar_tc_kernel(BtParams P) {
     for (int seg_lo = 0; seg_lo < P.Nt && !fail; seg_lo += seg_nodes) {
       const BtRange br = bt_block_range(P.row_ptr, seg_lo, min(seg_lo + seg_nodes, P.Nt));
       const int n_begin = br.n_begin, n_end = br.n_end;
+      if (PROF) tiles_done += (unsigned long long)br.ntiles;
       float acc = 0.f;
       int cur = n_begin, node_lo = n_begin;
       float pre_x = 0.f, pre_y = 0.f, pre_z = 0.f;
@@ -608,6 +611,16 @@ bee_scalar_tc_kernel(BtParams P) {
     // one thread of each role: tid 0 (adds up the previous tile), 128 (geometry of the next tile), 256 (neither)
     if (PROF && P.prof != nullptr && (tid == 0 || tid == 128 || tid == 256))
       for (int i = 0; i < 12; i++) atomicAdd((unsigned long long*)&P.prof[(tid >> 7) * 12 + i], (unsigned long long)pc[i]);
+    if (PROF && P.prof != nullptr && tid == 0 && blockIdx.x < 256) {
+      // per block: start and end on the global timer (ns), tiles processed, the SM it ran on
+      unsigned long long t1; unsigned smid;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+      asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+      P.prof[64 + blockIdx.x] = (long long)t_block0;
+      P.prof[64 + 256 + blockIdx.x] = (long long)t1;
+      P.prof[64 + 512 + blockIdx.x] = (long long)tiles_done;
+      P.prof[64 + 768 + blockIdx.x] = (long long)smid;
+    }
   }
   if (fail && lane == 0 && P.status != nullptr) atomicOr(P.status, LD_FLAG_TIMEOUT);
   __syncthreads();

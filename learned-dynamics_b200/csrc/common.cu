@@ -2,6 +2,7 @@
 #include "common.cuh"
 #include <stdio.h>
 #include <string.h>
+#include <mutex>
 
 static thread_local char g_last_error[512] = "";
 
@@ -16,6 +17,32 @@ void ld_set_last_message(const char* msg) {
 }
 
 extern "C" const char* ld_last_error(void) { return g_last_error; }
+
+namespace {
+constexpr int WC_MAX_DEVICES = 64;
+std::mutex g_wc_mutex;
+int* g_wc_ring[WC_MAX_DEVICES] = {};
+unsigned g_wc_next[WC_MAX_DEVICES] = {};
+}  // namespace
+
+int ld_work_counter(cudaStream_t stream, int** counter) {
+  int dev = 0;
+  LD_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= WC_MAX_DEVICES) { ld_set_last_message("work counter: device index out of range"); return LD_ERR_UNSUPPORTED; }
+  int* slot = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_wc_mutex);
+    if (g_wc_ring[dev] == nullptr) {
+      int* ring = nullptr;
+      LD_CUDA_TRY(cudaMalloc(&ring, sizeof(int) * LD_WORK_COUNTERS));
+      g_wc_ring[dev] = ring;
+    }
+    slot = g_wc_ring[dev] + (g_wc_next[dev]++ % LD_WORK_COUNTERS);
+  }
+  LD_CUDA_TRY(cudaMemsetAsync(slot, 0, sizeof(int), stream));
+  *counter = slot;
+  return LD_OK;
+}
 
 extern "C" const char* ld_status_string(int status) {
   switch (status) {

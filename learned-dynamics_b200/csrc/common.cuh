@@ -43,6 +43,13 @@ static inline int ld_even_segments(long long Nt, long long want) {
   return (int)((Nt + nseg - 1) / nseg);
 }
 
+// A zeroed int32 in device memory for one launch that hands out work through an atomic counter: taken from a ring of
+// LD_WORK_COUNTERS per device (allocated at the first call on that device, which therefore must not be inside a stream
+// capture) and cleared in stream order before the launch. A counter is handed out again after LD_WORK_COUNTERS later
+// calls, far more launches than a stream holds in flight.
+#define LD_WORK_COUNTERS 4096
+int ld_work_counter(cudaStream_t stream, int** counter);
+
 // exclusive prefix sum of n int32 values; out[n] receives the total (out has n+1 entries).
 // scratch must hold ld_scan_scratch_ints(n) ints.
 size_t ld_scan_scratch_ints(long long n);
