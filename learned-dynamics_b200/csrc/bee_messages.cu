@@ -139,6 +139,9 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
       wb = cok ? P.enc_b[c] : 0.f;
     }
     {
+      // av = (011, 101, 121, 211, 111), ad = (022, 202, 112, 222, 212). Two of the sixty sums need no work per edge: 111
+      // (l1 cross phi_v) is the antisymmetric part of 112 (l1 phi_v^T) and is formed from its sums after the loop, and
+      // 022 (l0 phi_d, phi_d = pa rhat rhat^T) is symmetric, so only its upper triangle is accumulated
       float av[15], ad[45];
 #pragma unroll
       for (int i = 0; i < 15; i++) av[i] = 0.f;
@@ -216,14 +219,11 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
                 av[6 + x] = fmaf(d1, rp[x], av[6 + x]);           // 121: l_x phi_yx -> y
                 av[9 + x] += m2[x];                               // 211: l_xy phi_y -> x
               }
-              av[12] = fmaf(l1[1], rp[2], av[12]); av[12] = fmaf(-l1[2], rp[1], av[12]);   // 111: l x phi
-              av[13] = fmaf(l1[2], rp[0], av[13]); av[13] = fmaf(-l1[0], rp[2], av[13]);
-              av[14] = fmaf(l1[0], rp[1], av[14]); av[14] = fmaf(-l1[1], rp[0], av[14]);
 #pragma unroll
               for (int x = 0; x < 3; x++) {
 #pragma unroll
                 for (int y = 0; y < 3; y++) {
-                  ad[x * 3 + y] = fmaf(t0[x], rh[y], ad[x * 3 + y]);                  // 022
+                  if (y >= x) ad[x * 3 + y] = fmaf(t0[x], rh[y], ad[x * 3 + y]);      // 022, upper triangle
                   ad[9 + x * 3 + y] = fmaf(l2[x * 3 + y], pa, ad[9 + x * 3 + y]);     // 202
                   ad[18 + x * 3 + y] = fmaf(l1[x], rp[y], ad[18 + x * 3 + y]);        // 112
                   ad[27 + x * 3 + y] = fmaf(m2[x], rh[y], ad[27 + x * 3 + y]);        // 222: l_xy phi_zy -> xz
@@ -237,6 +237,10 @@ bee_vd_kernel(BeeEdgeParams P, float* __restrict__ S_v, float* __restrict__ S_d,
           }
         }
       }
+      ad[3] = ad[1]; ad[6] = ad[2]; ad[7] = ad[5];                                       // 022, lower triangle
+      av[12] = ad[18 + 1 * 3 + 2] - ad[18 + 2 * 3 + 1];                                  // 111 from 112
+      av[13] = ad[18 + 2 * 3 + 0] - ad[18 + 0 * 3 + 2];
+      av[14] = ad[18 + 0 * 3 + 1] - ad[18 + 1 * 3 + 0];
       if (cok) {
         if (out_bf16) {
           // the sums feed a tensor-core channel mixing that rounds its operands to BF16 anyway: store them rounded
