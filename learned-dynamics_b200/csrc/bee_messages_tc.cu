@@ -28,8 +28,11 @@ constexpr int BT_MMA_WARP = BT_WORK_WARPS;
 constexpr int BT_PROD_WARP = BT_WORK_WARPS + 1;
 constexpr int BT_THREADS = (BT_WORK_WARPS + 2) * 32;
 constexpr int BT_SYNC_THREADS = (BT_WORK_WARPS + 1) * 32;
-constexpr int BT_STAGES = 3;        // weight ring: 32 KB slabs (a bulk copy costs about the same issue time whatever its size)
-constexpr int BT_SLAB_BYTES = 32 * 1024;
+// weight ring: two slabs of 48 KB. Every slab costs the issuing thread and the producer a few hundred cycles whatever its
+// size, so few large slabs beat many small ones at the same 96 KB in flight: per 21.5M-edge launch 23.0 ms with 2 x 48 KB,
+// 23.5 with 3 x 32, 24.9 with 4 x 24, 26.4 with 6 x 16, 32.3 with 12 x 8
+constexpr int BT_STAGES = 2;
+constexpr int BT_SLAB_BYTES = 48 * 1024;
 constexpr int BT_LAYERS = 4;
 // Byte stride between the 8-column panels of the operand tile: 128 rows x 16 bytes plus one 16-byte pad, so that the
 // panels a warp of the product phase writes to (32 channels = 4 panels, same row) fall into different banks
@@ -40,7 +43,7 @@ struct BtLayer {
   const float* bias;        // may be null
   int a_panel;              // first 8-column panel of A this layer reads
   int ksteps;               // K / 16
-  int slab_ksteps;          // K-steps per weight slab: 32 KB / (N * 32 B)
+  int slab_ksteps;          // K-steps per weight slab: BT_SLAB_BYTES / (N * 32 B)
   int N;                    // output width (multiple of 64, <= 256)
   int act;                  // 0 none, 2 LeakyReLU(0.1)
   int out_col;              // A column where the epilogue writes its BF16 result (-1: last layer)
