@@ -34,6 +34,7 @@ constexpr int BT_SYNC_THREADS = (BT_WORK_WARPS + 1) * 32;
 constexpr int BT_STAGES = 2;
 constexpr int BT_SLAB_BYTES = 48 * 1024;
 constexpr int BT_LAYERS = 4;
+constexpr uint32_t BT_WRES_COL = 384;   // tensor-memory columns [384, 512): resident weights of the transposed last layer
 // Byte stride between the 8-column panels of the operand tile: 128 rows x 16 bytes plus one 16-byte pad, so that the
 // panels a warp of the product phase writes to (32 channels = 4 panels, same row) fall into different banks
 constexpr int BT_PANEL = BT_EDGES * 16 + 16;
@@ -47,6 +48,7 @@ struct BtLayer {
   int N;                    // output width (multiple of 64, <= 256)
   int act;                  // 0 none, 2 LeakyReLU(0.1)
   int out_col;              // A column where the epilogue writes its BF16 result (-1: last layer)
+  int ks_resident;          // leading K-steps whose weights stay in tensor memory for the whole kernel (transposed last layer)
 };
 
 struct BtParams {
@@ -173,6 +175,23 @@ bee_scalar_tc_kernel(BtParams P) {
   const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
   const int seg_nodes = P.seg_nodes > 0 ? P.seg_nodes : P.Nt;
   int fail = 0;
+  if (P.layer[BT_LAYERS - 1].ks_resident > 0 && tid < 128) {
+    // Weights of the last layer that multiply the second hidden layer (K = 2a of its 3a), once per kernel into tensor
+    // memory: lane = output channel, eight columns per K-step (sixteen BF16 values, two per column). The last layer is
+    // issued with the weights as the M operand, so these K-steps take their A operand from here and only the K = a
+    // of the direct term streams through the ring: 329 KB instead of 393 KB of weights per tile, one slab fewer to wait for.
+    const BtLayer& L = P.layer[BT_LAYERS - 1];
+    const uint4* wp = reinterpret_cast<const uint4*>(L.w);
+    for (int ks = 0; ks < L.ks_resident; ks++) {
+      const uint4 c0 = __ldg(wp + (size_t)(2 * ks) * L.N + tid), c1 = __ldg(wp + (size_t)(2 * ks + 1) * L.N + tid);
+      const uint32_t r[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      tc::tmem_st8(tmem_row + BT_WRES_COL + (uint32_t)ks * 8u, r);
+    }
+    tc::tmem_st_wait();
+    tc::fence_before_sync();
+  }
+  __syncthreads();
+  tc::fence_after_sync();
 
   if (warp == BT_PROD_WARP) {
     // ===== producer: weight slabs through the ring =========================================================
@@ -183,7 +202,7 @@ bee_scalar_tc_kernel(BtParams P) {
         for (long long t = 0; t < ntiles && !fail; t++) {
           for (int l = 0; l < BT_LAYERS && !fail; l++) {
             const BtLayer& L = P.layer[l];
-            for (int ks = 0; ks < L.ksteps; ks += L.slab_ksteps, loads++) {
+            for (int ks = L.ks_resident; ks < L.ksteps; ks += L.slab_ksteps, loads++) {
               const uint32_t st = loads % BT_STAGES, use = loads / BT_STAGES;
               const uint32_t bytes = (uint32_t)min(L.slab_ksteps, L.ksteps - ks) * L.N * 32;
               if (use >= 1 && !tc::mbar_wait(&bar_empty[st], (use - 1) & 1)) { fail = 1; break; }
@@ -224,7 +243,15 @@ bee_scalar_tc_kernel(BtParams P) {
             uint64_t ad = tc::smem_desc(a_base + P.layer[l].a_panel * BT_PANEL, BT_PANEL, 128);
             const uint64_t a_step = (uint64_t)((2 * BT_PANEL) >> 4), b_step = (uint64_t)((2 * l_N * 16) >> 4);
             uint32_t accumulate = 0u;
-            for (int ks0 = 0; ks0 < l_ksteps; ks0 += l_slab, mmas++) {
+            const int l_res = P.layer[l].ks_resident;
+            // the part of the last layer's weights that lives in tensor memory (columns [384, 512), A operand of the
+            // transposed product) needs no slab: its MMAs go first, while the one streamed slab is on its way
+            for (int kk = 0; kk < l_res; kk++) {
+              tc::mma_bf16_ta(d_tmem, tmem_base + BT_WRES_COL + (uint32_t)kk * 8u, ad, idesc, accumulate);
+              accumulate = 1u;
+              ad += a_step;
+            }
+            for (int ks0 = l_res; ks0 < l_ksteps; ks0 += l_slab, mmas++) {
               const uint32_t st = mmas % BT_STAGES, use = mmas / BT_STAGES;
               if (!tc::mbar_wait(&bar_full[st], use & 1)) { fail = 1; break; }
               tc::fence_after_sync();
@@ -654,10 +681,10 @@ extern "C" int ld_bee_messages_scalar_bf16_tc(const int* row_ptr, const int* dst
   P.row_ptr = row_ptr; P.dst = dst; P.rij = rij; P.Nt = Nt; P.chan = C; P.dim_a = A; P.r0 = r0; P.scale = scale;
   P.L0 = L0; P.L1 = L1; P.L2 = L2; P.enc_w = enc_w; P.enc_b = enc_b; P.jacobi = jacobi;
   const int sk1 = BT_SLAB_BYTES / (A * 32), sk2 = BT_SLAB_BYTES / (2 * A * 32);
-  P.layer[0] = BtLayer{(const __nv_bfloat16*)Yp, nullptr, 0, 3 * C / 16, sk1, A, 0, 2 * A};
-  P.layer[1] = BtLayer{(const __nv_bfloat16*)W1p, b1, 2 * A / 8, A / 16, sk2, 2 * A, 2, 0};
-  P.layer[2] = BtLayer{(const __nv_bfloat16*)W2p, b2, 0, 2 * A / 16, sk2, 2 * A, 2, 0};
-  P.layer[3] = BtLayer{(const __nv_bfloat16*)W3p, b3, 0, 3 * A / 16, sk1, A, 0, -1};
+  P.layer[0] = BtLayer{(const __nv_bfloat16*)Yp, nullptr, 0, 3 * C / 16, sk1, A, 0, 2 * A, 0};
+  P.layer[1] = BtLayer{(const __nv_bfloat16*)W1p, b1, 2 * A / 8, A / 16, sk2, 2 * A, 2, 0, 0};
+  P.layer[2] = BtLayer{(const __nv_bfloat16*)W2p, b2, 0, 2 * A / 16, sk2, 2 * A, 2, 0, 0};
+  P.layer[3] = BtLayer{(const __nv_bfloat16*)W3p, b3, 0, 3 * A / 16, sk1, A, 0, -1, A == 128 ? 2 * A / 16 : 0};
   const int cols = 3 * (C > A ? C : A);
   const size_t a_bytes = (size_t)(cols / 8) * BT_PANEL;
   const size_t staging = (size_t)BT_EDGES * A * 4;
