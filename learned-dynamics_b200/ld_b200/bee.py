@@ -200,20 +200,20 @@ class Messages(nn.Module):
     def forward(self, graph, r_ij, x_a, x_v, x_d, add_input=False):
         """add_input: returns the inputs plus the messages (the residual form the layers use), added inside the kernels'
         epilogues on the tensor-core path"""
-        out = self._forward(graph, r_ij, x_a, x_v, x_d, add_input)
-        if add_input and not self._added:
+        out, added = self._forward(graph, r_ij, x_a, x_v, x_d, add_input)
+        if add_input and not added:
             out = (x_a + out[0], x_v + out[1], x_d + out[2])
         return out
 
-    def _forward(self, graph, r_ij, x_a, x_v, x_d, add_input=False):
-        self._added = False
+    def _forward(self, graph, r_ij, x_a, x_v, x_d, add_input):
+        """returns (messages, whether the inputs were already added to them)"""
         if torch.is_grad_enabled() or not x_a.is_cuda:
-            return self._forward_unfused(graph, r_ij, x_a, x_v, x_d)
+            return self._forward_unfused(graph, r_ij, x_a, x_v, x_d), False
         batch, nodes = x_a.shape[0], x_a.shape[1]
         Nt, C, dev = batch * nodes, self.chan, x_a.device
         if (self.precision == "bf16" and self.fused_kernel and C == 128 and self.dim_a == 128 and self.dim_v % 32 == 0
                 and self.dim_d % 32 == 0):
-            return self._forward_fused_tc(graph, r_ij, x_a, x_v, x_d)
+            return self._forward_fused_tc(graph, r_ij, x_a, x_v, x_d), False
         w = self._pack()
         feat16 = self.precision == "bf16" and C % 32 == 0 and C <= 512
         if feat16:
@@ -282,8 +282,7 @@ class Messages(nn.Module):
         else:
             B_v = ops.tensor_linear(1, w["Yv"], S_v)
             B_d = ops.tensor_linear(2, w["Yd"], S_d)
-        self._added = fuse_add
-        return (B_a.reshape(batch, nodes, -1), B_v.reshape(batch, nodes, -1, 3), B_d.reshape(batch, nodes, -1, 3, 3))
+        return (B_a.reshape(batch, nodes, -1), B_v.reshape(batch, nodes, -1, 3), B_d.reshape(batch, nodes, -1, 3, 3)), fuse_add
 
     def _forward_unfused(self, graph, r_ij, x_a, x_v, x_d):
         rad_enc_ij = self.lin_enc(radial_encode_8(r_ij, self.r0))
