@@ -47,7 +47,7 @@ DEFAULT_WORKLOAD = "polymers_l2_1024x256"
 # DRAM bytes per processed edge of the dominant kernel, from the committed profiler captures of a smaller case
 # (profiles/): read + write bytes of one launch / its edge count. Traffic is dominated by per-edge inputs (rij, dst)
 # and by one pass over the node features, both proportional to the edge count at fixed degree.
-DRAM_BYTES_PER_EDGE = {"bee_scalar_tc_kernel": 63.1, "bee_vd_kernel": 204.3, "bee_vd_tc_kernel": 208.0, "bee_fused_tc_kernel": 217.2,
+DRAM_BYTES_PER_EDGE = {"bee_scalar_tc_kernel": 83.0, "bee_vd_kernel": 200.4, "bee_vd_tc_kernel": 208.0, "bee_fused_tc_kernel": 217.2,
                        "painn_message_tc_kernel": 33.8}
 # timer regions of the edge kernels of an l<=2 message layer -> kernel names
 BEE_EDGE_REGIONS = {"bee_messages_fused_tc": "bee_fused_tc_kernel", "bee_messages_scalar_tc": "bee_scalar_tc_kernel",
